@@ -1,0 +1,137 @@
+"""bf16 GEMM on the tcgen05 tensor cores and the autograd ``linear`` built on it.
+
+``gemm`` computes ``C (+)= alpha * op(A) @ op(B)^T (+ bias)`` with either operand stored K-major or
+MN-major, so that the forward, dgrad and wgrad products of a linear layer all read their operands
+as they lie in memory. On a CPU-only machine the same function evaluates the product with PyTorch
+(the reference implementation that the GPU tests compare against).
+
+``linear`` is the drop-in for ``torch.nn.functional.linear`` used by every projection of the models
+in this package. Its backward accumulates the weight gradient straight into ``weight.main_grad``
+when the parameter carries such a buffer (the flat gradient buffers of the sharded data-parallel
+engines), which removes the separate gradient tensor and the accumulate pass.
+
+Reference counterpart: cuBLAS behind ``nn.Linear`` (atorch/modules/distributed_modules/layers.py:117-151).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .. import _lib
+
+
+def _pitch(t: torch.Tensor) -> int:
+    return t.stride(0) if t.dim() == 2 else t.shape[-1]
+
+
+def gemm_reference(a, b, a_mn=False, b_mn=False, out=None, out_dtype=None, accumulate=False, alpha=1.0, bias=None):
+    """fp32-accumulated PyTorch evaluation of the same contract (the oracle for the kernel)."""
+    A = a.t() if a_mn else a
+    B = b.t() if b_mn else b
+    r = (A.float() @ B.float().t()) * alpha
+    if bias is not None:
+        r = r + bias.float()
+    if out is not None:
+        if accumulate:
+            r = r + out.float()
+        out.copy_(r.to(out.dtype))
+        return out
+    return r.to(out_dtype or a.dtype)
+
+
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    a_mn: bool = False,
+    b_mn: bool = False,
+    out: Optional[torch.Tensor] = None,
+    out_dtype: Optional[torch.dtype] = None,
+    accumulate: bool = False,
+    alpha: float = 1.0,
+    bias: Optional[torch.Tensor] = None,
+    tile_n: int = 0,
+    max_ctas: int = 0,
+) -> torch.Tensor:
+    """``out[M,N] (+)= alpha * A[M,K] @ B[N,K]^T (+ bias[N])``.
+
+    ``a`` is stored ``[M,K]`` (or ``[K,M]`` when ``a_mn``), ``b`` is stored ``[N,K]`` (or ``[K,N]``
+    when ``b_mn``). Inputs are bf16, accumulation is fp32, the output is bf16 or fp32.
+    """
+    assert a.dim() == 2 and b.dim() == 2
+    M, K = (a.shape[1], a.shape[0]) if a_mn else a.shape
+    N, Kb = (b.shape[1], b.shape[0]) if b_mn else b.shape
+    assert K == Kb, f"reduction dims differ: {K} vs {Kb}"
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype or torch.bfloat16, device=a.device)
+        assert not accumulate
+    if not _lib.use_kernels(a, b, out) or a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or (N % 8) or (K % 8) or (M % 8):
+        return gemm_reference(a, b, a_mn, b_mn, out, None, accumulate, alpha, bias)
+    if a.stride(-1) != 1:
+        a = a.contiguous()
+    if b.stride(-1) != 1:
+        b = b.contiguous()
+    assert out.stride(-1) == 1 and out.dtype in (torch.bfloat16, torch.float32)
+    L = _lib.lib()
+    rc = L.atb_gemm_bf16(
+        _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias),
+        ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
+        ctypes.c_longlong(_pitch(a)), ctypes.c_longlong(_pitch(b)), ctypes.c_longlong(_pitch(out)),
+        ctypes.c_int(int(a_mn)), ctypes.c_int(int(b_mn)),
+        ctypes.c_int(int(out.dtype == torch.float32)), ctypes.c_int(int(accumulate)),
+        ctypes.c_float(alpha), ctypes.c_int(tile_n), ctypes.c_int(max_ctas),
+        _lib.stream_ptr(), _lib.ptr(_lib.status_word(a.device)),
+    )
+    _lib.check(rc, f"atb_gemm_bf16 M={M} N={N} K={K}")
+    return out
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, residual):
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1])
+        ctx.save_for_backward(x2, weight)
+        ctx.has_bias = bias is not None
+        ctx.has_res = residual is not None
+        ctx.x_shape = shp
+        ctx.weight_ref = weight
+        if residual is not None:
+            # out = residual + x W^T : the epilogue accumulates into a copy of the residual stream
+            out = residual.reshape(-1, weight.shape[0]).clone()
+            gemm(x2, weight, out=out, accumulate=True, bias=bias)
+        else:
+            out = gemm(x2, weight, bias=bias, out_dtype=x.dtype)
+        return out.view(*shp[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if dy2.stride(-1) != 1:
+            dy2 = dy2.contiguous()
+        dx = dw = db = dres = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, weight, b_mn=True, out_dtype=x2.dtype).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            mg = getattr(ctx.weight_ref, "main_grad", None)
+            if mg is not None:
+                gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, accumulate=True)
+                ctx.weight_ref.grad_added_to_main_grad = True
+            else:
+                dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=weight.dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.sum(0)
+        if ctx.has_res and ctx.needs_input_grad[3]:
+            dres = dy
+        return dx, dw, db, dres
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+           residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``residual + x @ weight.T + bias`` with the tcgen05 GEMM in forward, dgrad and wgrad."""
+    if x.dtype != torch.bfloat16 or not _lib.use_kernels(x, weight):
+        y = torch.nn.functional.linear(x, weight.to(x.dtype), None if bias is None else bias.to(x.dtype))
+        return y if residual is None else residual + y
+    return _Linear.apply(x, weight, bias, residual)

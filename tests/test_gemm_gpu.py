@@ -1,0 +1,101 @@
+"""tcgen05 GEMM against an fp32 PyTorch reference: all operand layouts, ragged shapes, epilogues."""
+import pytest
+import torch
+
+from atorch_b200 import _lib
+from atorch_b200.ops import gemm, gemm_reference, linear
+
+pytestmark = pytest.mark.gpu
+
+
+def _mk(rows, cols, dev="cuda"):
+    return (torch.randn(rows, cols, device=dev, dtype=torch.float32) * 0.5).to(torch.bfloat16)
+
+
+def _check(out, ref, K):
+    torch.cuda.synchronize()
+    _lib.check_status(out.device)
+    err = (out.float() - ref.float()).abs().max().item()
+    scale = ref.float().abs().max().item() + 1e-6
+    assert err / scale < 2e-2, f"max err {err} vs scale {scale}"
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 512, 256), (384, 264, 136), (1000, 1032, 520),
+                                   (4096, 4096, 1024), (128, 4096, 4096), (72, 96, 40)])
+def test_gemm_layouts(M, N, K, a_mn, b_mn):
+    torch.manual_seed(M + N + K)
+    a = _mk(K, M) if a_mn else _mk(M, K)
+    b = _mk(K, N) if b_mn else _mk(N, K)
+    ref = gemm_reference(a, b, a_mn, b_mn, out_dtype=torch.float32)
+    for tile_n in (128, 256):
+        out = gemm(a, b, a_mn=a_mn, b_mn=b_mn, tile_n=tile_n)
+        _check(out, ref, K)
+
+
+def test_gemm_fp32_out_accumulate_alpha_bias():
+    torch.manual_seed(1)
+    M, N, K = 512, 768, 384
+    a, b = _mk(M, K), _mk(N, K)
+    bias = _mk(1, N)[0]
+    c0 = torch.randn(M, N, device="cuda")
+    out = c0.clone()
+    gemm(a, b, out=out, accumulate=True, alpha=0.5, bias=bias)
+    ref = c0 + 0.5 * (a.float() @ b.float().t()) + bias.float()
+    _check(out, ref, K)
+    c1 = _mk(M, N)
+    out = c1.clone()
+    gemm(a, b, out=out, accumulate=True)
+    _check(out, c1.float() + a.float() @ b.float().t(), K)
+
+
+def test_gemm_strided_operands():
+    torch.manual_seed(2)
+    big = _mk(512, 1024)
+    a = big[:, 256:768]  # pitch 1024, K = 512
+    b = _mk(256, 512)
+    out = gemm(a, b)
+    _check(out, a.float() @ b.float().t(), 512)
+
+
+def test_gemm_many_tiles_persistent():
+    # more tiles than SMs: exercises accumulator double buffering and ring wrap-around
+    torch.manual_seed(3)
+    M, N, K = 4096, 11008, 512
+    a, b = _mk(M, K), _mk(N, K)
+    out = gemm(a, b)
+    idx = torch.randint(0, M, (64,), device="cuda")
+    ref = a[idx].float() @ b.float().t()
+    _check(out[idx], ref, K)
+    out2 = gemm(a, b, max_ctas=7)
+    assert torch.equal(out, out2)
+
+
+def test_linear_autograd_matches_torch():
+    torch.manual_seed(4)
+    x = _mk(96, 256).requires_grad_()
+    w = _mk(512, 256).requires_grad_()
+    res = _mk(96, 512).requires_grad_()
+    y = linear(x, w, residual=res)
+    dy = _mk(96, 512)
+    y.backward(dy)
+    xr, wr, rr = (t.detach().float().requires_grad_() for t in (x, w, res))
+    yr = rr + xr @ wr.t()
+    yr.backward(dy.float())
+    _check(y, yr, 256)
+    _check(x.grad, xr.grad, 512)
+    _check(w.grad, wr.grad, 96)
+    assert torch.equal(res.grad, dy)
+
+
+def test_linear_main_grad_accumulation():
+    torch.manual_seed(5)
+    x = _mk(128, 256).requires_grad_()
+    w = _mk(384, 256).requires_grad_()
+    w.main_grad = torch.zeros(384, 256, device="cuda", dtype=torch.float32)
+    dy = _mk(128, 384)
+    for _ in range(2):
+        linear(x, w).backward(dy)
+    assert w.grad is None
+    ref = 2 * (dy.float().t() @ x.detach().float())
+    _check(w.main_grad, ref, 128)
