@@ -86,7 +86,8 @@ class _CrossEntropy(torch.autograd.Function):
     def backward(ctx, dloss):
         logits, labels, lse = ctx.saved_tensors
         vocab_start, v_total, ignore_index, smoothing, z, inplace = ctx.cfg
-        dlogits = logits if inplace else torch.empty_like(logits)
+        dlogits = logits if inplace else torch.empty_strided(logits.shape, logits.stride(), dtype=logits.dtype,
+                                                              device=logits.device)
         _bwd_launch(logits, labels, lse, dloss.contiguous().float(), dlogits, vocab_start, v_total, ignore_index,
                     smoothing, z)
         return dlogits, None, None, None, None, None, None

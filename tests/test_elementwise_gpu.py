@@ -150,7 +150,8 @@ def test_adamw_and_agd_steps():
 def test_sum_squares_and_outer_sgd():
     torch.manual_seed(7)
     x = torch.randn(1 << 20, device="cuda")
-    assert abs(ops.sum_squares(x).item() - x.double().pow(2).sum().item()) < 1e-1
+    ref = x.double().pow(2).sum().item()
+    assert abs(ops.sum_squares(x).item() - ref) < 2e-6 * ref
     n = 5000
     synced, buf, pg = torch.randn(n, device="cuda"), torch.zeros(n, device="cuda"), torch.randn(n, device="cuda")
     p = torch.empty(n, device="cuda", dtype=torch.bfloat16)
