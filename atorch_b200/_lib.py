@@ -15,7 +15,7 @@ from typing import Optional
 import torch
 
 _LIB_PATH = Path(__file__).resolve().parent / "_C" / "libatb.so"
-_lib: Optional[ctypes.CDLL] = None
+_lib = None
 _tried = False
 
 
@@ -23,11 +23,40 @@ class KernelError(RuntimeError):
     """A launcher rejected its arguments or a kernel reported a non-zero status."""
 
 
+launch_count = 0  # kernels of this library launched so far in this process
+_NOT_LAUNCHES = {"atb_norm_bwd_parts", "atb_sumsq_parts"}
+
+
+class _CountingLib:
+    """Proxy over the ctypes library that counts kernel launches (one per launcher call)."""
+
+    def __init__(self, cdll):
+        self._cdll = cdll
+        self._cache = {}
+
+    def __getattr__(self, name):
+        fn = self._cache.get(name)
+        if fn is None:
+            raw = getattr(self._cdll, name)
+            if name in _NOT_LAUNCHES:
+                fn = raw
+            else:
+                def fn(*a, _raw=raw):
+                    global launch_count
+                    launch_count += 1
+                    return _raw(*a)
+            self._cache[name] = fn
+        return fn
+
+    def has(self, name) -> bool:
+        return hasattr(self._cdll, name)
+
+
 def lib_path() -> Path:
     return _LIB_PATH
 
 
-def lib() -> Optional[ctypes.CDLL]:
+def lib():
     """The loaded library, or None on a CPU-only machine."""
     global _lib, _tried
     if _lib is not None:
@@ -44,7 +73,7 @@ def lib() -> Optional[ctypes.CDLL]:
             _build.build()
         else:
             raise KernelError(f"{_LIB_PATH} is missing: run `python -m atorch_b200.build`")
-    _lib = ctypes.CDLL(str(_LIB_PATH))
+    _lib = _CountingLib(ctypes.CDLL(str(_LIB_PATH)))
     return _lib
 
 

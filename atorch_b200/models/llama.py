@@ -94,6 +94,9 @@ class RMSNorm(nn.Module):
         self.weight = nn.Parameter(torch.ones(dim))
         self.eps = eps
 
+    def reset_parameters(self):
+        nn.init.ones_(self.weight)
+
     def forward(self, x, residual=None):
         return ops.rms_norm(x, self.weight, self.eps, residual)
 

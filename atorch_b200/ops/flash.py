@@ -12,7 +12,7 @@ from .. import _lib
 
 def kernels_built() -> bool:
     L = _lib.lib()
-    return L is not None and hasattr(L, "atb_flash_fwd")
+    return L is not None and L.has("atb_flash_fwd")
 
 
 def supported(q, k, v, dropout_p=0.0, additive_mask=None, additive_bias=None) -> bool:

@@ -1,0 +1,2 @@
+from .agd import AGD
+from .bf16_optimizer import BF16Optimizer

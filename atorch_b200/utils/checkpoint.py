@@ -67,7 +67,13 @@ class _Checkpoint(torch.autograd.Function):
 def checkpoint_function(run: Callable, *args: Any, preserve_rng_state: bool = False, **kwargs: Any):
     """Checkpointed call of ``run(*args, **kwargs)``; tensors anywhere in the arguments are tracked."""
     flat, spec = tree_flatten((args, kwargs))
-    return _Checkpoint.apply(run, spec, preserve_rng_state, len(flat), *flat)
+    extra = []
+    if not any(isinstance(t, torch.Tensor) and t.requires_grad for t in flat):
+        # parameters inside `run` may still need gradients: an extra scalar that requires grad makes
+        # the node differentiable (it rides after the real arguments and is ignored by `run`)
+        dev = next((t.device for t in flat if isinstance(t, torch.Tensor)), None)
+        extra = [torch.zeros((), device=dev, requires_grad=True)]
+    return _Checkpoint.apply(run, spec, preserve_rng_state, len(flat), *flat, *extra)
 
 
 def checkpoint_module(module: torch.nn.Module, *args: Any, preserve_rng_state: bool = False, **kwargs: Any):

@@ -1,0 +1,242 @@
+"""Headline benchmark: tokens/s of one Llama-2 7B FSDP (ZeRO-3) bf16 training step.
+
+    python bench.py --gpus N --steps K --warmup W            # this framework
+    python bench.py --impl reference --gpus N ...             # the unmodified reference from baseline/_ref
+
+For N > 1 launch with ``python -m torch.distributed.run --nnodes=1 --nproc-per-node N
+--master-addr 127.0.0.1 --master-port P bench.py --gpus N ...``. Rank 0 prints one JSON line.
+
+Config (fixed by the benchmark definition): 32 layers, hidden 4096, 32 heads, SwiGLU 11008, vocab
+32000, seq 4096, micro-batch 1 per GPU, AdamW lr 3e-4 with fp32 master weights and optimizer
+state, activation checkpointing per layer, synthetic uniform token ids, random-init weights.
+
+Two numbers per run: ``value`` is timed on the device with CUDA events around K steps whose
+inputs already sit on the GPU; ``e2e.value`` times K steps driven through the public API
+(``auto_accelerate`` result objects) where every step copies its batch from pinned host memory
+and reads the loss back to the host.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+
+MODELS = {
+    "llama2-7b": dict(vocab_size=32000, hidden_size=4096, intermediate_size=11008, num_hidden_layers=32,
+                      num_attention_heads=32, num_key_value_heads=32, max_position_embeddings=4096),
+    "llama2-13b": dict(vocab_size=32000, hidden_size=5120, intermediate_size=13824, num_hidden_layers=40,
+                       num_attention_heads=40, num_key_value_heads=40, max_position_embeddings=4096),
+    "llama-1.3b": dict(vocab_size=32000, hidden_size=2048, intermediate_size=5504, num_hidden_layers=24,
+                       num_attention_heads=16, num_key_value_heads=16, max_position_embeddings=2048),
+    "tiny": dict(vocab_size=2048, hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+                 num_attention_heads=4, num_key_value_heads=4, max_position_embeddings=512),
+}
+# tokens/s/GPU derived from the reference's published 204.67 TFLOPs/GPU (8xA100, 61.18 GFLOP/token)
+PUBLISHED_TOKENS_PER_S_PER_GPU = 3345.0
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="llama2-7b", choices=sorted(MODELS))
+    ap.add_argument("--seq", type=int, default=None)
+    ap.add_argument("--mbs", type=int, default=1)
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons of this rank's GPU while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.index), "-lms", "200"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        sm, mx, reasons = [], None, set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx = float(f[2])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        # median over the samples taken under load (the upper half of the sorted list is under load)
+        med = sm[len(sm) // 2] if sm else None
+        return {"sm_mhz": med, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    sys.path.insert(0, ROOT)
+    import atorch_b200
+    from atorch_b200 import _lib
+    from atorch_b200.auto import auto_accelerate
+    from atorch_b200.models.llama import LlamaConfig, LlamaDecoderLayer, LlamaModel
+    from atorch_b200.ops import attention as attn_mod
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        atorch_b200.init_distributed("nccl", set_cuda_device_using_local_rank=True)
+    rank = dist.get_rank() if world > 1 else 0
+
+    mc = dict(MODELS[args.model])
+    seq = args.seq or mc["max_position_embeddings"]
+    cfg = LlamaConfig(**mc)
+    torch.manual_seed(1234)
+    with torch.device("meta"):
+        model = LlamaModel(cfg)
+
+    def loss_func(batch, outputs):
+        return outputs[0]
+
+    strategy = [
+        ("parallel_mode", ([("data", world)], None)),
+        ("fsdp", {"atorch_wrap_cls": (LlamaDecoderLayer,), "forward_prefetch": True, "limit_all_gathers": True,
+                  "sync_module_states": False}),
+        ("amp_native", {"dtype": torch.bfloat16}),
+        ("checkpoint", {"wrap_class": (LlamaDecoderLayer,), "no_reentrant": True}),
+    ]
+    status, res, _ = auto_accelerate(model, torch.optim.AdamW, loss_func=loss_func,
+                                     optim_args={"lr": 3e-4, "weight_decay": 0.01, "betas": (0.9, 0.999)},
+                                     load_strategy=strategy, ignore_dryrun_on_load_strategy=True)
+    assert status, "auto_accelerate failed"
+    model, optim = res.model, res.optim
+    B = args.mbs
+    gen = torch.Generator(device="cpu").manual_seed(100 + rank)
+    n_host = args.steps + args.warmup
+    host_batches = [torch.randint(0, cfg.vocab_size, (B, seq), generator=gen).pin_memory() for _ in range(n_host)]
+    dev_batch = host_batches[0].to(dev)
+
+    def step_device():
+        optim.zero_grad()
+        out = model(input_ids=dev_batch, labels=dev_batch, return_logits=False)
+        loss = loss_func(None, out)
+        loss.backward()
+        optim.step()
+        return loss
+
+    def step_e2e(i):
+        ids = host_batches[i % n_host].to(dev, non_blocking=True)
+        batch = res.prepare_input({"input_ids": ids, "labels": ids}, dev) if res.prepare_input else \
+            {"input_ids": ids, "labels": ids}
+        optim.zero_grad()
+        out = model(return_logits=False, **batch)
+        loss = res.loss_func(batch, out)
+        loss.backward()
+        optim.step()
+        return float(loss.item())
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = _lib.launch_count
+        s.record()
+        for i in range(steps):
+            last = fn(i)
+        e.record()
+        barrier()
+        ms = torch.tensor([s.elapsed_time(e)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()), _lib.launch_count - l0, last
+
+    for i in range(args.warmup):
+        step_device()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms, launches, last = timed(lambda i: step_device(), args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    _lib.check_status(dev)
+    tokens = world * B * seq * args.steps
+    value = tokens / (ms / 1e3)
+    e2e = None
+    if not args.no_e2e:
+        for i in range(2):
+            step_e2e(i)
+        ms2, _, last_loss = timed(step_e2e, args.steps)
+        e2e = {"value": round(tokens / (ms2 / 1e3), 1), "unit": "tokens/s", "h2d_bytes_per_step": B * seq * 8,
+               "d2h_bytes_per_step": 4, "ms_per_step": round(ms2 / args.steps, 2), "last_loss": last_loss}
+    if rank == 0:
+        flops = cfg.flops_per_token(seq, recompute=True)
+        out = {
+            "metric": "tokens/sec/box (device-timed, max over ranks) Llama-2 7B FSDP",
+            "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(ms / args.steps, 2), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": round(value / (PUBLISHED_TOKENS_PER_S_PER_GPU * world), 3) if args.model == "llama2-7b" else None,
+            "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights N(0,0.02)",
+            "impl": "ours",
+            "config": {"model": args.model, "global_batch": world * B, "seq_len": seq, "parallelism": f"fsdp{world}",
+                       "optimizer": "AdamW lr 3e-4, fp32 master + state", "activation_checkpointing": "per layer",
+                       "l2": "not flushed: 13.5 GB of bf16 weights and 108 GB of optimizer state stream per step "
+                             "(inputs larger than the 126 MB L2)"},
+            "hw_tflops_per_gpu": round(value / world * flops / 1e12, 1),
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+            "library_attention_calls": attn_mod.library_calls,
+            "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
+        }
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_reference(args):
+    from baseline.reference_bench import run as ref_run  # noqa: deferred, sets sys.path for baseline/_ref
+
+    ref_run(args, MODELS, PUBLISHED_TOKENS_PER_S_PER_GPU, ClockSampler)
+
+
+if __name__ == "__main__":
+    a = parse_args()
+    if a.impl == "reference":
+        sys.path.insert(0, ROOT)
+        run_reference(a)
+    else:
+        run_ours(a)
