@@ -110,7 +110,9 @@ def run_ours(args):
     from atorch_b200 import _lib
     from atorch_b200.auto import auto_accelerate
     from atorch_b200.models.llama import LlamaConfig, LlamaDecoderLayer, LlamaModel
-    from atorch_b200.ops import attention as attn_mod
+    import importlib
+
+    attn_mod = importlib.import_module("atorch_b200.ops.attention")
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
