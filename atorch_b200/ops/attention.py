@@ -90,7 +90,7 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = 
     """Attention over ``[B, S, H, D]`` tensors with the mask options described in the module docstring."""
     from . import flash
 
-    if flash.supported(q, k, v, dropout_p, additive_mask, additive_bias):
+    if flash.supported(q, k, v, dropout_p, additive_mask, additive_bias, key_padding_mask):
         return flash.flash_attention(q, k, v, causal=causal, softmax_scale=softmax_scale, glm_mask=glm_mask,
                                      pack_glm_mask=pack_glm_mask, key_padding_mask=key_padding_mask,
                                      cu_seqlens=cu_seqlens)

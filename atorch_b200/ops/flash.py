@@ -1,9 +1,22 @@
-"""Front end of the sm_100a flash-attention kernels (csrc/flash_attn.cu)."""
+"""Front end of the sm_100a flash-attention kernels (csrc/flash_attn.cu, csrc/flash_attn_bwd.cu).
+
+All masks are lowered to one per-row key interval ``[lo, hi)``:
+
+=====================  ==========================================================
+causal                 ``hi = i + 1 + (Sk - Sq)``
+GLM break-point g[b]   ``hi = max(i + 1, g[b])``
+packed GLM [b, 2, P]   ``hi = max(i + 1, max{e_p : s_p <= i})``
+key padding            ``hi = min(hi, number of valid keys)`` (right padding)
+packed sequences       ``lo = start of the row's sequence`` (``cu_seqlens``)
+=====================  ==========================================================
+
+(Reference semantics: atorch/modules/transformer/layers.py:1283-1408, docs/FA-glm.md:52-160.)
+"""
 from __future__ import annotations
 
 import ctypes
 import math
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
@@ -15,15 +28,130 @@ def kernels_built() -> bool:
     return L is not None and L.has("atb_flash_fwd")
 
 
-def supported(q, k, v, dropout_p=0.0, additive_mask=None, additive_bias=None) -> bool:
+def backward_built() -> bool:
+    L = _lib.lib()
+    return L is not None and L.has("atb_flash_bwd")
+
+
+def supported(q, k, v, dropout_p=0.0, additive_mask=None, additive_bias=None, key_padding_mask=None) -> bool:
     if not _lib.use_kernels(q, k, v) or not kernels_built():
         return False
     if dropout_p != 0.0 or additive_mask is not None or additive_bias is not None:
         return False
+    if (q.requires_grad or k.requires_grad or v.requires_grad) and torch.is_grad_enabled() and not backward_built():
+        return False
     B, Sq, Hq, D = q.shape
-    return (q.dtype == torch.bfloat16 and D == 128 and Hq % k.shape[2] == 0 and k.shape[1] % 8 == 0)
+    ok = q.dtype == torch.bfloat16 and D == 128 and Hq % k.shape[2] == 0
+    ok = ok and all(t.stride(-1) == 1 and t.stride(2) == D and t.stride(1) % 8 == 0 for t in (q, k, v))
+    ok = ok and all(t.stride(0) == t.stride(1) * t.shape[1] for t in (q, k, v))
+    return ok
+
+
+def row_intervals(B: int, Sq: int, Sk: int, device, causal: bool = False, glm_mask=None, pack_glm_mask=None,
+                  key_padding_mask=None, cu_seqlens=None) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
+    """Lower the mask arguments to int32 ``(row_lo, row_hi)`` of shape [B, Sq]; ``(None, None)`` when the
+    analytic causal / full form inside the kernel is enough."""
+    if glm_mask is None and pack_glm_mask is None and key_padding_mask is None and cu_seqlens is None:
+        return None, None
+    i = torch.arange(Sq, device=device, dtype=torch.int64)
+    shift = Sk - Sq
+    causal_like = causal or glm_mask is not None or pack_glm_mask is not None
+    hi = (i + 1 + shift).clamp(max=Sk)[None].expand(B, Sq).clone() if causal_like else \
+        torch.full((B, Sq), Sk, device=device, dtype=torch.int64)
+    lo = torch.zeros(B, Sq, device=device, dtype=torch.int64)
+    if glm_mask is not None:
+        hi = torch.maximum(hi, glm_mask.to(device).long().view(B, 1).expand(B, Sq))
+    if pack_glm_mask is not None:
+        pm = pack_glm_mask.to(device).long()
+        s, e = pm[:, 0], pm[:, 1]                       # [B, P]
+        valid = (s >= 0) & (e >= 0)
+        applies = valid[:, None, :] & (s[:, None, :] <= i[None, :, None])   # [B, Sq, P]
+        ext = torch.where(applies, e[:, None, :].expand(B, Sq, -1), torch.zeros((), device=device, dtype=torch.int64))
+        hi = torch.maximum(hi, ext.max(dim=-1).values)
+    if cu_seqlens is not None:
+        cu = cu_seqlens.to(device).long()
+        seg = torch.bucketize(i, cu[1:], right=True).clamp(max=cu.numel() - 2)
+        lo = torch.maximum(lo, cu[seg][None].expand(B, Sq))
+        if not causal_like:
+            hi = torch.minimum(hi, cu[seg + 1][None].expand(B, Sq))
+    if key_padding_mask is not None:
+        kp = key_padding_mask.to(device)
+        nvalid = kp.bool().sum(dim=1) if kp.dtype == torch.bool or kp.max() <= 1 else None
+        if nvalid is None:
+            raise ValueError("length-encoded key_padding_mask must be converted to cu_seqlens first")
+        hi = torch.minimum(hi, nvalid.view(B, 1).expand(B, Sq))
+    hi = hi.clamp(max=Sk)
+    return lo.to(torch.int32).contiguous(), hi.to(torch.int32).contiguous()
+
+
+def _token_stride(t: torch.Tensor) -> int:
+    return t.stride(1)
+
+
+def flash_fwd_raw(q, k, v, causal, softmax_scale, row_lo, row_hi):
+    """Launch the forward kernel. Returns (out [B,Sq,Hq,D] bf16, lse [B,Hq,Sq] fp32)."""
+    B, Sq, Hq, D = q.shape
+    Sk, Hkv = k.shape[1], k.shape[2]
+    out = torch.empty(B, Sq, Hq, D, dtype=q.dtype, device=q.device)
+    lse = torch.empty(B, Hq, Sq, dtype=torch.float32, device=q.device)
+    rc = _lib.lib().atb_flash_fwd(
+        _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(lse), _lib.ptr(row_lo), _lib.ptr(row_hi),
+        ctypes.c_int(B), ctypes.c_int(Sq), ctypes.c_int(Sk), ctypes.c_int(Hq), ctypes.c_int(Hkv),
+        ctypes.c_longlong(_token_stride(q)), ctypes.c_longlong(_token_stride(k)), ctypes.c_longlong(_token_stride(v)),
+        ctypes.c_int(int(causal)), ctypes.c_float(softmax_scale), _lib.stream_ptr(),
+        _lib.ptr(_lib.status_word(q.device)))
+    _lib.check(rc, "atb_flash_fwd")
+    return out, lse
+
+
+def flash_bwd_raw(dout, q, k, v, out, lse, causal, softmax_scale, row_lo, row_hi):
+    """Launch the backward kernels. Returns (dq, dk, dv) shaped like q, k, v (contiguous)."""
+    B, Sq, Hq, D = q.shape
+    Sk, Hkv = k.shape[1], k.shape[2]
+    dq_acc = torch.zeros(B, Sq, Hq, D, dtype=torch.float32, device=q.device)
+    dk = torch.empty(B, Sk, Hq, D, dtype=q.dtype, device=q.device)
+    dv = torch.empty(B, Sk, Hq, D, dtype=q.dtype, device=q.device)
+    delta = torch.empty(B, Hq, Sq, dtype=torch.float32, device=q.device)
+    dq = torch.empty(B, Sq, Hq, D, dtype=q.dtype, device=q.device)
+    dout = dout if (dout.stride(-1) == 1 and dout.stride(2) == D and dout.stride(0) == dout.stride(1) * Sq) \
+        else dout.contiguous()
+    rc = _lib.lib().atb_flash_bwd(
+        _lib.ptr(dout), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(lse), _lib.ptr(delta),
+        _lib.ptr(dq_acc), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(row_lo), _lib.ptr(row_hi),
+        ctypes.c_int(B), ctypes.c_int(Sq), ctypes.c_int(Sk), ctypes.c_int(Hq), ctypes.c_int(Hkv),
+        ctypes.c_longlong(_token_stride(q)), ctypes.c_longlong(_token_stride(k)), ctypes.c_longlong(_token_stride(v)),
+        ctypes.c_longlong(_token_stride(dout)), ctypes.c_int(int(causal)), ctypes.c_float(softmax_scale),
+        _lib.stream_ptr(), _lib.ptr(_lib.status_word(q.device)))
+    _lib.check(rc, "atb_flash_bwd")
+    if Hkv != Hq:
+        g = Hq // Hkv
+        dk = dk.view(B, Sk, Hkv, g, D).float().sum(3).to(q.dtype)
+        dv = dv.view(B, Sk, Hkv, g, D).float().sum(3).to(q.dtype)
+    return dq, dk, dv
+
+
+class _FlashAttn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, causal, scale, row_lo, row_hi):
+        out, lse = flash_fwd_raw(q, k, v, causal, scale, row_lo, row_hi)
+        ctx.save_for_backward(q, k, v, out, lse, row_lo, row_hi)
+        ctx.cfg = (causal, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse, row_lo, row_hi = ctx.saved_tensors
+        causal, scale = ctx.cfg
+        dq, dk, dv = flash_bwd_raw(dout, q, k, v, out, lse, causal, scale, row_lo, row_hi)
+        return dq, dk, dv, None, None, None, None
 
 
 def flash_attention(q, k, v, causal=False, softmax_scale=None, glm_mask=None, pack_glm_mask=None,
                     key_padding_mask=None, cu_seqlens=None):
-    raise NotImplementedError
+    B, Sq, Hq, D = q.shape
+    Sk = k.shape[1]
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
+    if Sq == 1:
+        causal = False   # single-query decode sees every key
+    lo, hi = row_intervals(B, Sq, Sk, q.device, causal, glm_mask, pack_glm_mask, key_padding_mask, cu_seqlens)
+    return _FlashAttn.apply(q, k, v, bool(causal), float(scale), lo, hi)

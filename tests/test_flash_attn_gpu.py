@@ -1,0 +1,82 @@
+"""sm_100a flash attention against the dense fp32 reference, for every mask form."""
+import math
+
+import pytest
+import torch
+
+from atorch_b200 import _lib
+from atorch_b200.ops import attention_reference
+from atorch_b200.ops import flash
+
+pytestmark = pytest.mark.gpu
+
+
+def _qkv(B, Sq, Sk, Hq, Hkv, D=128, fused=False):
+    if fused and Sq == Sk:
+        qkv = torch.randn(B, Sq, Hq + 2 * Hkv, D, device="cuda", dtype=torch.bfloat16)
+        return qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hkv], qkv[:, :, Hq + Hkv:]
+    q = torch.randn(B, Sq, Hq, D, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(B, Sk, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(B, Sk, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    return q, k, v
+
+
+def _fwd(q, k, v, **kw):
+    B, Sq, Hq, D = q.shape
+    lo, hi = flash.row_intervals(B, Sq, k.shape[1], q.device, kw.get("causal", False), kw.get("glm_mask"),
+                                 kw.get("pack_glm_mask"), kw.get("key_padding_mask"), kw.get("cu_seqlens"))
+    out, lse = flash.flash_fwd_raw(q, k, v, kw.get("causal", False), 1.0 / math.sqrt(D), lo, hi)
+    torch.cuda.synchronize()
+    _lib.check_status(q.device)
+    return out, lse
+
+
+@pytest.mark.parametrize("B,Sq,Sk,Hq,Hkv", [(1, 128, 128, 1, 1), (2, 256, 256, 4, 4), (1, 1024, 1024, 8, 2),
+                                            (2, 200, 200, 2, 2), (1, 384, 640, 2, 1), (1, 1, 300, 4, 4)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_flash_fwd_basic(B, Sq, Sk, Hq, Hkv, causal):
+    torch.manual_seed(B * 1000 + Sq + Sk)
+    q, k, v = _qkv(B, Sq, Sk, Hq, Hkv, fused=(Sq == Sk and Hq == 4))
+    if Sq == 1:
+        causal = False
+    out, lse = _fwd(q, k, v, causal=causal)
+    ref = attention_reference(q, k, v, causal=causal)
+    assert torch.allclose(out.float(), ref.float(), rtol=2e-2, atol=2e-2), (out.float() - ref.float()).abs().max().item()
+    kf = k.float().repeat_interleave(Hq // Hkv, dim=2)
+    s = torch.einsum("bqhd,bkhd->bhqk", q.float(), kf) / math.sqrt(128)
+    if causal:
+        i = torch.arange(Sq, device="cuda")[:, None] + (Sk - Sq)
+        s = s.masked_fill(torch.arange(Sk, device="cuda")[None, :] > i, float("-inf"))
+    assert torch.allclose(lse, torch.logsumexp(s, -1), rtol=1e-3, atol=1e-2)
+
+
+def test_flash_fwd_glm_and_packed_masks():
+    torch.manual_seed(7)
+    B, S, H = 2, 512, 2
+    q, k, v = _qkv(B, S, S, H, H)
+    glm = torch.tensor([100, 333], device="cuda", dtype=torch.int32)
+    out, _ = _fwd(q, k, v, causal=True, glm_mask=glm)
+    ref = attention_reference(q, k, v, causal=True, glm_mask=glm)
+    assert torch.allclose(out.float(), ref.float(), rtol=2e-2, atol=2e-2)
+    pack = torch.tensor([[[0, 200, -1], [50, 300, -1]], [[10, 128, 400], [64, 256, 512]]], device="cuda",
+                        dtype=torch.int32)
+    out, _ = _fwd(q, k, v, causal=True, pack_glm_mask=pack)
+    ref = attention_reference(q, k, v, causal=True, pack_glm_mask=pack)
+    assert torch.allclose(out.float(), ref.float(), rtol=2e-2, atol=2e-2)
+
+
+def test_flash_fwd_padding_and_varlen():
+    torch.manual_seed(8)
+    B, S, H = 2, 384, 2
+    q, k, v = _qkv(B, S, S, H, H)
+    kp = torch.ones(B, S, dtype=torch.bool, device="cuda")
+    kp[0, 300:] = False
+    kp[1, 129:] = False
+    out, _ = _fwd(q, k, v, causal=False, key_padding_mask=kp)
+    ref = attention_reference(q, k, v, key_padding_mask=kp)
+    assert torch.allclose(out.float(), ref.float(), rtol=2e-2, atol=2e-2)
+    cu = torch.tensor([0, 100, 228, 384], device="cuda", dtype=torch.int32)
+    for causal in (True, False):
+        out, _ = _fwd(q, k, v, causal=causal, cu_seqlens=cu)
+        ref = attention_reference(q, k, v, causal=causal, cu_seqlens=cu)
+        assert torch.allclose(out.float(), ref.float(), rtol=2e-2, atol=2e-2)
