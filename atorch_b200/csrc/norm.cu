@@ -325,3 +325,100 @@ extern "C" int atb_colsum(const float* partial, void* out, int P, int N, int out
   else colsum_kernel<float><<<grid, 256, 0, st>>>(partial, (float*)out, P, N, accumulate);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free RMSNorm backward (declared in no_alloc.h).
+//
+// Some callers of this library cannot allocate device memory around a kernel: code that runs inside
+// a region where cudaMalloc is forbidden or deadlocks (a memory pool owned by another runtime, a
+// pre-sized inference/training arena, a callback or a latency-critical path that must not touch the
+// allocator, or a host framework that hands out only the input and output buffers). The regular
+// backward needs a [parts, N] fp32 scratch matrix for the deterministic weight-gradient reduction,
+// which the PyTorch wrapper allocates per call. This variant keeps that scratch in a file-scope
+// device array instead, so the caller passes inputs and outputs only.
+//
+// The array is NA_MAX_PARTS * NA_MAX_N floats (148 * 8192 * 4 B = 4.6 MiB) and is held by every GPU
+// that loads the library, until the process exits. Sizes beyond it (N > 8192) are rejected.
+// ------------------------------------------------------------------------------------------------
+#include <mutex>
+#include <cstdio>
+
+namespace {
+constexpr int NA_MAX_PARTS = 148;   // one partial row per SM
+constexpr int NA_MAX_N = 8192;
+constexpr int NA_MAX_DEVICES = 64;
+thread_local char g_na_error[256] = "";
+}  // namespace
+
+static __device__ __align__(256) float g_na_scratch[NA_MAX_PARTS * NA_MAX_N];
+
+namespace {
+// In host code `g_na_scratch` is only a stand-in for the symbol, not a device address; the address
+// that kernels may use is looked up once per device, with that device current.
+float* na_scratch_address() {
+  static std::mutex mu;
+  static float* ptrs[NA_MAX_DEVICES] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NA_MAX_DEVICES) {
+    snprintf(g_na_error, sizeof(g_na_error), "no current CUDA device (or device index >= %d)", NA_MAX_DEVICES);
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (ptrs[dev] == nullptr) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_na_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      snprintf(g_na_error, sizeof(g_na_error), "cudaGetSymbolAddress failed on device %d: %s", dev,
+               cudaGetErrorString(e));
+      return nullptr;
+    }
+    ptrs[dev] = static_cast<float*>(p);
+  }
+  return ptrs[dev];
+}
+}  // namespace
+
+extern "C" const char* atb_noalloc_last_error() { return g_na_error; }
+
+extern "C" int atb_noalloc_max_n() { return NA_MAX_N; }
+
+extern "C" int atb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
+                                       void* dw, int M, int N, int dtype, void* stream) {
+  g_na_error[0] = 0;
+  if (M <= 0 || N <= 0) {
+    snprintf(g_na_error, sizeof(g_na_error), "M and N must be positive (got M=%d N=%d)", M, N);
+    return -10;
+  }
+  if (N > NA_MAX_N) {
+    snprintf(g_na_error, sizeof(g_na_error), "N=%d exceeds the built-in scratch limit of %d columns", N, NA_MAX_N);
+    return -11;
+  }
+  if (N & 7) {
+    snprintf(g_na_error, sizeof(g_na_error), "N=%d must be a multiple of 8", N);
+    return -12;
+  }
+  if (dtype < 0 || dtype > 2) {
+    snprintf(g_na_error, sizeof(g_na_error), "dtype %d is not 0 (bf16), 1 (fp16) or 2 (fp32)", dtype);
+    return -13;
+  }
+  float* scratch = na_scratch_address();
+  if (scratch == nullptr) return -14;
+  const int parts = M < NA_MAX_PARTS ? M : NA_MAX_PARTS;
+  cudaStream_t st = (cudaStream_t)stream;
+  int rc;
+  // Every one of the `parts` partial rows is fully written by its CTA before the column sum reads
+  // it, so nothing has to be cleared between calls even though the array keeps old contents.
+  if (dtype == 0)
+    rc = launch_bwd<__nv_bfloat16, false>(dy, x, w, nullptr, rstd, nullptr, dx, scratch, nullptr, parts, M, N, st);
+  else if (dtype == 1)
+    rc = launch_bwd<__half, false>(dy, x, w, nullptr, rstd, nullptr, dx, scratch, nullptr, parts, M, N, st);
+  else
+    rc = launch_bwd<float, false>(dy, x, w, nullptr, rstd, nullptr, dx, scratch, nullptr, parts, M, N, st);
+  if (rc != 0) {
+    snprintf(g_na_error, sizeof(g_na_error), "backward kernel launch failed (%d)", rc);
+    return rc;
+  }
+  rc = atb_colsum(scratch, dw, parts, N, dtype, 0, stream);
+  if (rc != 0) snprintf(g_na_error, sizeof(g_na_error), "column-sum kernel launch failed (%d)", rc);
+  return rc;
+}
