@@ -1,0 +1,77 @@
+"""Micro-benchmark of the sm_100a flash attention (forward, backward) against torch SDPA.
+
+    python -m atorch_b200.benchmarks.attn_bench [--iters 10]
+"""
+from __future__ import annotations
+
+import argparse
+import math
+
+import torch
+
+from atorch_b200 import _lib
+from atorch_b200.ops import flash
+
+
+def time_fn(fn, iters, flush):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    evs = []
+    for _ in range(iters):
+        flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        evs.append((s, e))
+    torch.cuda.synchronize()
+    ts = sorted(s.elapsed_time(e) for s, e in evs)
+    return ts[len(ts) // 2] * 1e3
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--iters", type=int, default=10)
+    args = ap.parse_args(argv)
+    dev = torch.device("cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for (B, S, H, Hkv, causal) in [(1, 4096, 32, 32, True), (1, 4096, 32, 32, False), (4, 2048, 16, 16, True),
+                                   (1, 4096, 32, 8, True), (1, 8192, 32, 32, True)]:
+        D = 128
+        q = torch.randn(B, S, H, D, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        k = torch.randn(B, S, Hkv, D, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        v = torch.randn(B, S, Hkv, D, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        flops_f = 4.0 * B * H * S * S * D * (0.5 if causal else 1.0)
+        scale = 1.0 / math.sqrt(D)
+
+        def ours_f():
+            return flash.flash_fwd_raw(q, k, v, causal, scale, None, None)
+
+        def lib_f():
+            return torch.nn.functional.scaled_dot_product_attention(
+                q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=causal, enable_gqa=H != Hkv)
+        t_o, t_l = time_fn(ours_f, args.iters, flush), time_fn(lib_f, args.iters, flush)
+        _lib.check_status(dev)
+        line = (f"B{B} S{S} H{H}/{Hkv} causal={int(causal)} fwd: ours {t_o:8.1f} us {flops_f / t_o / 1e6:7.1f} TF | "
+                f"SDPA {t_l:8.1f} us {flops_f / t_l / 1e6:7.1f} TF")
+        if flash.backward_built():
+            out, lse = ours_f()
+            dout = torch.randn_like(out)
+
+            def ours_b():
+                return flash.flash_bwd_raw(dout, q, k, v, out, lse, causal, scale, None, None)
+            o2 = lib_f()
+            d2 = torch.randn_like(o2)
+
+            def lib_b():
+                return torch.autograd.grad(o2, (q, k, v), d2, retain_graph=True)
+            tb_o, tb_l = time_fn(ours_b, args.iters, flush), time_fn(lib_b, args.iters, flush)
+            _lib.check_status(dev)
+            line += (f" || bwd: ours {tb_o:8.1f} us {2.5 * flops_f / tb_o / 1e6:7.1f} TF | "
+                     f"SDPA {tb_l:8.1f} us {2.5 * flops_f / tb_l / 1e6:7.1f} TF")
+        print(line, flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -88,6 +88,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   int* kv_range = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_slot + 2));  // [4]: t0, t1, full_lo, full_hi
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // a wait already ran out somewhere in this stream of work: do not start, so that a failing
+  // launch ends after one wait limit instead of one per wave of CTAs
+  if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) return;
   const int qb = gridDim.x - 1 - blockIdx.x;  // heaviest (last) causal blocks first
   const int h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (p.Hq / p.Hkv);
@@ -243,7 +246,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     bool ok = true;
 
     auto accumulate_o = [&](int j) -> bool {  // O := O * alpha_j + O_j
-      if (!mbar_wait(o_full, j & 1, abort_flag, p.status)) return false;
+      if (!__all_sync(0xffffffffu, mbar_wait(o_full, j & 1, abort_flag, p.status))) return false;
       tc_fence_after();
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
@@ -259,7 +262,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     for (int j = 0; j < ntiles; ++j) {
       const int sb = j & 1;
       const int kv0 = (t0 + j) * BKV;
-      if (!mbar_wait(&s_full[sb], (j >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(&s_full[sb], (j >> 1) & 1, abort_flag, p.status))) { ok = false; break; }
       tc_fence_after();
       float sv[64];
 #pragma unroll
@@ -289,7 +292,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       rm[half * 128 + r] = mx;
       __syncwarp();
       if (lane == 0) mbar_arrive(x_bar);
-      if (!mbar_wait(x_bar, j & 1, abort_flag, p.status)) { ok = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(x_bar, j & 1, abort_flag, p.status))) { ok = false; break; }
       mx = fmaxf(mx, rm[(half ^ 1) * 128 + r]);
       const float m_new = fmaxf(m_run, mx);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
@@ -307,7 +310,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       // previous tile's P V product must be folded in (and must have finished reading sP)
       if (j > 0) {
         if (!accumulate_o(j - 1)) { ok = false; break; }
-        if (!mbar_wait(p_free, (j - 1) & 1, abort_flag, p.status)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(p_free, (j - 1) & 1, abort_flag, p.status))) { ok = false; break; }
       }
       alpha_prev = alpha;
       // P tile, K-major 128B-swizzled: panel `half`, row r, 16-byte chunk c8 at slot (c8 ^ (r & 7))

@@ -1,0 +1,424 @@
+// Flash attention backward for sm_100a (head dim 128, bf16), tcgen05 + TMEM + TMA.
+//
+// One CTA per (128 keys, head, batch) walks the query blocks that can see its keys. Per query block:
+//   S  = Q K^T,  dP = dO V^T                      2 x tcgen05.mma -> TMEM   (K-major operands)
+//   P  = exp2(S c - lse),  dS = P (dP - delta) s    registers -> bf16 tiles in swizzled shared memory
+//   dV += P^T dO,  dK += dS^T Q                    accumulate in TMEM across query blocks (MN-major operands)
+//   dQ  = dS K                                      TMEM -> registers -> red.global.add.v4.f32
+// A [rows][64] bf16 panel with 128-byte swizzle is at the same time a K-major tile of the matrix and
+// an MN-major tile of its transpose, so P, dS, Q, dO and K are each stored once and read both ways.
+// TMEM: S | dP | dV | dK = 4 x 128 columns; dQ reuses the S columns.
+//
+// Warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warps 2..9 = element-wise work (thread
+// (row r, half h) owns columns [64h, 64h+64) of row r). `delta = rowsum(dO * O)` comes from a
+// small pre-pass; dQ is accumulated in fp32 and converted by a post-pass.
+//
+// Masks are per-row key intervals [lo, hi) as in the forward kernel.
+#include "common.cuh"
+
+namespace {
+using namespace atb;
+
+constexpr int BQ = 128, BKV = 128, HD = 128;
+constexpr int PANEL = 128 * 64 * 2;
+constexpr int TILE = 2 * PANEL;
+constexpr int N_EW = 256;
+constexpr int THREADS = 64 + N_EW;
+
+struct BwdParams {
+  const float* lse;    // [B, Hq, Sq]
+  const float* delta;  // [B, Hq, Sq]
+  float* dq_acc;       // [B, Sq, Hq, HD] fp32, zero-initialised
+  __nv_bfloat16* dk;   // [B, Sk, Hq, HD]
+  __nv_bfloat16* dv;   // [B, Sk, Hq, HD]
+  const int* row_lo;
+  const int* row_hi;
+  int B, Sq, Sk, Hq, Hkv, causal;
+  float scale, scale_log2;
+  int* status;
+};
+
+struct SmemB {
+  static constexpr int Q_OFF = 0;
+  static constexpr int DO_OFF = Q_OFF + TILE;
+  static constexpr int K_OFF = DO_OFF + TILE;
+  static constexpr int V_OFF = K_OFF + TILE;
+  static constexpr int P_OFF = V_OFF + TILE;
+  static constexpr int DS_OFF = P_OFF + TILE;
+  static constexpr int BAR_OFF = DS_OFF + TILE;  // 192 KB
+  static constexpr int NBARS = 7;
+  static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 64 + 1024;
+};
+
+ATB_DEVICE void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+
+__global__ void __launch_bounds__(THREADS, 1)
+flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
+                 const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, BwdParams p) {
+  using L = SmemB;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem + L::Q_OFF;
+  uint8_t* sdO = smem + L::DO_OFF;
+  uint8_t* sK = smem + L::K_OFF;
+  uint8_t* sV = smem + L::V_OFF;
+  uint8_t* sP = smem + L::P_OFF;
+  uint8_t* sdS = smem + L::DS_OFF;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint64_t* kv_full = bars;
+  uint64_t* qdo_full = bars + 1;
+  uint64_t* qdo_empty = bars + 2;
+  uint64_t* sdp_full = bars + 3;
+  uint64_t* pds_full = bars + 4;
+  uint64_t* dq_full = bars + 5;
+  uint64_t* acc_free = bars + 6;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::NBARS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* q_range = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_slot + 2));  // [2]: first, last+1 q block
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // a wait already ran out somewhere in this stream of work: do not start, so that a failing
+  // launch ends after one wait limit instead of one per wave of CTAs
+  if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) return;
+  const int kb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.Hq / p.Hkv);
+  const int kv0 = kb * BKV;
+  const int shift = p.Sk - p.Sq;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    mbar_init(qdo_full, 1);
+    mbar_init(qdo_empty, 1);
+    mbar_init(sdp_full, 1);
+    mbar_init(pds_full, N_EW / 32);
+    mbar_init(dq_full, 1);
+    mbar_init(acc_free, N_EW / 32);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc<1>(tmem_slot, 512);
+    tmem_relinquish<1>();
+  }
+  if (warp == 2) {
+    // query rows whose interval meets this key block
+    int rmin = INT_MAX, rmax = -1;
+    if (p.row_lo == nullptr && p.row_hi == nullptr) {
+      if (lane == 0) {
+        rmin = p.causal ? max(0, kv0 - shift) : 0;
+        rmax = p.Sq - 1;
+        if (rmin > rmax) { rmin = INT_MAX; rmax = -1; }
+      }
+    } else {
+      for (int i = lane; i < p.Sq; i += 32) {
+        const int lo = p.row_lo ? p.row_lo[(long long)b * p.Sq + i] : 0;
+        const int hi = p.row_hi ? p.row_hi[(long long)b * p.Sq + i] : (p.causal ? i + 1 + shift : p.Sk);
+        if (max(lo, kv0) < min(min(hi, p.Sk), kv0 + BKV)) { rmin = min(rmin, i); rmax = max(rmax, i); }
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      rmin = min(rmin, __shfl_xor_sync(0xffffffffu, rmin, o));
+      rmax = max(rmax, __shfl_xor_sync(0xffffffffu, rmax, o));
+    }
+    if (lane == 0) {
+      q_range[0] = rmax >= 0 ? rmin / BQ : 0;
+      q_range[1] = rmax >= 0 ? rmax / BQ + 1 : 0;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int qb0 = q_range[0], qb1 = q_range[1];
+  const int nblk = qb1 - qb0;
+  const long long q_row_base = (long long)b * p.Sq;
+  const long long k_row = (long long)b * p.Sk + kv0;
+
+  if (warp == 0) {
+    if (lane == 0 && nblk > 0) {
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmdO);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      mbar_expect_tx(kv_full, 2 * TILE);
+      tma_load_2d(sK, &tmK, kv_full, hk * HD, (int)k_row);
+      tma_load_2d(sK + PANEL, &tmK, kv_full, hk * HD + 64, (int)k_row);
+      tma_load_2d(sV, &tmV, kv_full, hk * HD, (int)k_row);
+      tma_load_2d(sV + PANEL, &tmV, kv_full, hk * HD + 64, (int)k_row);
+      for (int it = 0; it < nblk; ++it) {
+        if (!mbar_wait(qdo_empty, (it & 1) ^ 1, abort_flag, p.status)) break;
+        const int qrow = (int)(q_row_base + (long long)(qb0 + it) * BQ);
+        mbar_expect_tx(qdo_full, 2 * TILE);
+        tma_load_2d(sQ, &tmQ, qdo_full, h * HD, qrow);
+        tma_load_2d(sQ + PANEL, &tmQ, qdo_full, h * HD + 64, qrow);
+        tma_load_2d(sdO, &tmdO, qdo_full, h * HD, qrow);
+        tma_load_2d(sdO + PANEL, &tmdO, qdo_full, h * HD + 64, qrow);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && nblk > 0) {
+      constexpr uint32_t id_kk = umma_idesc(128, 128, 1, 1, false, false);
+      constexpr uint32_t id_mm = umma_idesc(128, 128, 1, 1, true, true);
+      constexpr uint32_t id_km = umma_idesc(128, 128, 1, 1, false, true);
+      const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO), aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP),
+                     adS = smem_u32(sdS);
+      const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdV = tmem_base + 256, tdK = tmem_base + 384;
+      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status);
+      for (int it = 0; ok && it < nblk; ++it) {
+        if (!mbar_wait(qdo_full, it & 1, abort_flag, p.status)) break;
+        if (!mbar_wait(acc_free, (it & 1) ^ 1, abort_flag, p.status)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {  // S = Q K^T over d
+          const uint32_t off = (k >> 2) * PANEL + (k & 3) * 32;
+          umma_f16<1>(tS, umma_desc_sw128(aQ + off, 16, 1024), umma_desc_sw128(aK + off, 16, 1024), id_kk, k != 0);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {  // dP = dO V^T over d
+          const uint32_t off = (k >> 2) * PANEL + (k & 3) * 32;
+          umma_f16<1>(tdP, umma_desc_sw128(adO + off, 16, 1024), umma_desc_sw128(aV + off, 16, 1024), id_kk, k != 0);
+        }
+        umma_commit(sdp_full);
+        if (!mbar_wait(pds_full, it & 1, abort_flag, p.status)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k)  // dV += P^T dO over q
+          umma_f16<1>(tdV, umma_desc_sw128(aP + k * 2048, PANEL, 1024), umma_desc_sw128(adO + k * 2048, PANEL, 1024),
+                      id_mm, (it | k) != 0);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)  // dK += dS^T Q over q
+          umma_f16<1>(tdK, umma_desc_sw128(adS + k * 2048, PANEL, 1024), umma_desc_sw128(aQ + k * 2048, PANEL, 1024),
+                      id_mm, (it | k) != 0);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {  // dQ = dS K over keys (into the S columns)
+          const uint32_t off = (k >> 2) * PANEL + (k & 3) * 32;
+          umma_f16<1>(tS, umma_desc_sw128(adS + off, 16, 1024), umma_desc_sw128(aK + k * 2048, PANEL, 1024), id_km,
+                      k != 0);
+        }
+        umma_commit(dq_full);
+        umma_commit(qdo_empty);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    bool ok = true;
+    for (int it = 0; it < nblk; ++it) {
+      const int i = (qb0 + it) * BQ + r;  // global query row
+      bool valid = i < p.Sq;
+      int lo = 0, hi = 0;
+      float lse2 = 0.f, delta = 0.f;
+      if (valid) {
+        const long long ridx = ((long long)b * p.Hq + h) * p.Sq + i;
+        const float l = p.lse[ridx];
+        if (l == -INFINITY) {
+          valid = false;
+        } else {
+          lse2 = l * 1.4426950408889634f;
+          delta = p.delta[ridx];
+          lo = p.row_lo ? p.row_lo[(long long)b * p.Sq + i] : 0;
+          hi = p.row_hi ? p.row_hi[(long long)b * p.Sq + i] : (p.causal ? i + 1 + shift : p.Sk);
+          lo = max(lo, 0);
+          hi = min(hi, p.Sk);
+        }
+      }
+      const bool row_full = valid && lo <= kv0 && hi >= kv0 + BKV;
+      if (!__all_sync(0xffffffffu, mbar_wait(sdp_full, it & 1, abort_flag, p.status))) { ok = false; break; }
+      tc_fence_after();
+      uint8_t* prow = sP + half * PANEL + r * 128;
+      uint8_t* dsrow = sdS + half * PANEL + r * 128;
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        uint32_t ts[32], td[32];
+        tmem_ld_32x32(lane_addr + half * 64 + cc * 32, ts);
+        tmem_ld_32x32(lane_addr + 128 + half * 64 + cc * 32, td);
+        tmem_ld_wait();
+        uint32_t pk[16], dk_[16];
+        const int c0 = kv0 + half * 64 + cc * 32;
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+          float p0 = exp2f(__uint_as_float(ts[c]) * p.scale_log2 - lse2);
+          float p1 = exp2f(__uint_as_float(ts[c + 1]) * p.scale_log2 - lse2);
+          if (!row_full) {
+            if (!valid || c0 + c < lo || c0 + c >= hi) p0 = 0.f;
+            if (!valid || c0 + c + 1 < lo || c0 + c + 1 >= hi) p1 = 0.f;
+          }
+          const float d0 = p0 * (__uint_as_float(td[c]) - delta) * p.scale;
+          const float d1 = p1 * (__uint_as_float(td[c + 1]) - delta) * p.scale;
+          pk[c >> 1] = pack_bf16x2(p0, p1);
+          dk_[c >> 1] = pack_bf16x2(d0, d1);
+        }
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int c8 = cc * 4 + q4;
+          const int slot = (c8 ^ (r & 7)) << 4;
+          *reinterpret_cast<uint4*>(prow + slot) = make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
+          *reinterpret_cast<uint4*>(dsrow + slot) =
+              make_uint4(dk_[q4 * 4], dk_[q4 * 4 + 1], dk_[q4 * 4 + 2], dk_[q4 * 4 + 3]);
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pds_full);
+      if (!__all_sync(0xffffffffu, mbar_wait(dq_full, it & 1, abort_flag, p.status))) { ok = false; break; }
+      tc_fence_after();
+      float* dqrow = p.dq_acc + (((long long)b * p.Sq + i) * p.Hq + h) * HD + half * 64;
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        uint32_t t[32];
+        tmem_ld_32x32(lane_addr + half * 64 + cc * 32, t);
+        tmem_ld_wait();
+        if (valid) {
+#pragma unroll
+          for (int c = 0; c < 32; c += 4)
+            red_add_v4(dqrow + cc * 32 + c, __uint_as_float(t[c]), __uint_as_float(t[c + 1]),
+                       __uint_as_float(t[c + 2]), __uint_as_float(t[c + 3]));
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_free);
+    }
+    // dV / dK of this key block: TMEM lane = key row. tcgen05.ld is a warp-wide (.sync.aligned)
+    // instruction: every lane executes it, only the global stores are predicated per row.
+    const int j = kv0 + r;
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      const bool store = j < p.Sk;
+      __nv_bfloat16* dvrow = p.dv + (((long long)b * p.Sk + j) * p.Hq + h) * HD + half * 64;
+      __nv_bfloat16* dkrow = p.dk + (((long long)b * p.Sk + j) * p.Hq + h) * HD + half * 64;
+      if (nblk > 0) tc_fence_after();
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        uint32_t tv[32], tk[32];
+        if (nblk > 0) {
+          tmem_ld_32x32(lane_addr + 256 + half * 64 + cc * 32, tv);
+          tmem_ld_32x32(lane_addr + 384 + half * 64 + cc * 32, tk);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) { tv[c] = 0u; tk[c] = 0u; }
+        }
+        if (store) {
+#pragma unroll
+          for (int c = 0; c < 32; c += 8) {
+            uint4 a, d;
+            a.x = pack_bf16x2(__uint_as_float(tv[c]), __uint_as_float(tv[c + 1]));
+            a.y = pack_bf16x2(__uint_as_float(tv[c + 2]), __uint_as_float(tv[c + 3]));
+            a.z = pack_bf16x2(__uint_as_float(tv[c + 4]), __uint_as_float(tv[c + 5]));
+            a.w = pack_bf16x2(__uint_as_float(tv[c + 6]), __uint_as_float(tv[c + 7]));
+            d.x = pack_bf16x2(__uint_as_float(tk[c]), __uint_as_float(tk[c + 1]));
+            d.y = pack_bf16x2(__uint_as_float(tk[c + 2]), __uint_as_float(tk[c + 3]));
+            d.z = pack_bf16x2(__uint_as_float(tk[c + 4]), __uint_as_float(tk[c + 5]));
+            d.w = pack_bf16x2(__uint_as_float(tk[c + 6]), __uint_as_float(tk[c + 7]));
+            *reinterpret_cast<uint4*>(dvrow + cc * 32 + c) = a;
+            *reinterpret_cast<uint4*>(dkrow + cc * 32 + c) = d;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t_start = globaltimer_ns();
+    while (globaltimer_ns() - t_start < 200000ull) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<1>(tmem_base, 512);
+  }
+}
+
+// delta[b, h, i] = sum_d dO[b, i, h, d] * O[b, i, h, d]; one warp per (b, i, h) row of 128 elements.
+__global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
+                                   float* __restrict__ delta, int B, int Sq, int Hq, long long do_stride) {
+  const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = (long long)B * Sq * Hq;
+  if (w >= total) return;
+  const int hh = (int)(w % Hq);
+  const long long tok = w / Hq;  // b * Sq + i
+  const uint2 a = *reinterpret_cast<const uint2*>(dO + tok * do_stride + hh * HD + lane * 4);
+  const uint2 o = *reinterpret_cast<const uint2*>(O + (tok * Hq + hh) * HD + lane * 4);
+  const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), o0 = unpack_bf16x2(o.x), o1 = unpack_bf16x2(o.y);
+  float s = a0.x * o0.x + a0.y * o0.y + a1.x * o1.x + a1.y * o1.y;
+  s = warp_sum(s);
+  if (lane == 0) {
+    const long long bb = tok / Sq, i = tok % Sq;
+    delta[(bb * Hq + hh) * Sq + i] = s;
+  }
+}
+
+__global__ void f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long n4) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    const float4 v = reinterpret_cast<const float4*>(src)[i];
+    uint2 o;
+    o.x = pack_bf16x2(v.x, v.y);
+    o.y = pack_bf16x2(v.z, v.w);
+    reinterpret_cast<uint2*>(dst)[i] = o;
+  }
+}
+
+}  // namespace
+
+// dq_acc must be zero on entry; dq/dk/dv are written. dk, dv are per query head ([B, Sk, Hq, 128]);
+// the caller sums head groups for grouped-query attention. `delta` is scratch [B, Hq, Sq].
+extern "C" int atb_flash_bwd(const void* dout, const void* q, const void* k, const void* v, const void* out,
+                             const float* lse, float* delta, float* dq_acc, void* dq, void* dk, void* dv,
+                             const int* row_lo, const int* row_hi, int B, int Sq, int Sk, int Hq, int Hkv,
+                             long long q_stride, long long k_stride, long long v_stride, long long do_stride,
+                             int causal, float softmax_scale, void* stream, int* status) {
+  if (B <= 0 || Sq <= 0 || Sk <= 0) return 0;
+  if (Hq % Hkv) return -1;
+  if ((q_stride | k_stride | v_stride | do_stride) & 7) return -1;
+  cudaStream_t st = (cudaStream_t)stream;
+  CUtensorMap tmQ, tmdO, tmK, tmV;
+  if (!make_tmap_2d(&tmQ, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)B * Sq, (uint64_t)Hq * HD, q_stride, BQ, 64,
+                    CU_TENSOR_MAP_SWIZZLE_128B))
+    return -2;
+  if (!make_tmap_2d(&tmdO, dout, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)B * Sq, (uint64_t)Hq * HD, do_stride,
+                    BQ, 64, CU_TENSOR_MAP_SWIZZLE_128B))
+    return -2;
+  if (!make_tmap_2d(&tmK, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)B * Sk, (uint64_t)Hkv * HD, k_stride, BKV,
+                    64, CU_TENSOR_MAP_SWIZZLE_128B))
+    return -2;
+  if (!make_tmap_2d(&tmV, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)B * Sk, (uint64_t)Hkv * HD, v_stride, BKV,
+                    64, CU_TENSOR_MAP_SWIZZLE_128B))
+    return -2;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(flash_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemB::TOTAL) !=
+        cudaSuccess)
+      return -4;
+    attr_set = true;
+  }
+  {
+    const long long warps = (long long)B * Sq * Hq;
+    const int threads = 256;
+    const long long blocks = (warps * 32 + threads - 1) / threads;
+    flash_delta_kernel<<<(unsigned)blocks, threads, 0, st>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out,
+                                                             delta, B, Sq, Hq, do_stride);
+  }
+  BwdParams p;
+  p.lse = lse; p.delta = delta; p.dq_acc = dq_acc; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv;
+  p.row_lo = row_lo; p.row_hi = row_hi;
+  p.B = B; p.Sq = Sq; p.Sk = Sk; p.Hq = Hq; p.Hkv = Hkv; p.causal = causal;
+  p.scale = softmax_scale; p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.status = status;
+  dim3 grid((Sk + BKV - 1) / BKV, Hq, B);
+  flash_bwd_kernel<<<grid, THREADS, SmemB::TOTAL, st>>>(tmQ, tmdO, tmK, tmV, p);
+  const long long n4 = (long long)B * Sq * Hq * HD / 4;
+  long long g = (n4 + 255) / 256;
+  if (g > 148 * 16) g = 148 * 16;
+  f32_to_bf16_kernel<<<(unsigned)g, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dq, n4);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}

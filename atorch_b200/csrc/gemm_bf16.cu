@@ -61,6 +61,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // a wait already ran out somewhere in this stream of work: do not start, so that a failing
+  // launch ends after one wait limit instead of one per wave of CTAs
+  if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return;
 
   const int tiles_m = (M + BM - 1) / BM;
   const int tiles_n = (N + BN - 1) / BN;
@@ -176,7 +179,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tile_coords(tile, m0, n0);
       const int acc = local & 1;
       const uint32_t acc_ph = (local >> 1) & 1;
-      if (!mbar_wait(&tfull[acc], acc_ph, abort_flag, status)) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(&tfull[acc], acc_ph, abort_flag, status))) break;
       tc_fence_after();
       const int row = m0 + q * 32 + lane;
       const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;

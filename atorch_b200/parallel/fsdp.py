@@ -564,6 +564,14 @@ class FSDPEngine:
         """After an optimizer updated the fp32 master: refresh the low-precision working shards."""
         if self.mixed:
             self.lp_shard.copy_(self.master)
+        self.invalidate_gathered()
+
+    def invalidate_gathered(self) -> None:
+        """Parameters changed (optimizer step, state-dict load): gathered copies are stale."""
+        if self.world > 1:
+            for u in self.units:
+                if u.gathered:
+                    self._free_full(u)
 
     def grad_norm(self, norm_type: float = 2.0) -> torch.Tensor:
         g = self.finalize_grads()
@@ -819,6 +827,7 @@ class FusedShardedOptimizer:
             ops.adamw_step(eng.master, self.exp_avg, self.exp_avg_sq, g, eng.lp_shard, pg["lr"], b1, b2, pg["eps"],
                            pg["weight_decay"], self.step_count, grad_scale_tensor=scale_t,
                            adamw_mode=self.kind == "adamw")
+        eng.invalidate_gathered()
         return loss
 
     def state_dict(self):

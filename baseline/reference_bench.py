@@ -77,7 +77,9 @@ def _run(args, MODELS, PUBLISHED, ClockSampler, torch, atorch, auto_accelerate, 
     def loss_func(inputs, output):
         return output.loss
 
-    strategy = [("parallel_mode", ([("data", world)], None, False, True)), "module_replace",
+    # the example asks for a device mesh; with one process the reference cannot build a 0-D mesh
+    # ("No `mesh_dim_names` found"), so the plain group form is used there
+    strategy = [("parallel_mode", ([("data", world)], None, False, world > 1)), "module_replace",
                 ("fsdp", {"sync_module_states": True, "limit_all_gathers": True, "forward_prefetch": True,
                           "atorch_wrap_cls": (LlamaDecoderLayer,)}),
                 ("amp_native", {"dtype": torch.bfloat16}),

@@ -80,3 +80,52 @@ def test_flash_fwd_padding_and_varlen():
         out, _ = _fwd(q, k, v, causal=causal, cu_seqlens=cu)
         ref = attention_reference(q, k, v, causal=causal, cu_seqlens=cu)
         assert torch.allclose(out.float(), ref.float(), rtol=2e-2, atol=2e-2)
+
+
+def _bwd_check(q, k, v, **kw):
+    from atorch_b200.ops import attention
+    qs = [t.detach().clone().requires_grad_() for t in (q, k, v)]
+    out = attention(*qs, **kw)
+    dout = torch.randn_like(out)
+    out.backward(dout)
+    torch.cuda.synchronize()
+    _lib.check_status(q.device)
+    rs = [t.detach().float().requires_grad_() for t in (q, k, v)]
+    ref = attention_reference(*rs, **kw)
+    ref.backward(dout.float())
+    assert torch.allclose(out.float(), ref, rtol=2e-2, atol=2e-2)
+    for name, a, b in zip("qkv", qs, rs):
+        err = (a.grad.float() - b.grad).abs().max().item()
+        scale = b.grad.abs().max().item() + 1e-6
+        assert err / scale < 3e-2, f"d{name}: max err {err} vs scale {scale}"
+
+
+@pytest.mark.parametrize("B,Sq,Sk,Hq,Hkv", [(1, 128, 128, 1, 1), (2, 256, 256, 2, 2), (1, 1024, 1024, 4, 2),
+                                            (2, 200, 200, 2, 2), (1, 384, 640, 2, 1)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_flash_bwd_basic(B, Sq, Sk, Hq, Hkv, causal):
+    torch.manual_seed(B * 100 + Sq)
+    q, k, v = _qkv(B, Sq, Sk, Hq, Hkv)
+    _bwd_check(q, k, v, causal=causal)
+
+
+def test_flash_bwd_masks():
+    torch.manual_seed(9)
+    B, S, H = 2, 512, 2
+    q, k, v = _qkv(B, S, S, H, H)
+    _bwd_check(q, k, v, causal=True, glm_mask=torch.tensor([100, 333], device="cuda", dtype=torch.int32))
+    pack = torch.tensor([[[0, 200, -1], [50, 300, -1]], [[10, 128, 400], [64, 256, 512]]], device="cuda",
+                        dtype=torch.int32)
+    _bwd_check(q, k, v, causal=True, pack_glm_mask=pack)
+    cu = torch.tensor([0, 100, 228, 512], device="cuda", dtype=torch.int32)
+    _bwd_check(q, k, v, causal=True, cu_seqlens=cu)
+    kp = torch.ones(B, S, dtype=torch.bool, device="cuda")
+    kp[0, 300:] = False
+    _bwd_check(q, k, v, causal=False, key_padding_mask=kp)
+
+
+def test_flash_in_fused_qkv_layout():
+    torch.manual_seed(10)
+    B, S, H = 1, 512, 4
+    qkv = torch.randn(B, S, 3 * H, 128, device="cuda", dtype=torch.bfloat16)
+    _bwd_check(qkv[:, :, :H], qkv[:, :, H:2 * H], qkv[:, :, 2 * H:], causal=True)
