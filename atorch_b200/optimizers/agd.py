@@ -9,7 +9,8 @@ Per parameter and step t (g = gradient, after optional coupled weight decay):
     u   = m_t / den  (optionally clamped to [-clip, clip])
     p  -= lr * sqrt(1-b2^t)/(1-b1^t) * u
 Decoupled weight decay multiplies p by (1 - lr*wd) (or (1 - wd) with ``fixed_decay``) first. The
-``win`` variant keeps a second sequence z with a reckless step and mixes it back into p.
+``win`` variant keeps a conservative sequence z (z -= step*u, shrunk by 1/(1+wd*step)) and sets
+p = tau*p - tau*2*step*u + 2*tau*z with tau = 1/(3 + 2*step*wd).
 
 The update runs through the fused flat kernel (csrc/optim.cu) for CUDA fp32 parameters without
 amsgrad/win; otherwise through the PyTorch expressions below.
@@ -96,11 +97,12 @@ class AGD(Optimizer):
             u.clamp_(-group["clip"], group["clip"])
         step = lr * math.sqrt(bc2) / bc1
         if group["win"]:
+            # Win acceleration: a conservative sequence z and a reckless step of twice the size,
+            # mixed 1/3 : 2/3 (z starts at the initial weights, as in the Win paper)
             z = st["z"]
-            reckless = 2.0 * step          # the reckless sequence uses a larger step
-            z.add_(u, alpha=-step)
-            z.mul_(1.0 / (1.0 + wd * step)) if wd else None
-            tau = step / (step + reckless)
-            p.mul_(tau).add_(z, alpha=1 - tau).add_(u, alpha=-tau * reckless)
+            z.add_(u, alpha=-step).mul_(1.0 / (1.0 + wd * step))
+            step2 = 2.0 * step
+            tau = 1.0 / (3.0 + step2 * wd)
+            p.mul_(tau).add_(u, alpha=-tau * step2).add_(z, alpha=2.0 * tau)
         else:
             p.add_(u, alpha=-step)
