@@ -57,19 +57,22 @@ def main(argv=None):
         dy = torch.randn(M, N, device=dev, dtype=torch.bfloat16)
         flops = 2.0 * M * N * K
         cases = [
-            ("fwd  x@W^T", lambda: gemm(x, w), lambda: torch.matmul(x, w.t())),
-            ("dgrad dy@W", lambda: gemm(dy, w, b_mn=True), lambda: torch.matmul(dy, w)),
-            ("wgrad dy^T@x", lambda: gemm(dy, x, a_mn=True, b_mn=True), lambda: torch.matmul(dy.t(), x)),
+            ("fwd  x@W^T", lambda kn: gemm(x, w, kernel=kn), lambda: torch.matmul(x, w.t())),
+            ("dgrad dy@W", lambda kn: gemm(dy, w, b_mn=True, kernel=kn), lambda: torch.matmul(dy, w)),
+            ("wgrad dy^T@x", lambda kn: gemm(dy, x, a_mn=True, b_mn=True, kernel=kn), lambda: torch.matmul(dy.t(), x)),
         ]
-        for name, ours, lib in cases:
-            t_ours = time_fn(ours, args.iters, flush)
+        for name, ours_k, lib in cases:
+            t_1 = time_fn(lambda: ours_k("1cta"), args.iters, flush)
+            t_2 = time_fn(lambda: ours_k("2cta"), args.iters, flush)
+            t_ours = min(t_1, t_2)
             t_lib = time_fn(lib, args.iters, flush)
             _lib.check_status(dev)
-            row = dict(shape=label, M=M, N=N, K=K, op=name, ours_us=round(t_ours, 1), cublas_us=round(t_lib, 1),
+            row = dict(shape=label, M=M, N=N, K=K, op=name, ours_us=round(t_ours, 1), cta1_us=round(t_1, 1),
+                       cta2_us=round(t_2, 1), cublas_us=round(t_lib, 1),
                        ours_tflops=round(flops / t_ours / 1e6, 1), cublas_tflops=round(flops / t_lib / 1e6, 1),
                        ratio=round(t_lib / t_ours, 3))
             rows.append(row)
-            print(f"{label:16s} {name:14s} ours {t_ours:8.1f} us {row['ours_tflops']:7.1f} TF | "
+            print(f"{label:16s} {name:14s} 1cta {t_1:8.1f} 2cta {t_2:8.1f} us best {row['ours_tflops']:7.1f} TF | "
                   f"cuBLAS {t_lib:8.1f} us {row['cublas_tflops']:7.1f} TF | ratio {row['ratio']:.3f}", flush=True)
     if args.json:
         with open(args.json, "w") as f:

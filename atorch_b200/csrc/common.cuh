@@ -229,13 +229,11 @@ ATB_DEVICE void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
 }
-// cta_group::2 commit that signals the same-offset barrier in every CTA of `cta_mask`.
-ATB_DEVICE void umma_commit_2cta(uint64_t* bar, uint16_t cta_mask) {
-  asm volatile(
-      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
-          smem_u32(bar)),
-      "h"(cta_mask)
-      : "memory");
+// cta_group::2 commit onto ONE barrier given by its shared::cluster address (own or partner CTA).
+// A CTA pair that must be told on both sides issues two of these.
+ATB_DEVICE void umma_commit_cg2(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
+               : "memory");
 }
 
 // 32 lanes x 32 consecutive fp32 columns: thread t of the warp gets lane (base_lane + t).
@@ -368,6 +366,7 @@ ATB_DEVICE __half from_f32<__half>(float v) { return __float2half_rn(v); }
 
 // Host-side: encode a 2-D tiled tensor map through the driver entry point (no libcuda link).
 #include <mutex>
+#include <cstdio>
 namespace atb {
 typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                     const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -396,6 +395,17 @@ inline bool make_tmap_2d(CUtensorMap* tm, const void* base, CUtensorMapDataType 
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_ERROR_INVALID_CONTEXT) {
+    // first CUDA work of this host thread (e.g. an autograd worker): bind the primary context
+    // through the runtime, then encode again
+    cudaFree(nullptr);
+    r = enc(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  }
+  if (r != CUDA_SUCCESS)
+    fprintf(stderr, "atb: cuTensorMapEncodeTiled failed (%d): base=%p rows=%llu cols=%llu ld=%llu box=%ux%u elt=%d\n",
+            (int)r, base, (unsigned long long)rows, (unsigned long long)cols, (unsigned long long)ld, box_rows,
+            box_cols, elt_bytes);
   return r == CUDA_SUCCESS;
 }
 }  // namespace atb

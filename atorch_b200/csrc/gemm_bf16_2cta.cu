@@ -1,0 +1,353 @@
+// bf16 GEMM for sm_100a with CTA pairs: tcgen05.mma.cta_group::2, 256 x 256 output tile per pair.
+//
+//   C[M,N] (+)= alpha * A[M,K] * B[N,K]^T (+ bias)        same contract as gemm_bf16.cu
+//
+// Two CTAs on neighbouring SMs form a cluster. Each loads its own 128 rows of A and its own 128
+// rows (half) of the B tile, 32 KB per stage instead of 48 KB, so the ring is 6 stages deep and
+// every byte of B is fetched once per pair. The leader CTA (cluster rank 0) issues the MMAs for
+// both SMs; each CTA's tensor memory receives its own 128 rows of the 256 x 256 accumulator and
+// each CTA runs its own epilogue. No TMA copy here is shared between CTAs: every load lands in
+// the shared memory of the CTA that issued it and only its completion is signalled to the leader.
+//
+// Barrier protocol (per stage s, per accumulator a):
+//   full[s]    leader only : leader's producer arrives with the pair's byte count (64 KB); the TMA
+//                            loads of BOTH CTAs complete on it
+//   empty[s]   both CTAs   : tcgen05.commit from the leader arrives on both
+//   tfull[a]   both CTAs   : tcgen05.commit from the leader arrives on both
+//   tempty[a]  leader only : the 4 epilogue warps of both CTAs arrive (8 arrivals)
+#include "common.cuh"
+
+namespace {
+using namespace atb;
+
+constexpr int BM = 128;   // rows of A per CTA (256 per pair)
+constexpr int BNH = 128;  // rows of B per CTA (256 per pair)
+constexpr int BN = 256;   // accumulator columns
+constexpr int BK = 64;
+constexpr int STAGES = 6;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int B_BYTES = BNH * BK * 2;
+constexpr int BAR_OFF = STAGES * (A_BYTES + B_BYTES);
+constexpr int SMEM_TOTAL = BAR_OFF + (2 * STAGES + 4) * 8 + 16 + 1024;
+
+struct Epi {
+  void* C;
+  const void* bias;
+  long long ldc;
+  float alpha;
+  int out_fp32, accumulate;
+};
+
+ATB_DEVICE uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+ATB_DEVICE void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `ptr` (a shared::cta pointer of this CTA) in CTA `rank` of the cluster
+ATB_DEVICE uint32_t map_to_cta(const void* ptr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(ptr)), "r"(rank));
+  return r;
+}
+// TMA load into this CTA's shared memory whose completion is counted on a barrier given by its
+// shared::cluster address (the leader's).
+ATB_DEVICE void tma_load_2d_pair(void* smem_dst, const CUtensorMap* tm, uint32_t bar_cluster_addr, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], "
+      "[%2];" ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+ATB_DEVICE void mbar_arrive_remote(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(192, 1)
+gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Epi ep, int M,
+                      int N, int K, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + BAR_OFF);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  // both CTAs of a pair read the same word, so they take the same decision
+  const bool skip = status != nullptr && *reinterpret_cast<volatile int*>(status) != 0;
+
+  const int tiles_m = (M + 2 * BM - 1) / (2 * BM);
+  const int tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = skip ? 0 : tiles_m * tiles_n;
+  const int num_kb = (K + BK - 1) / BK;
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+  constexpr int BAND = 8;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    mbar_init(&tfull[0], 1);
+    mbar_init(&tfull[1], 1);
+    mbar_init(&tempty[0], 8);
+    mbar_init(&tempty[1], 8);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc<2>(tmem_slot, 512);
+    tmem_relinquish<2>();
+  }
+  tc_fence_before();
+  cluster_sync_all();  // barriers of both CTAs initialised and visible before any remote arrive
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto tile_coords = [&](int tile, int& m0, int& n0) {
+    const int band_tiles = BAND * tiles_n;
+    const int band = tile / band_tiles;
+    const int rem = tile - band * band_tiles;
+    const int rows_in_band = min(BAND, tiles_m - band * BAND);
+    const int tn = rem / rows_in_band;
+    const int tm = band * BAND + (rem - tn * rows_in_band);
+    m0 = tm * 2 * BM;
+    n0 = tn * BN;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int tile = cluster_id; tile < num_tiles; tile += num_clusters) {
+        int m0, n0;
+        tile_coords(tile, m0, n0);
+        const int am0 = m0 + (int)rank * BM;   // this CTA's rows of A
+        const int bn0 = n0 + (int)rank * BNH;  // this CTA's rows of B
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, status)) goto producer_done;
+          if (leader) mbar_expect_tx(&full[s], 2 * (A_BYTES + B_BYTES));
+          const uint32_t bar = map_to_cta(&full[s], 0);
+          uint8_t* a_dst = sA + s * A_BYTES;
+          uint8_t* b_dst = sB + s * B_BYTES;
+          if constexpr (!A_MN) {
+            tma_load_2d_pair(a_dst, &tmA, bar, kb * BK, am0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(a_dst + j * 8192, &tmA, bar, am0 + j * 64, kb * BK);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d_pair(b_dst, &tmB, bar, kb * BK, bn0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BNH / 64; ++j) tma_load_2d_pair(b_dst + j * 8192, &tmB, bar, bn0 + j * 64, kb * BK);
+          }
+        }
+      }
+    }
+  producer_done:;
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = umma_idesc(2 * BM, BN, 1, 1, A_MN, B_MN);
+      uint32_t it = 0;
+      int local = 0;
+      for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_ph = (local >> 1) & 1;
+        if (!mbar_wait(&tempty[acc], acc_ph ^ 1, abort_flag, status)) goto mma_done;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full[s], ph, abort_flag, status)) goto mma_done;
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + s * A_BYTES);
+          const uint32_t b_addr = smem_u32(sB + s * B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t adesc = A_MN ? umma_desc_sw128(a_addr + k * 2048, 8192, 1024)
+                                        : umma_desc_sw128(a_addr + k * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? umma_desc_sw128(b_addr + k * 2048, 8192, 1024)
+                                        : umma_desc_sw128(b_addr + k * 32, 16, 1024);
+            umma_f16<2>(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit_cg2(smem_u32(&empty[s]));
+          umma_commit_cg2(map_to_cta(&empty[s], 1));
+        }
+        umma_commit_cg2(smem_u32(&tfull[acc]));
+        umma_commit_cg2(map_to_cta(&tfull[acc], 1));
+      }
+    }
+  mma_done:;
+  } else {
+    const int q = warp & 3;
+    int local = 0;
+    const uint32_t tempty_leader[2] = {map_to_cta(&tempty[0], 0), map_to_cta(&tempty[1], 0)};
+    for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++local) {
+      int m0, n0;
+      tile_coords(tile, m0, n0);
+      const int acc = local & 1;
+      const uint32_t acc_ph = (local >> 1) & 1;
+      if (!__all_sync(0xffffffffu, mbar_wait(&tfull[acc], acc_ph, abort_flag, status))) break;
+      tc_fence_after();
+      const int row = m0 + (int)rank * BM + q * 32 + lane;
+      const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_addr + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row < M && col0 < N) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * ep.alpha;
+          if (ep.bias != nullptr) {
+            const __nv_bfloat16* bias = reinterpret_cast<const __nv_bfloat16*>(ep.bias);
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < N) v[i] += __bfloat162float(bias[col0 + i]);
+          }
+          if (ep.out_fp32) {
+            float* crow = reinterpret_cast<float*>(ep.C) + (long long)row * ep.ldc + col0;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              if (col0 + i < N) {
+                float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                if (ep.accumulate) {
+                  const float4 old = *reinterpret_cast<const float4*>(crow + i);
+                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                *reinterpret_cast<float4*>(crow + i) = o;
+              }
+            }
+          } else {
+            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(ep.C) + (long long)row * ep.ldc + col0;
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              if (col0 + i < N) {
+                if (ep.accumulate) {
+                  const uint4 old = *reinterpret_cast<const uint4*>(crow + i);
+                  const float2 o0 = unpack_bf16x2(old.x), o1 = unpack_bf16x2(old.y), o2 = unpack_bf16x2(old.z),
+                               o3 = unpack_bf16x2(old.w);
+                  v[i] += o0.x; v[i + 1] += o0.y; v[i + 2] += o1.x; v[i + 3] += o1.y;
+                  v[i + 4] += o2.x; v[i + 5] += o2.y; v[i + 6] += o3.x; v[i + 7] += o3.y;
+                }
+                uint4 o;
+                o.x = pack_bf16x2(v[i], v[i + 1]);
+                o.y = pack_bf16x2(v[i + 2], v[i + 3]);
+                o.z = pack_bf16x2(v[i + 4], v[i + 5]);
+                o.w = pack_bf16x2(v[i + 6], v[i + 7]);
+                *reinterpret_cast<uint4*>(crow + i) = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_remote(tempty_leader[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  // neither CTA may leave (or free tensor memory) while its partner can still signal its barriers
+  // or while the leader's MMAs can still write into the partner's tensor memory
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc<2>(tmem_base, 512);
+  }
+}
+
+int g_sms = 0;
+int sm_count() {
+  if (g_sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (g_sms <= 0) g_sms = 148;
+  }
+  return g_sms;
+}
+
+template <bool A_MN, bool B_MN>
+int launch(const void* A, const void* B, const Epi& ep, int M, int N, int K, long long lda, long long ldb,
+           int max_ctas, cudaStream_t stream, int* status) {
+  CUtensorMap tmA, tmB;
+  bool ok;
+  if (!A_MN)
+    ok = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda, BM, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  else
+    ok = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, lda, BK, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (!ok) return -2;
+  if (!B_MN)
+    ok = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb, BNH, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+  else
+    ok = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb, BK, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (!ok) return -3;
+  auto kern = gemm_bf16_2cta_kernel<A_MN, B_MN>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL) != cudaSuccess) return -4;
+    attr_set = true;
+  }
+  const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+  int clusters = sm_count() / 2;
+  if (tiles < clusters) clusters = tiles;
+  if (max_ctas > 0 && clusters > max_ctas / 2) clusters = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * clusters, 1, 1);
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = SMEM_TOTAL;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, ep, M, N, K, status);
+  return e == cudaSuccess ? 0 : -5;
+}
+
+}  // namespace
+
+// Same arguments as atb_gemm_bf16 (gemm_bf16.cu) minus the tile choice. Best for M, N >= 256.
+extern "C" int atb_gemm_bf16_2cta(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
+                                  long long lda, long long ldb, long long ldc, int a_mn_major, int b_mn_major,
+                                  int out_fp32, int accumulate, float alpha, int max_ctas, void* stream, int* status) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((N & 7) || (lda & 7) || (ldb & 7) || (ldc & 3) || (!out_fp32 && (ldc & 7))) return -1;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
+    return -1;
+  Epi ep{C, bias, ldc, alpha, out_fp32, accumulate};
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (!a_mn_major && !b_mn_major) return launch<false, false>(A, B, ep, M, N, K, lda, ldb, max_ctas, st, status);
+  if (!a_mn_major && b_mn_major) return launch<false, true>(A, B, ep, M, N, K, lda, ldb, max_ctas, st, status);
+  if (a_mn_major && b_mn_major) return launch<true, true>(A, B, ep, M, N, K, lda, ldb, max_ctas, st, status);
+  return launch<true, false>(A, B, ep, M, N, K, lda, ldb, max_ctas, st, status);
+}

@@ -110,23 +110,48 @@ def cross_entropy(logits: torch.Tensor, labels: torch.Tensor, ignore_index: int 
                                float(lse_square_scale), inplace_backward, process_group)
 
 
-def _vocab_parallel_reference(logits, labels, ignore_index, smoothing, z, group):
-    """Differentiable PyTorch evaluation of the vocabulary-parallel loss (CPU / oracle path)."""
-    from torch.distributed.nn.functional import all_reduce as ar
+class _VocabParallelRef(torch.autograd.Function):
+    """PyTorch evaluation of the vocabulary-parallel loss (CPU / oracle path). The forward combines
+    the ranks' pieces with all-reduces; the backward is purely local, like the kernel's:
+    ``dlogits = dloss * (p (1 + 2 z lse) - (1 - eps) onehot - eps / V)`` on this rank's slice."""
 
-    world, rank = dist.get_world_size(group), dist.get_rank(group)
-    V = logits.shape[1]
-    lf = logits.float()
-    gmax = lf.max(dim=-1).values.detach()
-    dist.all_reduce(gmax, op=dist.ReduceOp.MAX, group=group)
-    sumexp = ar((lf - gmax[:, None]).exp().sum(-1), group=group)
-    lse = gmax + sumexp.log()
-    local = labels - rank * V
-    inside = (local >= 0) & (local < V) & (labels != ignore_index)
-    ll = torch.where(inside, lf.gather(1, local.clamp(0, V - 1)[:, None])[:, 0], torch.zeros_like(lse))
-    ll = ar(ll, group=group)
-    loss = (lse - ll) * (1.0 - smoothing)
-    if smoothing > 0:
-        loss = loss + smoothing * (lse - ar(lf.sum(-1), group=group) / (V * world))
-    loss = loss + z * lse * lse
-    return torch.where(labels != ignore_index, loss, torch.zeros_like(loss))
+    @staticmethod
+    def forward(ctx, logits, labels, ignore_index, smoothing, z, group):
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        V = logits.shape[1]
+        lf = logits.float()
+        gmax = lf.max(dim=-1).values
+        dist.all_reduce(gmax, op=dist.ReduceOp.MAX, group=group)
+        sumexp = (lf - gmax[:, None]).exp().sum(-1)
+        dist.all_reduce(sumexp, group=group)
+        lse = gmax + sumexp.log()
+        local = labels - rank * V
+        inside = (local >= 0) & (local < V) & (labels != ignore_index)
+        ll = torch.where(inside, lf.gather(1, local.clamp(0, V - 1)[:, None])[:, 0], torch.zeros_like(lse))
+        tot = lf.sum(-1)
+        packed = torch.stack([ll, tot])
+        dist.all_reduce(packed, group=group)
+        ll, tot = packed[0], packed[1]
+        loss = (lse - ll) * (1.0 - smoothing)
+        if smoothing > 0:
+            loss = loss + smoothing * (lse - tot / (V * world))
+        loss = loss + z * lse * lse
+        valid = labels != ignore_index
+        ctx.save_for_backward(logits, lse, local, inside, valid)
+        ctx.cfg = (smoothing, z, V * world)
+        return torch.where(valid, loss, torch.zeros_like(loss))
+
+    @staticmethod
+    def backward(ctx, dloss):
+        logits, lse, local, inside, valid = ctx.saved_tensors
+        smoothing, z, v_total = ctx.cfg
+        g = torch.where(valid, dloss.float(), torch.zeros_like(lse))
+        p = (logits.float() - lse[:, None]).exp()
+        d = p * (g * (1.0 + 2.0 * z * lse))[:, None] - (g * smoothing / v_total)[:, None]
+        idx = local.clamp(0, logits.shape[1] - 1)[:, None]
+        d.scatter_add_(1, idx, (-(g * (1.0 - smoothing)) * inside.float())[:, None])
+        return d.to(logits.dtype), None, None, None, None, None
+
+
+def _vocab_parallel_reference(logits, labels, ignore_index, smoothing, z, group):
+    return _VocabParallelRef.apply(logits, labels, ignore_index, float(smoothing), float(z), group)

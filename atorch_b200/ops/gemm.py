@@ -15,11 +15,16 @@ Reference counterpart: cuBLAS behind ``nn.Linear`` (atorch/modules/distributed_m
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
 
 from .. import _lib
+
+
+# CTA-pair kernel (tcgen05 cta_group::2, 256x256 tiles) for problems with M, N >= 256
+PAIR_KERNEL_DEFAULT = os.environ.get("ATB_GEMM_PAIR", "1") == "1"
 
 
 def _pitch(t: torch.Tensor) -> int:
@@ -53,6 +58,7 @@ def gemm(
     bias: Optional[torch.Tensor] = None,
     tile_n: int = 0,
     max_ctas: int = 0,
+    kernel: str = "auto",
 ) -> torch.Tensor:
     """``out[M,N] (+)= alpha * A[M,K] @ B[N,K]^T (+ bias[N])``.
 
@@ -74,6 +80,17 @@ def gemm(
         b = b.contiguous()
     assert out.stride(-1) == 1 and out.dtype in (torch.bfloat16, torch.float32)
     L = _lib.lib()
+    use_pair = kernel == "2cta" or (kernel == "auto" and PAIR_KERNEL_DEFAULT and M >= 256 and N >= 256 and tile_n == 0)
+    if use_pair:
+        rc = L.atb_gemm_bf16_2cta(
+            _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias),
+            ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
+            ctypes.c_longlong(_pitch(a)), ctypes.c_longlong(_pitch(b)), ctypes.c_longlong(_pitch(out)),
+            ctypes.c_int(int(a_mn)), ctypes.c_int(int(b_mn)),
+            ctypes.c_int(int(out.dtype == torch.float32)), ctypes.c_int(int(accumulate)),
+            ctypes.c_float(alpha), ctypes.c_int(max_ctas), _lib.stream_ptr(), _lib.ptr(_lib.status_word(a.device)))
+        _lib.check(rc, f"atb_gemm_bf16_2cta M={M} N={N} K={K}")
+        return out
     rc = L.atb_gemm_bf16(
         _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias),
         ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),

@@ -29,8 +29,10 @@ def test_gemm_layouts(M, N, K, a_mn, b_mn):
     b = _mk(K, N) if b_mn else _mk(N, K)
     ref = gemm_reference(a, b, a_mn, b_mn, out_dtype=torch.float32)
     for tile_n in (128, 256):
-        out = gemm(a, b, a_mn=a_mn, b_mn=b_mn, tile_n=tile_n)
+        out = gemm(a, b, a_mn=a_mn, b_mn=b_mn, tile_n=tile_n, kernel="1cta")
         _check(out, ref, K)
+    out = gemm(a, b, a_mn=a_mn, b_mn=b_mn, kernel="2cta")
+    _check(out, ref, K)
 
 
 def test_gemm_fp32_out_accumulate_alpha_bias():
@@ -69,6 +71,12 @@ def test_gemm_many_tiles_persistent():
     _check(out[idx], ref, K)
     out2 = gemm(a, b, max_ctas=7)
     assert torch.equal(out, out2)
+    out3 = gemm(a, b, kernel="1cta")
+    _check(out3[idx], ref, K)
+    c0 = torch.randn(M, N, device="cuda")
+    o4 = c0.clone()
+    gemm(a, b, out=o4, accumulate=True, alpha=0.5, kernel="2cta")
+    _check(o4[idx], c0[idx] + 0.5 * ref, K)
 
 
 def test_linear_autograd_matches_torch():

@@ -1,0 +1,122 @@
+"""Tensor-parallel layers, mappings, vocabulary-parallel loss and manual sharding on CPU/gloo (world 2)."""
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from tests.dist_utils import run_distributed
+
+
+def _layers(rank, world):
+    from atorch_b200.distributed import distributed as D
+    from atorch_b200.modules.distributed_modules import (ColumnParallelLinear, RowParallelLinear,
+                                                         VocabParallelEmbedding, vocab_parallel_cross_entropy)
+
+    D.create_parallel_group(([("tensor", world)], None))
+    torch.manual_seed(0)
+    fc1, fc2 = nn.Linear(16, 32), nn.Linear(32, 16)
+    emb = nn.Embedding(20, 16)
+    x_ids = torch.randint(0, 20, (3, 6))
+    ref_h = emb(x_ids)
+    ref = fc2(torch.relu(fc1(ref_h)))
+    ref.sum().backward()
+    for sp in (False, True):
+        col = ColumnParallelLinear(orig_module=fc1, sequence_parallel=sp)
+        row = RowParallelLinear(orig_module=fc2, sequence_parallel=sp)
+        vemb = VocabParallelEmbedding(orig_module=emb)
+        h = vemb(x_ids)
+        assert torch.allclose(h, ref_h, atol=1e-6)
+        if sp:          # activations are sharded along the sequence dim outside the block
+            out = row(torch.relu(col(h.chunk(world, dim=1)[rank].contiguous())))
+            assert torch.allclose(out, ref.chunk(world, dim=1)[rank], atol=1e-5)
+            out.sum().backward()
+            # every rank back-propagated only its sequence shard of the loss: weight grads are partial sums
+            for t, full in ((col.weight.grad, fc1.weight.grad.chunk(world, 0)[rank]),
+                            (row.weight.grad, fc2.weight.grad.chunk(world, 1)[rank])):
+                assert torch.allclose(t, full, atol=1e-5)
+            continue
+        out = row(torch.relu(col(h)))
+        assert torch.allclose(out, ref, atol=1e-5)
+        out.sum().backward()
+        assert torch.allclose(col.weight.grad, fc1.weight.grad.chunk(world, 0)[rank], atol=1e-5)
+        assert torch.allclose(row.weight.grad, fc2.weight.grad.chunk(world, 1)[rank], atol=1e-5)
+        assert torch.allclose(vemb.weight.grad, emb.weight.grad.chunk(world, 0)[rank], atol=1e-5)
+    # fused q|k|v style: stride 3
+    qkv = nn.Linear(8, 12, bias=False)
+    c3 = ColumnParallelLinear(orig_module=qkv, stride=3, gather_output=False)
+    xx = torch.randn(2, 8)
+    full = qkv(xx).view(2, 3, 4)
+    mine = c3(xx).view(2, 3, 2)
+    assert torch.allclose(mine, full[:, :, rank * 2:(rank + 1) * 2], atol=1e-6)
+    # vocabulary-parallel cross entropy vs dense
+    logits = torch.randn(7, 20, requires_grad=True)
+    labels = torch.randint(0, 20, (7,))
+    labels[2] = -100
+    dense = nn.functional.cross_entropy(logits, labels, reduction="none", ignore_index=-100)
+    dense.sum().backward()
+    local = logits.detach()[:, rank * 10:(rank + 1) * 10].clone().requires_grad_()
+    lp = vocab_parallel_cross_entropy(local, labels)
+    assert torch.allclose(lp, dense, atol=1e-5)
+    lp.sum().backward()
+    assert torch.allclose(local.grad, logits.grad[:, rank * 10:(rank + 1) * 10], atol=1e-5)
+
+
+def test_tp_layers_gloo():
+    run_distributed(_layers, world=2)
+
+
+def _mappings(rank, world):
+    from atorch_b200.modules.distributed_modules import (collect_and_reshard, gather_from_group, scatter_to_group,
+                                                         split_first_dim_gather_last_dim,
+                                                         split_last_dim_gather_first_dim)
+
+    full = torch.arange(24, dtype=torch.float32).view(4, 6)
+    mine = scatter_to_group(full.clone().requires_grad_(), None, dim=1)
+    assert torch.equal(mine, full[:, rank * 3:(rank + 1) * 3])
+    assert torch.equal(gather_from_group(mine, None, dim=1), full)
+    rows = full.chunk(world, 0)[rank].contiguous()                 # [2, 6] row shard
+    swapped = split_last_dim_gather_first_dim(rows, None)          # -> [4, 3] column shard
+    assert torch.equal(swapped, full[:, rank * 3:(rank + 1) * 3])
+    assert torch.equal(split_first_dim_gather_last_dim(swapped, None), rows)
+    assert torch.equal(collect_and_reshard(rows, 0, 1, None), full[:, rank * 3:(rank + 1) * 3])
+
+
+def test_mappings_gloo():
+    run_distributed(_mappings, world=2)
+
+
+class _Block(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.wte = nn.Embedding(16, 8)
+        self.c_fc = nn.Linear(8, 32)
+        self.c_proj = nn.Linear(32, 8)
+        self.drop = nn.Dropout(0.0)
+
+    def forward(self, ids):
+        return self.drop(self.c_proj(torch.relu(self.c_fc(self.wte(ids)))))
+
+
+def _manual(rank, world):
+    from atorch_b200.distributed import distributed as D
+    from atorch_b200.modules.distributed_modules import (ColumnParallelLinear, RowParallelLinear,
+                                                         VocabParallelEmbedding)
+    from atorch_b200.tensor_parallel.manual_tp import TPInfo, tp_manual_shard
+
+    D.create_parallel_group(([("tensor", world)], None))
+    torch.manual_seed(0)
+    m = _Block()
+    ids = torch.randint(0, 16, (2, 4))
+    ref = m(ids)
+    info = TPInfo()
+    info.shard_col("c_fc")
+    info.shard_row("c_proj")
+    info.shard_vocab("wte")
+    info.replic_drop("drop")
+    tp_manual_shard(m, info)
+    assert isinstance(m.c_fc, ColumnParallelLinear) and isinstance(m.c_proj, RowParallelLinear)
+    assert isinstance(m.wte, VocabParallelEmbedding) and info.is_vocab_parallelled()
+    assert torch.allclose(m(ids), ref, atol=1e-5)
+
+
+def test_manual_tp_gloo():
+    run_distributed(_manual, world=2)
