@@ -336,6 +336,13 @@ ATB_DEVICE float block_max(float v, float* red) {
   return t;
 }
 
+// 2^x on the special-function unit (ex2.approx.ftz): -inf -> 0, relative error ~2^-22
+ATB_DEVICE float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 ATB_DEVICE uint32_t pack_bf16x2(float a, float b) {
   __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&h);

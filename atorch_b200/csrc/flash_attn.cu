@@ -271,7 +271,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_ld_32x32(lane_addr + sb * BKV + half * 64 + cc * 32, t);
         tmem_ld_wait();
 #pragma unroll
-        for (int c = 0; c < 32; ++c) sv[cc * 32 + c] = __uint_as_float(t[c]) * p.scale_log2;
+        for (int c = 0; c < 32; ++c) sv[cc * 32 + c] = __uint_as_float(t[c]);
       }
       tc_fence_before();
       __syncwarp();
@@ -294,14 +294,18 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (lane == 0) mbar_arrive(x_bar);
       if (!__all_sync(0xffffffffu, mbar_wait(x_bar, j & 1, abort_flag, p.status))) { ok = false; break; }
       mx = fmaxf(mx, rm[(half ^ 1) * 128 + r]);
+      // m_run / mx are raw (unscaled) score maxima; the softmax scale (> 0) is folded into the
+      // exponent: p = 2^(s * c - m * c), one FFMA + one EX2 per element
       const float m_new = fmaxf(m_run, mx);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = exp2f(m_run - m_use);  // m_run = -inf -> 0
+      const float alpha = fast_exp2((m_run - m_use) * p.scale_log2);  // m_run = -inf -> 0
+      const float neg_ms = -m_use * p.scale_log2;
       float lsum = 0.f;
       uint32_t pk[32];
 #pragma unroll
       for (int c = 0; c < 64; c += 2) {
-        const float p0 = exp2f(sv[c] - m_use), p1 = exp2f(sv[c + 1] - m_use);
+        const float p0 = fast_exp2(fmaf(sv[c], p.scale_log2, neg_ms));
+        const float p1 = fast_exp2(fmaf(sv[c + 1], p.scale_log2, neg_ms));
         lsum += p0 + p1;
         pk[c >> 1] = pack_bf16x2(p0, p1);
       }
@@ -346,7 +350,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       if (half == 0)
         p.lse[((long long)b * p.Hq + h) * p.Sq + i] =
-            l_tot > 0.f ? (m_run + log2f(l_tot)) * 0.6931471805599453f : -INFINITY;
+            l_tot > 0.f ? (m_run * p.scale_log2 + log2f(l_tot)) * 0.6931471805599453f : -INFINITY;
     }
   }
 

@@ -243,8 +243,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const int c0 = kv0 + half * 64 + cc * 32;
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
-          float p0 = exp2f(__uint_as_float(ts[c]) * p.scale_log2 - lse2);
-          float p1 = exp2f(__uint_as_float(ts[c + 1]) * p.scale_log2 - lse2);
+          float p0 = fast_exp2(fmaf(__uint_as_float(ts[c]), p.scale_log2, -lse2));
+          float p1 = fast_exp2(fmaf(__uint_as_float(ts[c + 1]), p.scale_log2, -lse2));
           if (!row_full) {
             if (!valid || c0 + c < lo || c0 + c >= hi) p0 = 0.f;
             if (!valid || c0 + c + 1 < lo || c0 + c + 1 >= hi) p1 = 0.f;
