@@ -58,6 +58,9 @@ class ShardingConfig:
     param_init_fn: Optional[Callable[[nn.Module], None]] = None
     device: Optional[torch.device] = None
     checkpoint_units: bool = False                           # recompute each non-root unit in backward
+    fused_comm: bool = True                                  # peer-memory reduce-scatter kernels when possible
+    optimizer_in_backward: bool = False                      # fuse the AdamW step into the reduce-scatter
+    comm_blocks: int = 32                                    # CTAs a fused collective may occupy
     autocast: bool = True                                    # run forward under autocast(param_dtype)
 
 
@@ -263,6 +266,35 @@ class FSDPEngine:
         for u in self.units:
             self._init_unit_storage(u)
         self._wrap_unit_forwards()
+        self._setup_fused_comm()
+
+    def _setup_fused_comm(self) -> None:
+        """Symmetric gradient buffers for the fused reduce-scatter kernels: two rotating buffers of
+        the largest non-root unit plus one for the root unit (which stays live for the whole backward)."""
+        self.fused = False
+        self._fused_opt = None
+        if not (self.cfg.fused_comm and self.on_cuda and 1 < self.world <= 8 and self.replicas == 1
+                and self.compute_dtype in (torch.bfloat16, torch.float32)):
+            return
+        from . import symm
+
+        if not symm.available():
+            return
+        try:
+            non_root = [u.padded_numel for u in self.units if not u.is_root and u.has_trainable]
+            self._gbufs = [symm.SymmetricBuffer(max(non_root), self.compute_dtype, self.group, self.device)
+                           for _ in range(2)] if non_root else []
+            root = self.units[-1]
+            self._root_gbuf = symm.SymmetricBuffer(root.padded_numel, self.compute_dtype, self.group, self.device) \
+                if root.has_trainable else None
+        except Exception as e:   # symmetric memory unavailable on this system: keep the NCCL path
+            import logging
+
+            logging.getLogger("atorch.logger").warning("fused collectives disabled: %s", e)
+            return
+        self._gbuf_events = [None, None]
+        self._gbuf_rr = 0
+        self.fused = True
 
     def _materialize_meta(self, unit_set) -> None:
         """Give meta-device parameters real storage on the target device, module by module."""
@@ -409,7 +441,21 @@ class FSDPEngine:
     def _alloc_grads(self, u: FlatUnit) -> None:
         if u.full_grad is not None or not u.has_trainable:
             return
-        u.full_grad = torch.zeros(u.padded_numel, dtype=self.compute_dtype, device=self.device)
+        if self.fused:
+            if u.is_root:
+                buf, u._gbuf_idx = self._root_gbuf, -1
+            else:
+                idx = self._gbuf_rr % 2
+                self._gbuf_rr += 1
+                buf, u._gbuf_idx = self._gbufs[idx], idx
+                if self._gbuf_events[idx] is not None:   # the previous reduce-scatter out of this buffer
+                    torch.cuda.current_stream(self.device).wait_event(self._gbuf_events[idx])
+                    self._gbuf_events[idx] = None
+            u._gbuf = buf
+            u.full_grad = buf.tensor[: u.padded_numel]
+            u.full_grad.zero_()
+        else:
+            u.full_grad = torch.zeros(u.padded_numel, dtype=self.compute_dtype, device=self.device)
         for v, p in zip(u.views(u.full_grad), u.params):
             if p.requires_grad:
                 p.grad = v
@@ -452,6 +498,9 @@ class FSDPEngine:
                 dst.add_(g)
             u.fresh = False
             return
+        if self.fused:
+            self._reduce_grads_fused(u, dst, scale)
+            return
         rd = g if g.dtype == self.reduce_dtype else g.to(self.reduce_dtype)
         out = torch.empty(u.shard_numel, dtype=self.reduce_dtype, device=self.device)
         if self.comm_stream is not None:
@@ -476,6 +525,27 @@ class FSDPEngine:
             rd.record_stream(self.comm_stream)
             out.record_stream(self.comm_stream)
             g.record_stream(self.comm_stream)
+        u.fresh = False
+
+    def _reduce_grads_fused(self, u: FlatUnit, dst: torch.Tensor, scale: float) -> None:
+        """One kernel per unit on the communication stream: peers' gradient slices are summed over
+        NVLink in registers and land in the fp32 gradient shard - or, with ``optimizer_in_backward``,
+        go straight through the AdamW update into master / moments / working shard."""
+        cur = torch.cuda.current_stream(self.device)
+        self.comm_stream.wait_stream(cur)
+        buf = u._gbuf
+        with torch.cuda.stream(self.comm_stream):
+            opt = self._fused_opt
+            if opt is not None and opt.in_backward_ready():
+                so = u.shard_offset
+                opt.fused_unit_step(buf, u, so)
+            else:
+                buf.reduce_scatter_into(dst, scale=scale, accumulate=not u.fresh, numel=u.padded_numel,
+                                        max_blocks=self.cfg.comm_blocks)
+            if u._gbuf_idx >= 0:
+                ev = torch.cuda.Event()
+                ev.record(self.comm_stream)
+                self._gbuf_events[u._gbuf_idx] = ev
         u.fresh = False
 
     # ------------------------------------------------------------------------------ root hooks
@@ -797,6 +867,25 @@ class FusedShardedOptimizer:
         self.exp_avg_sq: Optional[torch.Tensor] = None
         self.step_count = 0
         self.state: Dict = {}
+        self._units_stepped = 0
+        if getattr(engine, "fused", False) and engine.cfg.optimizer_in_backward and kind == "adamw" \
+                and max_grad_norm is None:
+            engine._fused_opt = self
+
+    def in_backward_ready(self) -> bool:
+        return self.engine.mixed or self.engine.compute_dtype == torch.float32
+
+    def fused_unit_step(self, buf, u, so: int) -> None:
+        """Reduce-scatter + AdamW of one unit inside the backward pass (called on the communication stream)."""
+        self._ensure_state()
+        eng, pg = self.engine, self.param_groups[0]
+        n = u.shard_numel
+        b1, b2 = pg["betas"]
+        lp = eng.lp_shard[so: so + n] if eng.mixed else None
+        buf.reduce_scatter_adamw(eng.master[so: so + n], self.exp_avg[so: so + n], self.exp_avg_sq[so: so + n], lp,
+                                 pg["lr"], b1, b2, pg["eps"], pg["weight_decay"], self.step_count + 1,
+                                 grad_scale=1.0 / eng.world, numel=u.padded_numel, max_blocks=eng.cfg.comm_blocks)
+        self._units_stepped += 1
 
     def _ensure_state(self):
         if self.exp_avg is None:
@@ -809,6 +898,14 @@ class FusedShardedOptimizer:
     def step(self, closure=None):
         loss = closure() if closure is not None else None
         eng = self.engine
+        if eng.__dict__.get("_fused_opt") is self and self._units_stepped > 0:
+            # every unit was updated by its reduce-scatter kernel during the backward pass
+            self._units_stepped = 0
+            self.step_count += 1
+            if eng.comm_stream is not None:
+                torch.cuda.current_stream(eng.device).wait_stream(eng.comm_stream)
+            eng.invalidate_gathered()
+            return loss
         g = eng.finalize_grads()
         self._ensure_state()
         self.step_count += 1

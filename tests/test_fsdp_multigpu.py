@@ -20,7 +20,7 @@ def _batches(rank, steps=6):
     return [torch.randint(0, 1024, (2, 256), generator=g) for _ in range(steps)]
 
 
-def _build(world_strategy):
+def _build(world_strategy, fsdp_extra=None):
     from atorch_b200.auto import auto_accelerate
     from atorch_b200.models.llama import LlamaDecoderLayer, LlamaModel
 
@@ -28,15 +28,15 @@ def _build(world_strategy):
     model = LlamaModel(_cfg())
     ok, res, _ = auto_accelerate(
         model, torch.optim.AdamW, loss_func=lambda b, o: o[0], optim_args={"lr": 1e-3, "weight_decay": 0.0},
-        load_strategy=world_strategy + [("fsdp", {"atorch_wrap_cls": (LlamaDecoderLayer,)}),
+        load_strategy=world_strategy + [("fsdp", dict({"atorch_wrap_cls": (LlamaDecoderLayer,)}, **(fsdp_extra or {}))),
                                         ("amp_native", {"dtype": torch.bfloat16}),
                                         ("checkpoint", {"wrap_class": (LlamaDecoderLayer,)})])
     assert ok
     return res
 
 
-def _train_rank(rank, world, out_file):
-    res = _build(["parallel_mode"])
+def _train_rank(rank, world, out_file, fsdp_extra=None):
+    res = _build(["parallel_mode"], fsdp_extra)
     dev = torch.device("cuda", rank)
     losses = []
     for ids in _batches(rank):
@@ -54,9 +54,14 @@ def _train_rank(rank, world, out_file):
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_fsdp_two_gpus_tracks_single_gpu(tmp_path):
-    f = str(tmp_path / "l.pt")
-    run_distributed(_train_rank, world=2, args=(f,), backend="nccl", timeout=300)
-    multi = torch.load(f)
+    runs = {}
+    for name, extra in (("fused", None), ("nccl", {"fused_comm": False}), ("in_backward", {"optimizer_in_backward": True})):
+        f = str(tmp_path / f"l_{name}.pt")
+        run_distributed(_train_rank, world=2, args=(f, extra), backend="nccl", timeout=300)
+        runs[name] = torch.load(f)
+    multi = runs["fused"]
+    for name in ("nccl", "in_backward"):
+        assert max(abs(x - y) for x, y in zip(multi, runs[name])) < 0.03, (name, multi, runs[name])
     torch.cuda.set_device(0)
     res = _build([])
     single = []
