@@ -4,6 +4,8 @@ import sys
 import pytest
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+os.environ.setdefault("ATORCH_DRYRUN_WARMUP_STEP", "1")
+os.environ.setdefault("ATORCH_DRYRUN_PROFILE_STEP", "2")
 
 
 def pytest_configure(config):

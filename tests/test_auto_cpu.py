@@ -1,0 +1,109 @@
+"""auto_accelerate plumbing on CPU: strategies (list / pickle / file), adjust, search, clip, amp, half."""
+import pickle
+
+import torch
+import torch.nn as nn
+
+from atorch_b200.auto import Strategy, auto_accelerate, get_strategy, save_strategy
+from atorch_b200.auto.analyser import analyse_model
+from atorch_b200.auto.clip_grad_norm import clip_grad_norm
+from atorch_b200.auto.engine.search import BayesianGenerator, combination_candidates
+from atorch_b200.auto.opt_lib import OptimizationLibrary
+
+
+class Block(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.fc = nn.Linear(32, 32)
+
+    def forward(self, x):
+        return torch.relu(self.fc(x)) + x
+
+
+def model():
+    torch.manual_seed(0)
+    return nn.Sequential(nn.Linear(16, 32), Block(), Block(), nn.Linear(32, 4))
+
+
+def data():
+    g = torch.Generator().manual_seed(0)
+    return [(torch.randn(16, generator=g), int(torch.randint(0, 4, (), generator=g))) for _ in range(64)]
+
+
+def loss_func(batch, out):
+    return nn.functional.cross_entropy(out, batch[1])
+
+
+def test_strategy_roundtrip(tmp_path):
+    ok, s = get_strategy(["parallel_mode", ("amp_native", {"dtype": torch.bfloat16}), ("tensor_parallel", None)])
+    assert ok and s.names() == ["parallel_mode", "amp_native", "tensor_parallel"]
+    assert s.get("tensor_parallel")[2] is True
+    f = tmp_path / "s.pkl"
+    save_strategy(s, str(f))
+    ok, s2 = get_strategy(str(f))
+    assert ok and s2.names() == s.names()
+    ok, s3 = get_strategy(pickle.dumps(s))
+    assert ok and isinstance(s3, Strategy)
+    s.adjust_data_parallel(8)
+    assert s.get_parallel_mode() == (True, ([("data", 8)], None))
+    lib = OptimizationLibrary()
+    assert lib.validate_strategy(s) == (True, [])
+    assert lib.validate_strategy(Strategy([("nope", None, False)]))[0] is False
+    assert set(lib.opts) >= {"zero1", "zero2", "fsdp", "fsdp2", "parallel_mode", "auto_ddp", "amp_native", "fp8",
+                             "tensor_parallel", "module_replace", "checkpoint", "native_dynamo",
+                             "pipeline_parallel", "mixed_parallel", "sequence_parallel", "half",
+                             "deepspeed_3d_parallel"}
+
+
+def test_auto_accelerate_variants():
+    for strat in (["amp_native"], [("half", "bf16")], [("checkpoint", {"wrap_class": (Block,)})],
+                  [("fsdp", {"atorch_wrap_cls": ("Block",)}), ("amp_native", {"dtype": "bf16"})],
+                  ["zero1"], ["module_replace"]):
+        ok, res, best = auto_accelerate(model(), torch.optim.AdamW, data(), loss_func, optim_args={"lr": 1e-2},
+                                        dataloader_args={"batch_size": 16}, load_strategy=strat,
+                                        lr_scheduler_cls=torch.optim.lr_scheduler.StepLR,
+                                        lr_scheduler_args={"step_size": 1, "gamma": 0.9})
+        assert ok, strat
+        losses = []
+        for b in res.dataloader:
+            x = b[0] if res.prepare_input is None else res.prepare_input(b, "cpu")[0]
+            res.optim.zero_grad()
+            l = res.loss_func(b, res.model(x))
+            l.backward()
+            res.optim.step()
+            res.lr_scheduler.step()
+            losses.append(float(l))
+        assert all(v == v for v in losses), strat
+        assert res.optim.param_groups[0]["lr"] < 1e-2
+
+
+def test_search_and_analyse():
+    a = analyse_model(model())
+    assert a["opt_config_submodule_names"] == (Block,) and a["model_params_num"] > 0
+    c = combination_candidates(1, a)
+    assert len(c) >= 6 and all(s.names()[0] == "parallel_mode" for s in c)
+    class TakesBatch(nn.Module):          # model_input_format=None means model(batch)
+        def __init__(self):
+            super().__init__()
+            self.net = model()
+
+        def forward(self, batch):
+            return self.net(batch[0])
+    ok, res, best = auto_accelerate(TakesBatch(), torch.optim.SGD, data(), loss_func, optim_args={"lr": 1e-2},
+                                    dataloader_args={"batch_size": 16}, time_limit=60)
+    assert ok and best is not None and res.model is not None
+    g = BayesianGenerator(max_iter=6)
+    for _ in range(6):
+        combo = g.suggest()
+        if combo is None:
+            break
+        g.observe(combo, float(len([x for x in combo if x])))
+    assert len(g.tried) >= 4
+
+
+def test_clip_grad_norm_plain():
+    m = model()
+    m(torch.randn(8, 16)).sum().backward()
+    n = clip_grad_norm(m, 0.1)
+    after = torch.sqrt(sum(p.grad.pow(2).sum() for p in m.parameters()))
+    assert n > 0.1 and abs(after.item() - 0.1) < 1e-3
