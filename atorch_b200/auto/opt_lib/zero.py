@@ -71,7 +71,7 @@ def build_sharded_model(model_context, cfg: dict, reshard_after_forward: bool = 
         backward_prefetch=bool(cfg.pop("backward_prefetch", True)),
         sync_module_states=cfg.pop("sync_module_states", False),
         param_init_fn=cfg.pop("param_init_fn", None), device=device,
-        checkpoint_units=cfg.pop("checkpoint_units", False), fused_comm=cfg.pop("fused_comm", True),
+        checkpoint_units=cfg.pop("checkpoint_units", False), fused_comm=cfg.pop("fused_comm", False),
         optimizer_in_backward=cfg.pop("optimizer_in_backward", False), comm_blocks=cfg.pop("comm_blocks", 32))
     use_local_sgd = cfg.pop("use_local_sgd", False)
     lsgd = {k: cfg.pop(k, None) for k in ("local_sgd_config", "outer_optim_config", "gta_config")}

@@ -58,7 +58,7 @@ class ShardingConfig:
     param_init_fn: Optional[Callable[[nn.Module], None]] = None
     device: Optional[torch.device] = None
     checkpoint_units: bool = False                           # recompute each non-root unit in backward
-    fused_comm: bool = True                                  # peer-memory reduce-scatter kernels when possible
+    fused_comm: bool = False                                 # peer-memory reduce-scatter kernels instead of NCCL
     optimizer_in_backward: bool = False                      # fuse the AdamW step into the reduce-scatter
     comm_blocks: int = 32                                    # CTAs a fused collective may occupy
     autocast: bool = True                                    # run forward under autocast(param_dtype)

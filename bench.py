@@ -135,7 +135,7 @@ def run_ours(args):
     strategy = [
         ("parallel_mode", ([("data", world)], None)),
         ("fsdp", {"atorch_wrap_cls": (LlamaDecoderLayer,), "forward_prefetch": True, "limit_all_gathers": True,
-                  "sync_module_states": False, "fused_comm": os.environ.get("ATB_FUSED_COMM", "1") == "1",
+                  "sync_module_states": False, "fused_comm": os.environ.get("ATB_FUSED_COMM", "0") == "1",
                   "optimizer_in_backward": os.environ.get("ATB_OPT_IN_BACKWARD", "0") == "1"}),
         ("amp_native", {"dtype": torch.bfloat16}),
         ("checkpoint", {"wrap_class": (LlamaDecoderLayer,), "no_reentrant": True}),

@@ -55,7 +55,8 @@ def _train_rank(rank, world, out_file, fsdp_extra=None):
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_fsdp_two_gpus_tracks_single_gpu(tmp_path):
     runs = {}
-    for name, extra in (("fused", None), ("nccl", {"fused_comm": False}), ("in_backward", {"optimizer_in_backward": True})):
+    for name, extra in (("fused", {"fused_comm": True}), ("nccl", None),
+                        ("in_backward", {"fused_comm": True, "optimizer_in_backward": True})):
         f = str(tmp_path / f"l_{name}.pt")
         run_distributed(_train_rank, world=2, args=(f, extra), backend="nccl", timeout=300)
         runs[name] = torch.load(f)
