@@ -1,0 +1,77 @@
+"""Profiler, timers, loss-spike recorder, meta-init helpers, common utilities (CPU)."""
+import torch
+import torch.nn as nn
+
+from atorch_b200.common.constants import GPUCapability
+from atorch_b200.common.env import EnvSetting
+from atorch_b200.common.log_utils import TimeStats, Timer
+from atorch_b200.common.util_func import data_float_to_dtype, data_to_device, recursively_getattr
+from atorch_b200.utils.loss_spike_utils import TokenLossSpike
+from atorch_b200.utils.meta_model_utils import (build_recorded_module, init_empty_weights_with_disk_offload, is_meta,
+                                                materialize_modules_to_device, record_module_init)
+from atorch_b200.utils.prof import AProfiler
+from atorch_b200.utils.timer import ThroughputTimer
+
+
+def test_profiler_counts_linear_flops():
+    m = nn.Sequential(nn.Linear(8, 16), nn.ReLU(), nn.Linear(16, 4))
+    p = AProfiler(m)
+    p.start_profile()
+    m(torch.randn(5, 8))
+    p.stop_profile()
+    assert p.get_total_flops() == 2 * 5 * (8 * 16 + 16 * 4)
+    assert p.get_total_params() == 8 * 16 + 16 + 16 * 4 + 4
+    assert "Linear" in p.print_model_profile(output_file=None)
+    p.end_profile()
+    assert GPUCapability.peak("NVIDIA B200", "bf16") == 2250.0
+
+
+def test_timers_and_env(monkeypatch):
+    st = TimeStats()
+    with Timer("a", st):
+        pass
+    assert "a" in st.summary()
+    t = ThroughputTimer(batch_size=4, start_step=1, steps_per_output=2, logging_fn=lambda s: None)
+    for _ in range(4):
+        t.start()
+        t.stop()
+    assert t.avg_samples_per_sec() > 0
+    monkeypatch.setenv("MOE_FSDP_PREFETCH_NUM", "3")
+    assert EnvSetting().MOE_FSDP_PREFETCH_NUM == 3
+
+
+def test_loss_spike(tmp_path):
+    ls = TokenLossSpike(str(tmp_path), min_iter=10, min_loss=2.0)
+    assert not ls.save_loss("f.txt", 1.0, 20, "1.0,1.0", "a,b")
+    assert not ls.save_loss("f.txt", 5.0, 5, "5.0", "a")
+    assert ls.save_loss("f.txt", 5.0, 20, "4.0,6.0", "s1,s2")
+    rec = ls.parse("f.txt")
+    assert rec[0]["iter"] == 20 and rec[0]["losses"] == [4.0, 6.0] and rec[0]["sample_infos"] == ["s1", "s2"]
+    n = ls.decode_loss_spike(str(tmp_path / "out.txt"), fetch_sample=lambda s: [1, 2])
+    assert n == 2
+
+
+def test_meta_init_and_record():
+    with init_empty_weights_with_disk_offload():
+        m = nn.Sequential(nn.Linear(4, 4), nn.LayerNorm(4))
+    assert is_meta(m)
+    materialize_modules_to_device(m, "cpu")
+    assert not is_meta(m) and m(torch.randn(2, 4)).shape == (2, 4)
+    undo = record_module_init()
+
+    class Tiny(nn.Module):
+        def __init__(self, d, k=2):
+            super().__init__()
+            self.l = nn.Linear(d, k)
+    t = Tiny(3, k=5)
+    undo()
+    t2 = build_recorded_module(t)
+    assert t2.l.out_features == 5 and t2 is not t
+
+
+def test_util_funcs():
+    b = {"x": torch.ones(2), "y": [torch.ones(1, dtype=torch.int64)]}
+    b2 = data_float_to_dtype(data_to_device(b, "cpu"), torch.bfloat16)
+    assert b2["x"].dtype == torch.bfloat16 and b2["y"][0].dtype == torch.int64
+    m = nn.Sequential(nn.Linear(2, 2))
+    assert recursively_getattr(m, "0.weight") is m[0].weight
