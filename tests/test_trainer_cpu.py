@@ -1,0 +1,84 @@
+"""AtorchTrainer on CPU: training, logging, evaluation with metrics, checkpoint rotation, resume."""
+import os
+
+import torch
+import torch.nn as nn
+
+from atorch_b200.trainer import AtorchArguments, AtorchTrainer, TrainerCallback
+
+
+class Net(nn.Module):
+    def __init__(self):
+        super().__init__()
+        torch.manual_seed(0)
+        self.body = nn.Sequential(nn.Linear(8, 32), nn.ReLU(), nn.Linear(32, 3))
+
+    def forward(self, x, labels=None):
+        logits = self.body(x)
+        out = {"logits": logits}
+        if labels is not None:
+            out["loss"] = nn.functional.cross_entropy(logits, labels)
+        return out
+
+
+def dataset(n=96):
+    g = torch.Generator().manual_seed(1)
+    w = torch.randn(8, 3, generator=g)
+    xs = torch.randn(n, 8, generator=g)
+    return [{"x": x, "labels": (x @ w).argmax()} for x in xs]
+
+
+def args(tmp_path, **kw):
+    d = dict(output_dir=str(tmp_path), per_device_train_batch_size=8, learning_rate=5e-2, num_train_epochs=2,
+             logging_steps=4, save_steps=6, save_total_limit=2, atorch_opt="ddp", atorch_module_replace=False,
+             max_grad_norm=1.0, lr_scheduler_type="cosine", warmup_steps=2, eval_strategy="epoch",
+             metric_for_best_model="accuracy")
+    d.update(kw)
+    return AtorchArguments(**d)
+
+
+def accuracy(p):
+    return {"accuracy": float((p.predictions.argmax(-1) == p.label_ids).mean())}
+
+
+def test_train_eval_rotate_resume(tmp_path):
+    seen = []
+
+    class CB(TrainerCallback):
+        def on_log(self, args, state, control, logs=None, **kw):
+            seen.append(logs)
+    tr = AtorchTrainer(Net(), args(tmp_path), train_dataset=dataset(), eval_dataset=dataset(32),
+                       compute_metrics=accuracy, callbacks=[CB()])
+    state = tr.train()
+    assert state.global_step == 24
+    losses = [l["loss"] for l in state.log_history if "loss" in l]
+    assert losses[-1] < losses[0]
+    evals = [l for l in state.log_history if "eval_accuracy" in l]
+    assert len(evals) == 2 and evals[-1]["eval_accuracy"] > 0.5 and seen
+    ckpts = sorted(d for d in os.listdir(tmp_path) if d.startswith("checkpoint-"))
+    assert len(ckpts) <= 3 and "checkpoint-24" in ckpts
+    for f in ("pytorch_model.bin", "optimizer.pt", "scheduler.pt", "trainer_state.json", "rng_state.pth"):
+        assert os.path.exists(tmp_path / "checkpoint-24" / f), f
+    # resume from step 18 and reach the same final weights
+    ref = {k: v.clone() for k, v in tr.model.state_dict().items()}
+    tr2 = AtorchTrainer(Net(), args(tmp_path, save_steps=1000, eval_strategy="no"), train_dataset=dataset())
+    tr2.train(resume_from_checkpoint=str(tmp_path / "checkpoint-18"))
+    assert tr2.state.global_step == 24
+    for k, v in tr2.model.state_dict().items():
+        assert torch.allclose(v, ref[k], atol=1e-5), k
+
+
+def test_sharded_streaming_checkpoint_and_async(tmp_path):
+    a = args(tmp_path, atorch_opt="fsdp", atorch_wrap_cls=(nn.Linear,), save_by_streaming=True, async_save=True,
+             num_train_epochs=1, eval_strategy="no", metric_for_best_model=None)
+    tr = AtorchTrainer(Net(), a, train_dataset=dataset())
+    tr.train()
+    last = AtorchTrainer.get_last_checkpoint(str(tmp_path))
+    assert last.endswith("checkpoint-12") and os.path.exists(os.path.join(last, "streaming_ckpt", "ckpt_meta"))
+    tr2 = AtorchTrainer(Net(), a, train_dataset=dataset())
+    tr2.lr_scheduler = torch.optim.lr_scheduler.LambdaLR(
+        __import__("atorch_b200.auto.model_context", fromlist=["_SchedulerShim"])._SchedulerShim(tr2.optimizer),
+        lambda s: 1.0)
+    tr2._load_checkpoint(last)
+    for (k, v), (_, v2) in zip(tr.model.state_dict().items(), tr2.model.state_dict().items()):
+        assert torch.equal(v, v2), k
