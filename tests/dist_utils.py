@@ -29,7 +29,7 @@ def _worker(rank, world, port, backend, fn, args, err_q):
         raise
 
 
-def run_distributed(fn, world: int = 2, args=(), backend: str = "gloo", timeout: float = 240.0):
+def run_distributed(fn, world: int = 2, args=(), backend: str = "gloo", timeout: float = 120.0):
     """Spawn ``world`` processes running ``fn(rank, world, *args)``; raises if any rank fails."""
     ctx = mp.get_context("spawn")
     err_q = ctx.SimpleQueue()
@@ -37,8 +37,11 @@ def run_distributed(fn, world: int = 2, args=(), backend: str = "gloo", timeout:
     procs = [ctx.Process(target=_worker, args=(r, world, port, backend, fn, args, err_q)) for r in range(world)]
     for p in procs:
         p.start()
+    import time as _time
+
+    deadline = _time.time() + timeout
     for p in procs:
-        p.join(timeout)
+        p.join(max(0.1, deadline - _time.time()))
     failed = []
     for r, p in enumerate(procs):
         if p.is_alive():
