@@ -1,0 +1,155 @@
+"""Local SGD / EDiT on the sharded engine (hybrid shard: parameters sharded inside a ``zero`` group,
+replicas across a ``data`` group).
+
+After ``local_sgd_warmup_steps`` synchronous steps the gradient all-reduce across replicas is
+switched off, every replica group trains on its own for ``local_sgd_sync_interval`` steps, and then
+the sharded fp32 master weights are synchronised: pseudo-gradient = last synced shard - master shard,
+optional anomaly skip (EWMA of the pseudo-gradient norm over the shard group), reduction over the
+replica group (mean, or linear / GTA reducers, optionally weighted by the norm), clipping, outer
+optimizer step on the last-synced shard, write-back into master and working shards. The state per rank
+is only its shard. ``save_local_sgd_state_dict`` / ``load_local_sgd_state_dict`` persist
+``{"global_step", "outer_optim", "local_sgd_anomaly_detector"}`` per rank.
+(Reference: atorch/local_sgd/FSDP/core/_runtime_utils.py:21-188, _state_dict_utils.py:113-500.)
+"""
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from .anomaly import OnlineDynamicEWMA
+from .configs import GTAConfig, LocalSGDConfig, OuterOptimizerConfig
+from .reducers import build_reducer
+
+
+class ShardedLocalSGD:
+    def __init__(self, engine, cfg: LocalSGDConfig, outer: OuterOptimizerConfig, gta: GTAConfig):
+        self.engine, self.cfg, self.outer_cfg, self.gta = engine, cfg, outer, gta
+        self.replica_group = engine.cfg.replica_group
+        self.replicas = engine.replicas
+        self.global_step = 0
+        self.last_synced = engine.master.detach().clone()
+        temp = cfg.weight_softmax_temperature
+        if cfg.pseudo_gradnorm_reduce and temp is None:
+            temp = 1.0
+        self.reducer = build_reducer(gta, self.replica_group, temp)
+        kw = dict(outer.outer_optim_kwargs)
+        self.fused = None
+        self.outer_optimizer = None
+        self.param = torch.nn.Parameter(self.last_synced)
+        if outer.outer_optim_class is torch.optim.SGD and not kw.get("weight_decay") and not kw.get("dampening"):
+            self.fused = dict(lr=kw.get("lr", 1.0), momentum=kw.get("momentum", 0.0), nesterov=bool(kw.get("nesterov")))
+            self.momentum = torch.zeros_like(self.last_synced)
+        elif outer.outer_optim_class is not None:
+            self.outer_optimizer = outer.outer_optim_class([self.param], **kw)
+        self.outer_steps = 0
+        self.detector = OnlineDynamicEWMA(cfg.ewma_alpha, cfg.ewma_warmup_steps, cfg.ewma_threshold) \
+            if cfg.skip_anomaly else None
+
+    def skip_replica_reduce(self) -> bool:
+        """Replica all-reduce of gradients is needed only during the synchronous warm-up."""
+        return self.global_step >= self.cfg.local_sgd_warmup_steps
+
+    def should_sync(self) -> bool:
+        s, w = self.global_step, self.cfg.local_sgd_warmup_steps
+        return s >= w and (s - w) % self.cfg.local_sgd_sync_interval == 0
+
+    @torch.no_grad()
+    def after_optimizer_step(self) -> None:
+        if self.should_sync() and self.replicas > 1:
+            self.sync()
+        self.global_step += 1
+
+    @torch.no_grad()
+    def sync(self) -> None:
+        eng, cfg = self.engine, self.cfg
+        pg = self.last_synced - eng.master
+        kw = {}
+        if cfg.skip_anomaly or cfg.pseudo_gradnorm_reduce or cfg.clip_pseudo_grad is not None:
+            sq = ops.sum_squares(pg)
+            if eng.world > 1:
+                dist.all_reduce(sq, group=eng.group)
+            norm = sq.sqrt()
+            if cfg.skip_anomaly:
+                if self.detector.is_outlier(norm):
+                    pg.zero_()
+                    norm = norm + 1e6
+                else:
+                    self.detector.update(norm)
+            if cfg.pseudo_gradnorm_reduce:
+                kw["weight"] = -norm
+        if self.reducer is None:
+            pg.div_(self.replicas)
+            dist.all_reduce(pg, group=self.replica_group)
+        else:
+            self.reducer.reduce_tensor(pg, **kw)
+        scale = 1.0
+        if cfg.clip_pseudo_grad is not None:
+            sq = ops.sum_squares(pg)
+            if eng.world > 1:
+                dist.all_reduce(sq, group=eng.group)
+            scale = float(torch.clamp(cfg.clip_pseudo_grad / (sq.sqrt() + 1e-6), max=1.0))
+        if self.fused is not None:
+            f = self.fused
+            ops.outer_sgd_step(self.last_synced, self.momentum, pg, None, f["lr"], f["momentum"], f["nesterov"],
+                               self.outer_steps == 0 or f["momentum"] == 0.0, scale)
+        elif self.outer_optimizer is not None:
+            self.param.grad = pg.mul_(scale)
+            self.outer_optimizer.step()
+            self.param.grad = None
+        else:
+            self.last_synced.sub_(pg)
+        self.outer_steps += 1
+        eng.master.copy_(self.last_synced)
+        eng.sync_working_copy()
+
+    def state_dict(self) -> dict:
+        sd = {"global_step": self.global_step, "outer_steps": self.outer_steps,
+              "last_synced": self.last_synced.detach().cpu()}
+        if self.fused is not None:
+            sd["outer_optim"] = [{"momentum_buffer": self.momentum.cpu(), "rank": self.engine.rank, **self.fused}]
+        elif self.outer_optimizer is not None:
+            sd["outer_optim"] = [dict(self.outer_optimizer.state_dict(), rank=self.engine.rank)]
+        if self.detector is not None:
+            sd["local_sgd_anomaly_detector"] = [self.detector.state_dict()]
+        return sd
+
+    def load_state_dict(self, sd: dict) -> None:
+        self.global_step, self.outer_steps = sd["global_step"], sd.get("outer_steps", 0)
+        self.last_synced.copy_(sd["last_synced"])
+        if self.fused is not None and "outer_optim" in sd:
+            self.momentum.copy_(sd["outer_optim"][0]["momentum_buffer"])
+        elif self.outer_optimizer is not None and "outer_optim" in sd:
+            self.outer_optimizer.load_state_dict({k: v for k, v in sd["outer_optim"][0].items() if k != "rank"})
+        if self.detector is not None and "local_sgd_anomaly_detector" in sd:
+            self.detector.load_state_dict(sd["local_sgd_anomaly_detector"][0])
+
+
+def attach_local_sgd(model, local_sgd_config=None, outer_optim_config=None, gta_config=None) -> ShardedLocalSGD:
+    """Enable local SGD on a sharded model; the optimizers of :mod:`atorch_b200.parallel.fsdp` call
+    ``after_optimizer_step`` through the engine."""
+    eng = model.engine
+    lsgd = ShardedLocalSGD(eng, local_sgd_config or LocalSGDConfig(), outer_optim_config or OuterOptimizerConfig(),
+                           gta_config or GTAConfig())
+    eng.local_sgd = lsgd
+    return lsgd
+
+
+def save_local_sgd_state_dict(model, group=None, rank0_only: bool = False, full_state_dict: bool = False,
+                              cpu_offload: bool = True, save_dir: str = ".", ckpt_name: str = "local_sgd") -> str:
+    lsgd = model.engine.local_sgd
+    os.makedirs(save_dir, exist_ok=True)
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    path = os.path.join(save_dir, f"{ckpt_name}_{rank:02d}.pt")
+    torch.save(lsgd.state_dict(), path)
+    return path
+
+
+def load_local_sgd_state_dict(model, group=None, rank0_only: bool = False, full_state_dict: bool = False,
+                              load_dir: str = ".", ckpt_name: str = "local_sgd") -> None:
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    model.engine.local_sgd.load_state_dict(torch.load(os.path.join(load_dir, f"{ckpt_name}_{rank:02d}.pt"),
+                                                      weights_only=False))

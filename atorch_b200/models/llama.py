@@ -115,22 +115,31 @@ class LlamaDecoderLayer(nn.Module):
         self.gate_up_proj = nn.Linear(h, 2 * config.intermediate_size, bias=False)
         self.down_proj = nn.Linear(config.intermediate_size, h, bias=False)
 
+    @staticmethod
+    def _proj(mod: nn.Module, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Plain linears go straight to the fused GEMM (+ residual epilogue); replaced modules
+        (tensor-parallel, fp8) keep their own forward."""
+        if type(mod) is nn.Linear:
+            return ops.linear(x, mod.weight, mod.bias, residual)
+        y = mod(x)
+        return y if residual is None else residual + y
+
     def forward(self, h: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
                 positions: Optional[torch.Tensor] = None, attn_kwargs: Optional[dict] = None) -> torch.Tensor:
         B, S, _ = h.shape
         d = self.config.head_dim
         x = self.input_layernorm(h)
-        qkv = ops.linear(x, self.qkv_proj.weight)
+        qkv = self._proj(self.qkv_proj, x)
         qkv = ops.rope(qkv, cos, sin, self.n_q + self.n_kv, d, positions)
         qkv = qkv.view(B, S, self.n_q + 2 * self.n_kv, d)
         q = qkv[:, :, : self.n_q]
         k = qkv[:, :, self.n_q: self.n_q + self.n_kv]
         v = qkv[:, :, self.n_q + self.n_kv:]
         a = ops.attention(q, k, v, **(attn_kwargs or {"causal": True}))
-        h = ops.linear(a.reshape(B, S, self.n_q * d), self.o_proj.weight, residual=h)
+        h = self._proj(self.o_proj, a.reshape(B, S, self.n_q * d), h)
         x = self.post_attention_layernorm(h)
-        act = ops.swiglu(ops.linear(x, self.gate_up_proj.weight))
-        h = ops.linear(act, self.down_proj.weight, residual=h)
+        act = ops.swiglu(self._proj(self.gate_up_proj, x))
+        h = self._proj(self.down_proj, act, h)
         return h
 
 

@@ -218,6 +218,7 @@ class FSDPEngine:
         self.grad_shard: Optional[torch.Tensor] = None
         self._shard_params: Optional[List[Tuple[str, nn.Parameter]]] = None
         self.training_step = 0
+        self.local_sgd = None            # set by local_sgd.sharded.attach_local_sgd
         self._build(unit_modules)
 
     # ------------------------------------------------------------------------------------ build
@@ -490,7 +491,8 @@ class FSDPEngine:
         u.full_grad = None
         self._ensure_grad_shard()
         dst = self.grad_shard[u.shard_offset: u.shard_offset + u.shard_numel]
-        scale = 1.0 / (self.world * self.replicas)
+        skip_rep = self.local_sgd is not None and self.local_sgd.skip_replica_reduce()
+        scale = 1.0 / (self.world * (1 if skip_rep else self.replicas))
         if self.world == 1 and self.replicas == 1:
             if u.fresh:
                 dst.copy_(g)
@@ -514,7 +516,7 @@ class FSDPEngine:
                 dist.reduce_scatter_tensor(out, rd, op=dist.ReduceOp.SUM, group=self.group)
             else:
                 out.copy_(rd)
-            if self.replicas > 1:
+            if self.replicas > 1 and not (self.local_sgd is not None and self.local_sgd.skip_replica_reduce()):
                 dist.all_reduce(out, group=self.cfg.replica_group)
             if u.fresh:
                 dst.copy_(out)
@@ -835,6 +837,8 @@ class ShardedOptimizer:
         self.engine.attach_shard_grads()
         r = self.optimizer.step(closure) if closure is not None else self.optimizer.step()
         self.engine.sync_working_copy()
+        if self.engine.local_sgd is not None:
+            self.engine.local_sgd.after_optimizer_step()
         return r
 
     def zero_grad(self, set_to_none: bool = True):
@@ -925,6 +929,8 @@ class FusedShardedOptimizer:
                            pg["weight_decay"], self.step_count, grad_scale_tensor=scale_t,
                            adamw_mode=self.kind == "adamw")
         eng.invalidate_gathered()
+        if eng.local_sgd is not None:
+            eng.local_sgd.after_optimizer_step()
         return loss
 
     def state_dict(self):
