@@ -82,3 +82,25 @@ def test_sharded_streaming_checkpoint_and_async(tmp_path):
     tr2._load_checkpoint(last)
     for (k, v), (_, v2) in zip(tr.model.state_dict().items(), tr2.model.state_dict().items()):
         assert torch.equal(v, v2), k
+
+
+def test_trainer_v2_engine_loop_and_resume(tmp_path):
+    from atorch_b200.trainer import AtorchTrainerV2, AtorchTrainingArgs
+
+    a = AtorchTrainingArgs(output_dir=str(tmp_path), bf16=False, micro_batch_size=4, global_batch_size=8,
+                           learning_rate=5e-2, max_steps=12, logging_steps=4, save_steps=6, seq_length=1,
+                           lr_warmup_iters=2, recompute_granularity=None, async_save=True, spike_loss_ratio=0.5)
+    tr = AtorchTrainerV2(a, Net(), train_dataset=dataset(), eval_dataset=dataset(32), wrap_cls=(nn.Linear,))
+    assert tr.train_engine.num_micro == 2
+    st = tr.train()
+    assert st.global_step == 12 and st.consumed_train_samples == 96
+    losses = [l["loss"] for l in st.log_history if "loss" in l]
+    assert losses[-1] < losses[0]
+    assert tr.evaluate()["eval_loss"] < 2.0
+    assert os.path.exists(tmp_path / "iter_0000012" / "ckpt_meta")
+    tr2 = AtorchTrainerV2(a, Net(), train_dataset=dataset(), wrap_cls=(nn.Linear,))
+    tr2.train(resume_from_checkpoint=str(tmp_path))
+    assert tr2.state.global_step == 12
+    for (k, v), (_, v2) in zip(tr.train_engine.module.state_dict().items(),
+                               tr2.train_engine.module.state_dict().items()):
+        assert torch.equal(v, v2), k
