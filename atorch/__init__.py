@@ -1,0 +1,80 @@
+"""Import-path compatibility namespace: ``import atorch`` / ``from atorch.auto import auto_accelerate`` etc.
+resolve to the modules of ``atorch_b200``. A meta-path finder maps ``atorch.<path>`` to
+``atorch_b200.<path>`` with a small rename table for modules that live under a different name here.
+An ``atorch_addon`` module, if importable, is loaded at import time unless ``ATORCH_DISABLE_ADDON`` is set
+(as in the original package's ``__init__``)."""
+import importlib
+import importlib.abc
+import importlib.util
+import os
+import sys
+
+import atorch_b200
+from atorch_b200 import coworker_size, init_distributed, local_rank, rank, reset_distributed, world_size  # noqa: F401
+
+__version__ = atorch_b200.__version__
+
+_RENAMES = {
+    "atorch.auto.opt_lib.module_replace_optimization": "atorch_b200.auto.opt_lib.module_replace",
+    "atorch.auto.opt_lib.zero_optimization": "atorch_b200.auto.opt_lib.zero",
+    "atorch.auto.opt_lib.amp_optimization": "atorch_b200.auto.opt_lib.amp",
+    "atorch.auto.opt_lib.checkpoint_optimization": "atorch_b200.auto.opt_lib.checkpoint",
+    "atorch.auto.opt_lib.parallel_mode_optimization": "atorch_b200.auto.opt_lib.parallel_mode",
+    "atorch.local_sgd.configs": "atorch_b200.local_sgd.configs",
+    "atorch.local_sgd.DDP": "atorch_b200.local_sgd.averager",
+    "atorch.local_sgd.FSDP": "atorch_b200.local_sgd.sharded",
+    "atorch.modules.moe.topk_gating": "atorch_b200.modules.moe.gating",
+    "atorch.modules.moe.switch_gating": "atorch_b200.modules.moe.gating",
+    "atorch.modules.normalization.layernorm": "atorch_b200.modules.normalization",
+    "atorch.optimizers.low_bit.optim": "atorch_b200.optimizers.low_bit.optim",
+    "atorch.trainer.atorch_trainer_v2": "atorch_b200.trainer.atorch_trainer_v2",
+    "atorch.trainer.fsdp.fsdp_shard_async_saver": "atorch_b200.trainer.fsdp.fsdp_ckpt_saver",
+    "atorch.trainer.fsdp.fsdp_shard_dcp_loader": "atorch_b200.trainer.fsdp.fsdp_ckpt_saver",
+    "atorch.utils.numberic_checker": "atorch_b200.utils.numeric_checker",
+    "atorch.utils.dynamic_profiler": "atorch_b200.utils.dynamic_profiler",
+    "atorch.utils.inspector": "atorch_b200.utils.inspector",
+    "atorch.kernels": "atorch_b200.ops",
+    "atorch.ops.op_builder": "atorch_b200.ops.quantizer",
+    "atorch.ops.quantizer": "atorch_b200.ops.quantizer",
+    "atorch.data.shm_dataloader": "atorch_b200.data.shm_context",
+    "atorch.data.elastic_dataloader": "atorch_b200.data.elastic_dataset",
+    "atorch.data.unshuffled_batch_dataloader": "atorch_b200.data.unordered_dataloader",
+}
+
+
+class _AliasLoader(importlib.abc.Loader):
+    def __init__(self, target):
+        self.target = target
+
+    def create_module(self, spec):
+        return importlib.import_module(self.target)
+
+    def exec_module(self, module):
+        pass
+
+
+class _AliasFinder(importlib.abc.MetaPathFinder):
+    def find_spec(self, fullname, path=None, target=None):
+        if not fullname.startswith("atorch."):
+            return None
+        tgt = _RENAMES.get(fullname, "atorch_b200." + fullname[len("atorch."):])
+        try:
+            if importlib.util.find_spec(tgt) is None:
+                return None
+        except (ImportError, ValueError, AttributeError):
+            return None
+        spec = importlib.util.spec_from_loader(fullname, _AliasLoader(tgt))
+        real = importlib.util.find_spec(tgt)
+        if real is not None and real.submodule_search_locations is not None:
+            spec.submodule_search_locations = list(real.submodule_search_locations)
+        return spec
+
+
+if not any(isinstance(f, _AliasFinder) for f in sys.meta_path):
+    sys.meta_path.insert(0, _AliasFinder())
+
+if not os.environ.get("ATORCH_DISABLE_ADDON"):
+    try:
+        importlib.import_module("atorch_addon")
+    except ImportError:
+        pass
