@@ -15,9 +15,12 @@ using namespace atb;
 //   out[..., :D/2] = x1*cos - x2*sin ; out[..., D/2:] = x2*cos + x1*sin   (rotate_half form)
 // cos/sin: fp32 [S, D/2]; position of token t is pos[t] if pos != nullptr else t % S.
 // sign = +1 forward, -1 backward (the transpose of a rotation is the rotation by -theta).
-__global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restrict__ cosT,
-                            const float* __restrict__ sinT, const int* __restrict__ pos, long long T, int S,
-                            int nheads, int D, long long row_stride, float sign) {
+// When `src` differs from `x` the result is written to `x` from `src` (out of place) and the columns after the
+// rotated heads (`tail8` 16-byte vectors per row, e.g. the v heads) are copied through unchanged.
+__global__ void rope_kernel(__nv_bfloat16* x, const __nv_bfloat16* src,
+                            const float* __restrict__ cosT, const float* __restrict__ sinT,
+                            const int* __restrict__ pos, long long T, int S, int nheads, int D, long long row_stride,
+                            long long src_stride, int tail8, float sign) {
   const int half = D >> 1;
   const int vec_per_head = half >> 3;  // 8 bf16 per 16-byte vector
   const long long total = T * (long long)nheads * vec_per_head;
@@ -29,8 +32,9 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restri
     const long long t = th / nheads;
     const int p = pos ? pos[t] : (int)(t % S);
     __nv_bfloat16* base = x + t * row_stride + (long long)h * D + v * 8;
-    uint4 a = *reinterpret_cast<uint4*>(base);
-    uint4 b = *reinterpret_cast<uint4*>(base + half);
+    const __nv_bfloat16* sbase = src + t * src_stride + (long long)h * D + v * 8;
+    uint4 a = *reinterpret_cast<const uint4*>(sbase);
+    uint4 b = *reinterpret_cast<const uint4*>(sbase + half);
     const float4* c4 = reinterpret_cast<const float4*>(cosT + (long long)p * half + v * 8);
     const float4* s4 = reinterpret_cast<const float4*>(sinT + (long long)p * half + v * 8);
     float4 c0 = c4[0], c1 = c4[1], s0 = s4[0], s1 = s4[1];
@@ -49,6 +53,17 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restri
     }
     *reinterpret_cast<uint4*>(base) = a;
     *reinterpret_cast<uint4*>(base + half) = b;
+  }
+  if (tail8 > 0 && src != x) {
+    const long long ttotal = T * tail8;
+    const long long off = (long long)nheads * D;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < ttotal;
+         i += (long long)gridDim.x * blockDim.x) {
+      const long long t = i / tail8;
+      const int c = (int)(i - t * tail8) * 8;
+      *reinterpret_cast<uint4*>(x + t * row_stride + off + c) =
+          *reinterpret_cast<const uint4*>(src + t * src_stride + off + c);
+    }
   }
 }
 
@@ -160,13 +175,18 @@ inline int grid_for(long long work, int threads) {
 }
 }  // namespace
 
-extern "C" int atb_rope(void* x, const float* cosT, const float* sinT, const int* pos, long long T, int S, int nheads,
-                        int D, long long row_stride, int backward, void* stream) {
+// `src` == nullptr or == x: in place. Otherwise x (pitch row_stride) = rope(src (pitch src_stride)) and the
+// `tail_cols` columns after the rotated heads are copied unchanged.
+extern "C" int atb_rope(void* x, const void* src, const float* cosT, const float* sinT, const int* pos, long long T,
+                        int S, int nheads, int D, long long row_stride, long long src_stride, int tail_cols,
+                        int backward, void* stream) {
   if (T <= 0 || nheads <= 0) return 0;
-  if ((D & 15) || (row_stride & 7)) return -1;
+  if ((D & 15) || (row_stride & 7) || (src_stride & 7) || (tail_cols & 7)) return -1;
   const long long total = T * (long long)nheads * (D >> 4);
-  rope_kernel<<<grid_for(total, 256), 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)x, cosT, sinT, pos, T, S, nheads,
-                                                                      D, row_stride, backward ? -1.f : 1.f);
+  const __nv_bfloat16* s = src ? (const __nv_bfloat16*)src : (const __nv_bfloat16*)x;
+  rope_kernel<<<grid_for(total, 256), 256, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)x, s, cosT, sinT, pos, T, S, nheads,
+                                                                      D, row_stride, src ? src_stride : row_stride,
+                                                                      tail_cols >> 3, backward ? -1.f : 1.f);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 extern "C" int atb_swiglu_fwd(const void* gu, void* out, long long T, int F, long long gu_stride, long long out_stride,

@@ -29,8 +29,9 @@ struct BwdParams {
   const float* lse;    // [B, Hq, Sq]
   const float* delta;  // [B, Hq, Sq]
   float* dq_acc;       // [B, Sq, Hq, HD] fp32, zero-initialised
-  __nv_bfloat16* dk;   // [B, Sk, Hq, HD]
-  __nv_bfloat16* dv;   // [B, Sk, Hq, HD]
+  __nv_bfloat16* dk;   // token-major, head h at columns [h*HD, h*HD+HD) of a row of pitch dkv_stride
+  __nv_bfloat16* dv;
+  long long dkv_stride;
   const int* row_lo;
   const int* row_hi;
   int B, Sq, Sk, Hq, Hkv, causal;
@@ -292,8 +293,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       const bool store = j < p.Sk;
-      __nv_bfloat16* dvrow = p.dv + (((long long)b * p.Sk + j) * p.Hq + h) * HD + half * 64;
-      __nv_bfloat16* dkrow = p.dk + (((long long)b * p.Sk + j) * p.Hq + h) * HD + half * 64;
+      __nv_bfloat16* dvrow = p.dv + ((long long)b * p.Sk + j) * p.dkv_stride + h * HD + half * 64;
+      __nv_bfloat16* dkrow = p.dk + ((long long)b * p.Sk + j) * p.dkv_stride + h * HD + half * 64;
       if (nblk > 0) tc_fence_after();
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
@@ -358,28 +359,34 @@ __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ dO, const _
   }
 }
 
-__global__ void f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long n4) {
+// src: [rows, row_elems] fp32 contiguous -> dst rows of pitch dst_stride (bf16)
+__global__ void f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, long long n4,
+                                   int row_elems4, long long dst_stride) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
     const float4 v = reinterpret_cast<const float4*>(src)[i];
     uint2 o;
     o.x = pack_bf16x2(v.x, v.y);
     o.y = pack_bf16x2(v.z, v.w);
-    reinterpret_cast<uint2*>(dst)[i] = o;
+    const long long row = i / row_elems4;
+    const int c4 = (int)(i - row * row_elems4);
+    *reinterpret_cast<uint2*>(dst + row * dst_stride + c4 * 4) = o;
   }
 }
 
 }  // namespace
 
-// dq_acc must be zero on entry; dq/dk/dv are written. dk, dv are per query head ([B, Sk, Hq, 128]);
-// the caller sums head groups for grouped-query attention. `delta` is scratch [B, Hq, Sq].
+// dq_acc must be zero on entry; dq/dk/dv are written as token-major rows of pitch dq_stride / dkv_stride
+// elements (so they may be slices of one fused [tokens, (Hq + 2 Hq) * 128] gradient buffer). dk, dv are per
+// query head; the caller sums head groups for grouped-query attention. `delta` is scratch [B, Hq, Sq].
 extern "C" int atb_flash_bwd(const void* dout, const void* q, const void* k, const void* v, const void* out,
                              const float* lse, float* delta, float* dq_acc, void* dq, void* dk, void* dv,
                              const int* row_lo, const int* row_hi, int B, int Sq, int Sk, int Hq, int Hkv,
                              long long q_stride, long long k_stride, long long v_stride, long long do_stride,
-                             int causal, float softmax_scale, void* stream, int* status) {
+                             long long dq_stride, long long dkv_stride, int causal, float softmax_scale, void* stream,
+                             int* status) {
   if (B <= 0 || Sq <= 0 || Sk <= 0) return 0;
   if (Hq % Hkv) return -1;
-  if ((q_stride | k_stride | v_stride | do_stride) & 7) return -1;
+  if ((q_stride | k_stride | v_stride | do_stride | dq_stride | dkv_stride) & 7) return -1;
   cudaStream_t st = (cudaStream_t)stream;
   CUtensorMap tmQ, tmdO, tmK, tmV;
   if (!make_tmap_2d(&tmQ, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)B * Sq, (uint64_t)Hq * HD, q_stride, BQ, 64,
@@ -410,6 +417,7 @@ extern "C" int atb_flash_bwd(const void* dout, const void* q, const void* k, con
   }
   BwdParams p;
   p.lse = lse; p.delta = delta; p.dq_acc = dq_acc; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv;
+  p.dkv_stride = dkv_stride;
   p.row_lo = row_lo; p.row_hi = row_hi;
   p.B = B; p.Sq = Sq; p.Sk = Sk; p.Hq = Hq; p.Hkv = Hkv; p.causal = causal;
   p.scale = softmax_scale; p.scale_log2 = softmax_scale * 1.4426950408889634f;
@@ -419,6 +427,6 @@ extern "C" int atb_flash_bwd(const void* dout, const void* q, const void* k, con
   const long long n4 = (long long)B * Sq * Hq * HD / 4;
   long long g = (n4 + 255) / 256;
   if (g > 148 * 16) g = 148 * 16;
-  f32_to_bf16_kernel<<<(unsigned)g, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dq, n4);
+  f32_to_bf16_kernel<<<(unsigned)g, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dq, n4, Hq * HD / 4, dq_stride);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

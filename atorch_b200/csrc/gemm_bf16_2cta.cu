@@ -36,6 +36,8 @@ struct Epi {
   long long ldc;
   float alpha;
   int out_fp32, accumulate;
+  const void* residual;  // optional bf16 [M, N] added in the epilogue (pitch ldr); bf16 output only
+  long long ldr;
 };
 
 ATB_DEVICE uint32_t cluster_ctarank() {
@@ -250,6 +252,14 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                   v[i] += o0.x; v[i + 1] += o0.y; v[i + 2] += o1.x; v[i + 3] += o1.y;
                   v[i + 4] += o2.x; v[i + 5] += o2.y; v[i + 6] += o3.x; v[i + 7] += o3.y;
                 }
+                if (ep.residual != nullptr) {
+                  const uint4 rr = *reinterpret_cast<const uint4*>(
+                      reinterpret_cast<const __nv_bfloat16*>(ep.residual) + (long long)row * ep.ldr + col0 + i);
+                  const float2 r0 = unpack_bf16x2(rr.x), r1 = unpack_bf16x2(rr.y), r2 = unpack_bf16x2(rr.z),
+                               r3 = unpack_bf16x2(rr.w);
+                  v[i] += r0.x; v[i + 1] += r0.y; v[i + 2] += r1.x; v[i + 3] += r1.y;
+                  v[i + 4] += r2.x; v[i + 5] += r2.y; v[i + 6] += r3.x; v[i + 7] += r3.y;
+                }
                 uint4 o;
                 o.x = pack_bf16x2(v[i], v[i + 1]);
                 o.y = pack_bf16x2(v[i + 2], v[i + 3]);
@@ -339,12 +349,14 @@ int launch(const void* A, const void* B, const Epi& ep, int M, int N, int K, lon
 // Same arguments as atb_gemm_bf16 (gemm_bf16.cu) minus the tile choice. Best for M, N >= 256.
 extern "C" int atb_gemm_bf16_2cta(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
                                   long long lda, long long ldb, long long ldc, int a_mn_major, int b_mn_major,
-                                  int out_fp32, int accumulate, float alpha, int max_ctas, void* stream, int* status) {
+                                  int out_fp32, int accumulate, float alpha, int max_ctas, const void* residual,
+                                  long long ldr, void* stream, int* status) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((N & 7) || (lda & 7) || (ldb & 7) || (ldc & 3) || (!out_fp32 && (ldc & 7))) return -1;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
     return -1;
-  Epi ep{C, bias, ldc, alpha, out_fp32, accumulate};
+  if (residual != nullptr && (out_fp32 || (ldr & 7) || (reinterpret_cast<uintptr_t>(residual) & 15))) return -1;
+  Epi ep{C, bias, ldc, alpha, out_fp32, accumulate, residual, ldr};
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (!a_mn_major && !b_mn_major) return launch<false, false>(A, B, ep, M, N, K, lda, ldb, max_ctas, st, status);
   if (!a_mn_major && b_mn_major) return launch<false, true>(A, B, ep, M, N, K, lda, ldb, max_ctas, st, status);

@@ -26,6 +26,7 @@ import torch
 import torch.nn as nn
 
 from .. import ops
+from ..ops import flash
 from ..utils.checkpoint import checkpoint_module
 
 
@@ -102,6 +103,12 @@ class RMSNorm(nn.Module):
 
 
 class LlamaDecoderLayer(nn.Module):
+    # parameters whose gradients are only ever written by this package's kernels (GEMM epilogue, norm
+    # column sums): sharded engines may skip zero-filling their gradient buffers (looked up by name
+    # after materialisation, since moving a module off the meta device re-creates its Parameters)
+    _atb_direct_grad_params = ("qkv_proj.weight", "o_proj.weight", "gate_up_proj.weight", "down_proj.weight",
+                               "input_layernorm.weight", "post_attention_layernorm.weight")
+
     def __init__(self, config: LlamaConfig, layer_idx: int = 0):
         super().__init__()
         self.config = config
@@ -135,7 +142,12 @@ class LlamaDecoderLayer(nn.Module):
         q = qkv[:, :, : self.n_q]
         k = qkv[:, :, self.n_q: self.n_q + self.n_kv]
         v = qkv[:, :, self.n_q + self.n_kv:]
-        a = ops.attention(q, k, v, **(attn_kwargs or {"causal": True}))
+        kw = attn_kwargs or {"causal": True}
+        if self.n_q == self.n_kv and flash.supported(q, k, v, kw.get("dropout_p", 0.0), kw.get("additive_mask"),
+                                                     kw.get("additive_bias")) and flash.backward_built():
+            a = flash.flash_attention_qkv(qkv, self.n_q, **kw)      # fused layout in, fused gradient out
+        else:
+            a = ops.attention(q, k, v, **kw)
         h = self._proj(self.o_proj, a.reshape(B, S, self.n_q * d), h)
         x = self.post_attention_layernorm(h)
         act = ops.swiglu(self._proj(self.gate_up_proj, x))
@@ -156,6 +168,8 @@ class LlamaModel(nn.Module):
         self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False)
         if config.tie_word_embeddings:
             self.lm_head.weight = self.embed_tokens.weight
+        self._atb_direct_grad_params = ("norm.weight",) if config.tie_word_embeddings else \
+            ("norm.weight", "lm_head.weight")
         self._rope_cache: Dict = {}
         self.apply(self._init_weights)
 

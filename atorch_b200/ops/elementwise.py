@@ -37,30 +37,36 @@ def rope_reference(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, nheads
     return x2.view(x.shape)
 
 
-def _rope_launch(x2, cos, sin, positions, nheads, head_dim, backward):
-    T = x2.shape[0]
-    rc = _lib.lib().atb_rope(_lib.ptr(x2), _lib.ptr(cos), _lib.ptr(sin), _lib.ptr(positions),
+def _rope_launch(dst2, src2, cos, sin, positions, nheads, head_dim, backward):
+    """dst2 = rope(src2) (rows = tokens); the columns after the rotated heads are copied through."""
+    T, W = dst2.shape
+    rc = _lib.lib().atb_rope(_lib.ptr(dst2), _lib.ptr(src2), _lib.ptr(cos), _lib.ptr(sin), _lib.ptr(positions),
                              ctypes.c_longlong(T), ctypes.c_int(cos.shape[0]), ctypes.c_int(nheads),
-                             ctypes.c_int(head_dim), ctypes.c_longlong(x2.stride(0)), ctypes.c_int(int(backward)),
-                             _lib.stream_ptr())
+                             ctypes.c_int(head_dim), ctypes.c_longlong(dst2.stride(0)),
+                             ctypes.c_longlong(src2.stride(0)), ctypes.c_int(W - nheads * head_dim),
+                             ctypes.c_int(int(backward)), _lib.stream_ptr())
     _lib.check(rc, "atb_rope")
 
 
 class _Rope(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, cos, sin, positions, nheads, head_dim):
-        out = x.contiguous().clone()
+        src = x.reshape(-1, x.shape[-1])
+        src = src if src.stride(-1) == 1 else src.contiguous()
+        out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
         ctx.save_for_backward(cos, sin, positions)
         ctx.cfg = (nheads, head_dim)
-        _rope_launch(out.view(-1, out.shape[-1]), cos, sin, positions, nheads, head_dim, False)
+        _rope_launch(out.view(-1, out.shape[-1]), src, cos, sin, positions, nheads, head_dim, False)
         return out
 
     @staticmethod
     def backward(ctx, dy):
         cos, sin, positions = ctx.saved_tensors
         nheads, head_dim = ctx.cfg
-        dx = dy.contiguous().clone()
-        _rope_launch(dx.view(-1, dx.shape[-1]), cos, sin, positions, nheads, head_dim, True)
+        src = dy.reshape(-1, dy.shape[-1])
+        src = src if src.stride(-1) == 1 else src.contiguous()
+        dx = torch.empty(dy.shape, dtype=dy.dtype, device=dy.device)
+        _rope_launch(dx.view(-1, dx.shape[-1]), src, cos, sin, positions, nheads, head_dim, True)
         return dx, None, None, None, None, None
 
 

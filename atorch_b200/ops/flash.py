@@ -104,15 +104,22 @@ def flash_fwd_raw(q, k, v, causal, softmax_scale, row_lo, row_hi):
     return out, lse
 
 
-def flash_bwd_raw(dout, q, k, v, out, lse, causal, softmax_scale, row_lo, row_hi):
-    """Launch the backward kernels. Returns (dq, dk, dv) shaped like q, k, v (contiguous)."""
+def flash_bwd_raw(dout, q, k, v, out, lse, causal, softmax_scale, row_lo, row_hi, fused_out: bool = False):
+    """Launch the backward kernels. Returns (dq, dk, dv) shaped like q, k, v. With ``fused_out`` (and
+    equal query / key-value head counts) the three are slices of ONE ``[B, S, 3*H, D]`` buffer laid out
+    like a fused q|k|v projection output, so the gradient of that projection needs no concatenation."""
     B, Sq, Hq, D = q.shape
     Sk, Hkv = k.shape[1], k.shape[2]
     dq_acc = torch.zeros(B, Sq, Hq, D, dtype=torch.float32, device=q.device)
-    dk = torch.empty(B, Sk, Hq, D, dtype=q.dtype, device=q.device)
-    dv = torch.empty(B, Sk, Hq, D, dtype=q.dtype, device=q.device)
     delta = torch.empty(B, Hq, Sq, dtype=torch.float32, device=q.device)
-    dq = torch.empty(B, Sq, Hq, D, dtype=q.dtype, device=q.device)
+    if fused_out and Hkv == Hq and Sq == Sk:
+        fused = torch.empty(B, Sq, 3 * Hq, D, dtype=q.dtype, device=q.device)
+        dq, dk, dv = fused[:, :, :Hq], fused[:, :, Hq: 2 * Hq], fused[:, :, 2 * Hq:]
+    else:
+        fused = None
+        dq = torch.empty(B, Sq, Hq, D, dtype=q.dtype, device=q.device)
+        dk = torch.empty(B, Sk, Hq, D, dtype=q.dtype, device=q.device)
+        dv = torch.empty(B, Sk, Hq, D, dtype=q.dtype, device=q.device)
     dout = dout if (dout.stride(-1) == 1 and dout.stride(2) == D and dout.stride(0) == dout.stride(1) * Sq) \
         else dout.contiguous()
     rc = _lib.lib().atb_flash_bwd(
@@ -120,13 +127,16 @@ def flash_bwd_raw(dout, q, k, v, out, lse, causal, softmax_scale, row_lo, row_hi
         _lib.ptr(dq_acc), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(row_lo), _lib.ptr(row_hi),
         ctypes.c_int(B), ctypes.c_int(Sq), ctypes.c_int(Sk), ctypes.c_int(Hq), ctypes.c_int(Hkv),
         ctypes.c_longlong(_token_stride(q)), ctypes.c_longlong(_token_stride(k)), ctypes.c_longlong(_token_stride(v)),
-        ctypes.c_longlong(_token_stride(dout)), ctypes.c_int(int(causal)), ctypes.c_float(softmax_scale),
+        ctypes.c_longlong(_token_stride(dout)), ctypes.c_longlong(_token_stride(dq)),
+        ctypes.c_longlong(_token_stride(dk)), ctypes.c_int(int(causal)), ctypes.c_float(softmax_scale),
         _lib.stream_ptr(), _lib.ptr(_lib.status_word(q.device)))
     _lib.check(rc, "atb_flash_bwd")
     if Hkv != Hq:
         g = Hq // Hkv
         dk = dk.view(B, Sk, Hkv, g, D).float().sum(3).to(q.dtype)
         dv = dv.view(B, Sk, Hkv, g, D).float().sum(3).to(q.dtype)
+    if fused is not None:
+        return fused
     return dq, dk, dv
 
 
@@ -155,3 +165,33 @@ def flash_attention(q, k, v, causal=False, softmax_scale=None, glm_mask=None, pa
         causal = False   # single-query decode sees every key
     lo, hi = row_intervals(B, Sq, Sk, q.device, causal, glm_mask, pack_glm_mask, key_padding_mask, cu_seqlens)
     return _FlashAttn.apply(q, k, v, bool(causal), float(scale), lo, hi)
+
+
+class _FlashAttnQKV(torch.autograd.Function):
+    """Attention on a fused projection output ``qkv [B, S, 3*H, D]`` (q heads, then k, then v). The
+    backward emits one fused gradient tensor in the same layout: no slice-backward zero fills or adds."""
+
+    @staticmethod
+    def forward(ctx, qkv, H, causal, scale, row_lo, row_hi):
+        q, k, v = qkv[:, :, :H], qkv[:, :, H: 2 * H], qkv[:, :, 2 * H:]
+        out, lse = flash_fwd_raw(q, k, v, causal, scale, row_lo, row_hi)
+        ctx.save_for_backward(qkv, out, lse, row_lo, row_hi)
+        ctx.cfg = (H, causal, scale)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, out, lse, row_lo, row_hi = ctx.saved_tensors
+        H, causal, scale = ctx.cfg
+        q, k, v = qkv[:, :, :H], qkv[:, :, H: 2 * H], qkv[:, :, 2 * H:]
+        dqkv = flash_bwd_raw(dout, q, k, v, out, lse, causal, scale, row_lo, row_hi, fused_out=True)
+        return dqkv, None, None, None, None, None
+
+
+def flash_attention_qkv(qkv: torch.Tensor, num_heads: int, causal: bool = True, softmax_scale=None, **mask_kwargs):
+    """qkv: ``[B, S, 3*num_heads, D]``; returns ``[B, S, num_heads, D]``."""
+    B, S, _, D = qkv.shape
+    scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
+    lo, hi = row_intervals(B, S, S, qkv.device, causal, mask_kwargs.get("glm_mask"), mask_kwargs.get("pack_glm_mask"),
+                           mask_kwargs.get("key_padding_mask"), mask_kwargs.get("cu_seqlens"))
+    return _FlashAttnQKV.apply(qkv, num_heads, bool(causal), float(scale), lo, hi)

@@ -59,6 +59,7 @@ def gemm(
     tile_n: int = 0,
     max_ctas: int = 0,
     kernel: str = "auto",
+    residual: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """``out[M,N] (+)= alpha * A[M,K] @ B[N,K]^T (+ bias[N])``.
 
@@ -73,7 +74,10 @@ def gemm(
         out = torch.empty(M, N, dtype=out_dtype or torch.bfloat16, device=a.device)
         assert not accumulate
     if not _lib.use_kernels(a, b, out) or a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or (N % 8) or (K % 8) or (M % 8):
-        return gemm_reference(a, b, a_mn, b_mn, out, None, accumulate, alpha, bias)
+        r = gemm_reference(a, b, a_mn, b_mn, out, None, accumulate, alpha, bias)
+        if residual is not None:
+            r.add_(residual.to(r.dtype))
+        return r
     if a.stride(-1) != 1:
         a = a.contiguous()
     if b.stride(-1) != 1:
@@ -88,7 +92,9 @@ def gemm(
             ctypes.c_longlong(_pitch(a)), ctypes.c_longlong(_pitch(b)), ctypes.c_longlong(_pitch(out)),
             ctypes.c_int(int(a_mn)), ctypes.c_int(int(b_mn)),
             ctypes.c_int(int(out.dtype == torch.float32)), ctypes.c_int(int(accumulate)),
-            ctypes.c_float(alpha), ctypes.c_int(max_ctas), _lib.stream_ptr(), _lib.ptr(_lib.status_word(a.device)))
+            ctypes.c_float(alpha), ctypes.c_int(max_ctas), _lib.ptr(residual),
+            ctypes.c_longlong(_pitch(residual) if residual is not None else 0), _lib.stream_ptr(),
+            _lib.ptr(_lib.status_word(a.device)))
         _lib.check(rc, f"atb_gemm_bf16_2cta M={M} N={N} K={K}")
         return out
     rc = L.atb_gemm_bf16(
@@ -97,7 +103,8 @@ def gemm(
         ctypes.c_longlong(_pitch(a)), ctypes.c_longlong(_pitch(b)), ctypes.c_longlong(_pitch(out)),
         ctypes.c_int(int(a_mn)), ctypes.c_int(int(b_mn)),
         ctypes.c_int(int(out.dtype == torch.float32)), ctypes.c_int(int(accumulate)),
-        ctypes.c_float(alpha), ctypes.c_int(tile_n), ctypes.c_int(max_ctas),
+        ctypes.c_float(alpha), ctypes.c_int(tile_n), ctypes.c_int(max_ctas), _lib.ptr(residual),
+        ctypes.c_longlong(_pitch(residual) if residual is not None else 0),
         _lib.stream_ptr(), _lib.ptr(_lib.status_word(a.device)),
     )
     _lib.check(rc, f"atb_gemm_bf16 M={M} N={N} K={K}")
@@ -115,9 +122,10 @@ class _Linear(torch.autograd.Function):
         ctx.x_shape = shp
         ctx.weight_ref = weight
         if residual is not None:
-            # out = residual + x W^T : the epilogue accumulates into a copy of the residual stream
-            out = residual.reshape(-1, weight.shape[0]).clone()
-            gemm(x2, weight, out=out, accumulate=True, bias=bias)
+            # out = residual + x W^T : the epilogue reads the residual stream and adds it before the store
+            r2 = residual.reshape(-1, weight.shape[0])
+            r2 = r2 if r2.stride(-1) == 1 else r2.contiguous()
+            out = gemm(x2, weight, bias=bias, out_dtype=x.dtype, residual=r2)
         else:
             out = gemm(x2, weight, bias=bias, out_dtype=x.dtype)
         return out.view(*shp[:-1], weight.shape[0])
@@ -134,7 +142,9 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             mg = getattr(ctx.weight_ref, "main_grad", None)
             if mg is not None:
-                gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, accumulate=True)
+                first = getattr(ctx.weight_ref, "_atb_first", False)     # untouched buffer: overwrite, no zero fill
+                gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, accumulate=not first)
+                ctx.weight_ref._atb_first = False
                 ctx.weight_ref.grad_added_to_main_grad = True
             else:
                 dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=weight.dtype)

@@ -66,7 +66,9 @@ def _param_grad(param, partial, parts):
     """Reduce the partial rows into ``param.main_grad`` (accumulating) or into a fresh grad tensor."""
     mg = getattr(param, "main_grad", None)
     if mg is not None:
-        _colsum(partial, parts, mg, True)
+        first = getattr(param, "_atb_first", False)
+        _colsum(partial, parts, mg, not first)
+        param._atb_first = False
         param.grad_added_to_main_grad = True
         return None
     g = torch.empty_like(param)

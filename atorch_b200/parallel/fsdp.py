@@ -219,6 +219,7 @@ class FSDPEngine:
         self._shard_params: Optional[List[Tuple[str, nn.Parameter]]] = None
         self.training_step = 0
         self.local_sgd = None            # set by local_sgd.sharded.attach_local_sgd
+        self._fp32_accum = False
         self._build(unit_modules)
 
     # ------------------------------------------------------------------------------------ build
@@ -241,6 +242,12 @@ class FSDPEngine:
             return res
 
         self._materialize_meta(unit_set)
+        for m in self.module.modules():
+            for n in getattr(m, "_atb_direct_grad_params", ()):
+                try:
+                    m.get_parameter(n)._atb_direct_grad = True
+                except AttributeError:
+                    pass
         seen: Set[int] = set()
         ordered = [m for _, m in self.module.named_modules() if id(m) in unit_set]
         plan = [(names[id(m)], m, False) for m in ordered] + [("", self.module, True)]
@@ -439,10 +446,36 @@ class FSDPEngine:
         if self.cfg.reshard_after_forward and not u.is_root:
             self._free_full(u)
 
+    def _direct_grads(self) -> bool:
+        """One rank, no replicas: the unit gradient buffers ARE slices of the global gradient buffer
+        (compute dtype), nothing is reduced or copied. Accumulating over micro-batches switches the
+        engine to an fp32 gradient shard (see ``_switch_to_fp32_accumulation``)."""
+        return self.world == 1 and self.replicas == 1 and not self._fp32_accum
+
+    def _switch_to_fp32_accumulation(self) -> None:
+        if self._fp32_accum:
+            return
+        self._fp32_accum = True
+        if self.grad_shard is not None and self.grad_shard.dtype != torch.float32:
+            self.grad_shard = self.grad_shard.float()
+
+    def _first_write_ok(self) -> bool:
+        """Kernels that write a parameter gradient can overwrite on first touch (no zero fill) only when
+        the kernel path is certain: CUDA, library loaded, bf16 compute."""
+        from .. import _lib
+
+        return self.on_cuda and self.compute_dtype == torch.bfloat16 and _lib.have_kernels()
+
     def _alloc_grads(self, u: FlatUnit) -> None:
         if u.full_grad is not None or not u.has_trainable:
             return
-        if self.fused:
+        if self._direct_grads() and not u.fresh:
+            self._switch_to_fp32_accumulation()       # a second micro-batch: accumulate in fp32 from now on
+        if self._direct_grads():
+            self._ensure_grad_shard()
+            u.full_grad = self.grad_shard[u.shard_offset: u.shard_offset + u.padded_numel]
+            zero_all = False
+        elif self.fused:
             if u.is_root:
                 buf, u._gbuf_idx = self._root_gbuf, -1
             else:
@@ -454,11 +487,20 @@ class FSDPEngine:
                     self._gbuf_events[idx] = None
             u._gbuf = buf
             u.full_grad = buf.tensor[: u.padded_numel]
-            u.full_grad.zero_()
+            zero_all = False
         else:
-            u.full_grad = torch.zeros(u.padded_numel, dtype=self.compute_dtype, device=self.device)
+            u.full_grad = torch.empty(u.padded_numel, dtype=self.compute_dtype, device=self.device)
+            zero_all = False
+        first_ok = self._first_write_ok()
+        if not first_ok:
+            u.full_grad.zero_()
         for v, p in zip(u.views(u.full_grad), u.params):
             if p.requires_grad:
+                if first_ok:
+                    if getattr(p, "_atb_direct_grad", False):
+                        p._atb_first = True           # the writing kernel overwrites instead of accumulating
+                    else:
+                        v.zero_()
                 p.grad = v
                 p.main_grad = v
 
@@ -478,17 +520,25 @@ class FSDPEngine:
 
     def _ensure_grad_shard(self) -> None:
         if self.grad_shard is None:
-            self.grad_shard = torch.zeros(self.total_shard, dtype=torch.float32, device=self.device)
+            dt = self.compute_dtype if (self.world == 1 and self.replicas == 1 and not self._fp32_accum) \
+                else torch.float32
+            self.grad_shard = torch.zeros(self.total_shard, dtype=dt, device=self.device)
 
     def _reduce_grads(self, u: FlatUnit) -> None:
         g = u.full_grad
         if g is None:
             return
-        for p in u.params:
+        for v, p in zip(u.views(g), u.params):
+            if getattr(p, "_atb_first", False):       # no kernel wrote this gradient in this backward
+                v.zero_()
+                p._atb_first = False
             p.grad = None
             if hasattr(p, "main_grad"):
                 del p.main_grad
         u.full_grad = None
+        if self._direct_grads():
+            u.fresh = False                           # gradients already sit in the global buffer
+            return
         self._ensure_grad_shard()
         dst = self.grad_shard[u.shard_offset: u.shard_offset + u.shard_numel]
         skip_rep = self.local_sgd is not None and self.local_sgd.skip_replica_reduce()
@@ -625,6 +675,9 @@ class FSDPEngine:
 
     def attach_shard_grads(self) -> None:
         g = self.finalize_grads()
+        if g.dtype != torch.float32:                  # generic optimizers want gradients in the parameter dtype
+            self._switch_to_fp32_accumulation()
+            g = self.grad_shard
         it = iter(self.shard_parameters())
         for u in self.units:
             gs = g[u.shard_offset: u.shard_offset + u.shard_numel]
