@@ -21,14 +21,20 @@ namespace {
 using namespace atb;
 
 constexpr int BM = 128;   // rows of A per CTA (256 per pair)
-constexpr int BNH = 128;  // rows of B per CTA (256 per pair)
-constexpr int BN = 256;   // accumulator columns
 constexpr int BK = 64;
-constexpr int STAGES = 6;
 constexpr int A_BYTES = BM * BK * 2;
-constexpr int B_BYTES = BNH * BK * 2;
-constexpr int BAR_OFF = STAGES * (A_BYTES + B_BYTES);
-constexpr int SMEM_TOTAL = BAR_OFF + (2 * STAGES + 4) * 8 + 16 + 1024;
+
+// BN = accumulator columns of the pair's tile (256 or 128); each CTA loads BN/2 rows of B.
+// The narrower tile exists for wave quantisation: 256 tiles of 256x256 fill 74 CTA pairs 3.46 times
+// (4 waves, 86 % busy), the same problem in 256x128 tiles takes 7 waves of half the length (99 %).
+template <int BN>
+struct Cfg {
+  static constexpr int BNH = BN / 2;
+  static constexpr int STAGES = BN == 256 ? 6 : 8;
+  static constexpr int B_BYTES = BNH * BK * 2;
+  static constexpr int BAR_OFF = STAGES * (A_BYTES + B_BYTES);
+  static constexpr int SMEM_TOTAL = BAR_OFF + (2 * STAGES + 4) * 8 + 16 + 1024;
+};
 
 struct Epi {
   void* C;
@@ -68,10 +74,12 @@ ATB_DEVICE void mbar_arrive_remote(uint32_t bar_cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 
-template <bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Epi ep, int M,
                       int N, int K, int* status) {
+  constexpr int BNH = Cfg<BN>::BNH, STAGES = Cfg<BN>::STAGES, B_BYTES = Cfg<BN>::B_BYTES,
+                BAR_OFF = Cfg<BN>::BAR_OFF;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
@@ -113,7 +121,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     tma_prefetch_desc(&tmB);
   }
   if (warp == 1) {
-    tmem_alloc<2>(tmem_slot, 512);
+    tmem_alloc<2>(tmem_slot, 2 * BN);
     tmem_relinquish<2>();
   }
   tc_fence_before();
@@ -288,7 +296,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   cluster_sync_all();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc<2>(tmem_base, 512);
+    tmem_dealloc<2>(tmem_base, 2 * BN);
   }
 }
 
@@ -303,7 +311,7 @@ int sm_count() {
   return g_sms;
 }
 
-template <bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN>
 int launch(const void* A, const void* B, const Epi& ep, int M, int N, int K, long long lda, long long ldb,
            int max_ctas, cudaStream_t stream, int* status) {
   CUtensorMap tmA, tmB;
@@ -314,11 +322,13 @@ int launch(const void* A, const void* B, const Epi& ep, int M, int N, int K, lon
     ok = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, lda, BK, 64, CU_TENSOR_MAP_SWIZZLE_128B);
   if (!ok) return -2;
   if (!B_MN)
-    ok = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb, BNH, BK, CU_TENSOR_MAP_SWIZZLE_128B);
+    ok = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb, Cfg<BN>::BNH, BK,
+                      CU_TENSOR_MAP_SWIZZLE_128B);
   else
     ok = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb, BK, 64, CU_TENSOR_MAP_SWIZZLE_128B);
   if (!ok) return -3;
-  auto kern = gemm_bf16_2cta_kernel<A_MN, B_MN>;
+  auto kern = gemm_bf16_2cta_kernel<BN, A_MN, B_MN>;
+  constexpr int SMEM_TOTAL = Cfg<BN>::SMEM_TOTAL;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL) != cudaSuccess) return -4;
@@ -349,8 +359,8 @@ int launch(const void* A, const void* B, const Epi& ep, int M, int N, int K, lon
 // Same arguments as atb_gemm_bf16 (gemm_bf16.cu) minus the tile choice. Best for M, N >= 256.
 extern "C" int atb_gemm_bf16_2cta(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
                                   long long lda, long long ldb, long long ldc, int a_mn_major, int b_mn_major,
-                                  int out_fp32, int accumulate, float alpha, int max_ctas, const void* residual,
-                                  long long ldr, void* stream, int* status) {
+                                  int out_fp32, int accumulate, float alpha, int tile_n, int max_ctas,
+                                  const void* residual, long long ldr, void* stream, int* status) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((N & 7) || (lda & 7) || (ldb & 7) || (ldc & 3) || (!out_fp32 && (ldc & 7))) return -1;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
@@ -358,8 +368,18 @@ extern "C" int atb_gemm_bf16_2cta(const void* A, const void* B, void* C, const v
   if (residual != nullptr && (out_fp32 || (ldr & 7) || (reinterpret_cast<uintptr_t>(residual) & 15))) return -1;
   Epi ep{C, bias, ldc, alpha, out_fp32, accumulate, residual, ldr};
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (!a_mn_major && !b_mn_major) return launch<false, false>(A, B, ep, M, N, K, lda, ldb, max_ctas, st, status);
-  if (!a_mn_major && b_mn_major) return launch<false, true>(A, B, ep, M, N, K, lda, ldb, max_ctas, st, status);
-  if (a_mn_major && b_mn_major) return launch<true, true>(A, B, ep, M, N, K, lda, ldb, max_ctas, st, status);
-  return launch<true, false>(A, B, ep, M, N, K, lda, ldb, max_ctas, st, status);
+  // The 256-wide tile is the default. The 128-wide one fills the last wave better (256 tiles of 256x256
+  // occupy 74 CTA pairs for 4 waves at 86 %), but measured 1.5x slower per FLOP on B200: its 256-cycle
+  // stages leave the single MMA-issuing thread no slack. It stays selectable with tile_n = 128.
+  const bool narrow = tile_n == 128;
+#define ATB_PAIR_DISPATCH(BN_)                                                                                     \
+  do {                                                                                                             \
+    if (!a_mn_major && !b_mn_major) return launch<BN_, false, false>(A, B, ep, M, N, K, lda, ldb, max_ctas, st, status); \
+    if (!a_mn_major && b_mn_major) return launch<BN_, false, true>(A, B, ep, M, N, K, lda, ldb, max_ctas, st, status);   \
+    if (a_mn_major && b_mn_major) return launch<BN_, true, true>(A, B, ep, M, N, K, lda, ldb, max_ctas, st, status);     \
+    return launch<BN_, true, false>(A, B, ep, M, N, K, lda, ldb, max_ctas, st, status);                                  \
+  } while (0)
+  if (narrow) ATB_PAIR_DISPATCH(128);
+  ATB_PAIR_DISPATCH(256);
+#undef ATB_PAIR_DISPATCH
 }

@@ -18,6 +18,7 @@ Per-layer dataflow (all bf16, fp32 accumulation inside the kernels):
 """
 from __future__ import annotations
 
+import collections
 import math
 from dataclasses import dataclass, field
 from typing import Dict, Optional
@@ -44,6 +45,7 @@ class LlamaConfig:
     initializer_range: float = 0.02
     tie_word_embeddings: bool = False
     gradient_checkpointing: bool = False
+    reuse_attention_in_recompute: bool = True   # checkpointed blocks keep attention out/lse instead of recomputing
 
     def __post_init__(self):
         if self.num_key_value_heads is None:
@@ -121,6 +123,7 @@ class LlamaDecoderLayer(nn.Module):
         self.post_attention_layernorm = RMSNorm(h, config.rms_norm_eps)
         self.gate_up_proj = nn.Linear(h, 2 * config.intermediate_size, bias=False)
         self.down_proj = nn.Linear(config.intermediate_size, h, bias=False)
+        self._attn_cache = collections.deque(maxlen=64)
 
     @staticmethod
     def _proj(mod: nn.Module, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -145,7 +148,8 @@ class LlamaDecoderLayer(nn.Module):
         kw = attn_kwargs or {"causal": True}
         if self.n_q == self.n_kv and flash.supported(q, k, v, kw.get("dropout_p", 0.0), kw.get("additive_mask"),
                                                      kw.get("additive_bias")) and flash.backward_built():
-            a = flash.flash_attention_qkv(qkv, self.n_q, **kw)      # fused layout in, fused gradient out
+            cache = self._attn_cache if (self.training and self.config.reuse_attention_in_recompute) else None
+            a = flash.flash_attention_qkv(qkv, self.n_q, recompute_cache=cache, **kw)   # fused gradient out
         else:
             a = ops.attention(q, k, v, **kw)
         h = self._proj(self.o_proj, a.reshape(B, S, self.n_q * d), h)

@@ -172,9 +172,12 @@ class _FlashAttnQKV(torch.autograd.Function):
     backward emits one fused gradient tensor in the same layout: no slice-backward zero fills or adds."""
 
     @staticmethod
-    def forward(ctx, qkv, H, causal, scale, row_lo, row_hi):
+    def forward(ctx, qkv, H, causal, scale, row_lo, row_hi, cached):
         q, k, v = qkv[:, :, :H], qkv[:, :, H: 2 * H], qkv[:, :, 2 * H:]
-        out, lse = flash_fwd_raw(q, k, v, causal, scale, row_lo, row_hi)
+        if cached is not None:
+            out, lse = cached          # output and log-sum-exp kept from the first pass of a checkpointed block
+        else:
+            out, lse = flash_fwd_raw(q, k, v, causal, scale, row_lo, row_hi)
         ctx.save_for_backward(qkv, out, lse, row_lo, row_hi)
         ctx.cfg = (H, causal, scale)
         return out
@@ -185,13 +188,31 @@ class _FlashAttnQKV(torch.autograd.Function):
         H, causal, scale = ctx.cfg
         q, k, v = qkv[:, :, :H], qkv[:, :, H: 2 * H], qkv[:, :, 2 * H:]
         dqkv = flash_bwd_raw(dout, q, k, v, out, lse, causal, scale, row_lo, row_hi, fused_out=True)
-        return dqkv, None, None, None, None, None
+        return dqkv, None, None, None, None, None, None
 
 
-def flash_attention_qkv(qkv: torch.Tensor, num_heads: int, causal: bool = True, softmax_scale=None, **mask_kwargs):
-    """qkv: ``[B, S, 3*num_heads, D]``; returns ``[B, S, num_heads, D]``."""
+def flash_attention_qkv(qkv: torch.Tensor, num_heads: int, causal: bool = True, softmax_scale=None,
+                        recompute_cache=None, **mask_kwargs):
+    """qkv: ``[B, S, 3*num_heads, D]``; returns ``[B, S, num_heads, D]``.
+
+    ``recompute_cache`` (a deque owned by the calling layer) lets an activation-checkpointed block keep
+    the attention output and log-sum-exp of its first (no-grad) pass: that pass appends ``(out, lse)``,
+    the recomputation pops it and skips the forward kernel. 32 MB per layer at 7B scale buys one
+    attention forward per layer per step."""
     B, S, _, D = qkv.shape
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
     lo, hi = row_intervals(B, S, S, qkv.device, causal, mask_kwargs.get("glm_mask"), mask_kwargs.get("pack_glm_mask"),
                            mask_kwargs.get("key_padding_mask"), mask_kwargs.get("cu_seqlens"))
-    return _FlashAttnQKV.apply(qkv, num_heads, bool(causal), float(scale), lo, hi)
+    cached = None
+    if recompute_cache is not None:
+        if not torch.is_grad_enabled():
+            H = num_heads
+            out, lse = flash_fwd_raw(qkv[:, :, :H], qkv[:, :, H: 2 * H], qkv[:, :, 2 * H:], bool(causal), float(scale),
+                                     lo, hi)
+            recompute_cache.append((out, lse))
+            return out
+        if len(recompute_cache) > 0:
+            cached = recompute_cache.popleft()
+            if cached[0].shape != (B, S, num_heads, D):
+                cached = None
+    return _FlashAttnQKV.apply(qkv, num_heads, bool(causal), float(scale), lo, hi, cached)

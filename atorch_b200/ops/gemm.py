@@ -84,7 +84,7 @@ def gemm(
         b = b.contiguous()
     assert out.stride(-1) == 1 and out.dtype in (torch.bfloat16, torch.float32)
     L = _lib.lib()
-    use_pair = kernel == "2cta" or (kernel == "auto" and PAIR_KERNEL_DEFAULT and M >= 256 and N >= 256 and tile_n == 0)
+    use_pair = kernel == "2cta" or (kernel == "auto" and PAIR_KERNEL_DEFAULT and M >= 256 and N >= 256)
     if use_pair:
         rc = L.atb_gemm_bf16_2cta(
             _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias),
@@ -92,7 +92,7 @@ def gemm(
             ctypes.c_longlong(_pitch(a)), ctypes.c_longlong(_pitch(b)), ctypes.c_longlong(_pitch(out)),
             ctypes.c_int(int(a_mn)), ctypes.c_int(int(b_mn)),
             ctypes.c_int(int(out.dtype == torch.float32)), ctypes.c_int(int(accumulate)),
-            ctypes.c_float(alpha), ctypes.c_int(max_ctas), _lib.ptr(residual),
+            ctypes.c_float(alpha), ctypes.c_int(tile_n), ctypes.c_int(max_ctas), _lib.ptr(residual),
             ctypes.c_longlong(_pitch(residual) if residual is not None else 0), _lib.stream_ptr(),
             _lib.ptr(_lib.status_word(a.device)))
         _lib.check(rc, f"atb_gemm_bf16_2cta M={M} N={N} K={K}")

@@ -86,7 +86,7 @@ def pack_nonlinear(x: torch.Tensor, qmap: torch.Tensor, bits: int = 4, group_siz
             c = (c[0::2] | (c[1::2] << 4))
             return c[: (n + 1) // 2], am
         return c[:n], am
-    code = torch.empty(n if bits == 8 else (groups * group_size) // 2, dtype=torch.uint8, device=x.device)
+    code = torch.zeros(n if bits == 8 else (groups * group_size) // 2, dtype=torch.uint8, device=x.device)
     am = torch.empty(groups, dtype=torch.float32, device=x.device)
     rc = _lib.lib().atb_pack_nonlinear(_lib.ptr(xf), _lib.ptr(code), _lib.ptr(am),
                                        _lib.ptr(qmap.to(x.device).float().contiguous()), ctypes.c_longlong(n),

@@ -129,3 +129,29 @@ def test_flash_in_fused_qkv_layout():
     B, S, H = 1, 512, 4
     qkv = torch.randn(B, S, 3 * H, 128, device="cuda", dtype=torch.bfloat16)
     _bwd_check(qkv[:, :, :H], qkv[:, :, H:2 * H], qkv[:, :, 2 * H:], causal=True)
+
+
+def test_llama_block_reuses_attention_in_recompute():
+    from atorch_b200.models.llama import LlamaConfig, LlamaDecoderLayer
+    from atorch_b200.ops import rope_tables
+    from atorch_b200.utils.checkpoint import checkpoint_module
+
+    torch.manual_seed(11)
+    cfg = LlamaConfig(vocab_size=64, hidden_size=256, intermediate_size=512, num_hidden_layers=1,
+                      num_attention_heads=2, num_key_value_heads=2, max_position_embeddings=256)
+    layer = LlamaDecoderLayer(cfg).cuda().bfloat16().train()
+    cos, sin = rope_tables(256, 128, device="cuda")
+    x = torch.randn(2, 256, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    before = _lib.launch_count
+    y = checkpoint_module(layer, x, cos, sin)
+    assert len(layer._attn_cache) == 1
+    y.float().pow(2).sum().backward()
+    with_cache = _lib.launch_count - before
+    assert len(layer._attn_cache) == 0
+    g1 = x.grad.clone()
+    x.grad = None
+    cfg.reuse_attention_in_recompute = False
+    before = _lib.launch_count
+    checkpoint_module(layer, x, cos, sin).float().pow(2).sum().backward()
+    assert _lib.launch_count - before == with_cache + 1      # one more flash forward
+    assert torch.equal(g1, x.grad)

@@ -31,8 +31,9 @@ def test_gemm_layouts(M, N, K, a_mn, b_mn):
     for tile_n in (128, 256):
         out = gemm(a, b, a_mn=a_mn, b_mn=b_mn, tile_n=tile_n, kernel="1cta")
         _check(out, ref, K)
-    out = gemm(a, b, a_mn=a_mn, b_mn=b_mn, kernel="2cta")
-    _check(out, ref, K)
+    for tile_n in (0, 128, 256):
+        out = gemm(a, b, a_mn=a_mn, b_mn=b_mn, kernel="2cta", tile_n=tile_n)
+        _check(out, ref, K)
 
 
 def test_gemm_fp32_out_accumulate_alpha_bias():
@@ -77,6 +78,15 @@ def test_gemm_many_tiles_persistent():
     o4 = c0.clone()
     gemm(a, b, out=o4, accumulate=True, alpha=0.5, kernel="2cta")
     _check(o4[idx], c0[idx] + 0.5 * ref, K)
+
+
+def test_residual_epilogue():
+    torch.manual_seed(6)
+    M, N, K = 512, 4096, 256
+    a, b, r = _mk(M, K), _mk(N, K), _mk(M, N)
+    for kern in ("1cta", "2cta"):
+        out = gemm(a, b, residual=r, kernel=kern)
+        _check(out, r.float() + a.float() @ b.float().t(), K)
 
 
 def test_linear_autograd_matches_torch():
