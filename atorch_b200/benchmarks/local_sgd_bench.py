@@ -29,7 +29,8 @@ def main(argv=None):
     cfg = LlamaConfig.tiny() if a.tiny else LlamaConfig.llama_1p3b()
     seq, mbs = (64, 2) if a.tiny else (2048, 4)
     torch.manual_seed(1234)
-    model = LlamaModel(cfg)
+    with torch.device(dev):
+        model = LlamaModel(cfg)
     if a.H == 0:          # synchronous data parallel
         strategy = ["parallel_mode", ("fsdp", {"atorch_wrap_cls": (LlamaDecoderLayer,)}),
                     ("amp_native", {"dtype": torch.bfloat16}), ("checkpoint", {"wrap_class": (LlamaDecoderLayer,)})]

@@ -38,18 +38,14 @@ def main(argv=None):
     cfg = MixtralConfig.tiny_moe(**kw) if a.tiny else MixtralConfig.mixtral_bench(**kw)
     seq = 64 if a.tiny else 4096
     torch.manual_seed(1234 + rank)                       # experts differ per rank; shared parts are synchronised below
-    model = MixtralModel(cfg)
-    if dev.type == "cuda":
-        model = model.to(dev)
+    with torch.device(dev):                              # initialise directly on the device
+        model = MixtralModel(cfg)
     expert_params = [p for m in model.modules() if isinstance(m, Grouped_GEMM_MoE) for p in m.parameters()]
     for p in expert_params:
         p.data = p.data.to(torch.bfloat16 if dev.type == "cuda" else p.dtype)
     strategy = [("fsdp", {"atorch_wrap_cls": (MixtralDecoderLayer,), "atorch_ignored_cls": (Grouped_GEMM_MoE,),
                           "sync_module_states": True}),
                 ("amp_native", {"dtype": torch.bfloat16})]
-    if world > 1:
-        with D.ParallelGroupContextManager("dp_"):
-            pass
     ok, res, _ = auto_accelerate(model, torch.optim.AdamW, loss_func=lambda b, o: o[0], optim_args={"lr": 3e-4},
                                  load_strategy=strategy)
     assert ok

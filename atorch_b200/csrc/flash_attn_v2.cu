@@ -1,0 +1,352 @@
+// Flash attention forward, two query tiles per CTA (head dim 128, bf16) for sm_100a.
+//
+// One CTA owns 256 query rows as two 128-row tiles A and B that share every K/V tile. Warp 0 = TMA
+// producer, warp 1 = MMA issuer / TMEM owner, warps 2..5 = softmax of tile A, warps 6..9 = softmax of
+// tile B; a softmax thread owns one whole row (128 scores), so no row statistics are exchanged.
+//
+//   TMEM:  S_A | S_B | O_A | O_B   (4 x 128 fp32 columns)
+//   per K/V tile j:   S_T = Q_T K_j^T  ->  P_T = 2^(S_T c - m_T c) (bf16, shared memory)  ->  O_T += P_T V_j
+//
+// O accumulates in tensor memory. The reference maximum m_T of a row is only raised when the new row
+// maximum exceeds it by more than 2^8 (in the exponent domain); then the row of O_T is rescaled in
+// TMEM by the owning thread, which is safe because the single P buffer is only rewritten after every
+// earlier P.V product has completed. While tile A's warps exponentiate, the tensor core works for tile
+// B and vice versa: issue order  PV_A(j), S_A(j+1), PV_B(j), S_B(j+1).
+//
+// Masks: per-row key interval [lo, hi) exactly as in flash_attn.cu.
+#include "common.cuh"
+
+namespace {
+using namespace atb;
+
+constexpr int BQ = 128, BKV = 128, HD = 128;
+constexpr int PANEL = 128 * 64 * 2;
+constexpr int TILE = 2 * PANEL;
+constexpr int THREADS = 64 + 256;
+constexpr float RESCALE_THRESHOLD = 8.f;   // log2 units
+
+struct Params {
+  __nv_bfloat16* O;
+  float* lse;
+  const int* row_lo;
+  const int* row_hi;
+  int B, Sq, Sk, Hq, Hkv, causal;
+  float scale_log2;
+  int* status;
+};
+
+struct L2 {
+  static constexpr int Q_OFF = 0;                    // tile A, tile B
+  static constexpr int K_OFF = Q_OFF + 2 * TILE;     // 2 stages
+  static constexpr int V_OFF = K_OFF + 2 * TILE;     // 2 stages
+  static constexpr int P_OFF = V_OFF + 2 * TILE;     // one buffer shared by both tiles
+  static constexpr int BAR_OFF = P_OFF + TILE;       // 224 KB
+  static constexpr int NBARS = 1 + 8 + 2 + 2 + 2 + 1 + 2;
+  static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 64 + 1024;
+};
+
+__global__ void __launch_bounds__(THREADS, 1)
+flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                  const __grid_constant__ CUtensorMap tmV, Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem + L2::Q_OFF;
+  uint8_t* sK = smem + L2::K_OFF;
+  uint8_t* sV = smem + L2::V_OFF;
+  uint8_t* sP = smem + L2::P_OFF;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L2::BAR_OFF);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;      // [2]
+  uint64_t* k_empty = bars + 3;     // [2]
+  uint64_t* v_full = bars + 5;      // [2]
+  uint64_t* v_empty = bars + 7;     // [2]
+  uint64_t* s_full = bars + 9;      // [2] per query tile
+  uint64_t* s_free = bars + 11;     // [2]
+  uint64_t* p_full = bars + 13;     // [2]
+  uint64_t* p_free = bars + 15;     // one: counts every P.V product
+  uint64_t* o_full = bars + 16;     // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L2::NBARS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* kv_range = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_slot + 2));  // t0, t1
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) return;
+  const int qb = gridDim.x - 1 - blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.Hq / p.Hkv);
+  const int q0 = qb * 2 * BQ;
+  const int shift = p.Sk - p.Sq;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 4);
+      mbar_init(&p_full[i], 4); mbar_init(&o_full[i], 1);
+    }
+    mbar_init(p_free, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc<1>(tmem_slot, 512); tmem_relinquish<1>(); }
+  if (warp == 2) {   // union of the key intervals of all 256 rows
+    int umin = INT_MAX, umax = 0;
+    for (int r = lane; r < 2 * BQ; r += 32) {
+      const int i = q0 + r;
+      if (i >= p.Sq) continue;
+      int lo = p.row_lo ? p.row_lo[(long long)b * p.Sq + i] : 0;
+      int hi = p.row_hi ? p.row_hi[(long long)b * p.Sq + i] : (p.causal ? i + 1 + shift : p.Sk);
+      lo = max(lo, 0); hi = min(hi, p.Sk);
+      if (hi > lo) { umin = min(umin, lo); umax = max(umax, hi); }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      umin = min(umin, __shfl_xor_sync(0xffffffffu, umin, o));
+      umax = max(umax, __shfl_xor_sync(0xffffffffu, umax, o));
+    }
+    if (lane == 0) {
+      kv_range[0] = umax > umin ? umin / BKV : 0;
+      kv_range[1] = umax > umin ? (umax + BKV - 1) / BKV : 0;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int t0 = kv_range[0], n = kv_range[1] - kv_range[0];
+  const long long q_row0 = (long long)b * p.Sq + q0;
+  const long long k_row0 = (long long)b * p.Sk;
+
+  if (warp == 0) {
+    if (lane == 0 && n > 0) {
+      tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+      mbar_expect_tx(q_full, 2 * TILE);
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        tma_load_2d(sQ + t * TILE, &tmQ, q_full, h * HD, (int)(q_row0 + t * BQ));
+        tma_load_2d(sQ + t * TILE + PANEL, &tmQ, q_full, h * HD + 64, (int)(q_row0 + t * BQ));
+      }
+      for (int j = 0; j < n; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        const int krow = (int)(k_row0 + (long long)(t0 + j) * BKV);
+        if (!mbar_wait(&k_empty[s], ph ^ 1, abort_flag, p.status)) break;
+        mbar_expect_tx(&k_full[s], TILE);
+        tma_load_2d(sK + s * TILE, &tmK, &k_full[s], hk * HD, krow);
+        tma_load_2d(sK + s * TILE + PANEL, &tmK, &k_full[s], hk * HD + 64, krow);
+        if (!mbar_wait(&v_empty[s], ph ^ 1, abort_flag, p.status)) break;
+        mbar_expect_tx(&v_full[s], TILE);
+        tma_load_2d(sV + s * TILE, &tmV, &v_full[s], hk * HD, krow);
+        tma_load_2d(sV + s * TILE + PANEL, &tmV, &v_full[s], hk * HD + 64, krow);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && n > 0) {
+      constexpr uint32_t idesc_s = umma_idesc(BQ, BKV, 1, 1, false, false);
+      constexpr uint32_t idesc_o = umma_idesc(BQ, HD, 1, 1, false, true);
+      const uint32_t p_addr = smem_u32(sP);
+      // S_T(j) = Q_T K_j^T into the tile's S columns; the K stage is released after tile B's product
+      auto issue_s = [&](int t, int j) -> bool {
+        const int s = j & 1;
+        if (t == 0 && !mbar_wait(&k_full[s], (j >> 1) & 1, abort_flag, p.status)) return false;
+        if (!mbar_wait(&s_free[t], (j & 1) ^ 1, abort_flag, p.status)) return false;
+        tc_fence_after();
+        const uint32_t q_addr = smem_u32(sQ + t * TILE), k_addr = smem_u32(sK + s * TILE);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {
+          const uint32_t off = (k >> 2) * PANEL + (k & 3) * 32;
+          umma_f16<1>(tmem_base + t * BKV, umma_desc_sw128(q_addr + off, 16, 1024),
+                      umma_desc_sw128(k_addr + off, 16, 1024), idesc_s, k != 0);
+        }
+        umma_commit(&s_full[t]);
+        if (t == 1) umma_commit(&k_empty[s]);
+        return true;
+      };
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.status);
+      ok = ok && issue_s(0, 0) && issue_s(1, 0);
+      for (int j = 0; ok && j < n; ++j) {
+        const int s = j & 1;
+#pragma unroll 1
+        for (int t = 0; t < 2 && ok; ++t) {
+          if (!mbar_wait(&p_full[t], j & 1, abort_flag, p.status)) { ok = false; break; }
+          if (t == 0 && !mbar_wait(&v_full[s], (j >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t v_addr = smem_u32(sV + s * TILE);
+#pragma unroll
+          for (int k = 0; k < BKV / 16; ++k) {
+            const uint32_t a_off = (k >> 2) * PANEL + (k & 3) * 32;
+            umma_f16<1>(tmem_base + 2 * BKV + t * HD, umma_desc_sw128(p_addr + a_off, 16, 1024),
+                        umma_desc_sw128(v_addr + k * 2048, PANEL, 1024), idesc_o, (j | k) != 0);
+          }
+          umma_commit(p_free);
+          umma_commit(&o_full[t]);
+          if (t == 1) umma_commit(&v_empty[s]);
+          if (j + 1 < n) ok = issue_s(t, j + 1);
+        }
+      }
+    }
+  } else {
+    const int t = (warp - 2) >> 2;            // query tile of this warp
+    const int quarter = warp & 3;             // TMEM lane quarter
+    const int r = quarter * 32 + lane;        // row inside the tile
+    const int i = q0 + t * BQ + r;            // global query row
+    const bool row_valid = i < p.Sq;
+    int lo = 0, hi = 0;
+    if (row_valid) {
+      lo = p.row_lo ? p.row_lo[(long long)b * p.Sq + i] : 0;
+      hi = p.row_hi ? p.row_hi[(long long)b * p.Sq + i] : (p.causal ? i + 1 + shift : p.Sk);
+      lo = max(lo, 0); hi = min(hi, p.Sk);
+    }
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const uint32_t s_addr = lane_addr + t * BKV, o_addr = lane_addr + 2 * BKV + t * HD;
+    float m_ref = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n; ++j) {
+      const int kv0 = (t0 + j) * BKV;
+      if (!__all_sync(0xffffffffu, mbar_wait(&s_full[t], j & 1, abort_flag, p.status))) { ok = false; break; }
+      tc_fence_after();
+      float sv[128];
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t tr[32];
+        tmem_ld_32x32(s_addr + cc * 32, tr);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 32; ++c) sv[cc * 32 + c] = __uint_as_float(tr[c]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free[t]);
+      if (!(row_valid && lo <= kv0 && hi >= kv0 + BKV)) {
+#pragma unroll
+        for (int c = 0; c < 128; ++c)
+          if (kv0 + c < lo || kv0 + c >= hi) sv[c] = -INFINITY;
+      }
+      float mx = sv[0];
+#pragma unroll
+      for (int c = 1; c < 128; ++c) mx = fmaxf(mx, sv[c]);
+      // raise the reference maximum only when it pays: a stale one costs nothing while 2^(gap) fits bf16/fp32
+      float alpha = 1.f;
+      const bool raise = (mx > m_ref) && (m_ref == -INFINITY || (mx - m_ref) * p.scale_log2 > RESCALE_THRESHOLD);
+      if (raise) {
+        alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - mx) * p.scale_log2);
+        m_ref = mx;
+        l_run *= alpha;
+      }
+      // the P buffer (shared by both tiles) and this tile's O columns are quiescent once the previous
+      // P.V product, whichever tile it belonged to, has completed
+      const int g = 2 * j + t;
+      if (g > 0 && !__all_sync(0xffffffffu, mbar_wait(p_free, (g - 1) & 1, abort_flag, p.status))) { ok = false; break; }
+      if (j > 0 && __any_sync(0xffffffffu, raise)) {
+        tc_fence_after();
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          uint32_t tr[32];
+          tmem_ld_32x32(o_addr + cc * 32, tr);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) tr[c] = __float_as_uint(__uint_as_float(tr[c]) * alpha);
+          tmem_st_32x32(o_addr + cc * 32, tr);
+        }
+        tmem_st_wait();
+      }
+      const float neg_ms = (m_ref == -INFINITY) ? 0.f : -m_ref * p.scale_log2;
+      float lsum = 0.f;
+      uint8_t* prow = sP + r * 128;
+#pragma unroll
+      for (int c8 = 0; c8 < 16; ++c8) {       // 16 chunks of 8 columns; chunks 0..7 -> panel 0, 8..15 -> panel 1
+        uint32_t pk[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float p0 = fast_exp2(fmaf(sv[c8 * 8 + 2 * q], p.scale_log2, neg_ms));
+          const float p1 = fast_exp2(fmaf(sv[c8 * 8 + 2 * q + 1], p.scale_log2, neg_ms));
+          lsum += p0 + p1;
+          pk[q] = pack_bf16x2(p0, p1);
+        }
+        *reinterpret_cast<uint4*>(prow + (c8 >> 3) * PANEL + (((c8 & 7) ^ (r & 7)) << 4)) =
+            make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      }
+      l_run += lsum;
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[t]);
+    }
+    if (ok && n > 0) ok = __all_sync(0xffffffffu, mbar_wait(&o_full[t], (n - 1) & 1, abort_flag, p.status));
+    if (ok) {
+      if (n > 0) tc_fence_after();
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      __nv_bfloat16* orow = p.O + (((long long)b * p.Sq + i) * p.Hq + h) * HD;
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t tr[32];
+        if (n > 0) {
+          tmem_ld_32x32(o_addr + cc * 32, tr);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) tr[c] = 0u;
+        }
+        if (row_valid) {
+#pragma unroll
+          for (int c = 0; c < 32; c += 8) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(tr[c]) * inv, __uint_as_float(tr[c + 1]) * inv);
+            v.y = pack_bf16x2(__uint_as_float(tr[c + 2]) * inv, __uint_as_float(tr[c + 3]) * inv);
+            v.z = pack_bf16x2(__uint_as_float(tr[c + 4]) * inv, __uint_as_float(tr[c + 5]) * inv);
+            v.w = pack_bf16x2(__uint_as_float(tr[c + 6]) * inv, __uint_as_float(tr[c + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + cc * 32 + c) = v;
+          }
+        }
+      }
+      if (row_valid)
+        p.lse[((long long)b * p.Hq + h) * p.Sq + i] =
+            l_run > 0.f ? (m_ref * p.scale_log2 + log2f(l_run)) * 0.6931471805599453f : -INFINITY;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    const uint64_t t_start = globaltimer_ns();
+    while (globaltimer_ns() - t_start < 200000ull) __nanosleep(1000);
+  }
+  if (warp == 1) { tc_fence_after(); tmem_dealloc<1>(tmem_base, 512); }
+}
+
+}  // namespace
+
+// Same contract as atb_flash_fwd (flash_attn.cu).
+extern "C" int atb_flash_fwd_v2(const void* q, const void* k, const void* v, void* o, float* lse, const int* row_lo,
+                                const int* row_hi, int B, int Sq, int Sk, int Hq, int Hkv, long long q_stride,
+                                long long k_stride, long long v_stride, int causal, float softmax_scale, void* stream,
+                                int* status) {
+  if (B <= 0 || Sq <= 0 || Sk <= 0) return 0;
+  if (Hq % Hkv) return -1;
+  if ((q_stride | k_stride | v_stride) & 7) return -1;
+  CUtensorMap tmQ, tmK, tmV;
+  if (!make_tmap_2d(&tmQ, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)B * Sq, (uint64_t)Hq * HD, q_stride, BQ,
+                    64, CU_TENSOR_MAP_SWIZZLE_128B))
+    return -2;
+  if (!make_tmap_2d(&tmK, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)B * Sk, (uint64_t)Hkv * HD, k_stride,
+                    BKV, 64, CU_TENSOR_MAP_SWIZZLE_128B))
+    return -2;
+  if (!make_tmap_2d(&tmV, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)B * Sk, (uint64_t)Hkv * HD, v_stride,
+                    BKV, 64, CU_TENSOR_MAP_SWIZZLE_128B))
+    return -2;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(flash_fwd2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L2::TOTAL) != cudaSuccess)
+      return -4;
+    attr_set = true;
+  }
+  Params p;
+  p.O = (__nv_bfloat16*)o; p.lse = lse; p.row_lo = row_lo; p.row_hi = row_hi;
+  p.B = B; p.Sq = Sq; p.Sk = Sk; p.Hq = Hq; p.Hkv = Hkv; p.causal = causal;
+  p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.status = status;
+  dim3 grid((Sq + 2 * BQ - 1) / (2 * BQ), Hq, B);
+  flash_fwd2_kernel<<<grid, THREADS, L2::TOTAL, (cudaStream_t)stream>>>(tmQ, tmK, tmV, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
