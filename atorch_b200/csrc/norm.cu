@@ -342,6 +342,7 @@ extern "C" int atb_colsum(const float* partial, void* out, int P, int N, int out
 // ------------------------------------------------------------------------------------------------
 #include <mutex>
 #include <cstdio>
+#include "no_alloc.h"   // the declarations below must match the header that callers compile against
 
 namespace {
 constexpr int NA_MAX_PARTS = 148;   // one partial row per SM

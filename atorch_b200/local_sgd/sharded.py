@@ -31,7 +31,14 @@ class ShardedLocalSGD:
         self.replica_group = engine.cfg.replica_group
         self.replicas = engine.replicas
         self.global_step = 0
-        self.last_synced = engine.master.detach().clone()
+        # The baseline of the pseudo-gradient is the state at the END of the synchronous warm-up (the
+        # reference creates last_synced_params lazily at its first sync, which it runs before the
+        # first local step: FSDP/core/_runtime_utils.py:106). Taking it any earlier would make the
+        # whole warm-up progress show up as one huge pseudo-gradient in the first outer step.
+        self.last_synced = torch.empty_like(engine.master)
+        self._baseline_set = False
+        if cfg.local_sgd_warmup_steps <= 0:
+            self.reset_baseline()
         temp = cfg.weight_softmax_temperature
         if cfg.pseudo_gradnorm_reduce and temp is None:
             temp = 1.0
@@ -62,10 +69,14 @@ class ShardedLocalSGD:
         if self.should_sync() and self.replicas > 1:
             self.sync()
         self.global_step += 1
+        if not self._baseline_set and self.global_step >= self.cfg.local_sgd_warmup_steps:
+            self.reset_baseline()                     # last synchronous step done: replicas are identical
 
     @torch.no_grad()
     def sync(self) -> None:
         eng, cfg = self.engine, self.cfg
+        if not self._baseline_set:
+            self.reset_baseline()
         pg = self.last_synced - eng.master
         kw = {}
         if cfg.skip_anomaly or cfg.pseudo_gradnorm_reduce or cfg.clip_pseudo_grad is not None:
@@ -106,9 +117,16 @@ class ShardedLocalSGD:
         eng.master.copy_(self.last_synced)
         eng.sync_working_copy()
 
+    @torch.no_grad()
+    def reset_baseline(self) -> None:
+        """Take the current master shard as the last synchronised weights (end of the warm-up, or after
+        the parameters were replaced by a state-dict load)."""
+        self.last_synced.copy_(self.engine.master)
+        self._baseline_set = True
+
     def state_dict(self) -> dict:
         sd = {"global_step": self.global_step, "outer_steps": self.outer_steps,
-              "last_synced": self.last_synced.detach().cpu()}
+              "last_synced": (self.last_synced if self._baseline_set else self.engine.master).detach().cpu()}
         if self.fused is not None:
             sd["outer_optim"] = [{"momentum_buffer": self.momentum.cpu(), "rank": self.engine.rank, **self.fused}]
         elif self.outer_optimizer is not None:
@@ -120,6 +138,7 @@ class ShardedLocalSGD:
     def load_state_dict(self, sd: dict) -> None:
         self.global_step, self.outer_steps = sd["global_step"], sd.get("outer_steps", 0)
         self.last_synced.copy_(sd["last_synced"])
+        self._baseline_set = True
         if self.fused is not None and "outer_optim" in sd:
             self.momentum.copy_(sd["outer_optim"][0]["momentum_buffer"])
         elif self.outer_optimizer is not None and "outer_optim" in sd:

@@ -123,7 +123,7 @@ class LlamaDecoderLayer(nn.Module):
         self.post_attention_layernorm = RMSNorm(h, config.rms_norm_eps)
         self.gate_up_proj = nn.Linear(h, 2 * config.intermediate_size, bias=False)
         self.down_proj = nn.Linear(config.intermediate_size, h, bias=False)
-        self._attn_cache = collections.deque(maxlen=64)
+        self._attn_cache = collections.OrderedDict()   # pass token -> (out, lse), see ops/flash.py
 
     @staticmethod
     def _proj(mod: nn.Module, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -195,24 +195,36 @@ def flash_attention_qkv(qkv: torch.Tensor, num_heads: int, causal: bool = True, 
                         recompute_cache=None, **mask_kwargs):
     """qkv: ``[B, S, 3*num_heads, D]``; returns ``[B, S, num_heads, D]``.
 
-    ``recompute_cache`` (a deque owned by the calling layer) lets an activation-checkpointed block keep
-    the attention output and log-sum-exp of its first (no-grad) pass: that pass appends ``(out, lse)``,
-    the recomputation pops it and skips the forward kernel. 32 MB per layer at 7B scale buys one
-    attention forward per layer per step."""
+    ``recompute_cache`` (an ``OrderedDict`` owned by the calling layer) lets an activation-checkpointed
+    block keep the attention output and log-sum-exp of its first (no-grad) pass: that pass stores
+    ``(out, lse)`` under the pass token of its checkpoint node (utils/checkpoint.py), the recomputation
+    of the same node takes the entry with the same token and skips the forward kernel. A forward that
+    is not the first pass of a checkpointed block has no token and neither stores nor reads, and an
+    entry whose backward never ran is evicted once more than ``RECOMPUTE_CACHE_LIMIT`` are held.
+    32 MB per layer at 7B scale buys one attention forward per layer per step."""
+    from ..utils.checkpoint import current_pass
+
     B, S, _, D = qkv.shape
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
     lo, hi = row_intervals(B, S, S, qkv.device, causal, mask_kwargs.get("glm_mask"), mask_kwargs.get("pack_glm_mask"),
                            mask_kwargs.get("key_padding_mask"), mask_kwargs.get("cu_seqlens"))
     cached = None
-    if recompute_cache is not None:
-        if not torch.is_grad_enabled():
+    cur = current_pass() if recompute_cache is not None else None
+    if cur is not None:
+        token, is_recompute = cur
+        if not is_recompute and not torch.is_grad_enabled():
             H = num_heads
             out, lse = flash_fwd_raw(qkv[:, :, :H], qkv[:, :, H: 2 * H], qkv[:, :, 2 * H:], bool(causal), float(scale),
                                      lo, hi)
-            recompute_cache.append((out, lse))
+            recompute_cache[token] = (out, lse)
+            while len(recompute_cache) > RECOMPUTE_CACHE_LIMIT:
+                recompute_cache.popitem(last=False)
             return out
-        if len(recompute_cache) > 0:
-            cached = recompute_cache.popleft()
-            if cached[0].shape != (B, S, num_heads, D):
+        if is_recompute:
+            cached = recompute_cache.pop(token, None)
+            if cached is not None and cached[0].shape != (B, S, num_heads, D):
                 cached = None
     return _FlashAttnQKV.apply(qkv, num_heads, bool(causal), float(scale), lo, hi, cached)
+
+
+RECOMPUTE_CACHE_LIMIT = 16   # first passes in flight per layer (pipeline micro-batches) before eviction

@@ -37,6 +37,7 @@ import torch.nn as nn
 from torch.utils._pytree import tree_flatten, tree_unflatten
 
 from .. import ops
+from ..utils.checkpoint import checkpoint_pass, new_pass_token
 
 ALIGN = 8  # elements: 16 bytes in bf16, so every parameter can be a TMA operand
 
@@ -92,6 +93,7 @@ class FlatUnit:
         self.checkpoint = False
         self.orig_forward = None
         self.has_trainable = any(p.requires_grad for p in self.params)
+        self._zero_ranges: Optional[List[Tuple[int, int]]] = None
 
     # flat <-> parameter views -----------------------------------------------------------------
     def views(self, flat: torch.Tensor) -> List[torch.Tensor]:
@@ -100,6 +102,40 @@ class FlatUnit:
     def shard_range(self, rank: Optional[int] = None) -> Tuple[int, int]:
         r = self.engine.rank if rank is None else rank
         return r * self.shard_numel, (r + 1) * self.shard_numel
+
+    def uncovered_ranges(self, covered: Sequence[bool]) -> List[Tuple[int, int]]:
+        """Ranges of the flat buffer NOT inside a parameter flagged in ``covered``: alignment gaps,
+        the tail padding and the parameters left out. Adjacent ranges are merged."""
+        out: List[Tuple[int, int]] = []
+        pos = 0
+        for o, n, c in zip(self.offsets, self.numels, covered):
+            if c:
+                if o > pos:
+                    out.append((pos, o))
+                pos = o + n
+        if pos < self.padded_numel:
+            out.append((pos, self.padded_numel))
+        return out
+
+    def trainable_shard_segments(self) -> List[Tuple[int, int]]:
+        """Maximal runs of trainable parameters inside this rank's shard, as (start, end) offsets in the
+        shard. A run includes the alignment gaps between its parameters (and the tail padding when the
+        last parameter is trainable): their master values and gradients are zero, so an optimizer
+        update leaves them zero. Frozen parameters are never part of a run."""
+        lo, hi = self.shard_range()
+        segs: List[Tuple[int, int]] = []
+        bounds = list(self.offsets[1:]) + [self.padded_numel]
+        for o, nxt, p in zip(self.offsets, bounds, self.params):
+            if not p.requires_grad:
+                continue
+            s, e = max(o, lo), min(nxt, hi)
+            if e <= s:
+                continue
+            if segs and segs[-1][1] == s - lo:
+                segs[-1] = (segs[-1][0], e - lo)
+            else:
+                segs.append((s - lo, e - lo))
+        return segs
 
     def param_shard_slices(self) -> List[Tuple[int, int, int]]:
         """For each parameter: (start in this rank's shard, length, start inside the parameter)."""
@@ -131,7 +167,8 @@ class _UnitFn(torch.autograd.Function):
         eng._pre_forward(unit)
         if unit.checkpoint:
             ctx.save_for_backward(*[flat[i] for i in ctx.tensor_idx])
-            with torch.no_grad():
+            ctx.token = new_pass_token()
+            with torch.no_grad(), checkpoint_pass(ctx.token, False):
                 args, kwargs = tree_unflatten(flat, spec)
                 out = unit.orig_forward(*args, **kwargs)
             ctx.inner = None
@@ -172,7 +209,7 @@ class _UnitFn(torch.autograd.Function):
                 inner_in.append(d)
             ac_on, ac_dt = ctx.autocast
             cm = torch.autocast(eng.device.type, dtype=ac_dt) if ac_on else contextlib.nullcontext()
-            with torch.enable_grad(), cm:
+            with torch.enable_grad(), cm, checkpoint_pass(ctx.token, True):
                 args, kwargs = tree_unflatten(flat, ctx.spec)
                 out = unit.orig_forward(*args, **kwargs)
         else:
@@ -474,7 +511,6 @@ class FSDPEngine:
         if self._direct_grads():
             self._ensure_grad_shard()
             u.full_grad = self.grad_shard[u.shard_offset: u.shard_offset + u.padded_numel]
-            zero_all = False
         elif self.fused:
             if u.is_root:
                 buf, u._gbuf_idx = self._root_gbuf, -1
@@ -487,20 +523,24 @@ class FSDPEngine:
                     self._gbuf_events[idx] = None
             u._gbuf = buf
             u.full_grad = buf.tensor[: u.padded_numel]
-            zero_all = False
         else:
             u.full_grad = torch.empty(u.padded_numel, dtype=self.compute_dtype, device=self.device)
-            zero_all = False
         first_ok = self._first_write_ok()
         if not first_ok:
             u.full_grad.zero_()
+        else:
+            # only parameters whose gradient kernel overwrites on first touch may stay uninitialised:
+            # alignment gaps, tail padding, frozen parameters and every other parameter start at zero
+            # (the whole buffer is reduced, normed and fed to the optimizer)
+            if u._zero_ranges is None:
+                u._zero_ranges = u.uncovered_ranges(
+                    [p.requires_grad and getattr(p, "_atb_direct_grad", False) for p in u.params])
+            for s0, e0 in u._zero_ranges:
+                u.full_grad[s0:e0].zero_()
         for v, p in zip(u.views(u.full_grad), u.params):
             if p.requires_grad:
-                if first_ok:
-                    if getattr(p, "_atb_direct_grad", False):
-                        p._atb_first = True           # the writing kernel overwrites instead of accumulating
-                    else:
-                        v.zero_()
+                if first_ok and getattr(p, "_atb_direct_grad", False):
+                    p._atb_first = True               # the writing kernel overwrites instead of accumulating
                 p.grad = v
                 p.main_grad = v
 
@@ -753,6 +793,8 @@ class FSDPEngine:
                 if n:
                     ms[s: s + n].copy_(sd[name].reshape(-1)[ps: ps + n].to(torch.float32))
         self.sync_working_copy()
+        if self.local_sgd is not None:
+            self.local_sgd.reset_baseline()       # new weights: the next pseudo-gradient starts from them
         for n, b in self.module.named_buffers():
             if n in sd:
                 b.copy_(sd[n])
@@ -925,6 +967,7 @@ class FusedShardedOptimizer:
         self.step_count = 0
         self.state: Dict = {}
         self._units_stepped = 0
+        self._segs: Optional[List[Tuple[int, int]]] = None
         if getattr(engine, "fused", False) and engine.cfg.optimizer_in_backward and kind == "adamw" \
                 and max_grad_norm is None:
             engine._fused_opt = self
@@ -943,6 +986,22 @@ class FusedShardedOptimizer:
                                  pg["lr"], b1, b2, pg["eps"], pg["weight_decay"], self.step_count + 1,
                                  grad_scale=1.0 / eng.world, numel=u.padded_numel, max_blocks=eng.cfg.comm_blocks)
         self._units_stepped += 1
+
+    def _segments(self) -> List[Tuple[int, int]]:
+        """Ranges of the global shard buffers that the step updates: everything when all parameters
+        train (one launch), otherwise the runs of trainable parameters - frozen parameters get neither
+        an update nor weight decay."""
+        if self._segs is None:
+            segs: List[Tuple[int, int]] = []
+            for u in self.engine.units:
+                for s0, e0 in u.trainable_shard_segments():
+                    a, b = u.shard_offset + s0, u.shard_offset + e0
+                    if segs and segs[-1][1] == a:
+                        segs[-1] = (segs[-1][0], b)
+                    else:
+                        segs.append((a, b))
+            self._segs = segs
+        return self._segs
 
     def _ensure_state(self):
         if self.exp_avg is None:
@@ -973,14 +1032,17 @@ class FusedShardedOptimizer:
             scale_t = (self.max_grad_norm / (total + 1e-6)).clamp(max=1.0).float().reshape(1)
             self.last_grad_norm = total
         b1, b2 = pg["betas"]
-        if self.kind == "agd":
-            ops.agd_step(eng.master, self.exp_avg, self.exp_avg_sq, g, eng.lp_shard, pg["lr"], b1, b2, pg["delta"],
-                         pg["weight_decay"], self.step_count, grad_scale_tensor=scale_t, clip=self.clip,
-                         decouple=self.weight_decouple, fixed_decay=self.fixed_decay)
-        else:
-            ops.adamw_step(eng.master, self.exp_avg, self.exp_avg_sq, g, eng.lp_shard, pg["lr"], b1, b2, pg["eps"],
-                           pg["weight_decay"], self.step_count, grad_scale_tensor=scale_t,
-                           adamw_mode=self.kind == "adamw")
+        for s0, e0 in self._segments():
+            sl = slice(s0, e0)
+            lp = eng.lp_shard[sl] if eng.lp_shard is not None else None
+            if self.kind == "agd":
+                ops.agd_step(eng.master[sl], self.exp_avg[sl], self.exp_avg_sq[sl], g[sl], lp, pg["lr"], b1, b2,
+                             pg["delta"], pg["weight_decay"], self.step_count, grad_scale_tensor=scale_t,
+                             clip=self.clip, decouple=self.weight_decouple, fixed_decay=self.fixed_decay)
+            else:
+                ops.adamw_step(eng.master[sl], self.exp_avg[sl], self.exp_avg_sq[sl], g[sl], lp, pg["lr"], b1, b2,
+                               pg["eps"], pg["weight_decay"], self.step_count, grad_scale_tensor=scale_t,
+                               adamw_mode=self.kind == "adamw")
         eng.invalidate_gathered()
         if eng.local_sgd is not None:
             eng.local_sgd.after_optimizer_step()

@@ -8,10 +8,42 @@ replays identically.
 """
 from __future__ import annotations
 
-from typing import Any, Callable
+import contextlib
+import itertools
+import threading
+from typing import Any, Callable, Optional, Tuple
 
 import torch
 from torch.utils._pytree import tree_flatten, tree_unflatten
+
+# ---------------------------------------------------------------------------------------------
+# Pass tokens. The no-grad first pass of a checkpointed block and the recomputation of the SAME
+# block in the backward pass run under one shared token, so an operator inside the block can keep a
+# result of the first pass for the recomputation (ops/flash.py keeps attention output + lse) and be
+# certain that the two belong together. A forward that is not the first pass of a checkpointed block
+# (validation without .eval(), reference log-probs, a dry run) has no token and caches nothing.
+# ---------------------------------------------------------------------------------------------
+_tokens = itertools.count(1)
+_tls = threading.local()
+
+
+def new_pass_token() -> int:
+    return next(_tokens)
+
+
+@contextlib.contextmanager
+def checkpoint_pass(token: int, recompute: bool):
+    prev = getattr(_tls, "cur", None)
+    _tls.cur = (token, recompute)
+    try:
+        yield
+    finally:
+        _tls.cur = prev
+
+
+def current_pass() -> Optional[Tuple[int, bool]]:
+    """``(token, is_recompute)`` while a checkpointed block runs its first pass or its recomputation."""
+    return getattr(_tls, "cur", None)
 
 
 class _Checkpoint(torch.autograd.Function):
@@ -26,7 +58,8 @@ class _Checkpoint(torch.autograd.Function):
         if preserve_rng:
             ctx.cpu_rng = torch.get_rng_state()
             ctx.cuda_rng = torch.cuda.get_rng_state() if torch.cuda.is_available() else None
-        with torch.no_grad():
+        ctx.token = new_pass_token()
+        with torch.no_grad(), checkpoint_pass(ctx.token, False):
             args, kwargs = tree_unflatten(list(tensors), spec)
             out = run(*args, **kwargs)
         return out
@@ -47,7 +80,7 @@ class _Checkpoint(torch.autograd.Function):
             if ctx.cuda_rng is not None:
                 cuda_now = torch.cuda.get_rng_state()
                 torch.cuda.set_rng_state(ctx.cuda_rng)
-        with torch.enable_grad():
+        with torch.enable_grad(), checkpoint_pass(ctx.token, True):
             args, kwargs = tree_unflatten(flat, ctx.spec)
             out = ctx.run(*args, **kwargs)
         if ctx.preserve_rng:

@@ -155,3 +155,36 @@ def test_llama_block_reuses_attention_in_recompute():
     checkpoint_module(layer, x, cos, sin).float().pow(2).sum().backward()
     assert _lib.launch_count - before == with_cache + 1      # one more flash forward
     assert torch.equal(g1, x.grad)
+
+
+def test_recompute_cache_ignores_plain_no_grad_forward():
+    """A no-grad forward in train() mode (validation without .eval(), reference log-probs) must neither
+    fill the recompute cache nor be served to a later checkpointed step."""
+    from atorch_b200.models.llama import LlamaConfig, LlamaDecoderLayer
+    from atorch_b200.ops.elementwise import rope_tables
+    from atorch_b200.utils.checkpoint import checkpoint_module
+
+    cfg = LlamaConfig(vocab_size=64, hidden_size=256, intermediate_size=512, num_hidden_layers=1,
+                      num_attention_heads=2, num_key_value_heads=2, max_position_embeddings=256)
+    torch.manual_seed(3)
+    layer = LlamaDecoderLayer(cfg).cuda().bfloat16().train()
+    cos, sin = rope_tables(256, 128, device="cuda")
+    other = torch.randn(2, 256, 256, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        layer(other, cos, sin)                      # same shapes, different batch
+    assert len(layer._attn_cache) == 0
+    x = torch.randn(2, 256, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    checkpoint_module(layer, x, cos, sin).float().pow(2).sum().backward()
+    g_cache = x.grad.clone()
+    x.grad = None
+    cfg.reuse_attention_in_recompute = False
+    checkpoint_module(layer, x, cos, sin).float().pow(2).sum().backward()
+    assert torch.equal(g_cache, x.grad)
+    # a first pass whose backward never runs leaves one entry; it is not handed to another node
+    cfg.reuse_attention_in_recompute = True
+    y_lost = checkpoint_module(layer, other.clone().requires_grad_(), cos, sin)
+    del y_lost
+    assert len(layer._attn_cache) == 1
+    x.grad = None
+    checkpoint_module(layer, x, cos, sin).float().pow(2).sum().backward()
+    assert torch.equal(g_cache, x.grad)

@@ -136,3 +136,47 @@ def _state_dict_roundtrip(rank, world):
 
 def test_state_dict_and_clip():
     run_distributed(_state_dict_roundtrip, world=2)
+
+
+def _frozen_odd(rank, world, device_type):
+    """Odd-sized bias (alignment gaps, tail padding) and one frozen parameter: the sharded gradient norm
+    equals the unsharded one and the frozen weights neither move nor decay."""
+    from atorch_b200.auto import auto_accelerate
+
+    dev = torch.device(device_type, rank) if device_type == "cuda" else torch.device("cpu")
+    dtype_kw = [("amp_native", {"dtype": torch.bfloat16})] if device_type == "cuda" else []
+
+    def make():
+        torch.manual_seed(7)
+        m = nn.Sequential(nn.Linear(24, 37), nn.Tanh(), nn.Linear(37, 13), nn.Tanh(), nn.Linear(13, 5))
+        m[2].weight.requires_grad_(False)
+        return m
+
+    ok, res, _ = auto_accelerate(make(), torch.optim.AdamW, optim_args={"lr": 1e-2, "weight_decay": 0.1},
+                                 load_strategy=["parallel_mode", ("fsdp", {"atorch_wrap_cls": (nn.Linear,)})] + dtype_kw)
+    assert ok
+    ref = make().to(dev)
+    g = torch.Generator().manual_seed(11)
+    xs = [torch.randn(world * 4, 24, generator=g) for _ in range(3)]
+    frozen0 = ref[2].weight.detach().clone()
+    opt = torch.optim.AdamW([p for p in ref.parameters() if p.requires_grad], lr=1e-2, weight_decay=0.1)
+    tol = 5e-2 if device_type == "cuda" else 1e-5
+    for x in xs:
+        res.optim.zero_grad()
+        res.model(x[rank * 4:(rank + 1) * 4].to(dev)).float().pow(2).mean().backward()
+        norm = res.model.engine.grad_norm(2.0)
+        opt.zero_grad()
+        ref(x.to(dev)).pow(2).mean().backward()
+        ref_norm = torch.sqrt(sum(p.grad.float().pow(2).sum() for p in ref.parameters() if p.grad is not None))
+        assert torch.isfinite(norm)
+        assert abs(norm.item() - ref_norm.item()) <= tol * max(1.0, ref_norm.item()), (norm.item(), ref_norm.item())
+        res.optim.step()
+        opt.step()
+    sd = res.model.state_dict()
+    assert torch.equal(sd["2.weight"].to(frozen0.device).to(frozen0.dtype), frozen0)
+    for (n, p) in ref.named_parameters():
+        assert torch.allclose(sd[n].to(p.device), p.detach().float(), atol=10 * tol, rtol=10 * tol), n
+
+
+def test_fsdp_frozen_and_odd_sizes_gloo():
+    run_distributed(_frozen_odd, world=2, args=("cpu",))

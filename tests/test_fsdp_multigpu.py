@@ -74,3 +74,10 @@ def test_fsdp_two_gpus_tracks_single_gpu(tmp_path):
         res.optim.step()
         single.append(loss.item())
     assert max(abs(x - y) for x, y in zip(multi, single)) < 0.08, (multi, single)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_fsdp_frozen_and_odd_sizes_two_gpus():
+    from tests.test_fsdp_cpu import _frozen_odd
+
+    run_distributed(_frozen_odd, world=2, args=("cuda",), backend="nccl", timeout=300)

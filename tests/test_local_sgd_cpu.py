@@ -122,3 +122,47 @@ def _plain_average(rank, world):
 
 def test_plain_average():
     run_distributed(_plain_average, world=2)
+
+
+def _warmup_baseline(rank, world):
+    """With warm-up steps the first outer step starts from the weights at the END of the warm-up: the
+    pseudo-gradient of the first sync is only the drift of the local steps, never the warm-up progress.
+    Checked against the outer Nesterov step written out by hand."""
+    import torch.distributed as dist
+    import torch.nn as nn
+
+    from atorch_b200.auto import auto_accelerate
+    from atorch_b200.local_sgd import LocalSGDConfig, OuterOptimizerConfig
+
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(8, 8), nn.Tanh(), nn.Linear(8, 2))
+    fs = {"atorch_wrap_cls": (nn.Linear,), "use_local_sgd": True,
+          "local_sgd_config": LocalSGDConfig(local_sgd_sync_interval=2, local_sgd_warmup_steps=3),
+          "outer_optim_config": OuterOptimizerConfig(torch.optim.SGD, {"lr": 0.7, "momentum": 0.9, "nesterov": True})}
+    ok, res, _ = auto_accelerate(model, torch.optim.SGD, optim_args={"lr": 0.1},
+                                 load_strategy=[("parallel_mode", ([("zero", 1), ("data", 2)], None)), ("fsdp", fs)])
+    assert ok
+    eng, lsgd = res.model.engine, res.model.engine.local_sgd
+    g = torch.Generator().manual_seed(rank)
+    base = None
+    for step in range(4):
+        res.optim.zero_grad()
+        res.model(torch.randn(4, 8, generator=g)).pow(2).mean().backward()
+        if step == 3:                               # first local step; the sync follows its inner update
+            mean_grad = eng.finalize_grads().clone()
+            dist.all_reduce(mean_grad)
+            mean_grad /= world
+        res.optim.step()
+        if step == 2:                               # end of the synchronous warm-up
+            assert lsgd._baseline_set and torch.equal(lsgd.last_synced, eng.master)
+            base = eng.master.clone()
+    assert lsgd.outer_steps == 1
+    pg = 0.1 * mean_grad                            # base - mean_r(base - 0.1 * g_r)
+    expect = base - 0.7 * (pg + 0.9 * pg)           # first outer step: momentum buffer = pg
+    assert torch.allclose(eng.master, expect, atol=1e-6), (eng.master - expect).abs().max()
+
+
+def test_sharded_local_sgd_warmup_baseline_gloo():
+    from tests.dist_utils import run_distributed
+
+    run_distributed(_warmup_baseline, world=2)

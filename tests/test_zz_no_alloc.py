@@ -56,11 +56,14 @@ def _noalloc(L, dy, x, w, rstd, dt):
     return dx, dw
 
 
-@pytest.mark.parametrize("dtype,dt", [(torch.bfloat16, 0), (torch.float32, 2)])
-def test_noalloc_matches_regular_twice(dtype, dt):
+# size pairs: the second call of each pair is smaller, so stale scratch lies beyond what it writes;
+# (5, 8192) sits on the N limit with fewer rows than partial slots, (3, 8) is the smallest legal N
+@pytest.mark.parametrize("sizes", [[(777, 4096), (300, 1024)], [(5, 8192), (3, 8)]])
+@pytest.mark.parametrize("dtype,dt", [(torch.bfloat16, 0), (torch.float16, 1), (torch.float32, 2)])
+def test_noalloc_matches_regular_twice(dtype, dt, sizes):
     L = _raw_lib()
     torch.manual_seed(11)
-    for call, (M, N) in enumerate([(777, 4096), (300, 1024)]):   # second call: smaller, stale scratch beyond it
+    for call, (M, N) in enumerate(sizes):
         x = torch.randn(M, N, device="cuda", dtype=dtype)
         dy = torch.randn(M, N, device="cuda", dtype=dtype)
         w = (1 + 0.1 * torch.randn(N, device="cuda")).to(dtype)
