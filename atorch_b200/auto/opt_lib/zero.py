@@ -71,11 +71,15 @@ def build_sharded_model(model_context, cfg: dict, reshard_after_forward: bool = 
         backward_prefetch=bool(cfg.pop("backward_prefetch", True)),
         sync_module_states=cfg.pop("sync_module_states", False),
         param_init_fn=cfg.pop("param_init_fn", None), device=device,
-        checkpoint_units=cfg.pop("checkpoint_units", False), fused_comm=cfg.pop("fused_comm", False),
-        optimizer_in_backward=cfg.pop("optimizer_in_backward", False), comm_blocks=cfg.pop("comm_blocks", 32))
+        checkpoint_units=cfg.pop("checkpoint_units", False), fused_comm=cfg.pop("fused_comm", None),
+        optimizer_in_backward=cfg.pop("optimizer_in_backward", False), comm_blocks=cfg.pop("comm_blocks", 32),
+        prefetch_depth=int(cfg.pop("prefetch_depth", 2)))
+    # torch FSDP's limit_all_gathers (a rate limiter of in-flight all-gathers) maps onto the bounded
+    # prefetch depth of this engine: at most prefetch_depth + 1 units are ever gathered at once
+    cfg.pop("limit_all_gathers", None)
     use_local_sgd = cfg.pop("use_local_sgd", False)
     lsgd = {k: cfg.pop(k, None) for k in ("local_sgd_config", "outer_optim_config", "gta_config")}
-    for k in ("limit_all_gathers", "use_orig_params", "cpu_offload", "auto_wrap_policy", "wrap_trainable_outmost",
+    for k in ("use_orig_params", "cpu_offload", "auto_wrap_policy", "wrap_trainable_outmost",
               "intra_load", "fsdp_wrap_params_outmost", "backward_prefetch_policy", "ignored_modules",
               "keep_low_precision_grads"):
         cfg.pop(k, None)

@@ -160,11 +160,12 @@ inline int grid_for(long long work, int threads) {
 // grad_dtype: 0 bf16, 2 fp32. Buffers must be 16-byte aligned.
 extern "C" int atb_adamw(float* master, float* m, float* v, const void* grad, void* param_bf16, long long n, float lr,
                          float beta1, float beta2, float eps, float weight_decay, int step, float grad_scale,
-                         const float* grad_scale_ptr, int adamw_mode, int grad_dtype, void* stream) {
+                         const float* grad_scale_ptr, int adamw_mode, int grad_dtype, int max_blocks, void* stream) {
   if (n <= 0) return 0;
   AdamArgs a{lr, beta1, beta2, eps, weight_decay, 1.f - powf(beta1, (float)step), 1.f - powf(beta2, (float)step),
              grad_scale, adamw_mode};
-  const int grid = grid_for((n + 3) / 4, 256);
+  int grid = grid_for((n + 3) / 4, 256);
+  if (max_blocks > 0 && grid > max_blocks) grid = max_blocks;   // leave room for kernels sharing the SMs
   cudaStream_t st = (cudaStream_t)stream;
   if (grad_dtype == 0)
     adamw_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(master, m, v, (const __nv_bfloat16*)grad,

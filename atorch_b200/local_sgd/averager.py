@@ -12,6 +12,13 @@ parameter on the CPU and copies per parameter, atorch/local_sgd/DDP/outer_optim_
 the pseudo-gradient of the whole model is one subtraction, one all-reduce and, for SGD/Nesterov,
 one fused update kernel (``ops.outer_sgd_step``, csrc/optim.cu). Other outer optimizer classes run
 as ordinary torch optimizers on the flat ``last_synced`` parameter.
+
+On 2 to 8 GPUs of one NVSwitch domain, plain SGD/Nesterov without reducer, anomaly skipping or clipping
+takes ONE kernel for the whole outer step (csrc/comm.cu ``p2p_allreduce_nesterov_kernel``): the
+replicas' parameters sit in a symmetric buffer, every rank owns 1/W of the outer state (synchronised
+weights and momentum), reduces the mean of its slice over the peers (peer loads or multimem.ld_reduce),
+applies the Nesterov update and hands the new weights to every replica - no pseudo-gradient tensor,
+no separate all-reduce, and the outer state costs 1/W of the memory.
 (Reference: atorch/local_sgd/DDP/outer_optim_model_averager.py:17-194,
 stateful_post_localSGD_optimizer.py:6-20.)
 """
@@ -62,6 +69,8 @@ class OuterOptimPeriodicModelAverager:
         self._offsets: List[int] = []
         self.anomaly_detectors: Optional[List[OnlineDynamicEWMA]] = None
         self.outer_steps = 0
+        self._symm = None                  # symmetric parameter buffer of the one-kernel outer step
+        self._slice = None                 # (lo, hi) of this rank's part of the outer state
 
     # ------------------------------------------------------------------------------- state
     def state_dict(self) -> Dict:
@@ -70,7 +79,8 @@ class OuterOptimPeriodicModelAverager:
             sd["outer_optimizer"] = torch.utils._pytree.tree_map(
                 lambda x: x.cpu() if isinstance(x, torch.Tensor) else x, self.outer_optimizer.state_dict())
         elif self._fused_sgd is not None and self.momentum_buf is not None:
-            sd["outer_optimizer"] = {"fused_sgd": dict(self._fused_sgd), "momentum_buffer": self.momentum_buf.cpu(),
+            sd["outer_optimizer"] = {"fused_sgd": dict(self._fused_sgd),
+                                     "momentum_buffer": self._full_state(self.momentum_buf).cpu(),
                                      "outer_steps": self.outer_steps}
         if self.anomaly_detectors is not None:
             sd["anomaly_detectors"] = [d.state_dict() for d in self.anomaly_detectors]
@@ -87,9 +97,23 @@ class OuterOptimPeriodicModelAverager:
             for d, s in zip(self.anomaly_detectors, sd["anomaly_detectors"]):
                 d.load_state_dict(s)
 
+    def _full_state(self, t: torch.Tensor) -> torch.Tensor:
+        """Outer-state tensor over the whole model (all-gathered when it is sharded 1/W per rank)."""
+        if self._slice is None:
+            return t
+        world = dist.get_world_size(self.process_group)
+        full = torch.empty(t.numel() * world, dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(full, t.contiguous(), group=self.process_group)
+        return full[: self._numel]
+
     def _load_outer(self, osd) -> None:
         if "fused_sgd" in osd:
-            self.momentum_buf.copy_(osd["momentum_buffer"])
+            mb = osd["momentum_buffer"]
+            if self._slice is not None:
+                pad = torch.zeros(self._symm.numel, dtype=mb.dtype)
+                pad[: mb.numel()] = mb
+                mb = pad[self._slice[0]: self._slice[1]]
+            self.momentum_buf.copy_(mb)
             self.outer_steps = int(osd.get("outer_steps", 1))
         elif self.outer_optimizer is not None:
             self.outer_optimizer.load_state_dict(osd)
@@ -102,10 +126,13 @@ class OuterOptimPeriodicModelAverager:
             self._offsets.append(off)
             off += p.numel()
         flat = torch.cat([p.detach().reshape(-1).float() for p in params])
-        self.last_synced = torch.nn.Parameter(flat)
+        self._numel = flat.numel()
         cls, kw = self.outer_optim_config.outer_optim_class, dict(self.outer_optim_config.outer_optim_kwargs)
         plain_sgd = cls is torch.optim.SGD and not kw.get("dampening") and not kw.get("weight_decay") \
             and not kw.get("maximize")
+        if plain_sgd and self._one_kernel_possible(dev):
+            flat = self._setup_one_kernel(flat, dev)       # this rank's slice of the synchronised weights
+        self.last_synced = torch.nn.Parameter(flat)
         if plain_sgd:
             self._fused_sgd = dict(lr=kw.get("lr", 1e-3), momentum=kw.get("momentum", 0.0),
                                    nesterov=bool(kw.get("nesterov", False)))
@@ -119,6 +146,32 @@ class OuterOptimPeriodicModelAverager:
             c = self.local_sgd_config
             self.anomaly_detectors = [OnlineDynamicEWMA(c.ewma_alpha, c.ewma_warmup_steps, c.ewma_threshold)
                                       for _ in params]
+
+    def _one_kernel_possible(self, dev) -> bool:
+        import os
+
+        if dev.type != "cuda" or self.reducer is not None or self.skip_anomaly or self.pseudo_gradnorm_reduce \
+                or self.clip_pseudo_grad is not None or os.environ.get("ATB_FUSED_COMM", "1") == "0":
+            return False
+        from ..parallel import symm
+
+        return symm.available() and 1 < dist.get_world_size(self.process_group) <= 8
+
+    def _setup_one_kernel(self, flat: torch.Tensor, dev) -> torch.Tensor:
+        from ..parallel import symm
+
+        world, rank = dist.get_world_size(self.process_group), dist.get_rank(self.process_group)
+        n = (flat.numel() + 4 * world - 1) // (4 * world) * (4 * world)
+        try:
+            self._symm = symm.SymmetricBuffer(n, torch.float32, self.process_group, dev)
+        except Exception:
+            self._symm = None
+            return flat
+        sl = n // world
+        self._slice = (rank * sl, (rank + 1) * sl)
+        padded = torch.zeros(n, dtype=torch.float32, device=dev)
+        padded[: flat.numel()] = flat
+        return padded[self._slice[0]: self._slice[1]].clone()
 
     def should_sync(self) -> bool:
         return self.step >= self.warmup_steps and (self.step - self.warmup_steps) % self.local_sgd_sync_interval == 0
@@ -155,7 +208,23 @@ class OuterOptimPeriodicModelAverager:
             off += p.numel()
         return offs
 
+    def _outer_step_one_kernel(self, plist) -> None:
+        buf, f = self._symm, self._fused_sgd
+        buf.wait_peers_done()                      # peers may still pull the previous result out of this buffer
+        off = 0
+        for p in plist:                            # the replicas' current parameters, fp32, into the symmetric buffer
+            buf.tensor[off: off + p.numel()].copy_(p.detach().reshape(-1))
+            off += p.numel()
+        if off < buf.numel:
+            buf.tensor[off:].zero_()
+        buf.allreduce_nesterov(self.last_synced.data, self.momentum_buf, f["lr"], f["momentum"], f["nesterov"],
+                               self.outer_steps == 0 or f["momentum"] == 0.0)
+        self.outer_steps += 1
+        self._write_back(plist, buf.tensor)        # every replica's buffer now holds the new weights
+
     def _outer_step(self, plist, world) -> None:
+        if self._symm is not None:
+            return self._outer_step_one_kernel(plist)
         cur = torch.cat([p.detach().reshape(-1).float() for p in plist])
         pg = self.last_synced.data - cur
         weight_kw = {}

@@ -35,7 +35,14 @@ class ShardedLocalSGD:
         # reference creates last_synced_params lazily at its first sync, which it runs before the
         # first local step: FSDP/core/_runtime_utils.py:106). Taking it any earlier would make the
         # whole warm-up progress show up as one huge pseudo-gradient in the first outer step.
-        self.last_synced = torch.empty_like(engine.master)
+        self._symm, self._slice = None, None
+        kw0 = dict(outer.outer_optim_kwargs)
+        plain_sgd = outer.outer_optim_class is torch.optim.SGD and not kw0.get("weight_decay") and not kw0.get("dampening")
+        if plain_sgd and self._one_kernel_possible():
+            self._setup_one_kernel()
+        # with the one-kernel outer step every replica keeps 1/R of the outer state of its shard
+        n_state = engine.master.numel() if self._slice is None else self._slice[1] - self._slice[0]
+        self.last_synced = torch.empty(n_state, dtype=torch.float32, device=engine.master.device)
         self._baseline_set = False
         if cfg.local_sgd_warmup_steps <= 0:
             self.reset_baseline()
@@ -55,6 +62,43 @@ class ShardedLocalSGD:
         self.outer_steps = 0
         self.detector = OnlineDynamicEWMA(cfg.ewma_alpha, cfg.ewma_warmup_steps, cfg.ewma_threshold) \
             if cfg.skip_anomaly else None
+
+    def _one_kernel_possible(self) -> bool:
+        """The whole outer step as ONE kernel over peer memory (csrc/comm.cu p2p_allreduce_nesterov_kernel):
+        plain SGD/Nesterov, no reducer / anomaly skipping / clipping, 2..8 replicas on one NVSwitch domain."""
+        cfg, eng = self.cfg, self.engine
+        if not eng.on_cuda or self.replicas < 2 or self.replicas > 8 or cfg.skip_anomaly or cfg.pseudo_gradnorm_reduce \
+                or cfg.clip_pseudo_grad is not None or self.gta.reducer is not None \
+                or os.environ.get("ATB_FUSED_COMM", "1") == "0":
+            return False
+        from ..parallel import symm
+
+        return symm.available()
+
+    def _setup_one_kernel(self) -> None:
+        from ..parallel import symm
+
+        eng, R = self.engine, self.replicas
+        n = (eng.master.numel() + 4 * R - 1) // (4 * R) * (4 * R)
+        try:
+            self._symm = symm.SymmetricBuffer(n, torch.float32, self.replica_group, eng.device)
+        except Exception:
+            self._symm = None
+            return
+        r = dist.get_rank(self.replica_group)
+        self._slice = (r * (n // R), (r + 1) * (n // R))
+
+    def _master_slice(self) -> torch.Tensor:
+        """This rank's part of the (zero-padded) master shard, as the outer state is laid out."""
+        m = self.engine.master
+        if self._slice is None:
+            return m
+        lo, hi = self._slice
+        out = torch.zeros(hi - lo, dtype=m.dtype, device=m.device)
+        e = min(hi, m.numel())
+        if e > lo:
+            out[: e - lo] = m[lo:e]
+        return out
 
     def skip_replica_reduce(self) -> bool:
         """Replica all-reduce of gradients is needed only during the synchronous warm-up."""
@@ -77,6 +121,18 @@ class ShardedLocalSGD:
         eng, cfg = self.engine, self.cfg
         if not self._baseline_set:
             self.reset_baseline()
+        if self._symm is not None:
+            buf, f, n = self._symm, self.fused, eng.master.numel()
+            buf.wait_peers_done()
+            buf.tensor[:n].copy_(eng.master)
+            if n < buf.numel:
+                buf.tensor[n:].zero_()
+            buf.allreduce_nesterov(self.last_synced, self.momentum, f["lr"], f["momentum"], f["nesterov"],
+                                   self.outer_steps == 0 or f["momentum"] == 0.0)
+            self.outer_steps += 1
+            eng.master.copy_(buf.tensor[:n])
+            eng.sync_working_copy()
+            return
         pg = self.last_synced - eng.master
         kw = {}
         if cfg.skip_anomaly or cfg.pseudo_gradnorm_reduce or cfg.clip_pseudo_grad is not None:
@@ -121,12 +177,13 @@ class ShardedLocalSGD:
     def reset_baseline(self) -> None:
         """Take the current master shard as the last synchronised weights (end of the warm-up, or after
         the parameters were replaced by a state-dict load)."""
-        self.last_synced.copy_(self.engine.master)
+        self.last_synced.copy_(self._master_slice())
         self._baseline_set = True
 
     def state_dict(self) -> dict:
         sd = {"global_step": self.global_step, "outer_steps": self.outer_steps,
-              "last_synced": (self.last_synced if self._baseline_set else self.engine.master).detach().cpu()}
+              "last_synced": (self.last_synced if self._baseline_set else self._master_slice()).detach().cpu(),
+              "state_slice": self._slice}
         if self.fused is not None:
             sd["outer_optim"] = [{"momentum_buffer": self.momentum.cpu(), "rank": self.engine.rank, **self.fused}]
         elif self.outer_optimizer is not None:

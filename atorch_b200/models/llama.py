@@ -80,15 +80,19 @@ class LlamaConfig:
         per_layer = h * (h + 2 * kv) + h * h + 3 * h * f + 2 * h
         return L * per_layer + v * h * (1 if self.tie_word_embeddings else 2) + h
 
-    def flops_per_token(self, seq_len: int, recompute: bool = False) -> float:
+    def flops_per_token(self, seq_len: int, recompute: bool = False, attention_recompute: bool = True) -> float:
         """Megatron-convention matmul FLOPs per token of one training step (fwd + bwd = 3x fwd; the
         layer part counts 4x with activation recomputation), as in
-        examples/llama2/example_utils.py:146-183 of the reference."""
+        examples/llama2/example_utils.py:146-183 of the reference. With ``attention_recompute=False``
+        the attention product is counted 3x even under recomputation: blocks that keep the attention
+        output and log-sum-exp of their first pass do not execute it a second time."""
         h, f, v, L = self.hidden_size, self.intermediate_size, self.vocab_size, self.num_hidden_layers
         kv = self.num_key_value_heads * self.head_dim
-        layer = 2 * h * (h + 2 * kv) + 2 * h * h + 6 * h * f + 4 * seq_len * h
+        proj = 2 * h * (h + 2 * kv) + 2 * h * h + 6 * h * f
+        attn = 4 * seq_len * h
         head = 2 * h * v
-        return L * layer * (4 if recompute else 3) + head * 3
+        mult = 4 if recompute else 3
+        return L * (proj * mult + attn * (mult if attention_recompute else 3)) + head * 3
 
 
 class RMSNorm(nn.Module):

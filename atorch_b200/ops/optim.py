@@ -34,10 +34,12 @@ def adamw_reference(master, m, v, grad, param_lp, lr, beta1, beta2, eps, weight_
 def adamw_step(master: torch.Tensor, m: torch.Tensor, v: torch.Tensor, grad: torch.Tensor,
                param_lp: Optional[torch.Tensor], lr: float, beta1: float, beta2: float, eps: float,
                weight_decay: float, step: int, grad_scale: float = 1.0,
-               grad_scale_tensor: Optional[torch.Tensor] = None, adamw_mode: bool = True) -> None:
+               grad_scale_tensor: Optional[torch.Tensor] = None, adamw_mode: bool = True,
+               max_blocks: int = 0) -> None:
     """One fused AdamW step on flat fp32 ``master/m/v`` from a flat bf16/fp32 ``grad``; writes the
     bf16 working copy ``param_lp`` (may be None). ``grad_scale_tensor`` is an optional device scalar
-    multiplied into the gradient (clipping coefficient computed on the device)."""
+    multiplied into the gradient (clipping coefficient computed on the device). ``max_blocks`` caps the grid
+    (0 = enough CTAs to fill the GPU) for launches meant to share the SMs with other kernels."""
     n = master.numel()
     ok = (_lib.use_kernels(master, grad) and master.dtype == torch.float32 and grad.dtype in (torch.bfloat16, torch.float32)
           and (param_lp is None or param_lp.dtype == torch.bfloat16))
@@ -48,7 +50,7 @@ def adamw_step(master: torch.Tensor, m: torch.Tensor, v: torch.Tensor, grad: tor
                               ctypes.c_longlong(n), ctypes.c_float(lr), ctypes.c_float(beta1), ctypes.c_float(beta2),
                               ctypes.c_float(eps), ctypes.c_float(weight_decay), ctypes.c_int(step),
                               ctypes.c_float(grad_scale), _lib.ptr(grad_scale_tensor), ctypes.c_int(int(adamw_mode)),
-                              ctypes.c_int(_lib.DT[grad.dtype]), _lib.stream_ptr())
+                              ctypes.c_int(_lib.DT[grad.dtype]), ctypes.c_int(max_blocks), _lib.stream_ptr())
     _lib.check(rc, "atb_adamw")
 
 

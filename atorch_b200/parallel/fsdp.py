@@ -28,6 +28,7 @@ from __future__ import annotations
 
 import contextlib
 import math
+import os
 from dataclasses import dataclass, field
 from typing import Any, Callable, Dict, Iterable, List, Optional, Sequence, Set, Tuple, Union
 
@@ -59,9 +60,11 @@ class ShardingConfig:
     param_init_fn: Optional[Callable[[nn.Module], None]] = None
     device: Optional[torch.device] = None
     checkpoint_units: bool = False                           # recompute each non-root unit in backward
-    fused_comm: bool = False                                 # peer-memory reduce-scatter kernels instead of NCCL
-    optimizer_in_backward: bool = False                      # fuse the AdamW step into the reduce-scatter
+    fused_comm: Optional[bool] = None                        # own collectives over peer memory instead of NCCL
+    #                                                          (None: on when available, unless ATB_FUSED_COMM=0)
+    optimizer_in_backward: bool = False                      # AdamW of a unit right after its reduce-scatter
     comm_blocks: int = 32                                    # CTAs a fused collective may occupy
+    prefetch_depth: int = 2                                  # units gathered ahead of the computing one
     autocast: bool = True                                    # run forward under autocast(param_dtype)
 
 
@@ -246,7 +249,13 @@ class FSDPEngine:
         self.compute_dtype = config.param_dtype or torch.float32
         self.mixed = self.compute_dtype != torch.float32
         self.reduce_dtype = config.reduce_dtype or self.compute_dtype
-        self.comm_stream = torch.cuda.Stream(self.device) if (self.on_cuda and self.world * self.replicas > 1) else None
+        multi = self.on_cuda and self.world * self.replicas > 1
+        # all-gathers and reduce-scatters run on streams of their own, so that the prefetch of the
+        # next unit's parameters never queues behind the reduction of the previous unit's gradients
+        self.ag_stream = torch.cuda.Stream(self.device) if multi else None
+        self.rs_stream = torch.cuda.Stream(self.device) if multi else None
+        self.opt_stream = None                # 1-rank optimizer-in-backward (see FusedShardedOptimizer)
+        self._rs_group = None                 # second communicator for NCCL reduce-scatters (lazy)
         self.ignored = ignored_params or set()
         self.units: List[FlatUnit] = []
         self.exec_order: List[FlatUnit] = []
@@ -256,6 +265,7 @@ class FSDPEngine:
         self._shard_params: Optional[List[Tuple[str, nn.Parameter]]] = None
         self.training_step = 0
         self.local_sgd = None            # set by local_sgd.sharded.attach_local_sgd
+        self.accumulation_boundary = True  # False while micro-batches of one step are still being accumulated
         self._fp32_accum = False
         self._build(unit_modules)
 
@@ -310,16 +320,29 @@ class FSDPEngine:
         self.lp_shard = torch.zeros(off, dtype=self.compute_dtype, device=dev) if self.mixed else None
         for u in self.units:
             self._init_unit_storage(u)
+        self._non_root_units = [x for x in self.units if not x.is_root]
+        self._non_root_index = {id(x): i for i, x in enumerate(self._non_root_units)}
         self._wrap_unit_forwards()
         self._setup_fused_comm()
 
+    N_GRAD_BUFFERS = 3
+
     def _setup_fused_comm(self) -> None:
-        """Symmetric gradient buffers for the fused reduce-scatter kernels: two rotating buffers of
-        the largest non-root unit plus one for the root unit (which stays live for the whole backward)."""
+        """Own collectives over NVLink peer memory (parallel/symm.py, csrc/comm.cu):
+
+        * the low-precision working shards live in ONE symmetric buffer; a unit is all-gathered by the
+          copy engines straight out of the peers' shards (no SM, no NCCL kernel next to the GEMMs);
+        * gradients are written into symmetric buffers - ``N_GRAD_BUFFERS`` rotating ones of the largest
+          non-root unit plus one for the root unit, which stays live for the whole backward - and
+          reduce-scattered by a kernel that reads the peers' slices (or lets the switch add them) and
+          writes the fp32 gradient shard or runs AdamW in the same pass."""
         self.fused = False
         self._fused_opt = None
-        if not (self.cfg.fused_comm and self.on_cuda and 1 < self.world <= 8 and self.replicas == 1
-                and self.compute_dtype in (torch.bfloat16, torch.float32)):
+        want = self.cfg.fused_comm
+        if want is None:
+            want = os.environ.get("ATB_FUSED_COMM", "1") != "0"
+        if not (want and self.on_cuda and 1 < self.world <= 8 and self.replicas == 1
+                and self.compute_dtype == torch.bfloat16):
             return
         from . import symm
 
@@ -328,18 +351,30 @@ class FSDPEngine:
         try:
             non_root = [u.padded_numel for u in self.units if not u.is_root and u.has_trainable]
             self._gbufs = [symm.SymmetricBuffer(max(non_root), self.compute_dtype, self.group, self.device)
-                           for _ in range(2)] if non_root else []
+                           for _ in range(self.N_GRAD_BUFFERS)] if non_root else []
             root = self.units[-1]
             self._root_gbuf = symm.SymmetricBuffer(root.padded_numel, self.compute_dtype, self.group, self.device) \
                 if root.has_trainable else None
+            self._lp_symm = symm.SymmetricBuffer(self.total_shard, self.compute_dtype, self.group, self.device)
         except Exception as e:   # symmetric memory unavailable on this system: keep the NCCL path
             import logging
 
             logging.getLogger("atorch.logger").warning("fused collectives disabled: %s", e)
             return
-        self._gbuf_events = [None, None]
+        self._lp_symm.tensor.copy_(self.lp_shard)
+        self.lp_shard = self._lp_symm.tensor
+        self._gbuf_events = [None] * self.N_GRAD_BUFFERS
         self._gbuf_rr = 0
+        self._param_seq = self._lp_symm.signal(symm.CH_READY)     # this rank's parameters are in place
+        self._ready_waited = 0
         self.fused = True
+
+    def _params_changed(self) -> None:
+        """The working shards were rewritten on the current stream (optimizer step, state-dict load)."""
+        if self.fused:
+            from . import symm
+
+            self._param_seq = self._lp_symm.signal(symm.CH_READY)
 
     def _materialize_meta(self, unit_set) -> None:
         """Give meta-device parameters real storage on the target device, module by module."""
@@ -430,6 +465,8 @@ class FSDPEngine:
     def _free_full(self, u: FlatUnit) -> None:
         if self.world == 1:
             return
+        if u.gather_event is not None:            # a prefetch still in flight writes into this storage
+            torch.cuda.current_stream(self.device).wait_event(u.gather_event)
         u.full.untyped_storage().resize_(0)
         u.gathered = False
         u.gather_event = None
@@ -443,13 +480,26 @@ class FSDPEngine:
             return
         self._alloc_full(u)
         src = self._shard_src(u)
-        if self.comm_stream is not None:
+        if self.fused:
+            from . import symm
+
             cur = torch.cuda.current_stream(self.device)
-            self.comm_stream.wait_stream(cur)
-            with torch.cuda.stream(self.comm_stream):
+            self.ag_stream.wait_stream(cur)       # earlier users of the buffer's memory come first
+            with torch.cuda.stream(self.ag_stream):
+                if self._ready_waited != self._param_seq:      # once per parameter version
+                    self._lp_symm.wait(symm.CH_READY, self._param_seq)
+                    self._ready_waited = self._param_seq
+                self._lp_symm.copy_engine_all_gather(u.full, u.shard_offset, u.shard_numel)
+                ev = torch.cuda.Event()
+                ev.record(self.ag_stream)
+            u.gather_event = ev
+        elif self.ag_stream is not None:
+            cur = torch.cuda.current_stream(self.device)
+            self.ag_stream.wait_stream(cur)
+            with torch.cuda.stream(self.ag_stream):
                 dist.all_gather_into_tensor(u.full, src, group=self.group)
                 ev = torch.cuda.Event()
-                ev.record(self.comm_stream)
+                ev.record(self.ag_stream)
             u.gather_event = ev
         else:
             dist.all_gather_into_tensor(u.full, src, group=self.group)
@@ -467,17 +517,16 @@ class FSDPEngine:
         if torch.is_grad_enabled():
             self.exec_order.append(u)
         if self.cfg.forward_prefetch and self.world > 1:
-            nxt = self._next_in_order(u)
-            if nxt is not None:
+            for nxt in self._next_in_order(u):
                 self._unshard(nxt)
 
-    def _next_in_order(self, u: FlatUnit) -> Optional[FlatUnit]:
-        us = [x for x in self.units if not x.is_root]
-        try:
-            i = us.index(u)
-        except ValueError:
-            return None
-        return us[i + 1] if i + 1 < len(us) else None
+    def _next_in_order(self, u: FlatUnit) -> List[FlatUnit]:
+        """The ``prefetch_depth`` units that follow ``u`` in the forward pass."""
+        us = self._non_root_units
+        i = self._non_root_index.get(id(u))
+        if i is None:
+            return []
+        return us[i + 1: i + 1 + max(1, self.cfg.prefetch_depth)]
 
     def _post_forward(self, u: FlatUnit) -> None:
         if self.cfg.reshard_after_forward and not u.is_root:
@@ -515,12 +564,13 @@ class FSDPEngine:
             if u.is_root:
                 buf, u._gbuf_idx = self._root_gbuf, -1
             else:
-                idx = self._gbuf_rr % 2
+                idx = self._gbuf_rr % self.N_GRAD_BUFFERS
                 self._gbuf_rr += 1
                 buf, u._gbuf_idx = self._gbufs[idx], idx
-                if self._gbuf_events[idx] is not None:   # the previous reduce-scatter out of this buffer
+                if self._gbuf_events[idx] is not None:   # this rank's previous reduce-scatter out of this buffer
                     torch.cuda.current_stream(self.device).wait_event(self._gbuf_events[idx])
                     self._gbuf_events[idx] = None
+            buf.wait_peers_done()                        # ... and the peers' reads of it (bounded wait kernel)
             u._gbuf = buf
             u.full_grad = buf.tensor[: u.padded_numel]
         else:
@@ -550,8 +600,8 @@ class FSDPEngine:
         self._alloc_grads(u)
         if self.cfg.backward_prefetch and self.world > 1 and u in self.exec_order:
             i = self.exec_order.index(u)
-            if i > 0:
-                self._unshard(self.exec_order[i - 1])
+            for j in range(i - 1, max(i - 1 - max(1, self.cfg.prefetch_depth), -1), -1):
+                self._unshard(self.exec_order[j])
 
     def _post_backward(self, u: FlatUnit) -> None:
         self._reduce_grads(u)
@@ -568,6 +618,8 @@ class FSDPEngine:
         g = u.full_grad
         if g is None:
             return
+        if self._fused_opt is not None:
+            self._fused_opt.guard(u)
         for v, p in zip(u.views(g), u.params):
             if getattr(p, "_atb_first", False):       # no kernel wrote this gradient in this backward
                 v.zero_()
@@ -577,6 +629,9 @@ class FSDPEngine:
                 del p.main_grad
         u.full_grad = None
         if self._direct_grads():
+            opt = self._fused_opt
+            if opt is not None and opt.in_backward_ready(u):
+                opt.local_unit_step(u)                # AdamW of this unit overlaps the rest of the backward
             u.fresh = False                           # gradients already sit in the global buffer
             return
         self._ensure_grad_shard()
@@ -595,15 +650,15 @@ class FSDPEngine:
             return
         rd = g if g.dtype == self.reduce_dtype else g.to(self.reduce_dtype)
         out = torch.empty(u.shard_numel, dtype=self.reduce_dtype, device=self.device)
-        if self.comm_stream is not None:
+        if self.rs_stream is not None:
             cur = torch.cuda.current_stream(self.device)
-            self.comm_stream.wait_stream(cur)
-            cm = torch.cuda.stream(self.comm_stream)
+            self.rs_stream.wait_stream(cur)
+            cm = torch.cuda.stream(self.rs_stream)
         else:
             cm = contextlib.nullcontext()
         with cm:
             if self.world > 1:
-                dist.reduce_scatter_tensor(out, rd, op=dist.ReduceOp.SUM, group=self.group)
+                dist.reduce_scatter_tensor(out, rd, op=dist.ReduceOp.SUM, group=self._reduce_group())
             else:
                 out.copy_(rd)
             if self.replicas > 1 and not (self.local_sgd is not None and self.local_sgd.skip_replica_reduce()):
@@ -613,30 +668,40 @@ class FSDPEngine:
                 dst.mul_(scale)
             else:
                 dst.add_(out, alpha=scale)
-        if self.comm_stream is not None:
-            rd.record_stream(self.comm_stream)
-            out.record_stream(self.comm_stream)
-            g.record_stream(self.comm_stream)
+        if self.rs_stream is not None:
+            rd.record_stream(self.rs_stream)
+            out.record_stream(self.rs_stream)
+            g.record_stream(self.rs_stream)
         u.fresh = False
 
+    def _reduce_group(self):
+        """NCCL path: reduce-scatters use a communicator of their own (same ranks as the shard group), so
+        that they do not serialise with the all-gather prefetch inside one communicator's stream."""
+        if not self.on_cuda or os.environ.get("ATB_NCCL_SPLIT_STREAMS", "1") == "0":
+            return self.group
+        if self._rs_group is None:
+            ranks = dist.get_process_group_ranks(self.group if self.group is not None else dist.group.WORLD)
+            self._rs_group = dist.new_group(ranks)
+        return self._rs_group
+
     def _reduce_grads_fused(self, u: FlatUnit, dst: torch.Tensor, scale: float) -> None:
-        """One kernel per unit on the communication stream: peers' gradient slices are summed over
-        NVLink in registers and land in the fp32 gradient shard - or, with ``optimizer_in_backward``,
-        go straight through the AdamW update into master / moments / working shard."""
+        """One kernel per unit on the reduction stream: the peers' gradient slices are summed over
+        NVLink (peer loads in registers, or multimem.ld_reduce in the switch) and land in the fp32
+        gradient shard - or, with ``optimizer_in_backward``, go straight through the AdamW update into
+        master / moments / working shard."""
         cur = torch.cuda.current_stream(self.device)
-        self.comm_stream.wait_stream(cur)
+        self.rs_stream.wait_stream(cur)
         buf = u._gbuf
-        with torch.cuda.stream(self.comm_stream):
+        with torch.cuda.stream(self.rs_stream):
             opt = self._fused_opt
-            if opt is not None and opt.in_backward_ready():
-                so = u.shard_offset
-                opt.fused_unit_step(buf, u, so)
+            if opt is not None and opt.in_backward_ready(u):
+                opt.fused_unit_step(buf, u, u.shard_offset)
             else:
                 buf.reduce_scatter_into(dst, scale=scale, accumulate=not u.fresh, numel=u.padded_numel,
                                         max_blocks=self.cfg.comm_blocks)
             if u._gbuf_idx >= 0:
                 ev = torch.cuda.Event()
-                ev.record(self.comm_stream)
+                ev.record(self.rs_stream)
                 self._gbuf_events[u._gbuf_idx] = ev
         u.fresh = False
 
@@ -647,8 +712,7 @@ class FSDPEngine:
         self._unshard(root)
         self._wait_unshard(root)
         if self.world > 1 and self.cfg.forward_prefetch:
-            first = next((x for x in self.units if not x.is_root), None)
-            if first is not None:
+            for first in self._non_root_units[: max(1, self.cfg.prefetch_depth)]:
                 self._unshard(first)
         if torch.is_grad_enabled():
             self._alloc_grads(root)
@@ -680,8 +744,10 @@ class FSDPEngine:
                 self._reduce_grads(u)
             if not u.is_root and self.world > 1 and u.gathered:
                 self._free_full(u)
-        if self.comm_stream is not None:
-            torch.cuda.current_stream(self.device).wait_stream(self.comm_stream)
+        if self.rs_stream is not None:
+            torch.cuda.current_stream(self.device).wait_stream(self.rs_stream)
+        if self.opt_stream is not None:
+            torch.cuda.current_stream(self.device).wait_stream(self.opt_stream)
         self._bwd_pending = False
         self._final_cb_queued = False
 
@@ -733,6 +799,7 @@ class FSDPEngine:
 
     def invalidate_gathered(self) -> None:
         """Parameters changed (optimizer step, state-dict load): gathered copies are stale."""
+        self._params_changed()
         if self.world > 1:
             for u in self.units:
                 if u.gathered:
@@ -966,17 +1033,35 @@ class FusedShardedOptimizer:
         self.exp_avg_sq: Optional[torch.Tensor] = None
         self.step_count = 0
         self.state: Dict = {}
-        self._units_stepped = 0
-        self._segs: Optional[List[Tuple[int, int]]] = None
-        if getattr(engine, "fused", False) and engine.cfg.optimizer_in_backward and kind == "adamw" \
-                and max_grad_norm is None:
+        self._stepped: Set[int] = set()          # ids of the units already updated in this backward pass
+        self._segs: Dict = {}
+        if engine.cfg.optimizer_in_backward and max_grad_norm is None and engine.mixed and (
+                (getattr(engine, "fused", False) and kind == "adamw")
+                or (engine.world == 1 and engine.replicas == 1 and engine.on_cuda)):
             engine._fused_opt = self
 
-    def in_backward_ready(self) -> bool:
-        return self.engine.mixed or self.engine.compute_dtype == torch.float32
+    # ----------------------------------------------------------------- optimizer inside the backward
+    def in_backward_ready(self, u) -> bool:
+        """May unit ``u`` be updated right after its gradients are complete? Only on the boundary
+        micro-batch of a step whose gradients were not accumulated, and only for units without frozen
+        parameters (the per-unit kernels update the whole shard of the unit)."""
+        eng = self.engine
+        self.guard(u)
+        return (eng.accumulation_boundary and u.fresh and u.has_trainable
+                and all(p.requires_grad for p in u.params))
+
+    def guard(self, u) -> None:
+        if id(u) in self._stepped:
+            raise RuntimeError(
+                "optimizer_in_backward: a second backward pass reached a unit that was already updated in "
+                "this step. With gradient accumulation call set_gradient_accumulation_boundary(False) "
+                "before every micro-batch but the last one of a step.")
+
+    def set_gradient_accumulation_boundary(self, flag: bool) -> None:
+        self.engine.accumulation_boundary = bool(flag)
 
     def fused_unit_step(self, buf, u, so: int) -> None:
-        """Reduce-scatter + AdamW of one unit inside the backward pass (called on the communication stream)."""
+        """Reduce-scatter + AdamW of one unit inside the backward pass (called on the reduction stream)."""
         self._ensure_state()
         eng, pg = self.engine, self.param_groups[0]
         n = u.shard_numel
@@ -985,23 +1070,55 @@ class FusedShardedOptimizer:
         buf.reduce_scatter_adamw(eng.master[so: so + n], self.exp_avg[so: so + n], self.exp_avg_sq[so: so + n], lp,
                                  pg["lr"], b1, b2, pg["eps"], pg["weight_decay"], self.step_count + 1,
                                  grad_scale=1.0 / eng.world, numel=u.padded_numel, max_blocks=eng.cfg.comm_blocks)
-        self._units_stepped += 1
+        self._stepped.add(id(u))
 
-    def _segments(self) -> List[Tuple[int, int]]:
+    def local_unit_step(self, u) -> None:
+        """One rank: the update of unit ``u`` runs on a side stream while the backward pass goes on. The
+        memory-bound optimizer kernel shares the SMs with the compute-bound GEMMs (its grid is capped so
+        that GEMM CTAs still fit beside it), which hides most of its 28 bytes per parameter."""
+        self._ensure_state()
+        eng = self.engine
+        if eng.opt_stream is None:
+            eng.opt_stream = torch.cuda.Stream(eng.device)
+        cur = torch.cuda.current_stream(eng.device)
+        eng.opt_stream.wait_stream(cur)
+        sl = slice(u.shard_offset, u.shard_offset + u.shard_numel)
+        with torch.cuda.stream(eng.opt_stream):
+            self._update(sl, eng.grad_shard, self.step_count + 1, None, max_blocks=2 * 148)
+        self._stepped.add(id(u))
+
+    # -------------------------------------------------------------------------------- ordinary step
+    def _update(self, sl: slice, g: torch.Tensor, step: int, scale_t, max_blocks: int = 0) -> None:
+        eng, pg = self.engine, self.param_groups[0]
+        b1, b2 = pg["betas"]
+        lp = eng.lp_shard[sl] if eng.lp_shard is not None else None
+        if self.kind == "agd":
+            ops.agd_step(eng.master[sl], self.exp_avg[sl], self.exp_avg_sq[sl], g[sl], lp, pg["lr"], b1, b2,
+                         pg["delta"], pg["weight_decay"], step, grad_scale_tensor=scale_t,
+                         clip=self.clip, decouple=self.weight_decouple, fixed_decay=self.fixed_decay)
+        else:
+            ops.adamw_step(eng.master[sl], self.exp_avg[sl], self.exp_avg_sq[sl], g[sl], lp, pg["lr"], b1, b2,
+                           pg["eps"], pg["weight_decay"], step, grad_scale_tensor=scale_t,
+                           adamw_mode=self.kind == "adamw", max_blocks=max_blocks)
+
+    def _segments(self, skip: Optional[Set[int]] = None) -> List[Tuple[int, int]]:
         """Ranges of the global shard buffers that the step updates: everything when all parameters
         train (one launch), otherwise the runs of trainable parameters - frozen parameters get neither
-        an update nor weight decay."""
-        if self._segs is None:
+        an update nor weight decay. Units whose id is in ``skip`` are left out."""
+        key = frozenset(skip) if skip else None
+        if key not in self._segs:
             segs: List[Tuple[int, int]] = []
             for u in self.engine.units:
+                if skip and id(u) in skip:
+                    continue
                 for s0, e0 in u.trainable_shard_segments():
                     a, b = u.shard_offset + s0, u.shard_offset + e0
                     if segs and segs[-1][1] == a:
                         segs[-1] = (segs[-1][0], b)
                     else:
                         segs.append((a, b))
-            self._segs = segs
-        return self._segs
+            self._segs[key] = segs
+        return self._segs[key]
 
     def _ensure_state(self):
         if self.exp_avg is None:
@@ -1014,35 +1131,25 @@ class FusedShardedOptimizer:
     def step(self, closure=None):
         loss = closure() if closure is not None else None
         eng = self.engine
-        if eng.__dict__.get("_fused_opt") is self and self._units_stepped > 0:
-            # every unit was updated by its reduce-scatter kernel during the backward pass
-            self._units_stepped = 0
-            self.step_count += 1
-            if eng.comm_stream is not None:
-                torch.cuda.current_stream(eng.device).wait_stream(eng.comm_stream)
-            eng.invalidate_gathered()
-            return loss
-        g = eng.finalize_grads()
+        stepped, self._stepped = self._stepped, set()
+        if stepped:
+            # these units were updated during the backward pass; wait for those kernels
+            cur = torch.cuda.current_stream(eng.device)
+            for st in (eng.rs_stream, eng.opt_stream):
+                if st is not None:
+                    cur.wait_stream(st)
+        todo = self._segments(stepped)
         self._ensure_state()
         self.step_count += 1
-        pg = self.param_groups[0]
-        scale_t = None
-        if self.max_grad_norm is not None and self.max_grad_norm > 0:
-            total = eng.grad_norm(2.0)
-            scale_t = (self.max_grad_norm / (total + 1e-6)).clamp(max=1.0).float().reshape(1)
-            self.last_grad_norm = total
-        b1, b2 = pg["betas"]
-        for s0, e0 in self._segments():
-            sl = slice(s0, e0)
-            lp = eng.lp_shard[sl] if eng.lp_shard is not None else None
-            if self.kind == "agd":
-                ops.agd_step(eng.master[sl], self.exp_avg[sl], self.exp_avg_sq[sl], g[sl], lp, pg["lr"], b1, b2,
-                             pg["delta"], pg["weight_decay"], self.step_count, grad_scale_tensor=scale_t,
-                             clip=self.clip, decouple=self.weight_decouple, fixed_decay=self.fixed_decay)
-            else:
-                ops.adamw_step(eng.master[sl], self.exp_avg[sl], self.exp_avg_sq[sl], g[sl], lp, pg["lr"], b1, b2,
-                               pg["eps"], pg["weight_decay"], self.step_count, grad_scale_tensor=scale_t,
-                               adamw_mode=self.kind == "adamw")
+        if todo:
+            g = eng.finalize_grads()
+            scale_t = None
+            if self.max_grad_norm is not None and self.max_grad_norm > 0:
+                total = eng.grad_norm(2.0)
+                scale_t = (self.max_grad_norm / (total + 1e-6)).clamp(max=1.0).float().reshape(1)
+                self.last_grad_norm = total
+            for s0, e0 in todo:
+                self._update(slice(s0, e0), g, self.step_count, scale_t)
         eng.invalidate_gathered()
         if eng.local_sgd is not None:
             eng.local_sgd.after_optimizer_step()

@@ -135,8 +135,10 @@ def run_ours(args):
     strategy = [
         ("parallel_mode", ([("data", world)], None)),
         ("fsdp", {"atorch_wrap_cls": (LlamaDecoderLayer,), "forward_prefetch": True, "limit_all_gathers": True,
-                  "sync_module_states": False, "fused_comm": os.environ.get("ATB_FUSED_COMM", "0") == "1",
-                  "optimizer_in_backward": os.environ.get("ATB_OPT_IN_BACKWARD", "0") == "1"}),
+                  "sync_module_states": False,
+                  "fused_comm": {"0": False, "1": True}.get(os.environ.get("ATB_FUSED_COMM", ""), None),
+                  "optimizer_in_backward": os.environ.get("ATB_OPT_IN_BACKWARD", "0") == "1",
+                  "prefetch_depth": int(os.environ.get("ATB_PREFETCH_DEPTH", "2"))}),
         ("amp_native", {"dtype": torch.bfloat16}),
         ("checkpoint", {"wrap_class": (LlamaDecoderLayer,), "no_reentrant": True}),
     ]
@@ -207,7 +209,17 @@ def run_ours(args):
         e2e = {"value": round(tokens / (ms2 / 1e3), 1), "unit": "tokens/s", "h2d_bytes_per_step": B * seq * 8,
                "d2h_bytes_per_step": 4, "ms_per_step": round(ms2 / args.steps, 2), "last_loss": last_loss}
     if rank == 0:
-        flops = cfg.flops_per_token(seq, recompute=True)
+        reuse = bool(cfg.reuse_attention_in_recompute)
+        flops = cfg.flops_per_token(seq, recompute=True, attention_recompute=not reuse)   # executed FLOPs
+        eng = model.engine
+        if world == 1:
+            comm = "none (one rank)"
+        elif getattr(eng, "fused", False):
+            comm = ("own: copy-engine all-gather from symmetric shards + "
+                    + ("multimem.ld_reduce" if eng._gbufs and eng._gbufs[0].use_nvls else "peer-load")
+                    + " reduce-scatter kernel" + (" fused with AdamW" if eng._fused_opt is not None else ""))
+        else:
+            comm = "NCCL all-gather / reduce-scatter"
         out = {
             "metric": "tokens/sec/box (device-timed, max over ranks) Llama-2 7B FSDP",
             "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -216,7 +228,13 @@ def run_ours(args):
             "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights N(0,0.02)",
             "impl": "ours",
             "config": {"model": args.model, "global_batch": world * B, "seq_len": seq, "parallelism": f"fsdp{world}",
-                       "optimizer": "AdamW lr 3e-4, fp32 master + state", "activation_checkpointing": "per layer",
+                       "optimizer": "AdamW lr 3e-4, fp32 master + state"
+                                    + (", unit updates launched during the backward pass"
+                                       if model.engine._fused_opt is not None else ""),
+                       "activation_checkpointing": "per layer",
+                       "attention_recompute": "skipped (attention output + lse of the first pass are kept)"
+                                              if reuse else "executed",
+                       "collective": comm,
                        "l2": "not flushed: 13.5 GB of bf16 weights and 108 GB of optimizer state stream per step "
                              "(inputs larger than the 126 MB L2)"},
             "hw_tflops_per_gpu": round(value / world * flops / 1e12, 1),

@@ -37,6 +37,8 @@ def _build(world_strategy, fsdp_extra=None):
 
 def _train_rank(rank, world, out_file, fsdp_extra=None):
     res = _build(["parallel_mode"], fsdp_extra)
+    if fsdp_extra and fsdp_extra.get("fused_comm"):
+        assert res.model.engine.fused, "the peer-memory collectives were expected to be active"
     dev = torch.device("cuda", rank)
     losses = []
     for ids in _batches(rank):
@@ -55,7 +57,7 @@ def _train_rank(rank, world, out_file, fsdp_extra=None):
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_fsdp_two_gpus_tracks_single_gpu(tmp_path):
     runs = {}
-    for name, extra in (("fused", {"fused_comm": True}), ("nccl", None),
+    for name, extra in (("fused", {"fused_comm": True}), ("nccl", {"fused_comm": False}),
                         ("in_backward", {"fused_comm": True, "optimizer_in_backward": True})):
         f = str(tmp_path / f"l_{name}.pt")
         run_distributed(_train_rank, world=2, args=(f, extra), backend="nccl", timeout=300)
@@ -81,3 +83,39 @@ def test_fsdp_frozen_and_odd_sizes_two_gpus():
     from tests.test_fsdp_cpu import _frozen_odd
 
     run_distributed(_frozen_odd, world=2, args=("cuda",), backend="nccl", timeout=300)
+
+
+def _single_in_backward(out_file, flag):
+    torch.cuda.set_device(0)
+    from atorch_b200.auto import auto_accelerate
+    from atorch_b200.models.llama import LlamaDecoderLayer, LlamaModel
+
+    torch.manual_seed(0)
+    ok, res, _ = auto_accelerate(
+        LlamaModel(_cfg()), torch.optim.AdamW, loss_func=lambda b, o: o[0], optim_args={"lr": 1e-3},
+        load_strategy=[("fsdp", {"atorch_wrap_cls": (LlamaDecoderLayer,), "optimizer_in_backward": flag}),
+                       ("amp_native", {"dtype": torch.bfloat16}), ("checkpoint", {"wrap_class": (LlamaDecoderLayer,)})])
+    assert ok
+    losses = []
+    for ids in _batches(0):
+        ids = ids.cuda()
+        res.optim.zero_grad()
+        loss = res.model(input_ids=ids, labels=ids, return_logits=False)[0]
+        loss.backward()
+        res.optim.step()
+        losses.append(loss.item())
+    return losses, res
+
+
+def test_single_gpu_optimizer_in_backward_matches_plain_step():
+    """One rank: the per-unit AdamW launched on a side stream during the backward pass gives the same
+    trajectory as the single fused step after it; a second backward before step() is refused."""
+    a, _ = _single_in_backward(None, False)
+    b, res = _single_in_backward(None, True)
+    assert res.model.engine._fused_opt is res.optim
+    assert max(abs(x - y) for x, y in zip(a, b)) < 1e-3, (a, b)
+    ids = _batches(0)[0].cuda()
+    res.optim.zero_grad()
+    res.model(input_ids=ids, labels=ids, return_logits=False)[0].backward()
+    with pytest.raises(RuntimeError, match="second backward"):
+        res.model(input_ids=ids, labels=ids, return_logits=False)[0].backward()
