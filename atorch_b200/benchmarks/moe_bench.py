@@ -28,11 +28,17 @@ def main(argv=None):
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--layers", type=int, default=None)
+    ap.add_argument("--dispatcher", default="auto", choices=["auto", "PeerMemory", "AllToAll", "AllGather"],
+                    help="auto: PeerMemory (capacity factor 1.25, own kernels over NVLink) on GPUs, AllToAll elsewhere")
     a = ap.parse_args(argv)
     rank, world, dev = setup()
     if world > 1:
         D.create_parallel_group(([("expert", world)], None))
-    kw = dict(use_expert_parallelism=world > 1, fp8_experts=bool(a.fp8), gradient_checkpointing=True)
+    disp = a.dispatcher
+    if disp == "auto":
+        disp = "PeerMemory" if (dev.type == "cuda" and world > 1) else "AllToAll"
+    kw = dict(use_expert_parallelism=world > 1, fp8_experts=bool(a.fp8), gradient_checkpointing=True,
+              token_dispatcher_type=disp)
     if a.layers:
         kw["num_hidden_layers"] = a.layers
     cfg = MixtralConfig.tiny_moe(**kw) if a.tiny else MixtralConfig.mixtral_bench(**kw)
@@ -68,6 +74,7 @@ def main(argv=None):
                   "ms_per_step": round(ms / a.steps, 2), "dtype": "fp8 experts / bf16 rest" if a.fp8 else "bf16",
                   "config": {"layers": cfg.num_hidden_layers, "hidden": cfg.hidden_size, "experts": cfg.num_experts,
                              "top_k": cfg.top_k, "expert_ffn": cfg.expert_intermediate_size, "seq_len": seq,
+                             "dispatcher": disp, "capacity_factor": cfg.capacity_factor,
                              "parallelism": f"ep{world} + fsdp{world}"}})
 
 

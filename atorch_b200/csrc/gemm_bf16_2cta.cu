@@ -46,6 +46,20 @@ struct Epi {
   long long ldr;
 };
 
+// Row groups with device-resident fill counts (mixture-of-experts buffers: `rows` slots per group, only
+// the first counts[g] hold data and the rest is zero).
+//   m_rows > 0 : rows of A / C form groups of m_rows (a multiple of 256). A tile that starts at or beyond
+//                its group's count does no loads and no MMAs; its output is written as zeros.
+//   b_rows > 0 : every bm_rows rows of A / C (a multiple of 256; one expert's slots from all sources)
+//                multiply with their own B: the B tile coordinate is shifted by (m0 / bm_rows) * b_rows
+//                along B's row axis (N for K-major B, K for MN-major B): B is [n_b * b_rows, ...].
+//   k_rows > 0 : the reduction dim forms groups of k_rows (a multiple of 64); k-blocks at or beyond their
+//                group's count are skipped (both operands are zero there).
+struct Groups {
+  const int* counts;
+  int m_rows, b_rows, k_rows, bm_rows;
+};
+
 ATB_DEVICE uint32_t cluster_ctarank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -77,7 +91,7 @@ ATB_DEVICE void mbar_arrive_remote(uint32_t bar_cluster_addr) {
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Epi ep, int M,
-                      int N, int K, int* status) {
+                      int N, int K, Groups grp, int* status) {
   constexpr int BNH = Cfg<BN>::BNH, STAGES = Cfg<BN>::STAGES, B_BYTES = Cfg<BN>::B_BYTES,
                 BAR_OFF = Cfg<BN>::BAR_OFF;
   extern __shared__ uint8_t smem_raw[];
@@ -129,6 +143,27 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // identical decisions in every role: which tiles and which k-blocks carry data
+  auto tile_active = [&](int m0) -> bool {
+    if (grp.counts == nullptr) return true;
+    if (grp.m_rows > 0) {
+      const int g = m0 / grp.m_rows;
+      if (m0 - g * grp.m_rows >= grp.counts[g]) return false;
+    }
+    if (grp.k_rows > 0) {   // nothing to reduce over at all?
+      const int ng = (K + grp.k_rows - 1) / grp.k_rows;
+      bool any = false;
+      for (int g = 0; g < ng; ++g) any |= grp.counts[g] > 0;
+      return any;
+    }
+    return true;
+  };
+  auto kb_active = [&](int kb) -> bool {
+    if (grp.counts == nullptr || grp.k_rows <= 0) return true;
+    const int k0 = kb * BK, g = k0 / grp.k_rows;
+    return k0 - g * grp.k_rows < grp.counts[g];
+  };
+
   auto tile_coords = [&](int tile, int& m0, int& n0) {
     const int band_tiles = BAND * tiles_n;
     const int band = tile / band_tiles;
@@ -146,9 +181,13 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       for (int tile = cluster_id; tile < num_tiles; tile += num_clusters) {
         int m0, n0;
         tile_coords(tile, m0, n0);
+        if (!tile_active(m0)) continue;
         const int am0 = m0 + (int)rank * BM;   // this CTA's rows of A
-        const int bn0 = n0 + (int)rank * BNH;  // this CTA's rows of B
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int bshift = grp.b_rows > 0 ? (m0 / grp.bm_rows) * grp.b_rows : 0;   // this expert's own B
+        const int bn0 = n0 + (int)rank * BNH + (B_MN ? 0 : bshift);   // this CTA's rows of B
+        const int bk0 = B_MN ? bshift : 0;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!kb_active(kb)) continue;
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&empty[s], ph ^ 1, abort_flag, status)) goto producer_done;
@@ -166,8 +205,10 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             tma_load_2d_pair(b_dst, &tmB, bar, kb * BK, bn0);
           } else {
 #pragma unroll
-            for (int j = 0; j < BNH / 64; ++j) tma_load_2d_pair(b_dst + j * 8192, &tmB, bar, bn0 + j * 64, kb * BK);
+            for (int j = 0; j < BNH / 64; ++j)
+              tma_load_2d_pair(b_dst + j * 8192, &tmB, bar, bn0 + j * 64, bk0 + kb * BK);
           }
+          ++it;
         }
       }
     }
@@ -177,13 +218,20 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       constexpr uint32_t idesc = umma_idesc(2 * BM, BN, 1, 1, A_MN, B_MN);
       uint32_t it = 0;
       int local = 0;
-      for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++local) {
+      for (int tile = cluster_id; tile < num_tiles; tile += num_clusters) {
+        {
+          int m0, n0;
+          tile_coords(tile, m0, n0);
+          if (!tile_active(m0)) continue;
+        }
         const int acc = local & 1;
         const uint32_t acc_ph = (local >> 1) & 1;
         if (!mbar_wait(&tempty[acc], acc_ph ^ 1, abort_flag, status)) goto mma_done;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        bool first_kb = true;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!kb_active(kb)) continue;
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&full[s], ph, abort_flag, status)) goto mma_done;
@@ -196,13 +244,16 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                                         : umma_desc_sw128(a_addr + k * 32, 16, 1024);
             const uint64_t bdesc = B_MN ? umma_desc_sw128(b_addr + k * 2048, 8192, 1024)
                                         : umma_desc_sw128(b_addr + k * 32, 16, 1024);
-            umma_f16<2>(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16<2>(d_tmem, adesc, bdesc, idesc, (first_kb && k == 0) ? 0u : 1u);
           }
+          first_kb = false;
           umma_commit_cg2(smem_u32(&empty[s]));
           umma_commit_cg2(map_to_cta(&empty[s], 1));
+          ++it;
         }
         umma_commit_cg2(smem_u32(&tfull[acc]));
         umma_commit_cg2(map_to_cta(&tfull[acc], 1));
+        ++local;
       }
     }
   mma_done:;
@@ -210,9 +261,27 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const int q = warp & 3;
     int local = 0;
     const uint32_t tempty_leader[2] = {map_to_cta(&tempty[0], 0), map_to_cta(&tempty[1], 0)};
-    for (int tile = cluster_id; tile < num_tiles; tile += num_clusters, ++local) {
+    for (int tile = cluster_id; tile < num_tiles; tile += num_clusters) {
       int m0, n0;
       tile_coords(tile, m0, n0);
+      if (!tile_active(m0)) {
+        // an empty tile: its output is all zeros (left alone when accumulating)
+        const int zrow = m0 + (int)rank * BM + q * 32 + lane;
+        if (!ep.accumulate && zrow < M) {
+          for (int c = 0; c < BN; c += 8) {
+            if (n0 + c >= N) break;
+            if (ep.out_fp32) {
+              float* z = reinterpret_cast<float*>(ep.C) + (long long)zrow * ep.ldc + n0 + c;
+              *reinterpret_cast<float4*>(z) = make_float4(0.f, 0.f, 0.f, 0.f);
+              *reinterpret_cast<float4*>(z + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+            } else {
+              *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(ep.C) + (long long)zrow * ep.ldc + n0 + c) =
+                  make_uint4(0u, 0u, 0u, 0u);
+            }
+          }
+        }
+        continue;
+      }
       const int acc = local & 1;
       const uint32_t acc_ph = (local >> 1) & 1;
       if (!__all_sync(0xffffffffu, mbar_wait(&tfull[acc], acc_ph, abort_flag, status))) break;
@@ -282,6 +351,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_remote(tempty_leader[acc]);
+      ++local;
     }
   }
 
@@ -313,7 +383,7 @@ int sm_count() {
 
 template <int BN, bool A_MN, bool B_MN>
 int launch(const void* A, const void* B, const Epi& ep, int M, int N, int K, long long lda, long long ldb,
-           int max_ctas, cudaStream_t stream, int* status) {
+           int max_ctas, const Groups& grp, int b_extent_rows, cudaStream_t stream, int* status) {
   CUtensorMap tmA, tmB;
   bool ok;
   if (!A_MN)
@@ -321,11 +391,13 @@ int launch(const void* A, const void* B, const Epi& ep, int M, int N, int K, lon
   else
     ok = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, lda, BK, 64, CU_TENSOR_MAP_SWIZZLE_128B);
   if (!ok) return -2;
+  // with per-group B the tensor map spans all groups' weights (b_extent_rows rows)
   if (!B_MN)
-    ok = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb, Cfg<BN>::BNH, BK,
-                      CU_TENSOR_MAP_SWIZZLE_128B);
+    ok = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, b_extent_rows > 0 ? b_extent_rows : N, K, ldb,
+                      Cfg<BN>::BNH, BK, CU_TENSOR_MAP_SWIZZLE_128B);
   else
-    ok = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb, BK, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+    ok = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, b_extent_rows > 0 ? b_extent_rows : K, N, ldb, BK,
+                      64, CU_TENSOR_MAP_SWIZZLE_128B);
   if (!ok) return -3;
   auto kern = gemm_bf16_2cta_kernel<BN, A_MN, B_MN>;
   constexpr int SMEM_TOTAL = Cfg<BN>::SMEM_TOTAL;
@@ -350,22 +422,43 @@ int launch(const void* A, const void* B, const Epi& ep, int M, int N, int K, lon
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, ep, M, N, K, status);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, ep, M, N, K, grp, status);
   return e == cudaSuccess ? 0 : -5;
 }
 
 }  // namespace
 
-// Same arguments as atb_gemm_bf16 (gemm_bf16.cu) minus the tile choice. Best for M, N >= 256.
-extern "C" int atb_gemm_bf16_2cta(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
-                                  long long lda, long long ldb, long long ldc, int a_mn_major, int b_mn_major,
-                                  int out_fp32, int accumulate, float alpha, int tile_n, int max_ctas,
-                                  const void* residual, long long ldr, void* stream, int* status) {
+// Same arguments as atb_gemm_bf16 (gemm_bf16.cu) minus the tile choice, plus row groups (see Groups):
+// `group_counts` int32 device array or null with m_group_rows (multiple of 256) and / or k_group_rows
+// (multiple of 64); b_group_rows > 0: every bm_group_rows rows of A use their own B out of n_b stacked
+// ones, as described there. Best for M, N >= 256.
+extern "C" int atb_gemm_bf16_2cta_grouped(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
+                                          long long lda, long long ldb, long long ldc, int a_mn_major, int b_mn_major,
+                                          int out_fp32, int accumulate, float alpha, int tile_n, int max_ctas,
+                                          const void* residual, long long ldr, const int* group_counts,
+                                          int m_group_rows, int k_group_rows, int b_group_rows, int bm_group_rows,
+                                          int n_b, void* stream, int* status) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((N & 7) || (lda & 7) || (ldb & 7) || (ldc & 3) || (!out_fp32 && (ldc & 7))) return -1;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(C)) & 15)
     return -1;
   if (residual != nullptr && (out_fp32 || (ldr & 7) || (reinterpret_cast<uintptr_t>(residual) & 15))) return -1;
+  Groups grp{nullptr, 0, 0, 0, 0};
+  int b_extent = 0;
+  if ((m_group_rows % 256) || (k_group_rows % 64) || (bm_group_rows % 256) || m_group_rows < 0 ||
+      k_group_rows < 0 || b_group_rows < 0)
+    return -1;
+  if (group_counts != nullptr) {
+    grp.counts = group_counts;
+    grp.m_rows = m_group_rows;
+    grp.k_rows = k_group_rows;
+  }
+  if (b_group_rows > 0) {
+    if (bm_group_rows <= 0 || n_b <= 0) return -1;
+    grp.b_rows = b_group_rows;
+    grp.bm_rows = bm_group_rows;
+    b_extent = n_b * b_group_rows;
+  }
   Epi ep{C, bias, ldc, alpha, out_fp32, accumulate, residual, ldr};
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   // The 256-wide tile is the default. The 128-wide one fills the last wave better (256 tiles of 256x256
@@ -374,12 +467,24 @@ extern "C" int atb_gemm_bf16_2cta(const void* A, const void* B, void* C, const v
   const bool narrow = tile_n == 128;
 #define ATB_PAIR_DISPATCH(BN_)                                                                                     \
   do {                                                                                                             \
-    if (!a_mn_major && !b_mn_major) return launch<BN_, false, false>(A, B, ep, M, N, K, lda, ldb, max_ctas, st, status); \
-    if (!a_mn_major && b_mn_major) return launch<BN_, false, true>(A, B, ep, M, N, K, lda, ldb, max_ctas, st, status);   \
-    if (a_mn_major && b_mn_major) return launch<BN_, true, true>(A, B, ep, M, N, K, lda, ldb, max_ctas, st, status);     \
-    return launch<BN_, true, false>(A, B, ep, M, N, K, lda, ldb, max_ctas, st, status);                                  \
+    if (!a_mn_major && !b_mn_major)                                                                                \
+      return launch<BN_, false, false>(A, B, ep, M, N, K, lda, ldb, max_ctas, grp, b_extent, st, status);          \
+    if (!a_mn_major && b_mn_major)                                                                                 \
+      return launch<BN_, false, true>(A, B, ep, M, N, K, lda, ldb, max_ctas, grp, b_extent, st, status);           \
+    if (a_mn_major && b_mn_major)                                                                                  \
+      return launch<BN_, true, true>(A, B, ep, M, N, K, lda, ldb, max_ctas, grp, b_extent, st, status);            \
+    return launch<BN_, true, false>(A, B, ep, M, N, K, lda, ldb, max_ctas, grp, b_extent, st, status);             \
   } while (0)
   if (narrow) ATB_PAIR_DISPATCH(128);
   ATB_PAIR_DISPATCH(256);
 #undef ATB_PAIR_DISPATCH
+}
+
+extern "C" int atb_gemm_bf16_2cta(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
+                                  long long lda, long long ldb, long long ldc, int a_mn_major, int b_mn_major,
+                                  int out_fp32, int accumulate, float alpha, int tile_n, int max_ctas,
+                                  const void* residual, long long ldr, void* stream, int* status) {
+  return atb_gemm_bf16_2cta_grouped(A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn_major, b_mn_major, out_fp32,
+                                    accumulate, alpha, tile_n, max_ctas, residual, ldr, nullptr, 0, 0, 0, 0, 0, stream,
+                                    status);
 }

@@ -28,7 +28,8 @@ class MixtralConfig(LlamaConfig):
     fp8_experts: bool = False
     router_aux_loss_coef: float = 0.01
     router_z_loss_coef: float = 0.0
-    token_dispatcher_type: str = "AllToAll"
+    token_dispatcher_type: str = "AllToAll"     # "PeerMemory": capacity routing over NVLink peer memory
+    capacity_factor: float = 1.25                # slots per (rank, expert) = factor * tokens * top_k / experts
 
     @staticmethod
     def mixtral_bench(**kw) -> "MixtralConfig":
@@ -55,7 +56,8 @@ class SparseMLP(nn.Module):
         self.experts = Grouped_GEMM_MoE(cfg.hidden_size, cfg.expert_intermediate_size, 0.0, cfg.num_experts, cfg.top_k,
                                         use_swiglu=True, use_expert_parallelism=cfg.use_expert_parallelism,
                                         implementation_type="Megatron", token_dispatcher_type=cfg.token_dispatcher_type,
-                                        fp8=cfg.fp8_experts, initializer_range=cfg.initializer_range)
+                                        fp8=cfg.fp8_experts, initializer_range=cfg.initializer_range,
+                                        capacity_factor=cfg.capacity_factor)
 
     def forward(self, x):
         probs, idx = self.router(x)

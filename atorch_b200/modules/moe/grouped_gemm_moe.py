@@ -39,7 +39,8 @@ class Grouped_GEMM_MoE(nn.Module):
     def __init__(self, hidden_size, expert_intermediate_size, output_dropout_prob, num_experts, topk,
                  use_swiglu=False, use_bias=False, initializer_range=0.02, use_expert_parallelism=False,
                  expert_parallel_group=None, merge_w1_v1=True, transpose_w1=True, is_scale_gradient=False,
-                 implementation_type="Megatron", token_dispatcher_type="AllToAll", fp8: bool = False):
+                 implementation_type="Megatron", token_dispatcher_type="AllToAll", fp8: bool = False,
+                 capacity_factor: float = 1.25):
         super().__init__()
         self.hidden_size, self.expert_intermediate_size = hidden_size, expert_intermediate_size
         self.num_experts, self.topk, self.use_swiglu, self.use_bias = num_experts, topk, use_swiglu, use_bias
@@ -72,6 +73,18 @@ class Grouped_GEMM_MoE(nn.Module):
         rank = (dist.get_rank(self.expert_parallel_group) if (use_expert_parallelism and dist.is_initialized())
                 else 0)
         local = [rank * E + i for i in range(E)]
+        self.peer_exchange = False
+        if token_dispatcher_type == "PeerMemory":
+            # capacity-factor routing with the exchange done by this package's kernels over NVLink peer
+            # memory (csrc/moe.cu); needs expert parallelism on 2..8 GPUs of one NVSwitch domain
+            from .peer_dispatch import MoEPeerMemoryTokenDispatcher, available
+
+            if use_expert_parallelism and available(self.expert_parallel_group):
+                self.token_dispatcher = MoEPeerMemoryTokenDispatcher(
+                    E, local, num_experts, topk, self.expert_parallel_group, True, capacity_factor)
+                self.peer_exchange = True
+                return
+            token_dispatcher_type = "AllToAll"
         cls = MoEAllGatherTokenDispatcher if token_dispatcher_type in ("AllGather", "MindSpeedAllGather") \
             else MoEAllToAllTokenDispatcher
         self.token_dispatcher = cls(E, local, num_experts, topk, self.expert_parallel_group, use_expert_parallelism)
@@ -90,7 +103,31 @@ class Grouped_GEMM_MoE(nn.Module):
             return grouped_scaled_linear(x, w if w_is_nk else w.transpose(1, 2), sizes)
         return moe_ops.grouped_gemm(x, w, sizes, trans_b=w_is_nk)
 
+    def compute_expert_slots(self, x: torch.Tensor, counts: torch.Tensor) -> torch.Tensor:
+        """Expert MLP over an expert buffer ``[E_local * W * capacity, H]`` whose groups of ``capacity`` slots
+        are filled up to ``counts`` (int32, on the device) and zero beyond: grouped GEMMs that skip empty
+        tiles, no host sync. With fp8 experts the block-scaled path runs over all slots (static shapes)."""
+        from .peer_dispatch import grouped_linear
+
+        d = self.token_dispatcher
+        cap, W = d.bufs.capacity, d.ep_size
+        w1, w2 = self._scaled(self.w1), self._scaled(self.w2)
+        if self.fp8:
+            sizes = [W * cap] * self.num_local_experts
+            lin1 = lambda t, w, nk: self._gmm(t, w, sizes, nk)
+        else:
+            lin1 = lambda t, w, nk: grouped_linear(t, w, counts, cap, W, nk)
+        h = lin1(x, w1, self.transpose_w1)
+        if self.use_swiglu:
+            h = torch.nn.functional.silu(h) * lin1(x, self._scaled(self.v1), self.transpose_w1) \
+                if self.v1 is not None else ops.swiglu(h)
+        else:
+            h = torch.nn.functional.gelu(h)
+        return lin1(h, w2, False)
+
     def compute_expert(self, x: torch.Tensor, tokens_per_expert: torch.Tensor) -> torch.Tensor:
+        if self.peer_exchange:
+            return self.compute_expert_slots(x, tokens_per_expert)
         sizes = tokens_per_expert.tolist()
         w1, w2 = self._scaled(self.w1), self._scaled(self.w2)
         h = self._gmm(x, w1, sizes, self.transpose_w1)

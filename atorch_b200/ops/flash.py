@@ -6,7 +6,9 @@ All masks are lowered to one per-row key interval ``[lo, hi)``:
 causal                 ``hi = i + 1 + (Sk - Sq)``
 GLM break-point g[b]   ``hi = max(i + 1, g[b])``
 packed GLM [b, 2, P]   ``hi = max(i + 1, max{e_p : s_p <= i})``
-key padding            ``hi = min(hi, number of valid keys)`` (right padding)
+key padding            ``[lo, hi) = [first valid key, last valid key + 1)`` when the valid keys of a row are
+                       contiguous (right or left padding); masks with holes are unpadded into packed
+                       sequences (``cu_seqlens``) like the reference's varlen path
 packed sequences       ``lo = start of the row's sequence`` (``cu_seqlens``)
 =====================  ==========================================================
 
@@ -75,13 +77,22 @@ def row_intervals(B: int, Sq: int, Sk: int, device, causal: bool = False, glm_ma
         if not causal_like:
             hi = torch.minimum(hi, cu[seg + 1][None].expand(B, Sq))
     if key_padding_mask is not None:
-        kp = key_padding_mask.to(device)
-        nvalid = kp.bool().sum(dim=1) if kp.dtype == torch.bool or kp.max() <= 1 else None
-        if nvalid is None:
-            raise ValueError("length-encoded key_padding_mask must be converted to cu_seqlens first")
-        hi = torch.minimum(hi, nvalid.view(B, 1).expand(B, Sq))
+        kp = key_padding_mask.to(device).bool()
+        cnt = kp.sum(dim=1)
+        first = kp.int().argmax(dim=1)
+        last = Sk - 1 - kp.flip(1).int().argmax(dim=1)
+        # one host sync: an interval can only describe valid keys that lie next to each other
+        if not bool(((cnt == 0) | (last - first + 1 == cnt)).all()):
+            raise NonContiguousKeyMask()
+        last1 = torch.where(cnt > 0, last + 1, torch.zeros_like(last))
+        lo = torch.maximum(lo, first.view(B, 1).expand(B, Sq))
+        hi = torch.minimum(hi, last1.view(B, 1).expand(B, Sq))
     hi = hi.clamp(max=Sk)
     return lo.to(torch.int32).contiguous(), hi.to(torch.int32).contiguous()
+
+
+class NonContiguousKeyMask(ValueError):
+    """The valid keys of some row are not contiguous: no per-row interval describes the mask."""
 
 
 def _token_stride(t: torch.Tensor) -> int:
@@ -163,8 +174,31 @@ def flash_attention(q, k, v, causal=False, softmax_scale=None, glm_mask=None, pa
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
     if Sq == 1:
         causal = False   # single-query decode sees every key
-    lo, hi = row_intervals(B, Sq, Sk, q.device, causal, glm_mask, pack_glm_mask, key_padding_mask, cu_seqlens)
+    try:
+        lo, hi = row_intervals(B, Sq, Sk, q.device, causal, glm_mask, pack_glm_mask, key_padding_mask, cu_seqlens)
+    except NonContiguousKeyMask:
+        return _unpadded_attention(q, k, v, key_padding_mask, causal, scale, glm_mask, pack_glm_mask, cu_seqlens)
     return _FlashAttn.apply(q, k, v, bool(causal), float(scale), lo, hi)
+
+
+def _unpadded_attention(q, k, v, key_padding_mask, causal, scale, glm_mask, pack_glm_mask, cu_seqlens):
+    """Key-padding mask with holes (self-attention): drop the padded tokens, run the batch as packed
+    sequences, put the results back (padded positions get zeros). Mirrors the reference's unpad / pad
+    path (atorch/modules/transformer/layers.py:76-95,1363-1408)."""
+    B, S, H, D = q.shape
+    if k.shape[1] != S or glm_mask is not None or pack_glm_mask is not None or cu_seqlens is not None:
+        from .attention import attention_reference
+
+        return attention_reference(q, k, v, causal, scale, glm_mask, pack_glm_mask, key_padding_mask, cu_seqlens)
+    kp = key_padding_mask.to(q.device).bool()
+    idx = kp.reshape(-1).nonzero(as_tuple=False)[:, 0]
+    cu = torch.zeros(B + 1, dtype=torch.int32, device=q.device)
+    cu[1:] = kp.sum(1).cumsum(0)
+    pick = lambda t: t.reshape(B * S, t.shape[2], D).index_select(0, idx).unsqueeze(0)
+    out_p = flash_attention(pick(q), pick(k), pick(v), causal=causal, softmax_scale=scale, cu_seqlens=cu)
+    out = torch.zeros(B * S, H, D, dtype=q.dtype, device=q.device)
+    out = out.index_copy(0, idx, out_p[0])
+    return out.view(B, S, H, D)
 
 
 class _FlashAttnQKV(torch.autograd.Function):
@@ -206,8 +240,14 @@ def flash_attention_qkv(qkv: torch.Tensor, num_heads: int, causal: bool = True, 
 
     B, S, _, D = qkv.shape
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
-    lo, hi = row_intervals(B, S, S, qkv.device, causal, mask_kwargs.get("glm_mask"), mask_kwargs.get("pack_glm_mask"),
-                           mask_kwargs.get("key_padding_mask"), mask_kwargs.get("cu_seqlens"))
+    try:
+        lo, hi = row_intervals(B, S, S, qkv.device, causal, mask_kwargs.get("glm_mask"),
+                               mask_kwargs.get("pack_glm_mask"), mask_kwargs.get("key_padding_mask"),
+                               mask_kwargs.get("cu_seqlens"))
+    except NonContiguousKeyMask:
+        H = num_heads
+        return flash_attention(qkv[:, :, :H], qkv[:, :, H: 2 * H], qkv[:, :, 2 * H:], causal=causal,
+                               softmax_scale=softmax_scale, **mask_kwargs)
     cached = None
     cur = current_pass() if recompute_cache is not None else None
     if cur is not None:

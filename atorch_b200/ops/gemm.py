@@ -60,20 +60,41 @@ def gemm(
     max_ctas: int = 0,
     kernel: str = "auto",
     residual: Optional[torch.Tensor] = None,
+    groups: Optional[dict] = None,
 ) -> torch.Tensor:
     """``out[M,N] (+)= alpha * A[M,K] @ B[N,K]^T (+ bias[N])``.
 
     ``a`` is stored ``[M,K]`` (or ``[K,M]`` when ``a_mn``), ``b`` is stored ``[N,K]`` (or ``[K,N]``
     when ``b_mn``). Inputs are bf16, accumulation is fp32, the output is bf16 or fp32.
+
+    ``groups`` (mixture-of-experts buffers, CTA-pair kernel only): ``{"counts": int32 device tensor,
+    "m_rows": r}`` - rows of A come in groups of ``r`` slots (a multiple of 256) of which only the first
+    ``counts[g]`` hold data and the rest is zero: tiles beyond the count are not computed, their output is
+    zero. ``"k_rows": r`` - the same along the reduction dim (multiple of 64): empty k-blocks are skipped.
+    ``"n_b": E, "bm_rows": R`` - ``b`` holds E stacked operands and rows ``[e*R, (e+1)*R)`` of A use the
+    e-th (one launch for all local experts).
     """
     assert a.dim() == 2 and b.dim() == 2
     M, K = (a.shape[1], a.shape[0]) if a_mn else a.shape
     N, Kb = (b.shape[1], b.shape[0]) if b_mn else b.shape
+    n_b = int(groups.get("n_b", 1)) if groups else 1
+    if n_b > 1:                      # stacked B operands: [E*N, K] (or [E*K, N] when b_mn)
+        if b_mn:
+            Kb //= n_b
+        else:
+            N //= n_b
     assert K == Kb, f"reduction dims differ: {K} vs {Kb}"
     if out is None:
         out = torch.empty(M, N, dtype=out_dtype or torch.bfloat16, device=a.device)
         assert not accumulate
     if not _lib.use_kernels(a, b, out) or a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16 or (N % 8) or (K % 8) or (M % 8):
+        if n_b > 1:                  # reference: one product per stacked operand (inputs are zero beyond the counts)
+            R = groups["bm_rows"]
+            for e in range(n_b):
+                be = b[e * K: (e + 1) * K] if b_mn else b[e * N: (e + 1) * N]
+                gemm_reference(a[e * R: (e + 1) * R], be, a_mn, b_mn, out[e * R: (e + 1) * R], None, accumulate,
+                               alpha, bias)
+            return out
         r = gemm_reference(a, b, a_mn, b_mn, out, None, accumulate, alpha, bias)
         if residual is not None:
             r.add_(residual.to(r.dtype))
@@ -85,6 +106,22 @@ def gemm(
     assert out.stride(-1) == 1 and out.dtype in (torch.bfloat16, torch.float32)
     L = _lib.lib()
     use_pair = kernel == "2cta" or (kernel == "auto" and PAIR_KERNEL_DEFAULT and M >= 256 and N >= 256)
+    if groups is not None:
+        counts = groups.get("counts")
+        assert counts is None or (counts.dtype == torch.int32 and counts.is_cuda)
+        rc = L.atb_gemm_bf16_2cta_grouped(
+            _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias),
+            ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
+            ctypes.c_longlong(_pitch(a)), ctypes.c_longlong(_pitch(b)), ctypes.c_longlong(_pitch(out)),
+            ctypes.c_int(int(a_mn)), ctypes.c_int(int(b_mn)),
+            ctypes.c_int(int(out.dtype == torch.float32)), ctypes.c_int(int(accumulate)),
+            ctypes.c_float(alpha), ctypes.c_int(tile_n), ctypes.c_int(max_ctas), _lib.ptr(residual),
+            ctypes.c_longlong(_pitch(residual) if residual is not None else 0), _lib.ptr(counts),
+            ctypes.c_int(int(groups.get("m_rows", 0))), ctypes.c_int(int(groups.get("k_rows", 0))),
+            ctypes.c_int((K if b_mn else N) if n_b > 1 else 0), ctypes.c_int(int(groups.get("bm_rows", 0))),
+            ctypes.c_int(n_b), _lib.stream_ptr(), _lib.ptr(_lib.status_word(a.device)))
+        _lib.check(rc, f"atb_gemm_bf16_2cta_grouped M={M} N={N} K={K}")
+        return out
     if use_pair:
         rc = L.atb_gemm_bf16_2cta(
             _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias),

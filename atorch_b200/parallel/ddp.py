@@ -50,7 +50,8 @@ class _Bucket:
 class DistributedDataParallel(nn.Module):
     def __init__(self, module: nn.Module, process_group: Optional[dist.ProcessGroup] = None,
                  bucket_cap_mb: float = 25.0, find_unused_parameters: bool = False, broadcast_buffers: bool = True,
-                 sync_module_states: bool = True, gradient_predivide: bool = True, comm_blocks: int = 32):
+                 sync_module_states: bool = True, gradient_predivide: bool = True, comm_blocks: int = 32,
+                 param_filter=None):
         super().__init__()
         self.module = module
         self.comm_blocks = comm_blocks      # CTAs one bucket all-reduce may occupy beside the backward kernels
@@ -58,12 +59,20 @@ class DistributedDataParallel(nn.Module):
         self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
         self.require_backward_grad_sync = True
         self.broadcast_buffers = broadcast_buffers
-        params = [p for p in module.parameters() if p.requires_grad]
+        # ``param_filter(name, param) -> bool`` restricts this reducer to some of the parameters (the
+        # mixture-of-experts wrapper runs one reducer per group of ranks that replicate them)
+        named = [(n, p) for n, p in module.named_parameters() if p.requires_grad]
+        if param_filter is not None:
+            named = [(n, p) for n, p in named if param_filter(n, p)]
+        params = [p for _, p in named]
+        self._own = {id(p) for p in params}
         self.device = params[0].device if params else torch.device("cpu")
         self.comm_stream = torch.cuda.Stream(self.device) if (self.device.type == "cuda" and self.world > 1) else None
         if sync_module_states and self.world > 1:
             src = dist.get_global_rank(process_group, 0) if process_group is not None else 0
-            for t in list(module.parameters()) + list(module.buffers()):
+            own_params = [p for p in module.parameters() if param_filter is None or id(p) in self._own]
+            bufs = list(module.buffers()) if (param_filter is None or broadcast_buffers) else []
+            for t in own_params + bufs:
                 dist.broadcast(t.data, src=src, group=process_group)
         self.buckets: List[_Bucket] = []
         cap = int(bucket_cap_mb * 1024 * 1024)

@@ -59,6 +59,9 @@ class _Checkpoint(torch.autograd.Function):
             ctx.cpu_rng = torch.get_rng_state()
             ctx.cuda_rng = torch.cuda.get_rng_state() if torch.cuda.is_available() else None
         ctx.token = new_pass_token()
+        # the recomputation must run under the same autocast state as this pass
+        dev_type = next((t.device.type for t in tensors if isinstance(t, torch.Tensor)), "cpu")
+        ctx.autocast = (dev_type, torch.is_autocast_enabled(dev_type), torch.get_autocast_dtype(dev_type))
         with torch.no_grad(), checkpoint_pass(ctx.token, False):
             args, kwargs = tree_unflatten(list(tensors), spec)
             out = run(*args, **kwargs)
@@ -80,7 +83,9 @@ class _Checkpoint(torch.autograd.Function):
             if ctx.cuda_rng is not None:
                 cuda_now = torch.cuda.get_rng_state()
                 torch.cuda.set_rng_state(ctx.cuda_rng)
-        with torch.enable_grad(), checkpoint_pass(ctx.token, True):
+        dev_type, ac_on, ac_dtype = ctx.autocast
+        with torch.enable_grad(), torch.autocast(dev_type, dtype=ac_dtype, enabled=ac_on), \
+                checkpoint_pass(ctx.token, True):
             args, kwargs = tree_unflatten(flat, ctx.spec)
             out = ctx.run(*args, **kwargs)
         if ctx.preserve_rng:

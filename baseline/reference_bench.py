@@ -24,7 +24,7 @@ def _unavailable(why: str) -> None:
         print(json.dumps({"impl": "reference", "unavailable": why[:300]}), flush=True)
 
 
-def run(args, MODELS, PUBLISHED, ClockSampler) -> None:
+def run(args, MODELS, PUBLISHED, ClockSampler, helpers=None) -> None:
     if not os.path.isdir(os.path.join(REF_DIR, "atorch")):
         return _unavailable("baseline/_ref/atorch is missing: the reference was not installed on this machine")
     # the repository root must not shadow the reference's `atorch` package
@@ -42,14 +42,14 @@ def run(args, MODELS, PUBLISHED, ClockSampler) -> None:
         return _unavailable(f"import of the reference failed: {type(e).__name__}: {e}")
     try:
         _run(args, MODELS, PUBLISHED, ClockSampler, torch, atorch, auto_accelerate, data_to_device, LlamaConfig,
-             LlamaDecoderLayer, LlamaForCausalLM)
+             LlamaDecoderLayer, LlamaForCausalLM, helpers or {})
     except Exception as e:  # noqa
         traceback.print_exc()
         _unavailable(f"reference run failed: {type(e).__name__}: {str(e).splitlines()[0] if str(e) else ''}")
 
 
 def _run(args, MODELS, PUBLISHED, ClockSampler, torch, atorch, auto_accelerate, data_to_device, LlamaConfig,
-         LlamaDecoderLayer, LlamaForCausalLM):
+         LlamaDecoderLayer, LlamaForCausalLM, helpers):
     import torch.distributed as dist
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -73,6 +73,11 @@ def _run(args, MODELS, PUBLISHED, ClockSampler, torch, atorch, auto_accelerate, 
     torch.manual_seed(1234)
     with torch.device(dev):
         model = LlamaForCausalLM(cfg)
+    loss_curve = getattr(args, "loss_curve", 0)
+    if loss_curve:      # the same name-seeded weights as the other arm (plain tensor fills, nothing of its code)
+        with torch.no_grad():
+            for name, p in model.named_parameters():
+                helpers["name_seeded_init_"](name, p)
 
     def loss_func(inputs, output):
         return output.loss
@@ -91,6 +96,28 @@ def _run(args, MODELS, PUBLISHED, ClockSampler, torch, atorch, auto_accelerate, 
     assert status, "reference auto_accelerate returned status False"
     model, optim, prepare_input = res.model, res.optim, res.prepare_input
     B = args.mbs
+    if loss_curve:
+        losses = []
+        for ids in helpers["loss_stream"](cfg.vocab_size, B, seq, rank, loss_curve):
+            batch = {"input_ids": ids.to(dev), "labels": ids.to(dev)}
+            optim.zero_grad()
+            loss = res.loss_func(batch, model(**batch))
+            loss.backward()
+            optim.step()
+            t = loss.detach().float().clone()
+            if world > 1:
+                dist.all_reduce(t)
+            losses.append(float(t.item()) / world)
+        if rank == 0:
+            rec = {"impl": "reference", "n_gpus": world, "model": args.model, "seq_len": seq, "steps": loss_curve,
+                   "loss_curve": losses}
+            if getattr(args, "loss_out", None):
+                json.dump(rec, open(args.loss_out, "w"))
+            print(json.dumps({k: v for k, v in rec.items() if k != "loss_curve"} |
+                             {"first": losses[0], "last": losses[-1]}), flush=True)
+        if world > 1:
+            dist.barrier()
+        return
     gen = torch.Generator(device="cpu").manual_seed(100 + rank)
     n_host = args.steps + args.warmup
     host = [torch.randint(0, cfg.vocab_size, (B, seq), generator=gen).pin_memory() for _ in range(n_host)]

@@ -51,7 +51,47 @@ def parse_args():
     ap.add_argument("--seq", type=int, default=None)
     ap.add_argument("--mbs", type=int, default=1)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--loss-curve", type=int, default=0, metavar="K",
+                    help="instead of timing: train K steps on a fixed token stream from name-seeded weights and "
+                         "write the per-step losses to --loss-out (same stream and weights on both arms)")
+    ap.add_argument("--loss-out", default=None)
+    ap.add_argument("--compare-loss", nargs=2, metavar=("A.json", "B.json"), default=None,
+                    help="print max / mean |difference| of two loss-curve files and exit")
     return ap.parse_args()
+
+
+def name_seeded_init_(name: str, t) -> None:
+    """Fill tensor ``t`` (a parameter under its Hugging Face name) with N(0, 0.02) from a generator seeded by
+    the name, or with ones for norm weights: the same values whichever framework builds the model."""
+    import zlib
+
+    import torch
+
+    if name.endswith("norm.weight") or "layernorm" in name:
+        t.fill_(1.0)
+        return
+    g = torch.Generator(device=t.device)
+    g.manual_seed(zlib.crc32(name.encode()))
+    tmp = torch.empty(t.shape, dtype=torch.float32, device=t.device)
+    tmp.normal_(0.0, 0.02, generator=g)
+    t.copy_(tmp)
+
+
+def loss_stream(vocab: int, batch: int, seq: int, rank: int, steps: int):
+    """The token batches of the loss-curve mode (CPU generator: identical on both arms)."""
+    import torch
+
+    gen = torch.Generator(device="cpu").manual_seed(4242 + rank)
+    return [torch.randint(0, vocab, (batch, seq), generator=gen) for _ in range(steps)]
+
+
+def compare_loss(a_path: str, b_path: str) -> dict:
+    a, b = json.load(open(a_path)), json.load(open(b_path))
+    la, lb = a["loss_curve"], b["loss_curve"]
+    n = min(len(la), len(lb))
+    d = [abs(x - y) for x, y in zip(la[:n], lb[:n])]
+    return {"steps": n, "max_abs_diff": max(d), "mean_abs_diff": sum(d) / n, "first": [la[0], lb[0]],
+            "last": [la[n - 1], lb[n - 1]], "a": a.get("impl"), "b": b.get("impl")}
 
 
 class ClockSampler:
@@ -126,8 +166,37 @@ def run_ours(args):
     seq = args.seq or mc["max_position_embeddings"]
     cfg = LlamaConfig(**mc)
     torch.manual_seed(1234)
-    with torch.device("meta"):
-        model = LlamaModel(cfg)
+    if args.loss_curve:
+        # weights by Hugging Face parameter name, so that the reference arm starts from the same values
+        with torch.device(dev):
+            model = LlamaModel(cfg)
+        d, nq, nkv = cfg.head_dim, cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim
+        with torch.no_grad():
+            for name, p in model.named_parameters():
+                if name.startswith("layers."):
+                    _, idx, rest = name.split(".", 2)
+                    pre = f"model.layers.{idx}."
+                    if rest == "qkv_proj.weight":
+                        for nm, sl in (("q_proj", slice(0, nq)), ("k_proj", slice(nq, nq + nkv)),
+                                       ("v_proj", slice(nq + nkv, nq + 2 * nkv))):
+                            name_seeded_init_(pre + f"self_attn.{nm}.weight", p[sl])
+                    elif rest == "gate_up_proj.weight":
+                        f = cfg.intermediate_size
+                        name_seeded_init_(pre + "mlp.gate_proj.weight", p[:f])
+                        name_seeded_init_(pre + "mlp.up_proj.weight", p[f:])
+                    elif rest == "o_proj.weight":
+                        name_seeded_init_(pre + "self_attn.o_proj.weight", p)
+                    elif rest == "down_proj.weight":
+                        name_seeded_init_(pre + "mlp.down_proj.weight", p)
+                    else:
+                        name_seeded_init_(pre + rest, p)
+                elif name == "lm_head.weight":
+                    name_seeded_init_(name, p)
+                else:
+                    name_seeded_init_("model." + name, p)
+    else:
+        with torch.device("meta"):
+            model = LlamaModel(cfg)
 
     def loss_func(batch, outputs):
         return outputs[0]
@@ -148,6 +217,30 @@ def run_ours(args):
     assert status, "auto_accelerate failed"
     model, optim = res.model, res.optim
     B = args.mbs
+    if args.loss_curve:
+        losses = []
+        for ids in loss_stream(cfg.vocab_size, B, seq, rank, args.loss_curve):
+            ids = ids.to(dev)
+            optim.zero_grad()
+            loss = loss_func(None, model(input_ids=ids, labels=ids, return_logits=False))
+            loss.backward()
+            optim.step()
+            t = loss.detach().float().clone()
+            if world > 1:
+                dist.all_reduce(t)
+            losses.append(float(t.item()) / world)
+        _lib.check_status(dev)
+        if rank == 0:
+            rec = {"impl": "ours", "n_gpus": world, "model": args.model, "seq_len": seq, "steps": args.loss_curve,
+                   "loss_curve": losses}
+            if args.loss_out:
+                json.dump(rec, open(args.loss_out, "w"))
+            print(json.dumps({k: v for k, v in rec.items() if k != "loss_curve"} |
+                             {"first": losses[0], "last": losses[-1]}), flush=True)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     gen = torch.Generator(device="cpu").manual_seed(100 + rank)
     n_host = args.steps + args.warmup
     host_batches = [torch.randint(0, cfg.vocab_size, (B, seq), generator=gen).pin_memory() for _ in range(n_host)]
@@ -251,11 +344,15 @@ def run_ours(args):
 def run_reference(args):
     from baseline.reference_bench import run as ref_run  # noqa: deferred, sets sys.path for baseline/_ref
 
-    ref_run(args, MODELS, PUBLISHED_TOKENS_PER_S_PER_GPU, ClockSampler)
+    ref_run(args, MODELS, PUBLISHED_TOKENS_PER_S_PER_GPU, ClockSampler,
+            helpers={"name_seeded_init_": name_seeded_init_, "loss_stream": loss_stream})
 
 
 if __name__ == "__main__":
     a = parse_args()
+    if a.compare_loss:
+        print(json.dumps(compare_loss(*a.compare_loss)))
+        sys.exit(0)
     if a.impl == "reference":
         sys.path.insert(0, ROOT)
         run_reference(a)

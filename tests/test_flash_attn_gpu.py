@@ -188,3 +188,33 @@ def test_recompute_cache_ignores_plain_no_grad_forward():
     x.grad = None
     checkpoint_module(layer, x, cos, sin).float().pow(2).sum().backward()
     assert torch.equal(g_cache, x.grad)
+
+
+def test_flash_left_padded_and_holed_key_masks():
+    """Key-padding masks that are not right-padded: left padding (the usual layout for generation) stays an
+    interval per row, a mask with holes goes through the unpad path; both match dense attention on the
+    valid query rows, forward and backward."""
+    torch.manual_seed(21)
+    B, S, H = 2, 256, 2
+    q, k, v = _qkv(B, S, S, H, H)
+    left = torch.ones(B, S, dtype=torch.bool, device="cuda")
+    left[0, :70] = False
+    left[1, :3] = False
+    holes = torch.ones(B, S, dtype=torch.bool, device="cuda")
+    holes[0, 10:40] = False
+    holes[0, 200:] = False
+    holes[1, ::7] = False
+    for kp, causal in ((left, False), (left, True), (holes, False), (holes, True)):
+        qq, kk, vv = (t.detach().clone().requires_grad_() for t in (q, k, v))
+        out = flash.flash_attention(qq, kk, vv, causal=causal, key_padding_mask=kp)
+        qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+        ref = attention_reference(qr, kr, vr, causal=causal, key_padding_mask=kp)
+        rows = kp[:, :, None, None].expand_as(out)          # padded query rows are don't-care
+        assert torch.allclose(out.float()[rows], ref.float()[rows], rtol=2e-2, atol=2e-2), (causal, kp is holes)
+        g = torch.randn_like(out) * rows
+        out.backward(g)
+        ref.backward(g.float())
+        for a, b, name in ((qq.grad, qr.grad, "dq"), (kk.grad, kr.grad, "dk"), (vv.grad, vr.grad, "dv")):
+            tol = 5e-2 * max(1.0, b.abs().max().item())
+            assert (a.float() - b).abs().max().item() < tol, (name, causal, kp is holes)
+    _lib.check_status(q.device)

@@ -117,3 +117,42 @@ def test_linear_main_grad_accumulation():
     assert w.grad is None
     ref = 2 * (dy.float().t() @ x.detach().float())
     _check(w.main_grad, ref, 128)
+
+
+def test_grouped_gemm_with_device_counts():
+    """ops.gemm(groups=...): slot groups filled up to device-resident counts (zero beyond), empty tiles
+    skipped and written as zeros, one stacked B operand per expert, k-block skipping in the wgrad form."""
+    from atorch_b200 import ops
+
+    torch.manual_seed(4)
+    E, W, cap, K, N = 2, 3, 512, 256, 384
+    G = E * W
+    counts = torch.tensor([512, 0, 130, 256, 257, 1], dtype=torch.int32, device="cuda")
+    x = torch.randn(G * cap, K, device="cuda", dtype=torch.bfloat16)
+    rows = torch.arange(G * cap, device="cuda")
+    valid = (rows % cap) < counts[rows // cap]
+    x[~valid] = 0
+    w = (0.1 * torch.randn(E, N, K, device="cuda")).bfloat16()
+    out = torch.full((G * cap, N), 7.0, device="cuda", dtype=torch.bfloat16)      # stale contents everywhere
+    ops.gemm(x, w.reshape(E * N, K), out=out, groups={"counts": counts, "m_rows": cap, "n_b": E, "bm_rows": W * cap})
+    ref = torch.cat([x[e * W * cap:(e + 1) * W * cap].float() @ w[e].float().t() for e in range(E)])
+    assert torch.allclose(out.float(), ref, rtol=2e-2, atol=2e-2)
+    assert (out[~valid] == 0).all()
+    # dgrad form: B read MN-major, stacked along its row (k) axis
+    dy = torch.randn(G * cap, N, device="cuda", dtype=torch.bfloat16)
+    dy[~valid] = 0
+    dx = ops.gemm(dy, w.reshape(E * N, K), b_mn=True, groups={"counts": counts, "m_rows": cap, "n_b": E,
+                                                                "bm_rows": W * cap})
+    ref = torch.cat([dy[e * W * cap:(e + 1) * W * cap].float() @ w[e].float() for e in range(E)])
+    assert torch.allclose(dx.float(), ref, rtol=2e-2, atol=3e-2)
+    # wgrad form: the reduction runs over the slots, empty k-blocks are skipped
+    for e in range(E):
+        sl = slice(e * W * cap, (e + 1) * W * cap)
+        dw = ops.gemm(dy[sl], x[sl], a_mn=True, b_mn=True, groups={"counts": counts[e * W:(e + 1) * W], "k_rows": cap})
+        ref = dy[sl].float().t() @ x[sl].float()
+        assert torch.allclose(dw.float(), ref, rtol=2e-2, atol=2e-1), (dw.float() - ref).abs().max()
+    # all groups empty: zeros, not stale data
+    zc = torch.zeros(W, dtype=torch.int32, device="cuda")
+    dw = torch.full((N, K), 3.0, device="cuda", dtype=torch.bfloat16)
+    ops.gemm(dy[:W * cap], x[:W * cap], a_mn=True, b_mn=True, out=dw, groups={"counts": zc, "k_rows": cap})
+    assert (dw == 0).all()

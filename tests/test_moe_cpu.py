@@ -90,3 +90,43 @@ def _ep(rank, world, dispatcher, out_file):
 def test_expert_parallel_gloo(tmp_path):
     for disp in ("AllToAll", "AllGather"):
         run_distributed(_ep, world=2, args=(disp, str(tmp_path / disp)))
+
+
+def _moe_ddp(rank, world):
+    """Dense parameters are averaged over all ranks, expert parameters only over the ranks holding the same
+    experts (here: ranks {0, 2} and {1, 3})."""
+    import torch.distributed as dist
+
+    from atorch_b200.modules.moe import (Experts, MoEMixtureDistributedDataParallel, set_experts_ddp_process_group)
+
+    groups = [dist.new_group([0, 2]), dist.new_group([1, 3])]
+    set_experts_ddp_process_group(groups[rank % 2])
+    torch.manual_seed(0)
+
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.dense = nn.Linear(4, 4)
+            self.experts = Experts(nn.Linear(4, 4), 1)
+
+        def forward(self, x):
+            return self.experts(self.dense(x).unsqueeze(0)).squeeze(0) if False else self.dense(x) + \
+                self.experts.experts[0](x)
+    net = Net()
+    with torch.no_grad():                      # ranks of different expert groups hold different experts
+        for p in net.experts.parameters():
+            p.add_(float(rank % 2))
+    m = MoEMixtureDistributedDataParallel(net)
+    assert m.moe_params_names == {"experts.experts.0.weight", "experts.experts.0.bias"}
+    x = torch.full((2, 4), float(rank + 1))
+    m(x).sum().backward()
+    gd = net.dense.weight.grad.clone()
+    ge = net.experts.experts[0].weight.grad.clone()
+    # d/dW of sum(Wx+b) = column sums of x broadcast over rows: 2 * (rank + 1) per entry on this rank
+    assert torch.allclose(gd, torch.full_like(gd, 2 * (1 + 2 + 3 + 4) / 4.0))
+    mates = [1, 3] if rank % 2 == 0 else [2, 4]
+    assert torch.allclose(ge, torch.full_like(ge, 2 * sum(mates) / 2.0)), (rank, ge)
+
+
+def test_moe_mixture_ddp_gloo():
+    run_distributed(_moe_ddp, world=4)

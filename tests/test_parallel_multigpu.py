@@ -1,0 +1,241 @@
+"""Tensor / pipeline / expert / data parallelism on 2-4 GPUs over NCCL against single-GPU math, and the
+tiny variants of the hybrid, MoE and local-SGD benchmark drivers on the GPU kernels."""
+import glob
+
+import pytest
+import torch
+import torch.nn as nn
+
+from tests.dist_utils import run_distributed
+
+pytestmark = pytest.mark.gpu
+NGPU = torch.cuda.device_count()
+
+
+# --------------------------------------------------------------------------------------- tensor parallel
+def _tp_llama(rank, world):
+    from atorch_b200.auto import auto_accelerate
+    from atorch_b200.models.llama import LlamaConfig, LlamaModel
+    from atorch_b200.modules.distributed_modules import ColumnParallelLinear, RowParallelLinear
+
+    dev = torch.device("cuda", rank)
+    torch.manual_seed(0)
+    cfg = LlamaConfig(vocab_size=512, hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=4, max_position_embeddings=256)
+    ref = LlamaModel(cfg).to(dev).bfloat16()
+    ids = torch.randint(0, 512, (2, 256), device=dev)
+    ref_loss, _ = ref(ids, labels=ids)
+    ref_loss.backward()
+    model = LlamaModel(cfg).to(dev).bfloat16()
+    model.load_state_dict(ref.state_dict())
+    ok, res, _ = auto_accelerate(model, load_strategy=[("parallel_mode", ([("tensor", world)], None)),
+                                                       ("tensor_parallel", None)])
+    assert ok
+    m = res.model
+    assert isinstance(m.layers[0].qkv_proj, ColumnParallelLinear) and isinstance(m.layers[0].down_proj, RowParallelLinear)
+    loss, _ = m(ids, labels=ids)
+    assert abs(loss.item() - ref_loss.item()) < 3e-2, (loss.item(), ref_loss.item())
+    loss.backward()
+    # a replicated parameter (final norm weight) gets the same gradient as on one GPU
+    g, g_ref = m.norm.weight.grad.float(), ref.norm.weight.grad.float()
+    assert torch.allclose(g, g_ref, rtol=5e-2, atol=5e-2 * g_ref.abs().max().item())
+
+
+@pytest.mark.skipif(NGPU < 2, reason="needs 2 GPUs")
+def test_tensor_parallel_llama_matches_single_gpu():
+    run_distributed(_tp_llama, world=2, backend="nccl", timeout=300)
+
+
+# ------------------------------------------------------------------------------------- pipeline parallel
+def _run_pipe(rank, world, vpp, sche, out_file):
+    from atorch_b200.distributed import distributed as D
+    from atorch_b200.pipeline_parallel.pipe_module import PipeModuleConfig, make_pipe_module
+    from atorch_b200.pipeline_parallel.pipe_schedule import make_pipe_schedule_from_pipe_module
+    from tests.test_pipeline_cpu import _Chunk
+
+    dev = torch.device("cuda", rank)
+    D.create_parallel_group(([("pipe", world)], None))
+
+    def provider(model_config, layer_num, pre_process, post_process, start_layer_idx):
+        return _Chunk(layer_num, pre_process, post_process, start_layer_idx).to(dev)
+
+    cfg = PipeModuleConfig(total_layer_num=4, virtual_pp_size=vpp, sche_name=sche, n_microbatches=4, auto_ddp=False)
+    pm = make_pipe_module(model_provider=provider, loss_func=lambda o, t: ((o - t) ** 2).mean(), config=cfg)
+    sched = make_pipe_schedule_from_pipe_module(pm, cfg)
+    g = torch.Generator().manual_seed(3)
+    x, y = torch.randn(8, 8, generator=g).to(dev), torch.randn(8, 8, generator=g).to(dev)
+    first = pm.stage_ids[0] == 0
+    last = (pm.num_stages - 1) in pm.stage_ids
+    if first and last:
+        loss = sched.step(x, target=y)
+    elif first:
+        loss = sched.step(x)
+    elif last:
+        loss = sched.step(target=y)
+    else:
+        loss = sched.step()
+    grads = {}
+    for m, sid in zip(pm.stage_modules, pm.stage_ids):
+        for i, l in enumerate(m.layers):
+            grads[(sid, i)] = l.weight.grad.cpu().clone()
+    torch.save({"loss": None if loss is None else float(loss), "grads": grads, "ids": pm.stage_ids},
+               f"{out_file}.{rank}")
+
+
+@pytest.mark.skipif(NGPU < 2, reason="needs 2 GPUs")
+def test_pipeline_schedules_match_single_process_nccl(tmp_path):
+    from tests.test_pipeline_cpu import _reference
+
+    ref_loss, ref_grads = _reference()
+    for vpp, sche in ((1, "Schedule1F1B"), (2, "ScheduleInterleaved1F1B")):
+        f = str(tmp_path / f"p_{vpp}_{sche}")
+        run_distributed(_run_pipe, world=2, args=(vpp, sche, f), backend="nccl", timeout=300)
+        per = 4 // (2 * vpp)
+        seen_loss = False
+        for r in range(2):
+            d = torch.load(f"{f}.{r}")
+            if d["loss"] is not None:
+                assert abs(d["loss"] - ref_loss) < 1e-4
+                seen_loss = True
+            for (sid, i), gr in d["grads"].items():
+                assert torch.allclose(gr, ref_grads[sid * per + i], atol=1e-4), (sche, sid, i)
+        assert seen_loss
+
+
+# --------------------------------------------------------------------------------------- expert parallel
+def _ep(rank, world, dispatcher):
+    from atorch_b200.distributed import distributed as D
+    from atorch_b200.modules.moe import Grouped_GEMM_MoE
+    from tests.test_moe_cpu import _dense_moe
+
+    dev = torch.device("cuda", rank)
+    D.create_parallel_group(([("expert", world)], None))
+    torch.manual_seed(3)
+    H, F, NE = 256, 512, 4
+    full = Grouped_GEMM_MoE(H, F, 0.0, num_experts=NE, topk=2, use_swiglu=True)
+    moe = Grouped_GEMM_MoE(H, F, 0.0, num_experts=NE, topk=2, use_swiglu=True, use_expert_parallelism=True,
+                           token_dispatcher_type=dispatcher).to(dev).bfloat16()
+    E = moe.num_local_experts
+    with torch.no_grad():
+        moe.w1.copy_(full.w1[rank * E:(rank + 1) * E])
+        moe.w2.copy_(full.w2[rank * E:(rank + 1) * E])
+    g = torch.Generator().manual_seed(10 + rank)
+    x = (0.5 * torch.randn(64, H, generator=g)).to(dev).bfloat16().requires_grad_()
+    logits = torch.randn(64, NE, generator=g)
+    w, idx = torch.softmax(logits, -1).topk(2, -1)
+    if dispatcher == "PeerMemory":
+        assert moe.peer_exchange, "the peer-memory dispatcher was expected to be active"
+    probs = w.to(dev).bfloat16().requires_grad_()
+    y = moe(x, probs, idx.to(dev))
+    full_bf = full.to(dev).bfloat16().float()
+    xr = x.detach().float().requires_grad_()
+    pr = probs.detach().float().requires_grad_()
+    ref = _dense_moe(full_bf, xr, pr, idx.to(dev))
+    err = (y.float() - ref).abs().max().item()
+    assert err < 5e-2 * max(1.0, ref.abs().max().item()), (dispatcher, err)
+    gout = torch.randn(y.shape, generator=torch.Generator().manual_seed(99 + rank)).to(dev)
+    (y.float() * gout).sum().backward()
+    (ref * gout).sum().backward()
+    assert x.grad is not None and torch.isfinite(x.grad.float()).all() and moe.w1.grad is not None
+    gx_err = (x.grad.float() - xr.grad).abs().max().item()
+    assert gx_err < 6e-2 * max(1.0, xr.grad.abs().max().item()), (dispatcher, "dx", gx_err)
+    if probs.grad is not None:
+        gp_err = (probs.grad.float() - pr.grad).abs().max().item()
+        assert gp_err < 6e-2 * max(1.0, pr.grad.abs().max().item()), (dispatcher, "dprobs", gp_err)
+    # expert weight gradients: every rank holds its own experts; compare with the dense gradient summed over
+    # the ranks' tokens (all-reduce of the reference, which saw only this rank's tokens)
+    gw = full_bf.w1.grad.clone()
+    torch.distributed.all_reduce(gw)
+    mine = gw[rank * E:(rank + 1) * E]
+    gw_err = (moe.w1.grad.float() - mine).abs().max().item()
+    assert gw_err < 6e-2 * max(1.0, mine.abs().max().item()), (dispatcher, "dw1", gw_err)
+
+
+@pytest.mark.skipif(NGPU < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("dispatcher", ["PeerMemory", "AllToAll", "AllGather"])
+def test_expert_parallel_matches_dense(dispatcher):
+    run_distributed(_ep, world=2, args=(dispatcher,), backend="nccl", timeout=300)
+
+
+# ------------------------------------------------------------------------------------------ data parallel
+def _ddp(rank, world, out_file):
+    """Own bucketed DDP (all-reduce kernel over symmetric memory on NVSwitch systems) on fp32 gradients."""
+    from atorch_b200.parallel.ddp import DistributedDataParallel
+    from tests.test_fsdp_cpu import make_data, make_mlp
+
+    dev = torch.device("cuda", rank)
+    m = DistributedDataParallel(make_mlp().to(dev), bucket_cap_mb=0.5)
+    assert m.symm is not None or world > 8, "the symmetric-memory all-reduce path was expected to be active"
+    opt = torch.optim.AdamW(m.parameters(), lr=1e-3)
+    for x, y in make_data(rank, steps=8):
+        opt.zero_grad()
+        nn.functional.cross_entropy(m(x.to(dev)), y.to(dev)).backward()
+        opt.step()
+    if m.symm is not None:
+        m.symm.check()
+    if rank == 0:
+        torch.save({k: v.cpu() for k, v in m.state_dict().items()}, out_file)
+
+
+@pytest.mark.skipif(NGPU < 2, reason="needs 2 GPUs")
+def test_ddp_own_allreduce_matches_single_process(tmp_path):
+    from tests.test_fsdp_cpu import make_data, make_mlp
+
+    f = str(tmp_path / "ddp.pt")
+    run_distributed(_ddp, world=2, args=(f,), backend="nccl", timeout=300)
+    sd = torch.load(f)
+    m = make_mlp()
+    opt = torch.optim.AdamW(m.parameters(), lr=1e-3)
+    d0, d1 = make_data(0, steps=8), make_data(1, steps=8)
+    for (x0, y0), (x1, y1) in zip(d0, d1):
+        opt.zero_grad()
+        ((nn.functional.cross_entropy(m(x0), y0) + nn.functional.cross_entropy(m(x1), y1)) / 2).backward()
+        opt.step()
+    for k, v in m.state_dict().items():
+        assert torch.allclose(sd[k], v, atol=2e-4, rtol=2e-3), k
+
+
+# -------------------------------------------------------------------------- benchmark drivers, tiny configs
+def _moe(rank, world, fp8):
+    from atorch_b200.benchmarks import moe_bench
+
+    moe_bench.main(["--tiny", "--fp8", str(fp8), "--steps", "2", "--warmup", "1"])
+
+
+def _lsgd(rank, world, H):
+    from atorch_b200.benchmarks import local_sgd_bench
+
+    local_sgd_bench.main(["--tiny", "--H", str(H), "--windows", "1"])
+
+
+def _hybrid(rank, world, out, tp, pp):
+    from atorch_b200.benchmarks import hybrid_bench
+
+    losses = hybrid_bench.main(["--tiny", "--tp", str(tp), "--pp", str(pp), "--micro-batches", "4", "--steps", "4",
+                                "--warmup", "0"])
+    if losses:
+        torch.save(losses, f"{out}.{rank}")
+
+
+@pytest.mark.skipif(NGPU < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("fp8", [0, 1])
+def test_moe_bench_tiny_expert_parallel_nccl(fp8):
+    run_distributed(_moe, world=min(NGPU, 4), args=(fp8,), backend="nccl", timeout=300)
+
+
+@pytest.mark.skipif(NGPU < 2, reason="needs 2 GPUs")
+@pytest.mark.parametrize("H", [2, 0])
+def test_local_sgd_bench_tiny_nccl(H):
+    run_distributed(_lsgd, world=min(NGPU, 4), args=(H,), backend="nccl", timeout=300)
+
+
+@pytest.mark.skipif(NGPU < 2, reason="needs 2 GPUs")
+def test_hybrid_bench_tiny_nccl(tmp_path):
+    tp, pp = (2, 2) if NGPU >= 4 else (2, 1)
+    world = 8 if NGPU >= 8 else (4 if NGPU >= 4 else 2)
+    out = str(tmp_path / "h")
+    run_distributed(_hybrid, world=world, args=(out, tp, pp), backend="nccl", timeout=400)
+    files = glob.glob(out + ".*")
+    assert files
+    losses = torch.load(files[0])
+    assert all(l == l for l in losses) and losses[-1] < losses[0], losses

@@ -75,3 +75,34 @@ def test_util_funcs():
     assert b2["x"].dtype == torch.bfloat16 and b2["y"][0].dtype == torch.int64
     m = nn.Sequential(nn.Linear(2, 2))
     assert recursively_getattr(m, "0.weight") is m[0].weight
+
+
+def test_bench_loss_curve_helpers(tmp_path):
+    """bench.py's loss-curve mode: name-seeded weights and the token stream are reproducible, and the
+    comparison reports the largest per-step difference."""
+    import importlib.util
+    import json
+    import os
+
+    import torch
+
+    spec = importlib.util.spec_from_file_location("bench", os.path.join(os.path.dirname(os.path.dirname(__file__)),
+                                                                        "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    a, b = torch.empty(4, 6), torch.empty(4, 6)
+    bench.name_seeded_init_("model.layers.0.mlp.up_proj.weight", a)
+    bench.name_seeded_init_("model.layers.0.mlp.up_proj.weight", b)
+    assert torch.equal(a, b) and 0.005 < a.std() < 0.04
+    bench.name_seeded_init_("model.layers.0.mlp.down_proj.weight", b)
+    assert not torch.equal(a, b)
+    n = torch.empty(5)
+    bench.name_seeded_init_("model.norm.weight", n)
+    assert (n == 1).all()
+    s1, s2 = bench.loss_stream(100, 2, 8, 0, 3), bench.loss_stream(100, 2, 8, 0, 3)
+    assert all(torch.equal(x, y) for x, y in zip(s1, s2)) and not torch.equal(s1[0], s1[1])
+    fa, fb = tmp_path / "a.json", tmp_path / "b.json"
+    json.dump({"impl": "ours", "loss_curve": [10.0, 9.5, 9.0]}, open(fa, "w"))
+    json.dump({"impl": "reference", "loss_curve": [10.0, 9.4, 9.05]}, open(fb, "w"))
+    r = bench.compare_loss(str(fa), str(fb))
+    assert abs(r["max_abs_diff"] - 0.1) < 1e-9 and r["steps"] == 3
