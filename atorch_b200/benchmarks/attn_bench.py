@@ -1,4 +1,6 @@
-"""Micro-benchmark of the sm_100a flash attention (forward, backward) against torch SDPA.
+"""Micro-benchmark of the sm_100a flash attention (forward, backward) against torch SDPA (cuDNN) and
+flash_attn 2.8 (the kernel behind the reference's FlashAttnModule), when that package is importable.
+The forward is timed for both kernels of this package: one query tile per CTA and two tiles per CTA.
 
     python -m atorch_b200.benchmarks.attn_bench [--iters 10]
 """
@@ -51,10 +53,24 @@ def main(argv=None):
         def lib_f():
             return torch.nn.functional.scaled_dot_product_attention(
                 q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=causal, enable_gqa=H != Hkv)
-        t_o, t_l = time_fn(ours_f, args.iters, flush), time_fn(lib_f, args.iters, flush)
+        flash.FWD_TWO_TILES = False
+        t_o = time_fn(ours_f, args.iters, flush)
+        flash.FWD_TWO_TILES = True
+        t_o2 = time_fn(ours_f, args.iters, flush)
+        flash.FWD_TWO_TILES = False
+        t_l = time_fn(lib_f, args.iters, flush)
         _lib.check_status(dev)
         line = (f"B{B} S{S} H{H}/{Hkv} causal={int(causal)} fwd: ours {t_o:8.1f} us {flops_f / t_o / 1e6:7.1f} TF | "
+                f"ours(2 tiles) {t_o2:8.1f} us {flops_f / t_o2 / 1e6:7.1f} TF | "
                 f"SDPA {t_l:8.1f} us {flops_f / t_l / 1e6:7.1f} TF")
+        fa = None
+        try:
+            from flash_attn import flash_attn_func as fa
+        except Exception:
+            pass
+        if fa is not None:
+            t_fa = time_fn(lambda: fa(q, k, v, causal=causal), args.iters, flush)
+            line += f" | flash_attn {t_fa:8.1f} us {flops_f / t_fa / 1e6:7.1f} TF"
         if flash.backward_built():
             out, lse = ours_f()
             dout = torch.randn_like(out)
@@ -70,6 +86,10 @@ def main(argv=None):
             _lib.check_status(dev)
             line += (f" || bwd: ours {tb_o:8.1f} us {2.5 * flops_f / tb_o / 1e6:7.1f} TF | "
                      f"SDPA {tb_l:8.1f} us {2.5 * flops_f / tb_l / 1e6:7.1f} TF")
+            if fa is not None:
+                o3 = fa(q, k, v, causal=causal)
+                tb_fa = time_fn(lambda: torch.autograd.grad(o3, (q, k, v), d2, retain_graph=True), args.iters, flush)
+                line += f" | flash_attn {tb_fa:8.1f} us {2.5 * flops_f / tb_fa / 1e6:7.1f} TF"
         print(line, flush=True)
 
 

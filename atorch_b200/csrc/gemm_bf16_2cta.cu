@@ -15,6 +15,16 @@
 //   empty[s]   both CTAs   : tcgen05.commit from the leader arrives on both
 //   tfull[a]   both CTAs   : tcgen05.commit from the leader arrives on both
 //   tempty[a]  leader only : the 4 epilogue warps of both CTAs arrive (8 arrivals)
+//
+// Fused with collectives over NVLink (tensor parallelism with sequence-sharded activations):
+//   all-gather -> GEMM   the rows of A arrive shard by shard in a local buffer (copy engines pulling the
+//                        peers' shards); `Gate` carries one arrival flag per shard, the TMA producer of a
+//                        tile waits (bounded) for the flag of the shard that holds its rows, and the tiles
+//                        are visited starting with this rank's own shard, so the math starts at once and
+//                        the transfers hide behind it
+//   GEMM -> reduce-scatter  the epilogue adds every output row into the fp32 accumulation buffer of the
+//                        rank that owns the row (`red.add.f32` on peer pointers): no partial-sum tensor, no
+//                        separate collective, the reduction traffic overlaps the remaining tiles
 #include "common.cuh"
 
 namespace {
@@ -44,7 +54,46 @@ struct Epi {
   int out_fp32, accumulate;
   const void* residual;  // optional bf16 [M, N] added in the epilogue (pitch ldr); bf16 output only
   long long ldr;
+  // reduce-scatter epilogue (rs_rows > 0): row r goes to rank r / rs_rows, as fp32 atomic adds into
+  // rs_base[rank] + (r % rs_rows) * ldc + column; C is not written
+  float* rs_base[8];
+  int rs_rows;
 };
+
+// Arrival flags of the A operand (all-gather -> GEMM): rows [g * rows, (g + 1) * rows) are in place once
+// flags[g] >= epoch (wrap-safe). rot = first tile row to visit (this rank's own shard).
+struct Gate {
+  const unsigned int* flags;
+  unsigned int epoch;
+  int rows, rot;
+};
+
+__device__ unsigned long long g_gate_wait_ns = ATB_WAIT_LIMIT_NS;
+
+ATB_DEVICE bool gate_wait(const Gate& gate, int row_lo, int row_hi, volatile int* abort_flag, int* status) {
+  for (int g = row_lo / gate.rows; g <= (row_hi - 1) / gate.rows; ++g) {
+    const unsigned int* f = gate.flags + g;
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+    if ((int)(v - gate.epoch) >= 0) continue;
+    const unsigned long long limit = g_gate_wait_ns;
+    const uint64_t t0 = globaltimer_ns();
+    while (true) {
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+      if ((int)(v - gate.epoch) >= 0) break;
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > limit) {
+        *abort_flag = 1;
+        if (status) atomicCAS(status, 0, (int)ATB_ERR_PEER_TIMEOUT);
+        return false;
+      }
+      __nanosleep(200);
+    }
+  }
+  // the rows were written by the copy engines / generic proxy; the loads that follow go through TMA
+  asm volatile("fence.proxy.async.global;" ::: "memory");
+  return true;
+}
 
 // Row groups with device-resident fill counts (mixture-of-experts buffers: `rows` slots per group, only
 // the first counts[g] hold data and the rest is zero).
@@ -91,7 +140,7 @@ ATB_DEVICE void mbar_arrive_remote(uint32_t bar_cluster_addr) {
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Epi ep, int M,
-                      int N, int K, Groups grp, int* status) {
+                      int N, int K, Groups grp, Gate gate, int* status) {
   constexpr int BNH = Cfg<BN>::BNH, STAGES = Cfg<BN>::STAGES, B_BYTES = Cfg<BN>::B_BYTES,
                 BAR_OFF = Cfg<BN>::BAR_OFF;
   extern __shared__ uint8_t smem_raw[];
@@ -170,7 +219,11 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const int rem = tile - band * band_tiles;
     const int rows_in_band = min(BAND, tiles_m - band * BAND);
     const int tn = rem / rows_in_band;
-    const int tm = band * BAND + (rem - tn * rows_in_band);
+    int tm = band * BAND + (rem - tn * rows_in_band);
+    if (gate.rot > 0) {          // start with the rows that are already here
+      tm += gate.rot;
+      if (tm >= tiles_m) tm -= tiles_m;
+    }
     m0 = tm * 2 * BM;
     n0 = tn * BN;
   };
@@ -186,6 +239,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         const int bshift = grp.b_rows > 0 ? (m0 / grp.bm_rows) * grp.b_rows : 0;   // this expert's own B
         const int bn0 = n0 + (int)rank * BNH + (B_MN ? 0 : bshift);   // this CTA's rows of B
         const int bk0 = B_MN ? bshift : 0;
+        if (gate.flags != nullptr && !gate_wait(gate, am0, min(am0 + BM, M), abort_flag, status)) goto producer_done;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!kb_active(kb)) continue;
           const int s = it % STAGES;
@@ -267,7 +321,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       if (!tile_active(m0)) {
         // an empty tile: its output is all zeros (left alone when accumulating)
         const int zrow = m0 + (int)rank * BM + q * 32 + lane;
-        if (!ep.accumulate && zrow < M) {
+        if (!ep.accumulate && ep.rs_rows <= 0 && zrow < M) {
           for (int c = 0; c < BN; c += 8) {
             if (n0 + c >= N) break;
             if (ep.out_fp32) {
@@ -304,7 +358,17 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             for (int i = 0; i < 32; ++i)
               if (col0 + i < N) v[i] += __bfloat162float(bias[col0 + i]);
           }
-          if (ep.out_fp32) {
+          if (ep.rs_rows > 0) {
+            const int owner = row / ep.rs_rows;
+            float* crow = ep.rs_base[owner] + (long long)(row - owner * ep.rs_rows) * ep.ldc + col0;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              if (col0 + i < N)
+                asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(crow + i), "f"(v[i]),
+                             "f"(v[i + 1]), "f"(v[i + 2]), "f"(v[i + 3])
+                             : "memory");
+            }
+          } else if (ep.out_fp32) {
             float* crow = reinterpret_cast<float*>(ep.C) + (long long)row * ep.ldc + col0;
 #pragma unroll
             for (int i = 0; i < 32; i += 4) {
@@ -383,7 +447,7 @@ int sm_count() {
 
 template <int BN, bool A_MN, bool B_MN>
 int launch(const void* A, const void* B, const Epi& ep, int M, int N, int K, long long lda, long long ldb,
-           int max_ctas, const Groups& grp, int b_extent_rows, cudaStream_t stream, int* status) {
+           int max_ctas, const Groups& grp, int b_extent_rows, const Gate& gate, cudaStream_t stream, int* status) {
   CUtensorMap tmA, tmB;
   bool ok;
   if (!A_MN)
@@ -422,9 +486,18 @@ int launch(const void* A, const void* B, const Epi& ep, int M, int N, int K, lon
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, ep, M, N, K, grp, status);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, ep, M, N, K, grp, gate, status);
   return e == cudaSuccess ? 0 : -5;
 }
+
+// extra arguments of the next launch of this host thread (set and cleared by atb_gemm_bf16_2cta_fused)
+struct FusedArgs {
+  bool active;
+  Gate gate;
+  float* rs_base[8];
+  int rs_rows;
+};
+thread_local FusedArgs g_fused_args = {false, {nullptr, 0u, 1, 0}, {nullptr}, 0};
 
 }  // namespace
 
@@ -459,7 +532,13 @@ extern "C" int atb_gemm_bf16_2cta_grouped(const void* A, const void* B, void* C,
     grp.bm_rows = bm_group_rows;
     b_extent = n_b * b_group_rows;
   }
-  Epi ep{C, bias, ldc, alpha, out_fp32, accumulate, residual, ldr};
+  Epi ep{C, bias, ldc, alpha, out_fp32, accumulate, residual, ldr, {nullptr}, 0};
+  Gate gate{nullptr, 0u, 1, 0};
+  if (g_fused_args.active) {   // set by atb_gemm_bf16_2cta_fused for this one launch
+    gate = g_fused_args.gate;
+    for (int i = 0; i < 8; ++i) ep.rs_base[i] = g_fused_args.rs_base[i];
+    ep.rs_rows = g_fused_args.rs_rows;
+  }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   // The 256-wide tile is the default. The 128-wide one fills the last wave better (256 tiles of 256x256
   // occupy 74 CTA pairs for 4 waves at 86 %), but measured 1.5x slower per FLOP on B200: its 256-cycle
@@ -468,12 +547,12 @@ extern "C" int atb_gemm_bf16_2cta_grouped(const void* A, const void* B, void* C,
 #define ATB_PAIR_DISPATCH(BN_)                                                                                     \
   do {                                                                                                             \
     if (!a_mn_major && !b_mn_major)                                                                                \
-      return launch<BN_, false, false>(A, B, ep, M, N, K, lda, ldb, max_ctas, grp, b_extent, st, status);          \
+      return launch<BN_, false, false>(A, B, ep, M, N, K, lda, ldb, max_ctas, grp, b_extent, gate, st, status);          \
     if (!a_mn_major && b_mn_major)                                                                                 \
-      return launch<BN_, false, true>(A, B, ep, M, N, K, lda, ldb, max_ctas, grp, b_extent, st, status);           \
+      return launch<BN_, false, true>(A, B, ep, M, N, K, lda, ldb, max_ctas, grp, b_extent, gate, st, status);           \
     if (a_mn_major && b_mn_major)                                                                                  \
-      return launch<BN_, true, true>(A, B, ep, M, N, K, lda, ldb, max_ctas, grp, b_extent, st, status);            \
-    return launch<BN_, true, false>(A, B, ep, M, N, K, lda, ldb, max_ctas, grp, b_extent, st, status);             \
+      return launch<BN_, true, true>(A, B, ep, M, N, K, lda, ldb, max_ctas, grp, b_extent, gate, st, status);            \
+    return launch<BN_, true, false>(A, B, ep, M, N, K, lda, ldb, max_ctas, grp, b_extent, gate, st, status);             \
   } while (0)
   if (narrow) ATB_PAIR_DISPATCH(128);
   ATB_PAIR_DISPATCH(256);
@@ -487,4 +566,42 @@ extern "C" int atb_gemm_bf16_2cta(const void* A, const void* B, void* C, const v
   return atb_gemm_bf16_2cta_grouped(A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn_major, b_mn_major, out_fp32,
                                     accumulate, alpha, tile_n, max_ctas, residual, ldr, nullptr, 0, 0, 0, 0, 0, stream,
                                     status);
+}
+
+// Upper bound of the arrival-flag waits of the all-gather -> GEMM form, in nanoseconds (default 2 s).
+extern "C" int atb_set_gate_wait_ns(unsigned long long ns) {
+  return cudaMemcpyToSymbol(g_gate_wait_ns, &ns, sizeof(ns)) == cudaSuccess ? 0 : -5;
+}
+
+// The GEMM fused with a collective (see the file header). On top of atb_gemm_bf16_2cta:
+//   gate_flags != null : all-gather -> GEMM. A's rows arrive in shards of gate_rows rows (a multiple of 128);
+//                        shard g is in place once gate_flags[g] >= gate_epoch; tiles start at row gate_first_row.
+//   rs_ptrs != null    : GEMM -> reduce-scatter. rs_ptrs = `rs_world` device addresses of the ranks' fp32
+//                        accumulation buffers [rs_rows, N] (pitch ldc); output row r is added into rank
+//                        r / rs_rows' buffer. C may be null.
+extern "C" int atb_gemm_bf16_2cta_fused(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                                        long long ldb, long long ldc, int a_mn_major, int b_mn_major, float alpha,
+                                        const unsigned int* gate_flags, unsigned int gate_epoch, int gate_rows,
+                                        int gate_first_row, const unsigned long long* rs_ptrs, int rs_world,
+                                        int rs_rows, void* stream, int* status) {
+  FusedArgs fa = {true, {nullptr, 0u, 1, 0}, {nullptr}, 0};
+  if (gate_flags != nullptr) {
+    if (gate_rows <= 0 || (gate_rows % 128) || a_mn_major || gate_first_row < 0 || (gate_first_row % 256)) return -1;
+    fa.gate = Gate{gate_flags, gate_epoch, gate_rows, gate_first_row / 256};
+  }
+  void* c_arg = C;
+  int out_fp32 = 0;
+  if (rs_ptrs != nullptr) {
+    if (rs_world < 1 || rs_world > 8 || rs_rows <= 0 || (long long)rs_rows * rs_world < M) return -1;
+    for (int i = 0; i < rs_world; ++i) fa.rs_base[i] = reinterpret_cast<float*>(rs_ptrs[i]);
+    fa.rs_rows = rs_rows;
+    c_arg = fa.rs_base[0];     // only its alignment is checked; the epilogue never writes through it
+    out_fp32 = 1;
+  }
+  g_fused_args = fa;
+  const int rc = atb_gemm_bf16_2cta_grouped(A, B, c_arg, nullptr, M, N, K, lda, ldb, ldc, a_mn_major, b_mn_major,
+                                            out_fp32, 0, alpha, 0, 0, nullptr, 0, nullptr, 0, 0, 0, 0, 0, stream,
+                                            status);
+  g_fused_args.active = false;
+  return rc;
 }

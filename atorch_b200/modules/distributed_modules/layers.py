@@ -11,6 +11,10 @@ Two communication styles:
   activations outside the TP block are sharded along the sequence dim; column = all-gather(seq)
   then GEMM, row = GEMM then reduce-scatter(seq).
 
+  On 2..8 GPUs of one NVSwitch domain each of these is ONE GEMM launch fused with its collective
+  (``ops/tp_fused.py``: arrival-flag gated all-gather -> GEMM, GEMM -> reduce-scatter in the epilogue over
+  peer pointers); elsewhere ``torch.distributed`` collectives surround the GEMM.
+
 The GEMMs run on ``ops.linear`` (tcgen05 kernel on the GPU).
 (Reference: atorch/modules/distributed_modules/layers.py:90-760.)
 """
@@ -40,6 +44,21 @@ def _ws(g):
 
 def _rk(g):
     return dist.get_rank(g) if (dist.is_available() and dist.is_initialized()) else 0
+
+
+def _fusable(x: torch.Tensor, weight: torch.Tensor, group, rows_local: int, n: int, k: int) -> bool:
+    """May the fused collective+GEMM kernels take this call? (bf16 on CUDA, one sequence per call, whole
+    256-row tiles per shard, peer memory available, not switched off with ATB_FUSED_COMM=0)"""
+    import os
+
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16) or \
+            os.environ.get("ATB_FUSED_COMM", "1") == "0":
+        return False
+    if any(d != 1 for d in x.shape[:-2]):
+        return False
+    from ...ops import tp_fused
+
+    return tp_fused.shapes_ok(rows_local, n, k) and tp_fused.available(group)
 
 
 def _slice_rows(w: torch.Tensor, rank: int, world: int, stride: int = 1) -> torch.Tensor:
@@ -86,6 +105,16 @@ class ColumnParallelLinear(nn.Module):
             nn.init.zeros_(self.bias)
 
     def forward(self, x):
+        if self.sequence_parallel and self.world > 1 and x.dim() >= 2 and \
+                _fusable(x, self.weight, self.group, x.shape[-2], self.out_per_rank, self.in_features):
+            from ...ops.tp_fused import allgather_linear
+
+            y = allgather_linear(x, self.weight, self.group)      # all-gather(seq) fused into the GEMM
+            if self.bias is not None:
+                y = y + self.bias
+            if self.gather_output:
+                y = gather_from_group(y, self.group, dim=-1)
+            return y
         if self.sequence_parallel:
             x = all_gather_from_group(x, self.group, dim=x.dim() - 2)
         else:
@@ -134,6 +163,12 @@ class RowParallelLinear(nn.Module):
     def forward(self, x):
         if not self.input_is_parallel:
             x = scatter_to_group(x, self.group, dim=-1)
+        if self.sequence_parallel and self.world > 1 and x.dim() >= 2 and x.shape[-2] % self.world == 0 and \
+                _fusable(x, self.weight, self.group, x.shape[-2] // self.world, self.out_features, self.in_per_rank):
+            from ...ops.tp_fused import linear_reduce_scatter
+
+            y = linear_reduce_scatter(x, self.weight, self.group)  # reduce-scatter(seq) in the GEMM epilogue
+            return y if self.bias is None else y + self.bias
         y = ops.linear(x, self.weight)
         if self.sequence_parallel:
             y = reduce_scatter_to_group(y, self.group, dim=y.dim() - 2)

@@ -25,6 +25,12 @@ import torch
 from .. import _lib
 
 
+import os
+
+# forward kernel with two 128-row query tiles per CTA that share every K/V tile (csrc/flash_attn_v2.cu)
+FWD_TWO_TILES = os.environ.get("ATB_FLASH_V2", "0") == "1"
+
+
 def kernels_built() -> bool:
     L = _lib.lib()
     return L is not None and L.has("atb_flash_fwd")
@@ -105,7 +111,10 @@ def flash_fwd_raw(q, k, v, causal, softmax_scale, row_lo, row_hi):
     Sk, Hkv = k.shape[1], k.shape[2]
     out = torch.empty(B, Sq, Hq, D, dtype=q.dtype, device=q.device)
     lse = torch.empty(B, Hq, Sq, dtype=torch.float32, device=q.device)
-    rc = _lib.lib().atb_flash_fwd(
+    L = _lib.lib()
+    # two-query-tile kernel (flash_attn_v2.cu) for long enough sequences; the single-tile kernel otherwise
+    fwd = L.atb_flash_fwd_v2 if (FWD_TWO_TILES and Sq >= 256 and L.has("atb_flash_fwd_v2")) else L.atb_flash_fwd
+    rc = fwd(
         _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(lse), _lib.ptr(row_lo), _lib.ptr(row_hi),
         ctypes.c_int(B), ctypes.c_int(Sq), ctypes.c_int(Sk), ctypes.c_int(Hq), ctypes.c_int(Hkv),
         ctypes.c_longlong(_token_stride(q)), ctypes.c_longlong(_token_stride(k)), ctypes.c_longlong(_token_stride(v)),

@@ -113,3 +113,47 @@ def tp_config_from_3d(config) -> Tuple[Optional[dict], Optional[dict]]:
         pipe_cfg = {k: get(k) for k in ("total_layer_num", "model_provider", "n_microbatches", "sche_name",
                                         "input_output_mapping") if get(k) is not None}
     return tp_cfg, pipe_cfg
+
+
+def mark_sequence_parallel_replicated(model: nn.Module, classes=None) -> int:
+    """With sequence-parallel activations, parameters that are replicated over the tensor group but see only
+    this rank's part of the sequence (normalisation weights) end up with partial gradients. Flag them so that
+    :func:`sync_sequence_parallel_grads` can sum those gradients over the tensor group."""
+    n = 0
+    for m in model.modules():
+        is_norm = isinstance(m, classes) if classes else ("norm" in type(m).__name__.lower())
+        if is_norm:
+            for p in m.parameters(recurse=False):
+                p._atb_sp_replicated = True
+                n += 1
+    return n
+
+
+def sync_sequence_parallel_grads(model: nn.Module, group=None) -> None:
+    """Sum the gradients of the flagged parameters over the tensor group (one all-reduce of one flat tensor).
+    Works on a plain module (``.grad``) and on the sharded engine (slices of its gradient shard)."""
+    import torch
+    import torch.distributed as dist
+
+    group = group if group is not None else D.parallel_group("tensor")
+    if group is None or dist.get_world_size(group) == 1:
+        return
+    eng = getattr(model, "engine", None)
+    pieces = []
+    if eng is not None:
+        g = eng.finalize_grads()
+        for u in eng.units:
+            for p, (s0, n, _) in zip(u.params, u.param_shard_slices()):
+                if n and getattr(p, "_atb_sp_replicated", False):
+                    pieces.append(g[u.shard_offset + s0: u.shard_offset + s0 + n])
+    else:
+        pieces = [p.grad.view(-1) for p in model.parameters()
+                  if getattr(p, "_atb_sp_replicated", False) and p.grad is not None]
+    if not pieces:
+        return
+    flat = torch.cat([t.float() for t in pieces])
+    dist.all_reduce(flat, group=group)
+    off = 0
+    for t in pieces:
+        t.copy_(flat[off: off + t.numel()])
+        off += t.numel()

@@ -56,7 +56,8 @@ def parse_args():
                          "write the per-step losses to --loss-out (same stream and weights on both arms)")
     ap.add_argument("--loss-out", default=None)
     ap.add_argument("--compare-loss", nargs=2, metavar=("A.json", "B.json"), default=None,
-                    help="print max / mean |difference| of two loss-curve files and exit")
+                    help="print max / mean |difference| of two loss-curve files and exit (status 1 when the curves "
+                         "differ by more than the bf16 tolerance: mean 0.05, last-quarter mean 0.03, max 0.5)")
     return ap.parse_args()
 
 
@@ -90,8 +91,16 @@ def compare_loss(a_path: str, b_path: str) -> dict:
     la, lb = a["loss_curve"], b["loss_curve"]
     n = min(len(la), len(lb))
     d = [abs(x - y) for x, y in zip(la[:n], lb[:n])]
-    return {"steps": n, "max_abs_diff": max(d), "mean_abs_diff": sum(d) / n, "first": [la[0], lb[0]],
-            "last": [la[n - 1], lb[n - 1]], "a": a.get("impl"), "b": b.get("impl")}
+    tail = d[-max(1, n // 4):]
+    rec = {"steps": n, "max_abs_diff": max(d), "mean_abs_diff": sum(d) / n, "last_quarter_mean_abs_diff":
+           sum(tail) / len(tail), "first": [la[0], lb[0]], "last": [la[n - 1], lb[n - 1]], "a": a.get("impl"),
+           "b": b.get("impl")}
+    # two bf16 runs with different kernels and reduction orders drift apart step by step (training amplifies
+    # rounding differences, most of all in the first steps at full learning rate); what must hold is that the
+    # curves stay together on average and end together
+    rec["within_bf16_tolerance"] = (rec["mean_abs_diff"] <= 0.05 and rec["last_quarter_mean_abs_diff"] <= 0.03
+                                    and rec["max_abs_diff"] <= 0.5)
+    return rec
 
 
 class ClockSampler:
@@ -351,8 +360,9 @@ def run_reference(args):
 if __name__ == "__main__":
     a = parse_args()
     if a.compare_loss:
-        print(json.dumps(compare_loss(*a.compare_loss)))
-        sys.exit(0)
+        r = compare_loss(*a.compare_loss)
+        print(json.dumps(r))
+        sys.exit(0 if r["within_bf16_tolerance"] else 1)
     if a.impl == "reference":
         sys.path.insert(0, ROOT)
         run_reference(a)

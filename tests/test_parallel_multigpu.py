@@ -239,3 +239,97 @@ def test_hybrid_bench_tiny_nccl(tmp_path):
     assert files
     losses = torch.load(files[0])
     assert all(l == l for l in losses) and losses[-1] < losses[0], losses
+
+
+# ------------------------------------------------- tensor-parallel linears fused with their collectives
+def _tp_fused(rank, world):
+    """all-gather -> GEMM and GEMM -> reduce-scatter (ops/tp_fused.py) against torch.distributed collectives
+    around a plain matmul, forward and backward, twice in a row (buffers and flags are reused)."""
+    import torch.distributed as dist
+
+    from atorch_b200 import _lib
+    from atorch_b200.ops import tp_fused
+
+    dev = torch.device("cuda", rank)
+    assert tp_fused.available(dist.group.WORLD)
+    rows, K, N = 512, 384, 640
+    S = rows * world
+    for it in range(2):
+        g = torch.Generator().manual_seed(7 + 13 * rank + it)
+        x_loc = (0.5 * torch.randn(rows, K, generator=g)).to(dev).bfloat16().requires_grad_()
+        gw = torch.Generator().manual_seed(1000 + it)
+        w = (0.05 * torch.randn(N, K, generator=gw)).to(dev).bfloat16().requires_grad_()
+        # ---- all-gather -> GEMM
+        y = tp_fused.allgather_linear(x_loc, w, dist.group.WORLD)
+        xs = [torch.empty_like(x_loc) for _ in range(world)]
+        dist.all_gather(xs, x_loc.detach())
+        x_full = torch.cat(xs).float()
+        ref = x_full @ w.detach().float().t()
+        assert torch.allclose(y.float(), ref, rtol=2e-2, atol=2e-2), (it, (y.float() - ref).abs().max())
+        gy = torch.randn(S, N, generator=torch.Generator().manual_seed(55 + rank + it)).to(dev).bfloat16()
+        y.backward(gy)
+        dx_full = gy.float() @ w.detach().float()                       # every rank's contribution to all rows
+        dist.all_reduce(dx_full)
+        dx_ref = dx_full[rank * rows:(rank + 1) * rows]
+        assert torch.allclose(x_loc.grad.float(), dx_ref, rtol=3e-2, atol=3e-2 * dx_ref.abs().max().item()), it
+        dw_ref = gy.float().t() @ x_full
+        assert torch.allclose(w.grad.float(), dw_ref, rtol=3e-2, atol=3e-2 * dw_ref.abs().max().item()), it
+        # ---- GEMM -> reduce-scatter (row-parallel: every rank holds its own slice of the features)
+        x2 = (0.5 * torch.randn(S, K, generator=g)).to(dev).bfloat16().requires_grad_()
+        w2 = (0.05 * torch.randn(N, K, generator=g)).to(dev).bfloat16().requires_grad_()
+        y2 = tp_fused.linear_reduce_scatter(x2, w2, dist.group.WORLD)
+        part = x2.detach().float() @ w2.detach().float().t()
+        dist.all_reduce(part)
+        ref2 = part[rank * rows:(rank + 1) * rows]
+        assert torch.allclose(y2.float(), ref2, rtol=2e-2, atol=3e-2), (it, (y2.float() - ref2).abs().max())
+        gy2 = torch.randn(rows, N, generator=torch.Generator().manual_seed(77 + rank + it)).to(dev).bfloat16()
+        y2.backward(gy2)
+        gs = [torch.empty_like(gy2) for _ in range(world)]
+        dist.all_gather(gs, gy2)
+        gfull = torch.cat(gs).float()
+        dx2_ref = gfull @ w2.detach().float()
+        assert torch.allclose(x2.grad.float(), dx2_ref, rtol=3e-2, atol=3e-2 * dx2_ref.abs().max().item()), it
+        dw2_ref = gfull.t() @ x2.detach().float()
+        assert torch.allclose(w2.grad.float(), dw2_ref, rtol=3e-2, atol=3e-2 * dw2_ref.abs().max().item()), it
+    torch.cuda.synchronize()
+    _lib.check_status(dev)
+
+
+@pytest.mark.skipif(NGPU < 2, reason="needs 2 GPUs")
+def test_tp_linears_fused_with_collectives():
+    run_distributed(_tp_fused, world=min(NGPU, 4) if NGPU != 3 else 2, backend="nccl", timeout=300)
+
+
+def test_allgather_gemm_gate_times_out_cleanly():
+    """One GPU, no peer: an arrival flag that nothing sets. The GEMM's producer gives up after the (shortened)
+    limit, the kernel drains and frees its tensor memory, the status word reports a peer timeout, and the
+    next ordinary GEMM works."""
+    import ctypes
+
+    from atorch_b200 import _lib, ops
+
+    L = _lib.lib()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    a = torch.randn(512, 256, device=dev, dtype=torch.bfloat16)
+    b = torch.randn(256, 256, device=dev, dtype=torch.bfloat16)
+    y = torch.zeros(512, 256, device=dev, dtype=torch.bfloat16)
+    flags = torch.zeros(2, dtype=torch.int32, device=dev)
+    flags[0] = 1                                            # shard 0 arrived, shard 1 never does
+    assert L.atb_set_gate_wait_ns(ctypes.c_ulonglong(50_000_000)) == 0
+    try:
+        rc = L.atb_gemm_bf16_2cta_fused(
+            _lib.ptr(a), _lib.ptr(b), _lib.ptr(y), ctypes.c_int(512), ctypes.c_int(256), ctypes.c_int(256),
+            ctypes.c_longlong(256), ctypes.c_longlong(256), ctypes.c_longlong(256), ctypes.c_int(0), ctypes.c_int(0),
+            ctypes.c_float(1.0), _lib.ptr(flags), ctypes.c_uint(1), ctypes.c_int(256), ctypes.c_int(0), None,
+            ctypes.c_int(0), ctypes.c_int(0), _lib.stream_ptr(), _lib.ptr(_lib.status_word(dev)))
+        assert rc == 0
+        with pytest.raises(_lib.KernelError):
+            _lib.check_status(dev)
+    finally:
+        assert L.atb_set_gate_wait_ns(ctypes.c_ulonglong(2_000_000_000)) == 0
+    ref = a.float() @ b.float().t()
+    out = ops.gemm(a, b)
+    torch.cuda.synchronize()
+    _lib.check_status(dev)
+    assert torch.allclose(out.float(), ref, rtol=2e-2, atol=2e-1)

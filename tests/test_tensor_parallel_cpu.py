@@ -120,3 +120,39 @@ def _manual(rank, world):
 
 def test_manual_tp_gloo():
     run_distributed(_manual, world=2)
+
+
+def _tp_sp_chunk(rank, world):
+    """Sequence-parallel tensor parallelism of a Llama chunk: same loss as the unsharded chunk, and after
+    ``sync_sequence_parallel_grads`` the normalisation weights carry the full gradient."""
+    from atorch_b200.benchmarks.hybrid_bench import LlamaChunk
+    from atorch_b200.distributed import distributed as D
+    from atorch_b200.models.llama import LlamaConfig, RMSNorm, causal_lm_loss
+    from atorch_b200.parallel.tensor_parallel import (apply_tensor_parallel, mark_sequence_parallel_replicated,
+                                                      sync_sequence_parallel_grads)
+
+    D.create_parallel_group(([("tensor", world)], None))
+    cfg = LlamaConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=4, max_position_embeddings=16)
+    torch.manual_seed(0)
+    ref = LlamaChunk(cfg, 2, True, True, 0)
+    torch.manual_seed(0)
+    m = LlamaChunk(cfg, 2, True, True, 0, sp=True)
+    m.load_state_dict(ref.state_dict())
+    apply_tensor_parallel(m, {"sequence_parallel": True})
+    assert mark_sequence_parallel_replicated(m, (RMSNorm,)) == 5
+    ids = torch.randint(0, 64, (1, 16), generator=torch.Generator().manual_seed(1))
+    l_ref = causal_lm_loss(ref(ids), ids)
+    l_ref.backward()
+    loss = causal_lm_loss(m(ids), ids)
+    assert abs(loss.item() - l_ref.item()) < 1e-5, (loss.item(), l_ref.item())
+    loss.backward()
+    partial = m.norm.weight.grad.clone()
+    sync_sequence_parallel_grads(m)
+    assert torch.allclose(m.norm.weight.grad, ref.norm.weight.grad, atol=1e-5)
+    assert not torch.allclose(partial, ref.norm.weight.grad, atol=1e-5)
+    assert torch.allclose(m.layers[1].input_layernorm.weight.grad, ref.layers[1].input_layernorm.weight.grad, atol=1e-5)
+
+
+def test_sequence_parallel_chunk_gloo():
+    run_distributed(_tp_sp_chunk, world=2)
