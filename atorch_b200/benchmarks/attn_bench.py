@@ -88,7 +88,8 @@ def main(argv=None):
                      f"SDPA {tb_l:8.1f} us {2.5 * flops_f / tb_l / 1e6:7.1f} TF")
             if fa is not None:
                 o3 = fa(q, k, v, causal=causal)
-                tb_fa = time_fn(lambda: torch.autograd.grad(o3, (q, k, v), d2, retain_graph=True), args.iters, flush)
+                d3 = torch.randn_like(o3)
+                tb_fa = time_fn(lambda: torch.autograd.grad(o3, (q, k, v), d3, retain_graph=True), args.iters, flush)
                 line += f" | flash_attn {tb_fa:8.1f} us {2.5 * flops_f / tb_fa / 1e6:7.1f} TF"
         print(line, flush=True)
 

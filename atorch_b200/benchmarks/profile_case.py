@@ -108,16 +108,16 @@ def main(argv=None):
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29577")
-        dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", torch.cuda.current_device()))
         if case == "reduce_scatter":
             from atorch_b200.parallel.symm import SymmetricBuffer
 
-            buf = SymmetricBuffer(1 << 28, torch.bfloat16)
+            buf = SymmetricBuffer(1 << 27, torch.bfloat16)
             buf.use_nvls = False
             buf.tensor.normal_()
-            out = torch.empty(1 << 28, device=dev)
-            m, v, master = (torch.zeros(1 << 28, device=dev) for _ in range(3))
-            lp = torch.empty(1 << 28, device=dev, dtype=torch.bfloat16)
+            out = torch.empty(1 << 27, device=dev)
+            m, v, master = (torch.zeros(1 << 27, device=dev) for _ in range(3))
+            lp = torch.empty(1 << 27, device=dev, dtype=torch.bfloat16)
             for i in range(n):
                 buf.reduce_scatter_into(out, scale=1.0, max_blocks=32)
                 buf.reduce_scatter_adamw(master, m, v, lp, 1e-3, 0.9, 0.999, 1e-8, 0.01, i + 1, max_blocks=32)

@@ -285,9 +285,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           if (jj < lo || jj >= hi) sv[c] = -INFINITY;
         }
       }
-      float mx = sv[0];
+      // four independent chains instead of one chain of 63 dependent max operations
+      float mx4[4] = {sv[0], sv[1], sv[2], sv[3]};
 #pragma unroll
-      for (int c = 1; c < 64; ++c) mx = fmaxf(mx, sv[c]);
+      for (int c = 4; c < 64; c += 4) {
+        mx4[0] = fmaxf(mx4[0], sv[c]); mx4[1] = fmaxf(mx4[1], sv[c + 1]);
+        mx4[2] = fmaxf(mx4[2], sv[c + 2]); mx4[3] = fmaxf(mx4[3], sv[c + 3]);
+      }
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       float* rm = s_rowmax + (j & 1) * 256;
       rm[half * 128 + r] = mx;
       __syncwarp();
@@ -300,16 +305,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
       const float alpha = fast_exp2((m_run - m_use) * p.scale_log2);  // m_run = -inf -> 0
       const float neg_ms = -m_use * p.scale_log2;
-      float lsum = 0.f;
+      float ls4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t pk[32];
 #pragma unroll
       for (int c = 0; c < 64; c += 2) {
         const float p0 = fast_exp2(fmaf(sv[c], p.scale_log2, neg_ms));
         const float p1 = fast_exp2(fmaf(sv[c + 1], p.scale_log2, neg_ms));
-        lsum += p0 + p1;
+        ls4[(c >> 1) & 3] += p0 + p1;
         pk[c >> 1] = pack_bf16x2(p0, p1);
       }
-      l_run = l_run * alpha + lsum;
+      l_run = l_run * alpha + ((ls4[0] + ls4[1]) + (ls4[2] + ls4[3]));
       m_run = m_new;
       // previous tile's P V product must be folded in (and must have finished reading sP)
       if (j > 0) {

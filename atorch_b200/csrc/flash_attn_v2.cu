@@ -223,9 +223,14 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         for (int c = 0; c < 128; ++c)
           if (kv0 + c < lo || kv0 + c >= hi) sv[c] = -INFINITY;
       }
-      float mx = sv[0];
+      // four independent chains: a single chain of 127 dependent max operations would expose its latency
+      float mx4[4] = {sv[0], sv[1], sv[2], sv[3]};
 #pragma unroll
-      for (int c = 1; c < 128; ++c) mx = fmaxf(mx, sv[c]);
+      for (int c = 4; c < 128; c += 4) {
+        mx4[0] = fmaxf(mx4[0], sv[c]); mx4[1] = fmaxf(mx4[1], sv[c + 1]);
+        mx4[2] = fmaxf(mx4[2], sv[c + 2]); mx4[3] = fmaxf(mx4[3], sv[c + 3]);
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       // raise the reference maximum only when it pays: a stale one costs nothing while 2^(gap) fits bf16/fp32
       float alpha = 1.f;
       const bool raise = (mx > m_ref) && (m_ref == -INFINITY || (mx - m_ref) * p.scale_log2 > RESCALE_THRESHOLD);
@@ -252,7 +257,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         tmem_st_wait();
       }
       const float neg_ms = (m_ref == -INFINITY) ? 0.f : -m_ref * p.scale_log2;
-      float lsum = 0.f;
+      float ls4[4] = {0.f, 0.f, 0.f, 0.f};
       uint8_t* prow = sP + r * 128;
 #pragma unroll
       for (int c8 = 0; c8 < 16; ++c8) {       // 16 chunks of 8 columns; chunks 0..7 -> panel 0, 8..15 -> panel 1
@@ -261,13 +266,13 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         for (int q = 0; q < 4; ++q) {
           const float p0 = fast_exp2(fmaf(sv[c8 * 8 + 2 * q], p.scale_log2, neg_ms));
           const float p1 = fast_exp2(fmaf(sv[c8 * 8 + 2 * q + 1], p.scale_log2, neg_ms));
-          lsum += p0 + p1;
+          ls4[q] += p0 + p1;
           pk[q] = pack_bf16x2(p0, p1);
         }
         *reinterpret_cast<uint4*>(prow + (c8 >> 3) * PANEL + (((c8 & 7) ^ (r & 7)) << 4)) =
             make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
-      l_run += lsum;
+      l_run += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();

@@ -1,10 +1,11 @@
 """``ATorchGroupedLinear``: ``num_gemms`` linears (``weight{i}`` of shape ``[out, in]``) applied to the
 row groups of one input, ``forward(inp, m_splits, is_first_microbatch=None)``.
 
-With ``fp8`` on, all three GEMM families run block-scaled e4m3; quantised weights are cached and,
-unless ``FORCE_QUANTIZE_PER_MICROBATCH`` is set, re-used by later micro-batches
-(``is_first_microbatch=False``). ``fuse_wgrad_accumulation`` adds weight gradients into
-``weight{i}.main_grad``.
+With ``fp8`` on, all three GEMM families run block-scaled e4m3. The quantised weights live in a
+``WeightQuantCache``: ``is_first_microbatch=True`` (or ``None``) quantises them, ``is_first_microbatch=False``
+reuses what the first micro-batch of the step produced (unless ``FORCE_QUANTIZE_PER_MICROBATCH`` is set or a
+weight changed in between). ``fuse_wgrad_accumulation`` adds weight gradients into ``weight{i}.main_grad``
+and returns no ``.grad``.
 (Reference: atorch/modules/fp8/quantized_grouped_linear.py:36-584.)
 """
 from __future__ import annotations
@@ -17,7 +18,7 @@ import torch.nn as nn
 
 from ... import ops
 from ...ops import moe as moe_ops
-from .grouped import grouped_scaled_linear
+from .grouped import WeightQuantCache, grouped_scaled_linear
 
 
 class ATorchGroupedLinear(nn.Module):
@@ -36,17 +37,19 @@ class ATorchGroupedLinear(nn.Module):
                 self.register_parameter(f"bias{i}", nn.Parameter(torch.zeros(out_features, dtype=params_dtype,
                                                                            device=device)))
         self.force_requantize = os.environ.get("FORCE_QUANTIZE_PER_MICROBATCH", "0") in ("1", "true", "True")
+        self.quant_cache = WeightQuantCache()
 
     def weights(self) -> List[torch.Tensor]:
         return [getattr(self, f"weight{i}") for i in range(self.num_gemms)]
 
     def forward(self, inp: torch.Tensor, m_splits: List[int], is_first_microbatch: Optional[bool] = None):
         assert len(m_splits) == self.num_gemms and sum(m_splits) == inp.shape[0]
-        w = torch.stack(self.weights())
         if self.fp8 and inp.dtype == torch.bfloat16:
-            out = grouped_scaled_linear(inp, w, m_splits)
+            refresh = self.force_requantize or is_first_microbatch is None or bool(is_first_microbatch)
+            out = grouped_scaled_linear(inp, self.weights(), m_splits, cache=self.quant_cache, refresh=refresh,
+                                        fuse_wgrad_accumulation=self.fuse_wgrad_accumulation)
         else:
-            out = moe_ops.grouped_gemm(inp, w.to(inp.dtype), m_splits, trans_b=True)
+            out = moe_ops.grouped_gemm(inp, torch.stack(self.weights()).to(inp.dtype), m_splits, trans_b=True)
         if self.use_bias:
             idx = torch.repeat_interleave(torch.arange(self.num_gemms, device=inp.device),
                                           torch.tensor(m_splits, device=inp.device))

@@ -59,3 +59,34 @@ def test_grouped_linear():
     assert (y.float() - ref).abs().max() < 0.06 * ref.abs().max()
     y.float().sum().backward()
     assert gl.weight0.grad is not None and gl.weight1.grad.abs().sum() == 0
+
+
+def test_grouped_linear_weight_cache_and_wgrad_accumulation():
+    """ATorchGroupedLinear: later micro-batches reuse the quantised weights of the first one; with
+    fuse_wgrad_accumulation the weight gradients of all micro-batches add up in main_grad."""
+    import torch
+
+    from atorch_b200.modules.fp8.quantized_grouped_linear import ATorchGroupedLinear
+
+    torch.manual_seed(0)
+    lin = ATorchGroupedLinear(2, 128, 256, fp8=True, fuse_wgrad_accumulation=True)
+    ref = ATorchGroupedLinear(2, 128, 256, fp8=True)
+    for i in range(2):
+        getattr(ref, f"weight{i}").data.copy_(getattr(lin, f"weight{i}").data)
+        w = getattr(lin, f"weight{i}")
+        w.main_grad = torch.zeros_like(w, dtype=torch.float32)
+    xs = [torch.randn(256, 128, dtype=torch.bfloat16) for _ in range(3)]
+    for mb, x in enumerate(xs):
+        lin(x, [128, 128], is_first_microbatch=(mb == 0)).float().sum().backward()
+        ref(x, [128, 128]).float().sum().backward()
+    assert lin.quant_cache.misses == 2 and lin.quant_cache.hits == 4          # quantised once per weight
+    assert ref.quant_cache.misses == 6
+    for i in range(2):
+        w, wr = getattr(lin, f"weight{i}"), getattr(ref, f"weight{i}")
+        assert w.grad is None and getattr(w, "grad_added_to_main_grad", False)
+        assert torch.allclose(w.main_grad, wr.grad.float(), rtol=2e-2, atol=2e-1)
+    # a changed weight is re-quantised even when the caller says "not the first micro-batch"
+    with torch.no_grad():
+        lin.weight0.add_(1.0)
+    lin(xs[0], [128, 128], is_first_microbatch=False)
+    assert lin.quant_cache.misses == 3

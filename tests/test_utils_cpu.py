@@ -106,3 +106,41 @@ def test_bench_loss_curve_helpers(tmp_path):
     json.dump({"impl": "reference", "loss_curve": [10.0, 9.4, 9.05]}, open(fb, "w"))
     r = bench.compare_loss(str(fa), str(fb))
     assert abs(r["max_abs_diff"] - 0.1) < 1e-9 and r["steps"] == 3
+
+
+def test_small_utils_version_import_gc_trace(tmp_path):
+    import json
+    import pickle
+
+    from atorch_b200.utils import gc as mgc
+    from atorch_b200.utils import import_util, parse_memory_pickle, parse_trace_json, version
+
+    assert version.torch_version() >= (2, 0, 0) and version.torch_version("2.4.1+cu121") == (2, 4, 1)
+    assert version.package_version_bigger_than("torch", "1.0") and not version.package_version_smaller_than("torch", "1.0")
+    assert version.get_version("definitely_not_a_package") is None
+    assert import_util.import_module("os.path.join") is __import__("os").path.join
+    f = tmp_path / "m_mod.py"
+    f.write_text("X = 41 + 1\n")
+    assert import_util.import_module_from_py_file(str(f)).X == 42
+    assert import_util.is_triton_available() in (True, False) and not import_util.is_xla_device_available()
+    g = mgc.ManualGarbageCollection(gc_freq=2)
+    try:
+        assert [g.run(s) for s in (1, 2, 3, 4)] == [False, True, False, True]
+    finally:
+        g.restore()
+    ev = [{"ph": "X", "cat": "kernel", "name": "gemm_bf16_2cta_kernel", "ts": 0, "dur": 100},
+          {"ph": "X", "cat": "kernel", "name": "ncclDevKernel_AllGather", "ts": 50, "dur": 100},
+          {"ph": "X", "cat": "kernel", "name": "adamw_kernel", "ts": 200, "dur": 50},
+          {"ph": "X", "cat": "user_annotation", "name": "ProfilerStep#1", "ts": 0, "dur": 250}]
+    t = tmp_path / "trace.json"
+    t.write_text(json.dumps({"traceEvents": ev}))
+    r = parse_trace_json.parse_trace_file(str(t))
+    assert r["comm_busy_us"] == 100 and r["comm_hidden_us"] == 50 and r["comm_exposed_us"] == 50 and r["idle_us"] == 50
+    snap = {"segments": [{"blocks": [
+        {"state": "active_allocated", "size": 1 << 20, "frames": [{"filename": "torch/x.py", "line": 1, "name": "a"},
+                                                                   {"filename": "/m/model.py", "line": 7, "name": "fwd"}]},
+        {"state": "inactive", "size": 1 << 22, "frames": []}]}]}
+    p = tmp_path / "snap.pickle"
+    p.write_bytes(pickle.dumps(snap))
+    c = parse_memory_pickle.parse_memory_pickle_file(str(p), blocklist=["torch/"])
+    assert c["/m/model.py:7 fwd"] == 1 << 20 and sum(c.values()) == 1 << 20
