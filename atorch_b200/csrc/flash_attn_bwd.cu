@@ -7,11 +7,17 @@
 //   dQ  = dS K                                      TMEM -> registers -> red.global.add.v4.f32
 // A [rows][64] bf16 panel with 128-byte swizzle is at the same time a K-major tile of the matrix and
 // an MN-major tile of its transpose, so P, dS, Q, dO and K are each stored once and read both ways.
-// TMEM: S | dP | dV | dK = 4 x 128 columns; dQ reuses the S columns.
+// TMEM: S | dP | dV | dK = 4 x 128 columns; dQ reuses the dP columns.
 //
 // Warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warps 2..9 = element-wise work (thread
 // (row r, half h) owns columns [64h, 64h+64) of row r). `delta = rowsum(dO * O)` comes from a
 // small pre-pass; dQ is accumulated in fp32 and converted by a post-pass.
+//
+// Software pipeline over the query blocks (Q is double-buffered in shared memory):
+//   tensor core, when P(i), dS(i) are in shared memory:  S(i+1) | dV(i) | dK(i) | dQ(i)
+//   element-wise warps meanwhile:                        P(i+1) = exp2(S(i+1) c - lse)   (the exponentials)
+//   then:  dQ(i) out of TMEM (red.add)  ->  tensor core: dP(i+1)  ->  dS(i+1), P(i+1) to shared memory
+// so the exponentials and the loads of the next Q / dO tiles run under the three accumulating products.
 //
 // Masks are per-row key intervals [lo, hi) as in the forward kernel.
 #include "common.cuh"
@@ -40,21 +46,30 @@ struct BwdParams {
 };
 
 struct SmemB {
-  static constexpr int Q_OFF = 0;
-  static constexpr int DO_OFF = Q_OFF + TILE;
+  static constexpr int Q_OFF = 0;                 // two stages
+  static constexpr int DO_OFF = Q_OFF + 2 * TILE;
   static constexpr int K_OFF = DO_OFF + TILE;
   static constexpr int V_OFF = K_OFF + TILE;
   static constexpr int P_OFF = V_OFF + TILE;
   static constexpr int DS_OFF = P_OFF + TILE;
-  static constexpr int BAR_OFF = DS_OFF + TILE;  // 192 KB
-  static constexpr int NBARS = 7;
+  static constexpr int BAR_OFF = DS_OFF + TILE;  // 224 KB
+  static constexpr int NBARS = 12;
   static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 64 + 1024;
 };
+static_assert(SmemB::TOTAL <= 232448, "shared memory of the backward kernel exceeds 227 KB");
 
 ATB_DEVICE void red_add_v4(float* addr, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
                : "memory");
 }
+
+// Row of a query block as the element-wise thread sees it.
+struct RowInfo {
+  int i;          // global query row
+  bool valid;     // inside the sequence and not fully masked
+  int lo, hi;     // key interval
+  float lse2, delta;
+};
 
 __global__ void __launch_bounds__(THREADS, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
@@ -70,12 +85,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* sdS = smem + L::DS_OFF;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
   uint64_t* kv_full = bars;
-  uint64_t* qdo_full = bars + 1;
-  uint64_t* qdo_empty = bars + 2;
-  uint64_t* sdp_full = bars + 3;
-  uint64_t* pds_full = bars + 4;
-  uint64_t* dq_full = bars + 5;
-  uint64_t* acc_free = bars + 6;
+  uint64_t* q_full = bars + 1;    // [2]
+  uint64_t* q_free = bars + 3;    // [2]  dK(i) has read Q(i)
+  uint64_t* do_full = bars + 5;
+  uint64_t* do_free = bars + 6;   // dV(i) has read dO(i)
+  uint64_t* s_full = bars + 7;    // S(i) is in TMEM
+  uint64_t* dp_full = bars + 8;   // dP(i) is in TMEM
+  uint64_t* pds_full = bars + 9;  // P(i), dS(i) are in shared memory; S(i), dP(i) have been read
+  uint64_t* dq_full = bars + 10;  // dV(i), dK(i), dQ(i) are complete
+  uint64_t* dp_free = bars + 11;  // dQ(i) has been read out of the dP columns
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::NBARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* q_range = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_slot + 2));  // [2]: first, last+1 q block
@@ -91,12 +109,17 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    mbar_init(qdo_full, 1);
-    mbar_init(qdo_empty, 1);
-    mbar_init(sdp_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&q_free[i], 1);
+    }
+    mbar_init(do_full, 1);
+    mbar_init(do_free, 1);
+    mbar_init(s_full, 1);
+    mbar_init(dp_full, 1);
     mbar_init(pds_full, N_EW / 32);
     mbar_init(dq_full, 1);
-    mbar_init(acc_free, N_EW / 32);
+    mbar_init(dp_free, N_EW / 32);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -151,13 +174,16 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tma_load_2d(sV, &tmV, kv_full, hk * HD, (int)k_row);
       tma_load_2d(sV + PANEL, &tmV, kv_full, hk * HD + 64, (int)k_row);
       for (int it = 0; it < nblk; ++it) {
-        if (!mbar_wait(qdo_empty, (it & 1) ^ 1, abort_flag, p.status)) break;
+        const int qs = it & 1;
         const int qrow = (int)(q_row_base + (long long)(qb0 + it) * BQ);
-        mbar_expect_tx(qdo_full, 2 * TILE);
-        tma_load_2d(sQ, &tmQ, qdo_full, h * HD, qrow);
-        tma_load_2d(sQ + PANEL, &tmQ, qdo_full, h * HD + 64, qrow);
-        tma_load_2d(sdO, &tmdO, qdo_full, h * HD, qrow);
-        tma_load_2d(sdO + PANEL, &tmdO, qdo_full, h * HD + 64, qrow);
+        if (!mbar_wait(&q_free[qs], ((it >> 1) & 1) ^ 1, abort_flag, p.status)) break;
+        mbar_expect_tx(&q_full[qs], TILE);
+        tma_load_2d(sQ + qs * TILE, &tmQ, &q_full[qs], h * HD, qrow);
+        tma_load_2d(sQ + qs * TILE + PANEL, &tmQ, &q_full[qs], h * HD + 64, qrow);
+        if (!mbar_wait(do_free, (it & 1) ^ 1, abort_flag, p.status)) break;
+        mbar_expect_tx(do_full, TILE);
+        tma_load_2d(sdO, &tmdO, do_full, h * HD, qrow);
+        tma_load_2d(sdO + PANEL, &tmdO, do_full, h * HD + 64, qrow);
       }
     }
   } else if (warp == 1) {
@@ -165,43 +191,60 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       constexpr uint32_t id_kk = umma_idesc(128, 128, 1, 1, false, false);
       constexpr uint32_t id_mm = umma_idesc(128, 128, 1, 1, true, true);
       constexpr uint32_t id_km = umma_idesc(128, 128, 1, 1, false, true);
-      const uint32_t aQ = smem_u32(sQ), adO = smem_u32(sdO), aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP),
-                     adS = smem_u32(sdS);
+      const uint32_t adO = smem_u32(sdO), aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP), adS = smem_u32(sdS);
       const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdV = tmem_base + 256, tdK = tmem_base + 384;
-      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status);
-      for (int it = 0; ok && it < nblk; ++it) {
-        if (!mbar_wait(qdo_full, it & 1, abort_flag, p.status)) break;
-        if (!mbar_wait(acc_free, (it & 1) ^ 1, abort_flag, p.status)) break;
+      auto issue_s = [&](int it) -> bool {   // S(it) = Q(it) K^T over d
+        if (!mbar_wait(&q_full[it & 1], (it >> 1) & 1, abort_flag, p.status)) return false;
         tc_fence_after();
+        const uint32_t aQ = smem_u32(sQ + (it & 1) * TILE);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {  // S = Q K^T over d
+        for (int k = 0; k < 8; ++k) {
           const uint32_t off = (k >> 2) * PANEL + (k & 3) * 32;
           umma_f16<1>(tS, umma_desc_sw128(aQ + off, 16, 1024), umma_desc_sw128(aK + off, 16, 1024), id_kk, k != 0);
         }
+        umma_commit(s_full);
+        return true;
+      };
+      auto issue_dp = [&](int it) -> bool {  // dP(it) = dO(it) V^T over d
+        if (!mbar_wait(do_full, it & 1, abort_flag, p.status)) return false;
+        tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {  // dP = dO V^T over d
+        for (int k = 0; k < 8; ++k) {
           const uint32_t off = (k >> 2) * PANEL + (k & 3) * 32;
           umma_f16<1>(tdP, umma_desc_sw128(adO + off, 16, 1024), umma_desc_sw128(aV + off, 16, 1024), id_kk, k != 0);
         }
-        umma_commit(sdp_full);
+        umma_commit(dp_full);
+        return true;
+      };
+      bool ok = mbar_wait(kv_full, 0, abort_flag, p.status);
+      ok = ok && issue_s(0) && issue_dp(0);
+      for (int it = 0; ok && it < nblk; ++it) {
         if (!mbar_wait(pds_full, it & 1, abort_flag, p.status)) break;
         tc_fence_after();
+        if (it + 1 < nblk && !issue_s(it + 1)) break;
+        const uint32_t aQ = smem_u32(sQ + (it & 1) * TILE);
 #pragma unroll
         for (int k = 0; k < 8; ++k)  // dV += P^T dO over q
           umma_f16<1>(tdV, umma_desc_sw128(aP + k * 2048, PANEL, 1024), umma_desc_sw128(adO + k * 2048, PANEL, 1024),
                       id_mm, (it | k) != 0);
+        umma_commit(do_free);
 #pragma unroll
         for (int k = 0; k < 8; ++k)  // dK += dS^T Q over q
           umma_f16<1>(tdK, umma_desc_sw128(adS + k * 2048, PANEL, 1024), umma_desc_sw128(aQ + k * 2048, PANEL, 1024),
                       id_mm, (it | k) != 0);
+        umma_commit(&q_free[it & 1]);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {  // dQ = dS K over keys (into the S columns)
+        for (int k = 0; k < 8; ++k) {  // dQ = dS K over keys (into the dP columns)
           const uint32_t off = (k >> 2) * PANEL + (k & 3) * 32;
-          umma_f16<1>(tS, umma_desc_sw128(adS + off, 16, 1024), umma_desc_sw128(aK + k * 2048, PANEL, 1024), id_km,
+          umma_f16<1>(tdP, umma_desc_sw128(adS + off, 16, 1024), umma_desc_sw128(aK + k * 2048, PANEL, 1024), id_km,
                       k != 0);
         }
         umma_commit(dq_full);
-        umma_commit(qdo_empty);
+        if (it + 1 < nblk) {
+          if (!mbar_wait(dp_free, it & 1, abort_flag, p.status)) break;
+          tc_fence_after();
+          if (!issue_dp(it + 1)) break;
+        }
       }
     }
   } else {
@@ -209,84 +252,116 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    const uint32_t tS = lane_addr + half * 64, tdP = lane_addr + 128 + half * 64;
     bool ok = true;
-    for (int it = 0; it < nblk; ++it) {
-      const int i = (qb0 + it) * BQ + r;  // global query row
-      bool valid = i < p.Sq;
-      int lo = 0, hi = 0;
-      float lse2 = 0.f, delta = 0.f;
-      if (valid) {
-        const long long ridx = ((long long)b * p.Hq + h) * p.Sq + i;
+
+    auto row_info = [&](int it) -> RowInfo {
+      RowInfo ri;
+      ri.i = (qb0 + it) * BQ + r;
+      ri.valid = it < nblk && ri.i < p.Sq;
+      ri.lo = 0; ri.hi = 0; ri.lse2 = 0.f; ri.delta = 0.f;
+      if (ri.valid) {
+        const long long ridx = ((long long)b * p.Hq + h) * p.Sq + ri.i;
         const float l = p.lse[ridx];
         if (l == -INFINITY) {
-          valid = false;
+          ri.valid = false;
         } else {
-          lse2 = l * 1.4426950408889634f;
-          delta = p.delta[ridx];
-          lo = p.row_lo ? p.row_lo[(long long)b * p.Sq + i] : 0;
-          hi = p.row_hi ? p.row_hi[(long long)b * p.Sq + i] : (p.causal ? i + 1 + shift : p.Sk);
-          lo = max(lo, 0);
-          hi = min(hi, p.Sk);
+          ri.lse2 = l * 1.4426950408889634f;
+          ri.delta = p.delta[ridx];
+          ri.lo = p.row_lo ? p.row_lo[(long long)b * p.Sq + ri.i] : 0;
+          ri.hi = p.row_hi ? p.row_hi[(long long)b * p.Sq + ri.i] : (p.causal ? ri.i + 1 + shift : p.Sk);
+          ri.lo = max(ri.lo, 0);
+          ri.hi = min(ri.hi, p.Sk);
         }
       }
-      const bool row_full = valid && lo <= kv0 && hi >= kv0 + BKV;
-      if (!__all_sync(0xffffffffu, mbar_wait(sdp_full, it & 1, abort_flag, p.status))) { ok = false; break; }
+      return ri;
+    };
+    // dQ(it) of row `ri` leaves the dP columns for the fp32 accumulation buffer
+    auto drain_dq = [&](int it, const RowInfo& ri) -> bool {
+      if (!__all_sync(0xffffffffu, mbar_wait(dq_full, it & 1, abort_flag, p.status))) return false;
+      tc_fence_after();
+      float* dqrow = p.dq_acc + (((long long)b * p.Sq + ri.i) * p.Hq + h) * HD + half * 64;
+      uint32_t t0[32], t1[32];
+      tmem_ld_32x32(tdP, t0);
+      tmem_ld_32x32(tdP + 32, t1);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dp_free);
+      if (ri.i < p.Sq && it < nblk) {
+#pragma unroll
+        for (int c = 0; c < 32; c += 4)
+          red_add_v4(dqrow + c, __uint_as_float(t0[c]), __uint_as_float(t0[c + 1]), __uint_as_float(t0[c + 2]),
+                     __uint_as_float(t0[c + 3]));
+#pragma unroll
+        for (int c = 0; c < 32; c += 4)
+          red_add_v4(dqrow + 32 + c, __uint_as_float(t1[c]), __uint_as_float(t1[c + 1]), __uint_as_float(t1[c + 2]),
+                     __uint_as_float(t1[c + 3]));
+      }
+      return true;
+    };
+
+    RowInfo cur = row_info(0), prev = cur;
+    for (int it = 0; it < nblk; ++it) {
+      const RowInfo nxt = row_info(it + 1);   // issued early: the loads complete under this block's work
+      const bool row_full = cur.valid && cur.lo <= kv0 && cur.hi >= kv0 + BKV;
+      // ---- P(it) = exp2(S c - lse): runs while the tensor core accumulates dV, dK and forms dQ of block it-1
+      if (!__all_sync(0xffffffffu, mbar_wait(s_full, it & 1, abort_flag, p.status))) { ok = false; break; }
+      tc_fence_after();
+      float pv[64];
+      {
+        uint32_t s0[32], s1[32];
+        tmem_ld_32x32(tS, s0);
+        tmem_ld_32x32(tS + 32, s1);
+        tmem_ld_wait();
+        const int c0 = kv0 + half * 64;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          pv[c] = fast_exp2(fmaf(__uint_as_float(s0[c]), p.scale_log2, -cur.lse2));
+          pv[32 + c] = fast_exp2(fmaf(__uint_as_float(s1[c]), p.scale_log2, -cur.lse2));
+        }
+        if (!row_full) {
+#pragma unroll
+          for (int c = 0; c < 64; ++c)
+            if (!cur.valid || c0 + c < cur.lo || c0 + c >= cur.hi) pv[c] = 0.f;
+        }
+      }
+      // ---- dQ(it-1) out of the dP columns, which frees them for dP(it)
+      if (it > 0 && !drain_dq(it - 1, prev)) { ok = false; break; }
+      // ---- dS(it) = P (dP - delta) scale; P and dS to shared memory (free: dq_full(it-1) has been waited for)
+      if (!__all_sync(0xffffffffu, mbar_wait(dp_full, it & 1, abort_flag, p.status))) { ok = false; break; }
       tc_fence_after();
       uint8_t* prow = sP + half * PANEL + r * 128;
       uint8_t* dsrow = sdS + half * PANEL + r * 128;
-#pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        uint32_t ts[32], td[32];
-        tmem_ld_32x32(lane_addr + half * 64 + cc * 32, ts);
-        tmem_ld_32x32(lane_addr + 128 + half * 64 + cc * 32, td);
+      {
+        uint32_t d0[32], d1[32];
+        tmem_ld_32x32(tdP, d0);
+        tmem_ld_32x32(tdP + 32, d1);
         tmem_ld_wait();
-        uint32_t pk[16], dk_[16];
-        const int c0 = kv0 + half * 64 + cc * 32;
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          float p0 = fast_exp2(fmaf(__uint_as_float(ts[c]), p.scale_log2, -lse2));
-          float p1 = fast_exp2(fmaf(__uint_as_float(ts[c + 1]), p.scale_log2, -lse2));
-          if (!row_full) {
-            if (!valid || c0 + c < lo || c0 + c >= hi) p0 = 0.f;
-            if (!valid || c0 + c + 1 < lo || c0 + c + 1 >= hi) p1 = 0.f;
+        for (int c8 = 0; c8 < 8; ++c8) {
+          uint32_t pk[4], dk_[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int c = c8 * 8 + 2 * q;
+            const float dp0 = __uint_as_float(c < 32 ? d0[c & 31] : d1[c & 31]);
+            const float dp1 = __uint_as_float(c < 32 ? d0[(c + 1) & 31] : d1[(c + 1) & 31]);
+            pk[q] = pack_bf16x2(pv[c], pv[c + 1]);
+            dk_[q] = pack_bf16x2(pv[c] * (dp0 - cur.delta) * p.scale, pv[c + 1] * (dp1 - cur.delta) * p.scale);
           }
-          const float d0 = p0 * (__uint_as_float(td[c]) - delta) * p.scale;
-          const float d1 = p1 * (__uint_as_float(td[c + 1]) - delta) * p.scale;
-          pk[c >> 1] = pack_bf16x2(p0, p1);
-          dk_[c >> 1] = pack_bf16x2(d0, d1);
-        }
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int c8 = cc * 4 + q4;
           const int slot = (c8 ^ (r & 7)) << 4;
-          *reinterpret_cast<uint4*>(prow + slot) = make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
-          *reinterpret_cast<uint4*>(dsrow + slot) =
-              make_uint4(dk_[q4 * 4], dk_[q4 * 4 + 1], dk_[q4 * 4 + 2], dk_[q4 * 4 + 3]);
+          *reinterpret_cast<uint4*>(prow + slot) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          *reinterpret_cast<uint4*>(dsrow + slot) = make_uint4(dk_[0], dk_[1], dk_[2], dk_[3]);
         }
       }
       fence_proxy_async_smem();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_full);
-      if (!__all_sync(0xffffffffu, mbar_wait(dq_full, it & 1, abort_flag, p.status))) { ok = false; break; }
-      tc_fence_after();
-      float* dqrow = p.dq_acc + (((long long)b * p.Sq + i) * p.Hq + h) * HD + half * 64;
-#pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        uint32_t t[32];
-        tmem_ld_32x32(lane_addr + half * 64 + cc * 32, t);
-        tmem_ld_wait();
-        if (valid) {
-#pragma unroll
-          for (int c = 0; c < 32; c += 4)
-            red_add_v4(dqrow + cc * 32 + c, __uint_as_float(t[c]), __uint_as_float(t[c + 1]),
-                       __uint_as_float(t[c + 2]), __uint_as_float(t[c + 3]));
-        }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(acc_free);
+      prev = cur;
+      cur = nxt;
     }
+    if (ok && nblk > 0) ok = drain_dq(nblk - 1, prev);
     // dV / dK of this key block: TMEM lane = key row. tcgen05.ld is a warp-wide (.sync.aligned)
     // instruction: every lane executes it, only the global stores are predicated per row.
     const int j = kv0 + r;

@@ -4,16 +4,19 @@
 // producer, warp 1 = MMA issuer / TMEM owner, warps 2..5 = softmax of tile A, warps 6..9 = softmax of
 // tile B; a softmax thread owns one whole row (128 scores), so no row statistics are exchanged.
 //
-//   TMEM:  S_A | S_B | O_A | O_B   (4 x 128 fp32 columns)
-//   per K/V tile j:   S_T = Q_T K_j^T  ->  P_T = 2^(S_T c - m_T c) (bf16, shared memory)  ->  O_T += P_T V_j
+//   TMEM:  S_A | S_B | O_A | O_B   (4 x 128 fp32 columns); P_T (bf16) overwrites the first 64 columns of S_T
+//   per K/V tile j:   S_T = Q_T K_j^T  ->  P_T = 2^(S_T c - m_T c)  ->  O_T += P_T V_j
 //
-// O accumulates in tensor memory. The reference maximum m_T of a row is only raised when the new row
-// maximum exceeds it by more than 2^8 (in the exponent domain); then the row of O_T is rescaled in
-// TMEM by the owning thread, which is safe because the single P buffer is only rewritten after every
-// earlier P.V product has completed. While tile A's warps exponentiate, the tensor core works for tile
-// B and vice versa: issue order  PV_A(j), S_A(j+1), PV_B(j), S_B(j+1).
+// P never leaves tensor memory: the softmax thread stores its packed row with tcgen05.st and the P.V
+// product reads it as the A operand of tcgen05.mma. O accumulates in tensor memory. The reference maximum
+// m_T of a row is only raised when the new row maximum exceeds it by more than 2^8 (in the exponent
+// domain); then the row of O_T is rescaled in TMEM by the owning thread, which is safe because the scores
+// S_T(j) it has just waited for were issued after the product P_T(j-1) V and complete after it.
+// While tile A's warps exponentiate, the tensor core works for tile B and vice versa:
+// issue order  PV_A(j), S_A(j+1), PV_B(j), S_B(j+1).
 //
-// Masks: per-row key interval [lo, hi) exactly as in flash_attn.cu.
+// Masks: per-row key interval [lo, hi) exactly as in flash_attn.cu; each query tile walks only the K/V
+// tiles up to the last one that any of its rows can see.
 #include "common.cuh"
 
 namespace {
@@ -39,9 +42,8 @@ struct L2 {
   static constexpr int Q_OFF = 0;                    // tile A, tile B
   static constexpr int K_OFF = Q_OFF + 2 * TILE;     // 2 stages
   static constexpr int V_OFF = K_OFF + 2 * TILE;     // 2 stages
-  static constexpr int P_OFF = V_OFF + 2 * TILE;     // one buffer shared by both tiles
-  static constexpr int BAR_OFF = P_OFF + TILE;       // 224 KB
-  static constexpr int NBARS = 1 + 8 + 2 + 2 + 2 + 1 + 2;
+  static constexpr int BAR_OFF = V_OFF + 2 * TILE;   // 192 KB
+  static constexpr int NBARS = 1 + 8 + 2 + 2 + 2;
   static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 64 + 1024;
 };
 
@@ -53,21 +55,18 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   uint8_t* sQ = smem + L2::Q_OFF;
   uint8_t* sK = smem + L2::K_OFF;
   uint8_t* sV = smem + L2::V_OFF;
-  uint8_t* sP = smem + L2::P_OFF;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L2::BAR_OFF);
   uint64_t* q_full = bars;
   uint64_t* k_full = bars + 1;      // [2]
   uint64_t* k_empty = bars + 3;     // [2]
   uint64_t* v_full = bars + 5;      // [2]
   uint64_t* v_empty = bars + 7;     // [2]
-  uint64_t* s_full = bars + 9;      // [2] per query tile
-  uint64_t* s_free = bars + 11;     // [2]
-  uint64_t* p_full = bars + 13;     // [2]
-  uint64_t* p_free = bars + 15;     // one: counts every P.V product
-  uint64_t* o_full = bars + 16;     // [2]
+  uint64_t* s_full = bars + 9;      // [2] per query tile: S_T(j) is in TMEM (and P_T(j-1) V has completed)
+  uint64_t* p_full = bars + 11;     // [2] per query tile: P_T(j) is in TMEM
+  uint64_t* o_full = bars + 13;     // [2] per query tile: the last P.V product has completed
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L2::NBARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* kv_range = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_slot + 2));  // t0, t1
+  int* kv_range = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_slot + 2));  // t0, t1 of tile A, t1 of tile B
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (p.status != nullptr && *reinterpret_cast<volatile int*>(p.status) != 0) return;
@@ -82,39 +81,45 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&s_free[i], 4);
-      mbar_init(&p_full[i], 4); mbar_init(&o_full[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 4); mbar_init(&o_full[i], 1);
     }
-    mbar_init(p_free, 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
   if (warp == 1) { tmem_alloc<1>(tmem_slot, 512); tmem_relinquish<1>(); }
-  if (warp == 2) {   // union of the key intervals of all 256 rows
-    int umin = INT_MAX, umax = 0;
-    for (int r = lane; r < 2 * BQ; r += 32) {
-      const int i = q0 + r;
-      if (i >= p.Sq) continue;
-      int lo = p.row_lo ? p.row_lo[(long long)b * p.Sq + i] : 0;
-      int hi = p.row_hi ? p.row_hi[(long long)b * p.Sq + i] : (p.causal ? i + 1 + shift : p.Sk);
-      lo = max(lo, 0); hi = min(hi, p.Sk);
-      if (hi > lo) { umin = min(umin, lo); umax = max(umax, hi); }
-    }
+  if (warp == 2) {   // union of the key intervals of the rows of each tile
+    int umin[2] = {INT_MAX, INT_MAX}, umax[2] = {0, 0};
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      umin = min(umin, __shfl_xor_sync(0xffffffffu, umin, o));
-      umax = max(umax, __shfl_xor_sync(0xffffffffu, umax, o));
+    for (int t = 0; t < 2; ++t) {
+      for (int r = lane; r < BQ; r += 32) {
+        const int i = q0 + t * BQ + r;
+        if (i >= p.Sq) continue;
+        int lo = p.row_lo ? p.row_lo[(long long)b * p.Sq + i] : 0;
+        int hi = p.row_hi ? p.row_hi[(long long)b * p.Sq + i] : (p.causal ? i + 1 + shift : p.Sk);
+        lo = max(lo, 0); hi = min(hi, p.Sk);
+        if (hi > lo) { umin[t] = min(umin[t], lo); umax[t] = max(umax[t], hi); }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        umin[t] = min(umin[t], __shfl_xor_sync(0xffffffffu, umin[t], o));
+        umax[t] = max(umax[t], __shfl_xor_sync(0xffffffffu, umax[t], o));
+      }
     }
     if (lane == 0) {
-      kv_range[0] = umax > umin ? umin / BKV : 0;
-      kv_range[1] = umax > umin ? (umax + BKV - 1) / BKV : 0;
+      const int lo = min(umin[0], umin[1]);
+      const int first = lo == INT_MAX ? 0 : lo / BKV;
+      kv_range[0] = first;
+      kv_range[1] = umax[0] > umin[0] ? (umax[0] + BKV - 1) / BKV : first;
+      kv_range[2] = umax[1] > umin[1] ? (umax[1] + BKV - 1) / BKV : first;
     }
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int t0 = kv_range[0], n = kv_range[1] - kv_range[0];
+  const int t0 = kv_range[0];
+  const int nt[2] = {kv_range[1] - t0, kv_range[2] - t0};
+  const int n = max(nt[0], nt[1]);
   const long long q_row0 = (long long)b * p.Sq + q0;
   const long long k_row0 = (long long)b * p.Sk;
 
@@ -145,13 +150,15 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     if (lane == 0 && n > 0) {
       constexpr uint32_t idesc_s = umma_idesc(BQ, BKV, 1, 1, false, false);
       constexpr uint32_t idesc_o = umma_idesc(BQ, HD, 1, 1, false, true);
-      const uint32_t p_addr = smem_u32(sP);
-      // S_T(j) = Q_T K_j^T into the tile's S columns; the K stage is released after tile B's product
+      int k_ready = -1, v_ready = -1;   // newest K / V tile whose arrival has been waited for
+      // S_T(j) = Q_T K_j^T into the tile's S columns
       auto issue_s = [&](int t, int j) -> bool {
         const int s = j & 1;
-        if (t == 0 && !mbar_wait(&k_full[s], (j >> 1) & 1, abort_flag, p.status)) return false;
-        if (!mbar_wait(&s_free[t], (j & 1) ^ 1, abort_flag, p.status)) return false;
-        tc_fence_after();
+        if (k_ready < j) {
+          if (!mbar_wait(&k_full[s], (j >> 1) & 1, abort_flag, p.status)) return false;
+          k_ready = j;
+          tc_fence_after();
+        }
         const uint32_t q_addr = smem_u32(sQ + t * TILE), k_addr = smem_u32(sK + s * TILE);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
@@ -160,29 +167,33 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                       umma_desc_sw128(k_addr + off, 16, 1024), idesc_s, k != 0);
         }
         umma_commit(&s_full[t]);
-        if (t == 1) umma_commit(&k_empty[s]);
         return true;
       };
       bool ok = mbar_wait(q_full, 0, abort_flag, p.status);
-      ok = ok && issue_s(0, 0) && issue_s(1, 0);
+      for (int t = 0; t < 2 && ok; ++t)
+        if (nt[t] > 0) ok = issue_s(t, 0);
+      if (ok) umma_commit(&k_empty[0]);
       for (int j = 0; ok && j < n; ++j) {
         const int s = j & 1;
 #pragma unroll 1
         for (int t = 0; t < 2 && ok; ++t) {
-          if (!mbar_wait(&p_full[t], j & 1, abort_flag, p.status)) { ok = false; break; }
-          if (t == 0 && !mbar_wait(&v_full[s], (j >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t v_addr = smem_u32(sV + s * TILE);
+          if (j < nt[t]) {
+            if (!mbar_wait(&p_full[t], j & 1, abort_flag, p.status)) { ok = false; break; }
+            if (v_ready < j) {
+              if (!mbar_wait(&v_full[s], (j >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
+              v_ready = j;
+            }
+            tc_fence_after();
+            const uint32_t v_addr = smem_u32(sV + s * TILE);
 #pragma unroll
-          for (int k = 0; k < BKV / 16; ++k) {
-            const uint32_t a_off = (k >> 2) * PANEL + (k & 3) * 32;
-            umma_f16<1>(tmem_base + 2 * BKV + t * HD, umma_desc_sw128(p_addr + a_off, 16, 1024),
-                        umma_desc_sw128(v_addr + k * 2048, PANEL, 1024), idesc_o, (j | k) != 0);
+            for (int k = 0; k < BKV / 16; ++k)   // A = P_T: 16 bf16 keys per step = 8 TMEM columns
+              umma_f16_ts(tmem_base + 2 * BKV + t * HD, tmem_base + t * BKV + k * 8,
+                          umma_desc_sw128(v_addr + k * 2048, PANEL, 1024), idesc_o, (j | k) != 0);
+            if (j == nt[t] - 1) umma_commit(&o_full[t]);
           }
-          umma_commit(p_free);
-          umma_commit(&o_full[t]);
           if (t == 1) umma_commit(&v_empty[s]);
-          if (j + 1 < n) ok = issue_s(t, j + 1);
+          if (j + 1 < nt[t]) ok = issue_s(t, j + 1);
+          if (t == 1 && j + 1 < n) umma_commit(&k_empty[(j + 1) & 1]);
         }
       }
     }
@@ -192,6 +203,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const int r = quarter * 32 + lane;        // row inside the tile
     const int i = q0 + t * BQ + r;            // global query row
     const bool row_valid = i < p.Sq;
+    const int n_t = nt[t];
     int lo = 0, hi = 0;
     if (row_valid) {
       lo = p.row_lo ? p.row_lo[(long long)b * p.Sq + i] : 0;
@@ -202,91 +214,100 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const uint32_t s_addr = lane_addr + t * BKV, o_addr = lane_addr + 2 * BKV + t * HD;
     float m_ref = -INFINITY, l_run = 0.f;
     bool ok = true;
-    for (int j = 0; j < n; ++j) {
+    for (int j = 0; j < n_t; ++j) {
       const int kv0 = (t0 + j) * BKV;
       if (!__all_sync(0xffffffffu, mbar_wait(&s_full[t], j & 1, abort_flag, p.status))) { ok = false; break; }
       tc_fence_after();
-      float sv[128];
-#pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
-        uint32_t tr[32];
-        tmem_ld_32x32(s_addr + cc * 32, tr);
+      const bool full = row_valid && lo <= kv0 && hi >= kv0 + BKV;
+      // ---- pass 1: row maximum
+      float mx;
+      {
+        uint32_t x0[32], x1[32], x2[32], x3[32];
+        tmem_ld_32x32(s_addr, x0);
+        tmem_ld_32x32(s_addr + 32, x1);
+        tmem_ld_32x32(s_addr + 64, x2);
+        tmem_ld_32x32(s_addr + 96, x3);
         tmem_ld_wait();
+        if (!full) {
 #pragma unroll
-        for (int c = 0; c < 32; ++c) sv[cc * 32 + c] = __uint_as_float(tr[c]);
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_free[t]);
-      if (!(row_valid && lo <= kv0 && hi >= kv0 + BKV)) {
-#pragma unroll
-        for (int c = 0; c < 128; ++c)
-          if (kv0 + c < lo || kv0 + c >= hi) sv[c] = -INFINITY;
-      }
-      // four independent chains: a single chain of 127 dependent max operations would expose its latency
-      float mx4[4] = {sv[0], sv[1], sv[2], sv[3]};
-#pragma unroll
-      for (int c = 4; c < 128; c += 4) {
-        mx4[0] = fmaxf(mx4[0], sv[c]); mx4[1] = fmaxf(mx4[1], sv[c + 1]);
-        mx4[2] = fmaxf(mx4[2], sv[c + 2]); mx4[3] = fmaxf(mx4[3], sv[c + 3]);
-      }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      // raise the reference maximum only when it pays: a stale one costs nothing while 2^(gap) fits bf16/fp32
-      float alpha = 1.f;
-      const bool raise = (mx > m_ref) && (m_ref == -INFINITY || (mx - m_ref) * p.scale_log2 > RESCALE_THRESHOLD);
-      if (raise) {
-        alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - mx) * p.scale_log2);
-        m_ref = mx;
-        l_run *= alpha;
-      }
-      // the P buffer (shared by both tiles) and this tile's O columns are quiescent once the previous
-      // P.V product, whichever tile it belonged to, has completed
-      const int g = 2 * j + t;
-      if (g > 0 && !__all_sync(0xffffffffu, mbar_wait(p_free, (g - 1) & 1, abort_flag, p.status))) { ok = false; break; }
-      if (j > 0 && __any_sync(0xffffffffu, raise)) {
-        tc_fence_after();
-#pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {
-          uint32_t tr[32];
-          tmem_ld_32x32(o_addr + cc * 32, tr);
-          tmem_ld_wait();
-#pragma unroll
-          for (int c = 0; c < 32; ++c) tr[c] = __float_as_uint(__uint_as_float(tr[c]) * alpha);
-          tmem_st_32x32(o_addr + cc * 32, tr);
+          for (int c = 0; c < 32; ++c) {
+            if (kv0 + c < lo || kv0 + c >= hi) x0[c] = 0xff800000u;
+            if (kv0 + 32 + c < lo || kv0 + 32 + c >= hi) x1[c] = 0xff800000u;
+            if (kv0 + 64 + c < lo || kv0 + 64 + c >= hi) x2[c] = 0xff800000u;
+            if (kv0 + 96 + c < lo || kv0 + 96 + c >= hi) x3[c] = 0xff800000u;
+          }
         }
-        tmem_st_wait();
+        float m4[4] = {__uint_as_float(x0[0]), __uint_as_float(x1[0]), __uint_as_float(x2[0]), __uint_as_float(x3[0])};
+#pragma unroll
+        for (int c = 1; c < 32; ++c) {
+          m4[0] = fmaxf(m4[0], __uint_as_float(x0[c])); m4[1] = fmaxf(m4[1], __uint_as_float(x1[c]));
+          m4[2] = fmaxf(m4[2], __uint_as_float(x2[c])); m4[3] = fmaxf(m4[3], __uint_as_float(x3[c]));
+        }
+        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       }
+      // raise the reference maximum only when it pays: a stale one costs nothing while 2^(gap) fits bf16/fp32
+      const bool raise = (mx > m_ref) && (m_ref == -INFINITY || (mx - m_ref) * p.scale_log2 > RESCALE_THRESHOLD);
+      if (__any_sync(0xffffffffu, raise)) {
+        float alpha = 1.f;
+        if (raise) {
+          alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2((m_ref - mx) * p.scale_log2);
+          m_ref = mx;
+          l_run *= alpha;
+        }
+        if (j > 0) {   // O_T holds the products up to tile j-1 (complete: S_T(j) was issued after them)
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {
+            uint32_t tr[32];
+            tmem_ld_32x32(o_addr + cc * 32, tr);
+            tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 32; ++c) tr[c] = __float_as_uint(__uint_as_float(tr[c]) * alpha);
+            tmem_st_32x32(o_addr + cc * 32, tr);
+          }
+        }
+      }
+      // ---- pass 2: P = 2^(S c - m c) as packed bf16 over the first 64 columns of S (each chunk of 32 scores
+      // is read before the 16 columns it turns into are written, and those lie below the next chunk)
       const float neg_ms = (m_ref == -INFINITY) ? 0.f : -m_ref * p.scale_log2;
       float ls4[4] = {0.f, 0.f, 0.f, 0.f};
-      uint8_t* prow = sP + r * 128;
+      uint32_t xa[32], xb[32];
+      tmem_ld_32x32(s_addr, xa);
 #pragma unroll
-      for (int c8 = 0; c8 < 16; ++c8) {       // 16 chunks of 8 columns; chunks 0..7 -> panel 0, 8..15 -> panel 1
-        uint32_t pk[4];
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t (&x)[32] = (cc & 1) ? xb : xa;
+        uint32_t (&xn)[32] = (cc & 1) ? xa : xb;
+        tmem_ld_wait();
+        if (cc + 1 < 4) tmem_ld_32x32(s_addr + (cc + 1) * 32, xn);
+        uint32_t pk[16];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const float p0 = fast_exp2(fmaf(sv[c8 * 8 + 2 * q], p.scale_log2, neg_ms));
-          const float p1 = fast_exp2(fmaf(sv[c8 * 8 + 2 * q + 1], p.scale_log2, neg_ms));
-          ls4[q] += p0 + p1;
-          pk[q] = pack_bf16x2(p0, p1);
+        for (int c = 0; c < 32; c += 2) {
+          float p0 = fast_exp2(fmaf(__uint_as_float(x[c]), p.scale_log2, neg_ms));
+          float p1 = fast_exp2(fmaf(__uint_as_float(x[c + 1]), p.scale_log2, neg_ms));
+          if (!full) {
+            const int kk = kv0 + cc * 32 + c;
+            if (kk < lo || kk >= hi) p0 = 0.f;
+            if (kk + 1 < lo || kk + 1 >= hi) p1 = 0.f;
+          }
+          ls4[(c >> 1) & 3] += p0 + p1;
+          pk[c >> 1] = pack_bf16x2(p0, p1);
         }
-        *reinterpret_cast<uint4*>(prow + (c8 >> 3) * PANEL + (((c8 & 7) ^ (r & 7)) << 4)) =
-            make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        tmem_st_32x16(s_addr + cc * 16, pk);
       }
       l_run += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
-      fence_proxy_async_smem();
+      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[t]);
     }
-    if (ok && n > 0) ok = __all_sync(0xffffffffu, mbar_wait(&o_full[t], (n - 1) & 1, abort_flag, p.status));
+    if (ok && n_t > 0) ok = __all_sync(0xffffffffu, mbar_wait(&o_full[t], 0, abort_flag, p.status));
     if (ok) {
-      if (n > 0) tc_fence_after();
+      if (n_t > 0) tc_fence_after();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       __nv_bfloat16* orow = p.O + (((long long)b * p.Sq + i) * p.Hq + h) * HD;
 #pragma unroll
       for (int cc = 0; cc < 4; ++cc) {
         uint32_t tr[32];
-        if (n > 0) {
+        if (n_t > 0) {
           tmem_ld_32x32(o_addr + cc * 32, tr);
           tmem_ld_wait();
         } else {

@@ -46,7 +46,9 @@ class AtorchTrainingArgs:
     max_steps: int = -1
     num_train_epochs: float = 1.0
     recompute_granularity: Optional[str] = "full"     # None | selective | full
-    # logging / eval / save
+    # logging / eval / test / save (strategies: "no" | "steps" | "epoch", save also "samples")
+    logging_strategy: str = "steps"
+    logging_first_step: bool = False
     logging_steps: int = 10
     log_params_std: bool = False
     log_grad_diff_for_debug: bool = False
@@ -54,8 +56,16 @@ class AtorchTrainingArgs:
     evaluation_strategy: str = "no"
     eval_steps: Optional[int] = None
     eval_iters: int = 10
+    eval_delay: float = 0
+    test_strategy: str = "no"
+    test_steps: Optional[int] = None
+    test_delay: float = 0
+    test_on_save: bool = False
     save_strategy: str = "steps"
     save_steps: int = 500
+    save_samples: int = 0                              # save_strategy="samples": every this many consumed samples
+    extra_save_frequency_in_epoch: Optional[List[int]] = None   # extra saves at these steps inside every epoch
+    dynamic_save_config_path: Optional[str] = None     # JSON {"save_at_dynamic_steps": [..]}, re-read when it changes
     save_total_limit: Optional[int] = None
     async_save: bool = True
     resume_from_checkpoint: Optional[str] = None
@@ -68,15 +78,43 @@ class AtorchTrainingArgs:
     profiler_schedule_wait: int = 1
     profiler_schedule_warmup: int = 1
     profiler_schedule_active: int = 1
+    profiler_schedule_repeat: int = 1
+    profiler_schedule_skip_first: int = 0
     profiler_file_path: Optional[str] = None
+    profiler_config: Dict[str, Any] = field(default_factory=dict)   # overrides of torch.profiler.profile keywords
+    profile_ranks: List[int] = field(default_factory=lambda: [-1])  # [-1] = every rank
+    profile_use_gzip: bool = False
+    profile_step_start: int = 0                        # nsys: first / last profiled global step
+    profile_step_end: int = 0
+    dynamic_profiler_config_path: Optional[str] = None
     memory_snapshot_path: Optional[str] = None
     use_local_sgd: bool = False
     local_sgd_sync_interval: int = 1
     local_sgd_warmup_steps: int = 0
     extra_configs: Dict[str, Any] = field(default_factory=dict)
 
+    eval_type: Optional[str] = None                    # set by the trainer around an evaluation ("eval" | "test")
+
     def to_dict(self) -> dict:
         return asdict(self)
+
+    @property
+    def process_index(self) -> int:
+        import os
+
+        return int(os.environ.get("RANK", "0"))
+
+    @property
+    def is_main_process(self) -> bool:
+        return self.process_index == 0
+
+    @property
+    def global_train_batch_size(self) -> int:
+        import os
+
+        if self.global_batch_size:
+            return self.global_batch_size
+        return self.micro_batch_size * self.data_parallel_size(int(os.environ.get("WORLD_SIZE", "1")))
 
     def to_json_string(self) -> str:
         return json.dumps(self.to_dict(), indent=2, default=str)

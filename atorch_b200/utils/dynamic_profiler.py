@@ -116,3 +116,23 @@ class DynamicProfiler:
 
     def close(self) -> None:
         self.monitor.stop()
+
+
+_GLOBAL: Optional[DynamicProfiler] = None
+
+
+def init(config_path: str, rank: Optional[int] = None, poll_interval: float = 1.0) -> DynamicProfiler:
+    """Process-wide dynamic profiler (the form the trainer's profiler callback uses); ``step()`` below
+    advances it. (Reference: atorch/utils/dynamic_profiler/__init__.py ``init`` / ``step``.)"""
+    global _GLOBAL
+    if _GLOBAL is not None:
+        _GLOBAL.close()
+    if rank is None:
+        rank = int(os.environ.get("RANK", "0"))
+    _GLOBAL = DynamicProfiler(config_path, rank=rank, poll_interval=poll_interval)
+    return _GLOBAL
+
+
+def step() -> None:
+    if _GLOBAL is not None:
+        _GLOBAL.step()

@@ -69,6 +69,19 @@ def analyze(events: List[dict]) -> Dict:
         (comm if is_comm(name) else comp).append((ts, ts + dur))
     comp_m, comm_m = _merge(comp), _merge(comm)
     hidden = _intersect(comp_m, comm_m)
+    # mean duration of each compute kernel with and without a communication kernel or peer copy in flight
+    contention = defaultdict(lambda: [0, 0.0, 0, 0.0])
+    starts = [s for s, _ in comm_m]
+    import bisect
+    for e in kernels:
+        name, ts, dur = e.get("name", ""), float(e["ts"]), float(e.get("dur", 0.0))
+        if is_comm(name):
+            continue
+        k = bisect.bisect_right(starts, ts + dur) - 1
+        busy = k >= 0 and comm_m[k][1] > ts
+        c = contention[name]
+        c[2 if busy else 0] += 1
+        c[3 if busy else 1] += dur
     steps = [e for e in events if e.get("ph") == "X" and str(e.get("name", "")).startswith("ProfilerStep#")]
     span = (max(e for _, e in comp_m + comm_m) - min(s for s, _ in comp_m + comm_m)) if (comp_m or comm_m) else 0.0
     return {
@@ -77,6 +90,7 @@ def analyze(events: List[dict]) -> Dict:
         "comm_hidden_us": hidden, "comm_exposed_us": _length(comm_m) - hidden,
         "overlap_ratio": hidden / _length(comm_m) if comm_m else 1.0,
         "idle_us": max(span - _length(_merge(comp + comm)), 0.0),
+        "contention": {n: c for n, c in contention.items()},
         "top_kernels": sorted(((n, c, d) for n, (c, d) in per_kernel.items()), key=lambda t: -t[2])[:25],
     }
 
@@ -95,7 +109,11 @@ def print_profiler_summary(res: Dict, all_summary_path=None) -> None:
              f"(hidden {res['comm_hidden_us'] / n / 1e3:.2f}, exposed {res['comm_exposed_us'] / n / 1e3:.2f}), "
              f"idle {res['idle_us'] / n / 1e3:.2f} ms, overlap {100 * res['overlap_ratio']:.1f} %"]
     for name, cnt, dur in res["top_kernels"]:
-        lines.append(f"{dur / n / 1e3:9.3f} ms/step x{cnt // n:5d}  {name[:110]}")
+        line = f"{dur / n / 1e3:9.3f} ms/step x{cnt // n:5d}  {name[:110]}"
+        c = res.get("contention", {}).get(name)
+        if c and c[0] and c[2]:
+            line += f"  [alone {c[1] / c[0]:.1f} us x{c[0]}, with communication in flight {c[3] / c[2]:.1f} us x{c[2]}]"
+        lines.append(line)
     text = "\n".join(lines)
     print(text)
     if all_summary_path:
@@ -107,8 +125,13 @@ def main(argv=None) -> None:
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("trace")
     ap.add_argument("--out", default=None)
+    ap.add_argument("--steps", type=int, default=0, help="number of training steps in the trace when it carries "
+                                                         "no ProfilerStep annotations")
     a = ap.parse_args(argv)
-    print_profiler_summary(parse_trace_file(a.trace), a.out)
+    res = parse_trace_file(a.trace)
+    if a.steps > 0:
+        res["n_steps"] = a.steps
+    print_profiler_summary(res, a.out)
 
 
 if __name__ == "__main__":

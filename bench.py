@@ -55,6 +55,10 @@ def parse_args():
                     help="instead of timing: train K steps on a fixed token stream from name-seeded weights and "
                          "write the per-step losses to --loss-out (same stream and weights on both arms)")
     ap.add_argument("--loss-out", default=None)
+    ap.add_argument("--profile-steps", type=int, default=0, metavar="P",
+                    help="after the timed regions and the JSON line: run P more steps under torch.profiler on rank 0 "
+                         "and write the chrome trace to --profile-out (never part of a reported number)")
+    ap.add_argument("--profile-out", default="bench_trace.json")
     ap.add_argument("--compare-loss", nargs=2, metavar=("A.json", "B.json"), default=None,
                     help="print max / mean |difference| of two loss-curve files and exit (status 1 when the curves "
                          "differ by more than the bf16 tolerance: mean 0.05, last-quarter mean 0.03, max 0.5)")
@@ -345,6 +349,21 @@ def run_ours(args):
             "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
         }
         print(json.dumps(out), flush=True)
+    if args.profile_steps > 0:
+        barrier()
+        if rank == 0:
+            from torch.profiler import ProfilerActivity, profile
+
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                for i in range(args.profile_steps):
+                    step_device()
+                    torch.cuda.synchronize()
+            prof.export_chrome_trace(args.profile_out)
+        else:
+            for i in range(args.profile_steps):
+                step_device()
+                torch.cuda.synchronize()
+        barrier()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

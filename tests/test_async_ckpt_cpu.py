@@ -26,7 +26,7 @@ def test_async_save_tracker_and_load(tmp_path):
     saver.save(7, str(tmp_path), module=f, optimizer=opt, extra_state=ExtraState(iteration=7, consumed_samples=28))
     saver.finish()
     assert A.latest_checkpoint_step(str(tmp_path)) == 7
-    assert os.path.exists(tmp_path / "iter_0000007" / "flat_param.00000-00001")
+    assert os.path.exists(tmp_path / "iter_0000007" / ".metadata")   # torch.distributed.checkpoint format
     ref = {k: v.clone() for k, v in f.state_dict().items()}
     f2, opt2 = _sharded()
     with torch.no_grad():

@@ -78,3 +78,68 @@ def test_convert_flat_param(tmp_path):
     util = ShardTensorUtil(path, name_mapping_func_or_dict={"renamed": "0.weight"})
     assert torch.equal(util.load_tensor_by_name("renamed"), ref["0.weight"])
     assert torch.equal(util.load_param_slice("0.weight", 100, 300), ref["0.weight"].reshape(-1)[100:300])
+
+
+def _dcp_save(rank, world, path, fused):
+    from atorch_b200.parallel.fsdp import FSDP, FusedShardedOptimizer, ShardedOptimizer
+    from atorch_b200.utils import dcp_io
+
+    f = FSDP(make_mlp(), wrap_cls=(nn.Linear,))
+    opt = FusedShardedOptimizer(f.engine, "adamw", lr=1e-3) if fused else \
+        ShardedOptimizer(torch.optim.AdamW(f.parameters(), lr=1e-3), f.engine)
+    g = torch.Generator().manual_seed(7)
+    for _ in range(2):
+        opt.zero_grad()
+        f(torch.randn(4, 256, generator=g)).sum().backward()
+        opt.step()
+    dcp_io.save(f, opt, path, async_save=True)
+    dcp_io.wait()
+    sd = f.state_dict()
+    if rank == 0:
+        torch.save(sd, path + "/full_ref.pt")
+
+
+def _dcp_load(rank, world, path, fused):
+    from atorch_b200.parallel.fsdp import FSDP, FusedShardedOptimizer, ShardedOptimizer
+    from atorch_b200.utils import dcp_io
+
+    torch.manual_seed(123)
+    m = make_mlp()
+    with torch.no_grad():
+        for p in m.parameters():
+            p.add_(1.0)
+    f = FSDP(m, wrap_cls=(nn.Linear,))
+    opt = FusedShardedOptimizer(f.engine, "adamw", lr=1e-3) if fused else \
+        ShardedOptimizer(torch.optim.AdamW(f.parameters(), lr=1e-3), f.engine)
+    if not fused:      # a plain optimizer creates its state lazily: one throw-away step gives it its shape
+        opt.zero_grad()
+        f(torch.zeros(4, 256)).sum().backward()
+        opt.step()
+    dcp_io.load(f, opt, path)
+    sd = f.state_dict()
+    ref = torch.load(path + "/full_ref.pt")
+    for k, v in ref.items():
+        assert torch.equal(sd[k], v), k
+    g = torch.Generator().manual_seed(99)
+    opt.zero_grad()
+    f(torch.randn(4, 256, generator=g)).sum().backward()
+    opt.step()
+    sd2 = f.state_dict()
+    if rank == 0:
+        torch.save(sd2, path + f"/after_{world}.pt")
+
+
+def test_dcp_format_checkpoint_reshards_across_world_sizes(tmp_path):
+    import os
+
+    for fused in (True, False):
+        path = str(tmp_path / f"dcp_{int(fused)}")
+        os.makedirs(path)
+        run_distributed(_dcp_save, world=2, args=(path, fused))
+        files = sorted(os.listdir(path))
+        assert ".metadata" in files and "__0_0.distcp" in files and "__1_0.distcp" in files, files
+        for w in (2, 1, 3):
+            run_distributed(_dcp_load, world=w, args=(path, fused))
+        a2, a1, a3 = (torch.load(path + f"/after_{w}.pt") for w in (2, 1, 3))
+        for k in a2:
+            assert torch.allclose(a2[k], a1[k], atol=1e-6) and torch.allclose(a2[k], a3[k], atol=1e-6), k

@@ -1,11 +1,13 @@
-"""Sharded engine over NCCL on 2 GPUs: tiny Llama, bf16 compute, per-unit recompute; the loss curve
-must track a single-GPU run over the union batch."""
+"""Sharded engine on 2, 4 or 8 GPUs (all that the machine has): tiny Llama, bf16 compute, per-unit recompute;
+the loss curve must track a single-GPU run over the union batch."""
 import pytest
 import torch
 
 from tests.dist_utils import run_distributed
 
 pytestmark = pytest.mark.gpu
+NGPU = torch.cuda.device_count()
+WORLD = 8 if NGPU >= 8 else 4 if NGPU >= 4 else 2
 
 
 def _cfg():
@@ -60,7 +62,7 @@ def test_fsdp_two_gpus_tracks_single_gpu(tmp_path):
     for name, extra in (("fused", {"fused_comm": True}), ("nccl", {"fused_comm": False}),
                         ("in_backward", {"fused_comm": True, "optimizer_in_backward": True})):
         f = str(tmp_path / f"l_{name}.pt")
-        run_distributed(_train_rank, world=2, args=(f, extra), backend="nccl", timeout=300)
+        run_distributed(_train_rank, world=WORLD, args=(f, extra), backend="nccl", timeout=300)
         runs[name] = torch.load(f)
     multi = runs["fused"]
     for name in ("nccl", "in_backward"):
@@ -68,8 +70,8 @@ def test_fsdp_two_gpus_tracks_single_gpu(tmp_path):
     torch.cuda.set_device(0)
     res = _build([])
     single = []
-    for a, b in zip(_batches(0), _batches(1)):
-        ids = torch.cat([a, b]).cuda()
+    for parts in zip(*[_batches(r) for r in range(WORLD)]):
+        ids = torch.cat(parts).cuda()
         res.optim.zero_grad()
         loss = res.model(input_ids=ids, labels=ids, return_logits=False)[0]
         loss.backward()
@@ -82,7 +84,7 @@ def test_fsdp_two_gpus_tracks_single_gpu(tmp_path):
 def test_fsdp_frozen_and_odd_sizes_two_gpus():
     from tests.test_fsdp_cpu import _frozen_odd
 
-    run_distributed(_frozen_odd, world=2, args=("cuda",), backend="nccl", timeout=300)
+    run_distributed(_frozen_odd, world=WORLD, args=("cuda",), backend="nccl", timeout=300)
 
 
 def _single_in_backward(out_file, flag):

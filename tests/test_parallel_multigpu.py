@@ -10,6 +10,7 @@ from tests.dist_utils import run_distributed
 
 pytestmark = pytest.mark.gpu
 NGPU = torch.cuda.device_count()
+WORLD = 8 if NGPU >= 8 else 4 if NGPU >= 4 else 2   # expert- and data-parallel tests use every GPU of the machine
 
 
 # --------------------------------------------------------------------------------------- tensor parallel
@@ -111,7 +112,7 @@ def _ep(rank, world, dispatcher):
     dev = torch.device("cuda", rank)
     D.create_parallel_group(([("expert", world)], None))
     torch.manual_seed(3)
-    H, F, NE = 256, 512, 4
+    H, F, NE = 256, 512, max(4, world)
     full = Grouped_GEMM_MoE(H, F, 0.0, num_experts=NE, topk=2, use_swiglu=True)
     moe = Grouped_GEMM_MoE(H, F, 0.0, num_experts=NE, topk=2, use_swiglu=True, use_expert_parallelism=True,
                            token_dispatcher_type=dispatcher).to(dev).bfloat16()
@@ -154,7 +155,7 @@ def _ep(rank, world, dispatcher):
 @pytest.mark.skipif(NGPU < 2, reason="needs 2 GPUs")
 @pytest.mark.parametrize("dispatcher", ["PeerMemory", "AllToAll", "AllGather"])
 def test_expert_parallel_matches_dense(dispatcher):
-    run_distributed(_ep, world=2, args=(dispatcher,), backend="nccl", timeout=300)
+    run_distributed(_ep, world=WORLD, args=(dispatcher,), backend="nccl", timeout=300)
 
 
 # ------------------------------------------------------------------------------------------ data parallel
@@ -182,14 +183,13 @@ def test_ddp_own_allreduce_matches_single_process(tmp_path):
     from tests.test_fsdp_cpu import make_data, make_mlp
 
     f = str(tmp_path / "ddp.pt")
-    run_distributed(_ddp, world=2, args=(f,), backend="nccl", timeout=300)
+    run_distributed(_ddp, world=WORLD, args=(f,), backend="nccl", timeout=300)
     sd = torch.load(f)
     m = make_mlp()
     opt = torch.optim.AdamW(m.parameters(), lr=1e-3)
-    d0, d1 = make_data(0, steps=8), make_data(1, steps=8)
-    for (x0, y0), (x1, y1) in zip(d0, d1):
+    for parts in zip(*[make_data(r, steps=8) for r in range(WORLD)]):
         opt.zero_grad()
-        ((nn.functional.cross_entropy(m(x0), y0) + nn.functional.cross_entropy(m(x1), y1)) / 2).backward()
+        (sum(nn.functional.cross_entropy(m(x), y) for x, y in parts) / WORLD).backward()
         opt.step()
     for k, v in m.state_dict().items():
         assert torch.allclose(sd[k], v, atol=2e-4, rtol=2e-3), k

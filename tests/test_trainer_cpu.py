@@ -97,10 +97,58 @@ def test_trainer_v2_engine_loop_and_resume(tmp_path):
     losses = [l["loss"] for l in st.log_history if "loss" in l]
     assert losses[-1] < losses[0]
     assert tr.evaluate()["eval_loss"] < 2.0
-    assert os.path.exists(tmp_path / "iter_0000012" / "ckpt_meta")
+    assert os.path.exists(tmp_path / "iter_0000012" / ".metadata")
     tr2 = AtorchTrainerV2(a, Net(), train_dataset=dataset(), wrap_cls=(nn.Linear,))
     tr2.train(resume_from_checkpoint=str(tmp_path))
     assert tr2.state.global_step == 12
     for (k, v), (_, v2) in zip(tr.train_engine.module.state_dict().items(),
                                tr2.train_engine.module.state_dict().items()):
         assert torch.equal(v, v2), k
+
+
+def test_trainer_v2_flow_callback_samples_dynamic_steps_test_and_profiler(tmp_path):
+    import json
+
+    from atorch_b200.trainer import AtorchTrainerV2, AtorchTrainingArgs
+    from atorch_b200.trainer.trainer_callback import AtorchTrainerCallback, AtorchTrainerState
+
+    dyn = tmp_path / "dyn.json"
+    dyn.write_text(json.dumps({"save_at_dynamic_steps": [5]}))
+    prof_dir = tmp_path / "prof"
+    a = AtorchTrainingArgs(output_dir=str(tmp_path / "out"), bf16=False, micro_batch_size=4, global_batch_size=8,
+                           learning_rate=1e-2, max_steps=8, logging_steps=2, logging_first_step=True,
+                           save_strategy="samples", save_samples=24, seq_length=1, recompute_granularity=None,
+                           async_save=False, dynamic_save_config_path=str(dyn), test_strategy="steps", test_steps=4,
+                           profiler_type="nv", profiler_file_path=str(prof_dir), profiler_schedule_wait=1,
+                           profiler_schedule_warmup=1, profiler_schedule_active=1)
+
+    class Spy(AtorchTrainerCallback):
+        def __init__(self):
+            self.saves, self.evals, self.begun = [], [], 0
+
+        def on_save(self, args, state, control, **kw):
+            self.saves.append(state.global_step)
+
+        def on_save_begin(self, args, state, control, **kw):
+            self.begun += 1
+
+        def on_evaluate(self, args, state, control, metrics=None, **kw):
+            self.evals.append((state.global_step, sorted(metrics)))
+
+    spy = Spy()
+    tr = AtorchTrainerV2(a, Net(), train_dataset=dataset(), eval_dataset=dataset(32), wrap_cls=(nn.Linear,),
+                         callbacks=[spy])
+    st = tr.train()
+    # 8 samples per step: multiples of 24 consumed samples fall on steps 3 and 6; step 5 comes from the file
+    assert spy.saves == [3, 5, 6] and spy.begun == 3
+    assert spy.evals == [(4, ["test_loss"]), (8, ["test_loss"])]
+    assert [l["step"] for l in st.log_history if "step" in l] == [1, 2, 4, 6, 8]
+    assert st.consumed_train_tokens == 64 and st.current_step_in_epoch >= 1
+    assert any(f.endswith(".pt.trace.json") for f in os.listdir(prof_dir))
+    loaded = AtorchTrainerState.load_from_json(str(tmp_path / "out" / "trainer_state.json"))
+    assert loaded.global_step == 6
+    js = json.load(open(tmp_path / "out" / "trainer_state.json"))
+    js["future_field"] = 1
+    json.dump(js, open(tmp_path / "out" / "trainer_state.json", "w"))
+    filled = AtorchTrainerState.load_from_json(str(tmp_path / "out" / "trainer_state.json"), AtorchTrainerState())
+    assert filled.global_step == 6 and not hasattr(filled, "future_field")
