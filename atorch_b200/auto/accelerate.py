@@ -25,6 +25,7 @@ from __future__ import annotations
 
 import collections
 import logging
+import os
 import pickle
 from typing import Optional
 
@@ -170,10 +171,19 @@ def auto_accelerate(model, optim_func=None, dataset=None, loss_func=None, prepar
                       lr_scheduler_args=lr_scheduler_args, extra_args=extra)
     opt_lib = OptimizationLibrary()
     if load_strategy is None:
-        from .engine.search import search_strategy
+        from .engine import search as engine_search
 
-        ok, strategy = search_strategy(mc, opt_lib, excluded=excluded, included=included,
-                                       time_limit=extra.get("time_limit"), verbose=extra.get("verbose", False))
+        # the engine as a service on rank 0 (every rank is a client), or in-process when gRPC is not
+        # importable or ATORCH_ENGINE_IN_PROCESS=1
+        use_service = os.environ.get("ATORCH_ENGINE_IN_PROCESS", "0") != "1"
+        if use_service:
+            try:
+                import grpc  # noqa: F401
+            except ImportError:
+                use_service = False
+        fn = engine_search.search_strategy_with_service if use_service else engine_search.search_strategy
+        ok, strategy = fn(mc, opt_lib, excluded=excluded, included=included, time_limit=extra.get("time_limit"),
+                          verbose=extra.get("verbose", False))
         if not ok:
             return False, None, None
     else:

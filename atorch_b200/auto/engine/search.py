@@ -11,8 +11,9 @@ strategy.py:49-171, sg_algo/combination_sg.py:16-60, sg_algo/bayes_opt_sg.py:35-
      space is enlarged with ``included`` methods
   4. dry-run each candidate (rank 0 decides, the decision is broadcast so all ranks build the same
      strategies in the same order) and return the one with the best throughput.
-The engine runs in-process; :mod:`atorch_b200.auto.engine.service` exposes the same task loop over
-gRPC for jobs that want a separate planner process.
+``search_strategy`` runs the loop in-process; ``search_strategy_with_service`` runs it as the reference
+does: rank 0 hosts the engine (:mod:`atorch_b200.auto.engine.service`, task queue in
+:mod:`atorch_b200.auto.engine.executor`) and every rank asks it for tasks over gRPC.
 """
 from __future__ import annotations
 
@@ -191,3 +192,54 @@ def search_strategy(mc, opt_lib, excluded=None, included=None, time_limit: Optio
         return False, None
     best = max(ok, key=lambda i: i.throughput)
     return True, best.strategy
+
+
+def search_strategy_with_service(mc, opt_lib, excluded=None, included=None, time_limit: Optional[float] = None,
+                                 verbose: bool = False, algo: str = "combination") -> Tuple[bool, Optional[Strategy]]:
+    """Rank 0 starts the acceleration engine; all ranks (rank 0 too) loop get_task -> run -> report until the
+    engine hands out FINISH (best strategy) or FAIL."""
+    from ..accelerate import tune_strategy
+    from ..opt_lib.parallel_mode import ParallelModeOptimization
+    from .service import AccelerationEngine, AutoAccelerationClient, run_worker_loop
+    from .task import TaskType
+
+    world, rank = D.world_size() or 1, D.rank() or 0
+    engine, port = None, [0]
+    if rank == 0:
+        ctx = {"node_num": 1, "nproc_per_node": world}
+        engine = AccelerationEngine(ctx, included_opts=included, excluded_opts=excluded, time_limit=time_limit,
+                                    verbose=verbose, algo=algo)
+        port[0] = engine.start_service(0)
+    if D.is_distributed():
+        dist.broadcast_object_list(port, src=0)
+    import os
+
+    client = AutoAccelerationClient(f"{os.environ.get('MASTER_ADDR', '127.0.0.1') if rank else '127.0.0.1'}:{port[0]}",
+                                    rank)
+    cap = torch.cuda.get_device_capability() if torch.cuda.is_available() else None
+
+    def run_task(task):
+        if task.task_type == TaskType.ANALYSE:
+            return True, analyse_model(mc.model)
+        if task.task_type == TaskType.SETUP_PARALLEL_GROUP:
+            if D.is_distributed():
+                ParallelModeOptimization.setup_groups(task.task_info)
+            return True, None
+        st: Strategy = task.task_info
+        if not D.is_distributed():
+            st.remove_distributed_method(opt_lib)
+        st.remove_device_unsupported_method(opt_lib, cap)
+        if task.task_type == TaskType.TUNE:
+            return bool(tune_strategy(mc, st, opt_lib, time_limit)), st
+        res = dry_run_strategy(mc, st, opt_lib) or {}
+        res["throughput"] = _agree(res.get("throughput", 0.0))
+        if verbose:
+            logger.info("candidate %s -> %.2f samples/s", st.names(), res["throughput"])
+        return res["throughput"] > 0, res
+    try:
+        best = run_worker_loop(client, run_task)
+    finally:
+        client.close()
+        if engine is not None:
+            engine.tear_down(timeout=30.0)
+    return best is not None, best

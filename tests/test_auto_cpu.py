@@ -107,3 +107,74 @@ def test_clip_grad_norm_plain():
     n = clip_grad_norm(m, 0.1)
     after = torch.sqrt(sum(p.grad.pow(2).sum() for p in m.parameters()))
     assert n > 0.1 and abs(after.item() - 0.1) < 1e-3
+
+
+def test_engine_executor_state_machine_two_processes():
+    """ANALYSE by one process, then per candidate SETUP_PARALLEL_GROUP / DRYRUN by all, WAIT in between,
+    FINISH with the fastest candidate; a repeated parallel mode is not set up twice."""
+    from atorch_b200.auto.engine.executor import Executor
+    from atorch_b200.auto.engine.task import TaskProcessMode, TaskType
+
+    ex = Executor({"node_num": 1, "nproc_per_node": 2})
+    t0 = ex.get_task(0)
+    assert t0.task_type == TaskType.ANALYSE and t0.process_mode == TaskProcessMode.ONE_PROCESS
+    assert ex.get_task(1).task_type == TaskType.WAIT
+    ex.report_task_result(t0.task_id, 0, True, {"opt_config_submodule_names": (), "replaceable_pairs": []})
+    seen, setups, speed = [], 0, 0.0
+    for _ in range(200):
+        a, b = ex.get_task(0), ex.get_task(1)
+        if a.task_type == TaskType.WAIT and b.task_type == TaskType.WAIT:
+            continue
+        # an ALL_PROCESS task reaches both processes before either reports
+        assert a.task_id == b.task_id and a.process_mode == TaskProcessMode.ALL_PROCESS, (a, b)
+        if a.task_type in (TaskType.FINISH, TaskType.FAIL):
+            final = a
+            break
+        if a.task_type == TaskType.SETUP_PARALLEL_GROUP:
+            setups += 1
+            res = None
+        else:
+            assert a.task_type == TaskType.DRYRUN
+            speed += 1.0
+            names = tuple(a.task_info.names())
+            seen.append(names)
+            res = {"throughput": 100.0 - abs(speed - 3.0)}       # the third candidate is the fastest
+        ex.report_task_result(a.task_id, 1, True, res)
+        assert ex.get_task(1).task_type == TaskType.WAIT            # process 0 has not reported yet
+        ex.report_task_result(a.task_id, 0, True, res)
+    assert final.task_type == TaskType.FINISH and tuple(final.task_info.names()) == seen[2]
+    assert setups == 1 and len(seen) >= 4 and len(set(seen)) == len(seen)
+    assert ex.can_be_terminated
+    # every candidate failing ends in FAIL
+    ex2 = Executor({"node_num": 1, "nproc_per_node": 1}, time_limit=1000)
+    t = ex2.get_task(0)
+    ex2.report_task_result(t.task_id, 0, True, {})
+    while True:
+        t = ex2.get_task(0)
+        if t.task_type in (TaskType.FINISH, TaskType.FAIL):
+            break
+        ex2.report_task_result(t.task_id, 0, t.task_type != TaskType.DRYRUN, {"throughput": 0.0})
+    assert t.task_type == TaskType.FAIL
+
+
+def test_engine_service_round_trip_over_grpc():
+    from atorch_b200.auto.engine.service import AccelerationEngine, AutoAccelerationClient, run_worker_loop
+    from atorch_b200.auto.engine.task import TaskType
+
+    eng = AccelerationEngine({"node_num": 1, "nproc_per_node": 1}, algo="bo")
+    port = eng.start_service(0)
+    client = AutoAccelerationClient(f"127.0.0.1:{port}", 0)
+    ran = []
+
+    def run_task(task):
+        ran.append(task.task_type)
+        if task.task_type == TaskType.ANALYSE:
+            return True, {"opt_config_submodule_names": ("Linear",), "replaceable_pairs": []}
+        if task.task_type == TaskType.DRYRUN:
+            return True, {"throughput": 10.0 + ("fsdp" in task.task_info.names()) + 2 * ("amp_native" in task.task_info.names())}
+        return True, None
+    best = run_worker_loop(client, run_task, poll_interval=0.001)
+    client.close()
+    eng.tear_down(timeout=5)
+    assert ran[0] == TaskType.ANALYSE and ran.count(TaskType.DRYRUN) >= 4
+    assert "fsdp" in best.names() and "amp_native" in best.names()
