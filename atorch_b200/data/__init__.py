@@ -3,3 +3,4 @@ from .elastic_dataset import ElasticDataset, ShardService, get_elastic_dataloade
 from .preloader import GpuPreLoader
 from .shm_context import ShmDataContext, ShmDataloader
 from .unordered_dataloader import UnorderedDataLoader, UnshuffledBatchDataLoader
+from .coworker_dataset import CoworkerDataset, build_coworker_dataloader

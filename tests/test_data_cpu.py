@@ -62,3 +62,53 @@ def test_shm_dataloader(tmp_path):
     p.join(30)
     master.close()
     assert mine == theirs and len(mine) == 4
+
+
+def _square(x):
+    return None if x == 5 else torch.tensor([x * x], dtype=torch.float32)
+
+
+def _plus_one(i):
+    return i + 1
+
+
+def test_coworker_dataset_over_grpc_and_data_info_service():
+    """Two coworker services on 127.0.0.1; percentage mode and rpc-worker mode give the same batches as local
+    processing; failed samples are padded; the data-info directory hands out coworkers in arrival order."""
+    import queue
+    import threading
+
+    from atorch_b200.data import build_coworker_dataloader
+    from atorch_b200.service.coworker_data_service import create_coworker_rpc_service
+    from atorch_b200.service.data_info_service import create_data_info_service
+    from atorch_b200.service.rpc_clients import (CoworkerRpcClient, create_data_info_rpc_client,
+                                                 create_gpu_pod_rpc_clients)
+
+    q = queue.Queue()
+    servers = [create_coworker_rpc_service(0, q), create_coworker_rpc_service(0, None)]
+    for s in servers:
+        s.start()
+    addrs = [f"127.0.0.1:{s.bound_port}" for s in servers]
+    try:
+        assert CoworkerRpcClient(addrs[0]).ping()
+        want = [[(i + 1) ** 2 for i in range(b, b + 4)] for b in range(0, 16, 4)]
+        for kw in ({"coworker_process_percentage": 0.5}, {"num_rpc_workers": 1, "num_workers": 1}, {}):
+            dl = build_coworker_dataloader(_square, 16, pre_process_fn=_plus_one, batch_size=4, shuffle=False,
+                                           num_rpc_fuse=1, need_padding_for_none=True, coworker_addrs=addrs, **kw)
+            got = [sorted(int(v) for v in b.view(-1)) for b in dl]
+            for g, w in zip(got, want):
+                w = [v for v in w if v != 25]          # sample 4 -> 5 fails and is replaced by a random other one
+                assert all(v in g for v in w) and len(g) == 4, (kw, g, w)
+        # pull model: a coworker queues finished batches and reports them; the trainer asks where to fetch
+        info = create_data_info_service(0)
+        info.start()
+        q.put({"x": torch.ones(2)})
+        create_gpu_pod_rpc_clients([f"127.0.0.1:{info.bound_port}"])[0].report_data_info(addrs[0], 1)
+        where = create_data_info_rpc_client(f"127.0.0.1:{info.bound_port}").get_data_info()
+        assert where == addrs[0]
+        assert torch.equal(CoworkerRpcClient(where).get_batch_data()["x"], torch.ones(2))
+        info.stop(None)
+    finally:
+        for s in servers:
+            s.stop(None)
+    del threading
