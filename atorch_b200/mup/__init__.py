@@ -68,6 +68,46 @@ class MupLinear(nn.Linear):
             nn.init.zeros_(self.bias)
 
 
+class QKVLayer(MupLinear):
+    """Fused query/key/value projection (``out_features = 3 * width``, rows ordered q, k, v). With
+    ``q_zero_init`` (default) the query third of the weight starts at zero, which makes the attention
+    logits zero at initialisation as muP asks. (Reference: atorch/mup/module.py:148-207.)"""
+
+    def __init__(self, *a, q_zero_init: bool = True, **k):
+        super().__init__(*a, **k)
+        self._q_zero_init = q_zero_init
+
+    def mup_initial(self, mode: str = "mup", init_std: float = 1.0):
+        super().mup_initial(mode, init_std)
+        if self._q_zero_init:
+            fan_out = self.weight.shape[0]
+            assert fan_out % 3 == 0, "a fused q/k/v weight has 3 equal row blocks"
+            with torch.no_grad():
+                self.weight[: fan_out // 3].zero_()
+
+
+class QLayer(QKVLayer):
+    """Separate query projection: the whole weight starts at zero when ``q_zero_init``.
+    (Reference: atorch/mup/module.py:208-219.)"""
+
+    def mup_initial(self, mode: str = "mup", init_std: float = 1.0):
+        MupLinear.mup_initial(self, mode, init_std)
+        if self._q_zero_init:
+            with torch.no_grad():
+                self.weight.zero_()
+
+
+class MupModule(nn.Module):
+    """Base class whose ``mup_initial(mode)`` initialises every muP layer below it ("mup" or "sp").
+    (Reference: atorch/mup/module.py:9-26.)"""
+
+    def mup_initial(self, mode: str = "mup", init_std: float = 1.0):
+        assert mode in ("mup", "sp")
+        for m in self.modules():
+            if m is not self and hasattr(m, "mup_initial") and not isinstance(m, MupModule):
+                m.mup_initial(mode, init_std)
+
+
 class OutputLayer(nn.Linear):
     """Readout layer: ``output_mult * x / width_mult`` before the matmul; zero-initialised under muP."""
 

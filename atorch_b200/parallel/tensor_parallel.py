@@ -34,9 +34,28 @@ def _is_linear(m) -> bool:
 
 
 def plan_tensor_parallel(model: nn.Module, config: Optional[dict] = None) -> dict:
-    """Returns ``{"column": {name: kwargs}, "row": [names], "vocab": [names]}``."""
+    """Returns ``{"column": {name: kwargs}, "row": [names], "vocab": [names]}``.
+
+    ``config["planner"] == "mip"`` with ``config["sample_inputs"]`` (a tuple of example tensors): the layout
+    comes from the mixed-integer programme over the traced graph (``auto/mip_tp_planner.py``); a model that
+    cannot be traced falls back to the name rules below."""
     config = config or {}
     tp = D.parallel_group_size("tensor") or config.get("tp_size", 1)
+    if config.get("planner") == "mip" and config.get("sample_inputs") is not None and tp > 1:
+        try:
+            from ..auto.mip_tp_planner import MIPTensorParallelPlanner
+
+            lay = MIPTensorParallelPlanner(tp, memory_budget_bytes=config.get("memory_budget_bytes")).plan(
+                model, tuple(config["sample_inputs"]))
+            mods = dict(model.named_modules())
+            return {"column": {n: {} for n, v in lay.items() if v == "col" and _is_linear(mods[n])},
+                    "row": [n for n, v in lay.items() if v == "row" and _is_linear(mods[n])],
+                    "vocab": [n for n, v in lay.items() if v != "replicate" and isinstance(mods[n], nn.Embedding)],
+                    "sequence_parallel": bool(config.get("sequence_parallel")), "planner": "mip"}
+        except Exception as e:  # noqa: BLE001 - tracing is best effort
+            import logging
+
+            logging.getLogger("atorch.logger").warning("MIP tensor-parallel planner unavailable (%s); using rules", e)
     min_features = config.get("min_features", 2 * max(tp, 1))
     col: Dict[str, dict] = {}
     row: List[str] = []

@@ -96,3 +96,44 @@ def test_adaml_l1_zeroes_small_weights():
     p.grad = torch.zeros(3)
     opt.step()
     assert p[0].item() == 0.0 and abs(p[1].item() + 0.498) < 1e-6
+
+
+def test_partition_adam_matches_adamw_and_keeps_state_in_host_blocks():
+    import torch.nn as nn
+
+    from atorch_b200.optimizers import PartitionAdam
+
+    torch.manual_seed(0)
+    a = nn.Sequential(nn.Linear(16, 32), nn.Tanh(), nn.Linear(32, 4))
+    b = nn.Sequential(nn.Linear(16, 32), nn.Tanh(), nn.Linear(32, 4))
+    b.load_state_dict(a.state_dict())
+    groups = lambda m: [{"params": list(m[0].parameters())}, {"params": list(m[2].parameters()), "lr": 3e-3}]  # noqa: E731
+    oa = PartitionAdam(groups(a), lr=1e-3, weight_decay=0.01)
+    ob = torch.optim.AdamW(groups(b), lr=1e-3, weight_decay=0.01)
+    for i in range(5):
+        x = torch.randn(8, 16, generator=torch.Generator().manual_seed(i))
+        for m, o in ((a, oa), (b, ob)):
+            o.zero_grad()
+            m(x).pow(2).mean().backward()
+            o.step()
+    for p, q in zip(a.parameters(), b.parameters()):
+        assert torch.allclose(p, q, atol=1e-6), (p - q).abs().max()
+    blk = oa.state["group0"]["state_block"]
+    assert blk.numel() == 2 * (16 * 32 + 32) and blk.abs().sum() > 0 and oa.param_groups[1]["step"] == 5
+
+
+def test_mup_qkv_and_q_layers_zero_the_query_rows():
+    import torch.nn as nn
+
+    from atorch_b200.mup import MupModule, QKVLayer, QLayer
+
+    class Attn(MupModule):
+        def __init__(self):
+            super().__init__()
+            self.qkv, self.q, self.plain = QKVLayer(8, 24), QLayer(8, 8), QKVLayer(8, 24, q_zero_init=False)
+
+    m = Attn()
+    m.mup_initial("mup")
+    assert m.qkv.weight[:8].abs().sum() == 0 and m.qkv.weight[8:].abs().sum() > 0
+    assert m.q.weight.abs().sum() == 0 and m.plain.weight[:8].abs().sum() > 0
+    del nn

@@ -105,3 +105,59 @@ def test_selective_offload_cpu_passthrough():
     assert n == 2
     m(x).sum().backward()
     assert torch.allclose(m[0].weight.grad, g)
+
+
+def test_fx_meta_tools_and_mip_tensor_parallel_planner():
+    """Trace a transformer block, propagate shapes on meta tensors, solve the layout MIP: large layers pair
+    column→row (attention and MLP), tiny layers stay replicated, a memory budget forces sharding, and the
+    sharding-spec propagation names the collectives the chosen layout needs."""
+    import torch
+    import torch.nn as nn
+
+    from atorch_b200.auto.mip_tp_planner import MIPTensorParallelPlanner
+    from atorch_b200.utils.shape_prop import MetaShapeProp
+    from atorch_b200.utils.sharding_spec import MeshShardingSpec, reshard_plan
+    from atorch_b200.utils.spec_prop import SpecProp
+    from atorch_b200.utils.tracer import trace_model
+
+    class Block(nn.Module):
+        def __init__(self, h, f, heads):
+            super().__init__()
+            self.h, self.heads = h, heads
+            self.ln1, self.ln2 = nn.LayerNorm(h), nn.LayerNorm(h)
+            self.q, self.k, self.v, self.o = (nn.Linear(h, h) for _ in range(4))
+            self.up, self.down = nn.Linear(h, f), nn.Linear(f, h)
+
+        def forward(self, x):
+            b, s, _ = x.shape
+            y = self.ln1(x)
+            q, k, v = (l(y).view(b, s, self.heads, -1).transpose(1, 2) for l in (self.q, self.k, self.v))
+            a = torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)
+            x = x + self.o(a.transpose(1, 2).reshape(b, s, self.h))
+            return x + self.down(torch.nn.functional.gelu(self.up(self.ln2(x))))
+
+    big = Block(4096, 16384, 32)
+    gm = trace_model(big)
+    MetaShapeProp(gm).propagate(torch.empty(2, 2048, 4096, device="meta"))
+    up = next(n for n in gm.graph.nodes if n.target == "up")
+    assert up.meta["shape"] == (2, 2048, 16384) and up.meta["flops"] == 2.0 * 2 * 2048 * 16384 * 4096
+    assert up.meta["module_path"] == "up"
+    plan = MIPTensorParallelPlanner(tp_size=4).plan_graph(gm)
+    assert plan == {"q": "col", "k": "col", "v": "col", "o": "row", "up": "col", "down": "row"}, plan
+    sp = SpecProp(gm, plan)
+    sp.propagate()
+    kinds = sorted(op for _, _, ops in sp.conversions for op in ops)
+    assert kinds == ["all_reduce", "all_reduce"], sp.conversions          # one per row-parallel output
+    # tiny layers: communication outweighs the saved compute
+    small = Block(64, 128, 4)
+    plan_s = MIPTensorParallelPlanner(tp_size=4).plan(small, (torch.empty(1, 16, 64),))
+    assert set(plan_s.values()) == {"replicate"}, plan_s
+    # ... unless the parameters do not fit unsharded
+    total = sum(p.numel() * 4 for n, p in small.named_parameters() if "ln" not in n)
+    plan_m = MIPTensorParallelPlanner(tp_size=4, memory_budget_bytes=0.3 * total).plan(small, (torch.empty(1, 16, 64),))
+    assert sum(v != "replicate" for v in plan_m.values()) >= 5, plan_m
+    # conversions between specs
+    S, R, P = MeshShardingSpec.split(3, -1), MeshShardingSpec.replicated(3), MeshShardingSpec((-1, -1, -1), (0,))
+    assert reshard_plan(S, R) == ["all_gather"] and reshard_plan(R, S) == [] and reshard_plan(P, R) == ["all_reduce"]
+    assert reshard_plan(P, S) == ["reduce_scatter"] and reshard_plan(S, MeshShardingSpec.split(3, 1)) == ["all_to_all"]
+    assert S.shard_shape((2, 8, 64), (4,)) == (2, 8, 16)
