@@ -71,6 +71,15 @@ class OuterOptimPeriodicModelAverager:
         self.outer_steps = 0
         self._symm = None                  # symmetric parameter buffer of the one-kernel outer step
         self._slice = None                 # (lo, hi) of this rank's part of the outer state
+        # asynchronous mode: the decision to synchronise is taken on wall-clock time (mean over the ranks)
+        self.use_async, self.sync_time = c.use_async, c.local_sgd_sync_time
+        self.min_total_global_steps = c.min_total_global_steps
+        self.use_step_weight, self.step_weight_ratio = c.use_step_weight, c.step_weight_ratio
+        self.cpu_offload = c.cpu_offload
+        self.last_sync_timestamp: Optional[float] = None
+        self.last_total_global_step = 0
+        self._step_at_last_sync = 0
+        self._clock = __import__("time").time      # replaceable in tests
 
     # ------------------------------------------------------------------------------- state
     def state_dict(self) -> Dict:
@@ -151,7 +160,8 @@ class OuterOptimPeriodicModelAverager:
         import os
 
         if dev.type != "cuda" or self.reducer is not None or self.skip_anomaly or self.pseudo_gradnorm_reduce \
-                or self.clip_pseudo_grad is not None or os.environ.get("ATB_FUSED_COMM", "1") == "0":
+                or self.clip_pseudo_grad is not None or os.environ.get("ATB_FUSED_COMM", "1") == "0" \
+                or self.cpu_offload or (self.use_async and self.use_step_weight):
             return False
         from ..parallel import symm
 
@@ -173,8 +183,60 @@ class OuterOptimPeriodicModelAverager:
         padded[: flat.numel()] = flat
         return padded[self._slice[0]: self._slice[1]].clone()
 
+    def _all_reduce_scalar(self, v: float) -> float:
+        dev = "cuda" if dist.get_backend(self.process_group) == "nccl" else "cpu"
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, group=self.process_group)
+        return float(t.item())
+
     def should_sync(self) -> bool:
-        return self.step >= self.warmup_steps and (self.step - self.warmup_steps) % self.local_sgd_sync_interval == 0
+        """Step mode: every ``local_sgd_sync_interval`` steps after the warm-up. Asynchronous mode
+        (``use_async``): when at least ``local_sgd_sync_time`` seconds of wall-clock time (mean of the ranks'
+        clocks, so that every rank decides alike) have passed since the last synchronisation AND the replicas
+        together have made at least ``min_total_global_steps`` steps since then; the first call after the
+        warm-up synchronises and starts the clock. The small all-reduces of this test run every step on
+        every rank. (Reference: atorch/local_sgd/FSDP/core/_runtime_utils.py:37-83.)"""
+        if not self.use_async:
+            return self.step >= self.warmup_steps and \
+                (self.step - self.warmup_steps) % self.local_sgd_sync_interval == 0
+        if self.step < self.warmup_steps:
+            self.last_total_global_step = self._all_reduce_scalar(float(self.step))
+            return False
+        world = dist.get_world_size(self.process_group)
+        now = self._all_reduce_scalar(self._clock() / world)
+        if self.last_sync_timestamp is None:
+            self.last_total_global_step = self._all_reduce_scalar(float(self.step))
+            self.last_sync_timestamp = now
+            return True
+        if now - self.last_sync_timestamp < self.sync_time:
+            return False
+        total = self._all_reduce_scalar(float(self.step))
+        self.last_sync_timestamp = now
+        if total - self.last_total_global_step < self.min_total_global_steps:
+            return False
+        self.last_total_global_step = total
+        return True
+
+    def _step_weight(self, world: int) -> float:
+        """Share of this replica in the steps made since the last synchronisation (asynchronous mode with
+        ``use_step_weight``), else the plain ``1 / world``."""
+        if not (self.use_async and self.use_step_weight):
+            return 1.0 / world
+        mine = float(self.step - self._step_at_last_sync)
+        total = self._all_reduce_scalar(mine)
+        return mine / total if total > 0 else 1.0 / world
+
+    def _outer_state_to(self, device) -> None:
+        """Moves the synchronised weights and the outer optimizer's tensors (CPU offload between outer steps)."""
+        if self.last_synced is not None and self.last_synced.device != torch.device(device):
+            self.last_synced.data = self.last_synced.data.to(device, non_blocking=True)
+        if self.momentum_buf is not None and self.momentum_buf.device != torch.device(device):
+            self.momentum_buf = self.momentum_buf.to(device, non_blocking=True)
+        if self.outer_optimizer is not None:
+            for st in self.outer_optimizer.state.values():
+                for k, v in st.items():
+                    if isinstance(v, torch.Tensor):
+                        st[k] = v.to(device, non_blocking=True)
 
     # --------------------------------------------------------------------------------- step
     @torch.no_grad()
@@ -189,11 +251,16 @@ class OuterOptimPeriodicModelAverager:
             world = dist.get_world_size(self.process_group)
             if plain_average:
                 flat = torch.cat([p.detach().reshape(-1).float() for p in plist])
-                flat.div_(world)
+                flat.mul_(self._step_weight(world))
                 dist.all_reduce(flat, group=self.process_group)
                 self._write_back(plist, flat)
             else:
+                if self.cpu_offload and self._symm is None:
+                    self._outer_state_to(plist[0].device)
                 self._outer_step(plist, world)
+                if self.cpu_offload and self._symm is None and plist[0].device.type != "cpu":
+                    self._outer_state_to("cpu")
+            self._step_at_last_sync = self.step
         self.step += 1
 
     def _write_back(self, plist, flat) -> None:
@@ -241,9 +308,12 @@ class OuterOptimPeriodicModelAverager:
             if self.pseudo_gradnorm_reduce:
                 weight_kw["weight"] = -total_norm
         if self.reducer is None:
-            pg.div_(world)
+            pg.mul_(self._step_weight(world))
             dist.all_reduce(pg, group=self.process_group)
         else:
+            if self.use_async and self.use_step_weight:
+                weight_kw["step_weight"] = self._step_weight(world)
+                weight_kw["step_weight_ratio"] = self.step_weight_ratio
             self.reducer.reduce_tensor(pg, **weight_kw)
         frozen = self.skip_anomaly and float(pg.abs().sum()) < 1e-6
         if not frozen:

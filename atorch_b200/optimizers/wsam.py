@@ -45,37 +45,53 @@ class WeightedSAM(torch.optim.Optimizer):
         return [p for p in group["params"] if p.grad is not None]
 
     def _avg_grads(self, params) -> None:
-        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
-            world = dist.get_world_size()
-            for p in params:
-                p.grad.div_(world)
-                dist.all_reduce(p.grad)
+        """Average the gradients over the default process group: one all-reduce per dtype over a flattened
+        copy instead of one per parameter."""
+        if not (dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1) or not params:
+            return
+        world = dist.get_world_size()
+        by_dtype = {}
+        for p in params:
+            by_dtype.setdefault(p.grad.dtype, []).append(p.grad)
+        for grads in by_dtype.values():
+            flat = torch._utils._flatten_dense_tensors(grads)
+            flat.div_(world)
+            dist.all_reduce(flat)
+            torch._foreach_copy_(grads, torch._utils._unflatten_dense_tensors(flat, grads))
 
     def _grad_norm(self) -> torch.Tensor:
         dev = self.param_groups[0]["params"][0].device
         norms = []
         for g in self.param_groups:
-            for p in self._with_grad(g):
-                t = (p.abs() * p.grad) if g["adaptive"] else p.grad
-                norms.append(torch.linalg.vector_norm(t.float()).to(dev))
+            ps = self._with_grad(g)
+            if not ps:
+                continue
+            grads = [p.grad for p in ps]
+            ts = torch._foreach_mul(torch._foreach_abs(ps), grads) if g["adaptive"] else grads
+            norms += [n.to(dev, torch.float32) for n in torch._foreach_norm(ts)]
         return torch.linalg.vector_norm(torch.stack(norms)) if norms else torch.zeros((), device=dev)
 
     @torch.no_grad()
     def first_step(self, zero_grad: bool = False) -> None:
         gnorm = self._grad_norm()
         for group in self.param_groups:
-            scale = group["rho"] / (gnorm + group["sam_eps"])
             ps = self._with_grad(group)
-            for p in ps:
-                e_w = (p.pow(2) if group["adaptive"] else 1.0) * p.grad * scale.to(p)
-                p.add_(e_w)
-                self.state[p]["e_w"] = e_w
+            if not ps:
+                continue
+            scale = (group["rho"] / (gnorm + group["sam_eps"])).item()
+            e_ws = torch._foreach_mul([p.grad for p in ps], scale)
+            if group["adaptive"]:
+                torch._foreach_mul_(e_ws, torch._foreach_mul(ps, ps))
+            torch._foreach_add_(ps, e_ws)
+            for p, e in zip(ps, e_ws):
+                self.state[p]["e_w"] = e
             self._avg_grads(ps)
         if self.max_norm is not None:
             torch.nn.utils.clip_grad_norm_(self.model.parameters(), self.max_norm)
         for group in self.param_groups:
-            for p in self._with_grad(group):
-                self.state[p]["grad"] = p.grad.detach().clone()
+            ps = self._with_grad(group)
+            for p, g in zip(ps, torch._foreach_add([p.grad for p in ps], 0.0) if ps else []):
+                self.state[p]["grad"] = g
         if zero_grad:
             self.zero_grad()
 
@@ -83,24 +99,31 @@ class WeightedSAM(torch.optim.Optimizer):
     def second_step(self, zero_grad: bool = False) -> None:
         for group in self.param_groups:
             ps = self._with_grad(group)
+            if not ps:
+                continue
             self._avg_grads(ps)
-            for p in ps:
-                p.sub_(self.state[p]["e_w"])
+            torch._foreach_sub_(ps, [self.state[p]["e_w"] for p in ps])
         if self.max_norm is not None:
             torch.nn.utils.clip_grad_norm_(self.model.parameters(), self.max_norm)
         for group in self.param_groups:
-            for p in self._with_grad(group):
-                st = self.state[p]
-                if not self.decouple:
-                    p.grad.mul_(group["alpha"]).add_(st["grad"], alpha=1.0 - group["alpha"])
-                else:
-                    st["sharpness"] = p.grad.detach() - st["grad"]
-                    p.grad.copy_(st["grad"])
+            ps = self._with_grad(group)
+            if not ps:
+                continue
+            grads, first = [p.grad for p in ps], [self.state[p]["grad"] for p in ps]
+            if not self.decouple:
+                torch._foreach_mul_(grads, group["alpha"])
+                torch._foreach_add_(grads, first, alpha=1.0 - group["alpha"])
+            else:
+                for p, sh in zip(ps, torch._foreach_sub(grads, first)):
+                    self.state[p]["sharpness"] = sh
+                torch._foreach_copy_(grads, first)
         self.base_optimizer.step()
         if self.decouple:
             for group in self.param_groups:
-                for p in self._with_grad(group):
-                    p.add_(self.state[p]["sharpness"], alpha=-group["lr"] * group["alpha"])
+                ps = self._with_grad(group)
+                if ps:
+                    torch._foreach_add_(ps, [self.state[p]["sharpness"] for p in ps],
+                                        alpha=-group["lr"] * group["alpha"])
         if zero_grad:
             self.zero_grad()
 

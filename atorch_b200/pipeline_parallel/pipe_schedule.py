@@ -4,8 +4,10 @@ A schedule is first written down as an explicit per-rank list of actions
 ``(kind, stage_index, micro_batch)`` with kind in {F, B} (pure function, unit-tested without any
 process group), then executed: before every F the stage receives its activations (first stage:
 takes the micro-batch from the input), after it sends its outputs; B mirrors that with gradients.
-Sends are asynchronous and their handles are drained at the end of the step; receives for the next
-action are posted before the current compute finishes being consumed, so transfers overlap compute.
+Sends are asynchronous (their handles are drained at the end of the step), so a stage goes on computing
+while its output is on the wire; a receive is posted when its action starts and waited for at once —
+receives are not posted ahead, because NCCL runs the point-to-point operations of one communicator in
+stream order and two neighbours that both queue a receive before their send would wait on each other.
 
 ``schedule.step(*inputs, target=..., losses=[...], **batch_kwargs)``: inputs/kwargs are split into
 ``n_microbatches`` along dim 0 on the first stage; ``target`` is consumed by the last stage as

@@ -166,3 +166,41 @@ def test_sharded_local_sgd_warmup_baseline_gloo():
     from tests.dist_utils import run_distributed
 
     run_distributed(_warmup_baseline, world=2)
+
+
+def _async_mode(rank, world):
+    """Asynchronous (wall-clock) synchronisation: the decision comes from the mean of the ranks' clocks and the
+    replicas' total step count; the outer state lives on the host between outer steps (``cpu_offload``)."""
+    from atorch_b200.local_sgd import LocalSGDConfig, OuterOptimizerConfig, OuterOptimPeriodicModelAverager
+
+    cfg = LocalSGDConfig(use_async=True, local_sgd_sync_time=10.0, min_total_global_steps=6, local_sgd_warmup_steps=1,
+                         use_step_weight=True, cpu_offload=True)
+    av = OuterOptimPeriodicModelAverager(local_sgd_config=cfg, outer_optim_config=OuterOptimizerConfig(
+        torch.optim.SGD, {"lr": 1.0, "momentum": 0.0}))
+    now = [1000.0 + 3.0 * rank]            # the ranks' clocks disagree; the mean decides
+    av._clock = lambda: now[0]
+    torch.manual_seed(0)
+    p = torch.nn.Parameter(torch.zeros(4))
+    synced = []
+    for step in range(12):
+        with torch.no_grad():
+            # the warm-up step is synchronous (same update everywhere); then rank r drifts by r + 1 per step
+            p.add_(1.0 if step == 0 else float(rank + 1))
+        before = av.outer_steps if av._fused_sgd else None
+        s0 = av._step_at_last_sync
+        av.average_parameters([p])
+        if av._step_at_last_sync != s0 or (step == 1):
+            synced.append(step)
+        now[0] += 4.0                      # 4 s per step: 10 s are over after 3 steps, 6 total steps after 3 (2 ranks)
+        del before
+    # warm-up step 0: no sync; step 1: first sync starts the clock; then every third step (12 s >= 10 s, 6 steps)
+    assert synced == [1, 4, 7, 10], synced
+    # equal step counts -> weights 1/2: after a sync every replica holds the mean of the two drifts
+    assert av.last_synced.device.type == "cpu"
+    vals = [torch.zeros(4) for _ in range(world)]
+    torch.distributed.all_gather(vals, p.detach())
+    assert torch.allclose(vals[0] - vals[1], torch.full((4,), -1.0)), vals   # one local step apart since step 10
+
+
+def test_async_wall_clock_sync_step_weight_and_cpu_offload_gloo():
+    run_distributed(_async_mode, world=2)
