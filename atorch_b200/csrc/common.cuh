@@ -138,6 +138,13 @@ ATB_DEVICE void tma_store_2d(const CUtensorMap* tm, const void* smem_src, int x,
                "r"(smem_u32(smem_src)), "r"(x), "r"(y)
                : "memory");
 }
+// Element-wise fp32 add of a shared-memory tile into global memory by the TMA unit (asynchronous; completion
+// through the bulk group of the issuing thread). Coordinates must be non-negative, x a multiple of 4 floats.
+ATB_DEVICE void tma_reduce_add_2d(const CUtensorMap* tm, const void* smem_src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(tm)), "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
 ATB_DEVICE void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 ATB_DEVICE void tma_store_wait_read() {
@@ -294,6 +301,11 @@ ATB_DEVICE uint64_t umma_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes, uint
   return d;
 }
 
+// The same descriptor `bytes` further on in shared memory (the start-address field counts 16-byte units and
+// cannot carry out of its 14 bits for any address inside the 227 KB of a CTA): one 64-bit add per MMA in
+// place of rebuilding the descriptor, which matters when one thread issues an MMA every 64 clocks.
+ATB_DEVICE uint64_t umma_desc_advance(uint64_t desc, uint32_t bytes) { return desc + (uint64_t)(bytes >> 4); }
+
 // Instruction descriptor for kind::f16 / kind::f8f6f4 with fp32 accumulation.
 //   fmt: kind::f16: 0 = f16, 1 = bf16;  kind::f8f6f4: 0 = e4m3, 1 = e5m2
 ATB_DEVICE constexpr uint32_t umma_idesc(int m, int n, int a_fmt, int b_fmt, bool a_mn_major, bool b_mn_major) {
@@ -334,6 +346,37 @@ ATB_DEVICE float block_max(float v, float* red) {
   float t = (lane < nw) ? red[lane] : -INFINITY;
   t = warp_max(t);
   return t;
+}
+
+// Two fp32 values in one 64-bit register and the packed arithmetic of sm_100 on them: one instruction
+// does two fused multiply-adds (or adds), which halves the issue slots of element-wise fp32 work.
+ATB_DEVICE uint64_t f2_pack(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+ATB_DEVICE uint64_t f2_pack_bits(uint32_t a, uint32_t b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(a), "r"(b));
+  return r;
+}
+ATB_DEVICE void f2_unpack(uint64_t v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+ATB_DEVICE uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+ATB_DEVICE uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+ATB_DEVICE uint64_t f2_mul(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
 }
 
 // 2^x on the special-function unit (ex2.approx.ftz): -inf -> 0, relative error ~2^-22

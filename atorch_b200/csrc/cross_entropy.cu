@@ -57,20 +57,44 @@ __global__ void __launch_bounds__(CE_NT) ce_fwd_kernel(const T* __restrict__ log
   const T* x = logits + row * stride;
   float m = -INFINITY, s = 0.f, tot = 0.f;
   const int nvec = V >> 3;
-  for (int c = threadIdx.x; c < nvec; c += CE_NT) {
-    float v[8];
-    ld8<T>(x + c * 8, v);
-    float lm = v[0];
+  // the label and its logit are fetched now, so that the two dependent loads are not a serial tail of the row
+  long long lab = ignore_index;
+  float ll = 0.f;
+  if (threadIdx.x == 0) {
+    lab = labels[row];
+    const long long local = lab - vocab_start;
+    if (lab != ignore_index && local >= 0 && local < V) ll = to_f32<T>(x[local]);
+  }
+  constexpr float L2E = 1.4426950408889634f;
+  constexpr int U = 2;   // 16-byte loads in flight per thread; one rescale of the running sum per 16 elements
+  for (int c0 = threadIdx.x; c0 < nvec; c0 += U * CE_NT) {
+    float v[U][8];
 #pragma unroll
-    for (int j = 1; j < 8; ++j) lm = fmaxf(lm, v[j]);
-    const float nm = fmaxf(m, lm);
-    float acc = 0.f;
+    for (int u = 0; u < U; ++u) {
+      const int c = c0 + u * CE_NT;
+      if (c < nvec) {
+        ld8<T>(x + c * 8, v[u]);
+      } else {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      acc += __expf(v[j] - nm);
-      tot += v[j];
+        for (int j = 0; j < 8; ++j) v[u][j] = -INFINITY;
+      }
     }
-    s = s * __expf(m - nm) + acc;
+    float lm = v[0][0];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) lm = fmaxf(lm, v[u][j]);
+    const float nm = fmaxf(m, lm);
+    const float nms = (nm == -INFINITY) ? 0.f : -nm * L2E;
+    float acc[2] = {0.f, 0.f};
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        acc[j & 1] += fast_exp2(fmaf(v[u][j], L2E, nms));          // exp(v - nm); -inf padding gives 0
+        if (smoothing > 0.f && v[u][j] != -INFINITY) tot += v[u][j];
+      }
+    s = s * fast_exp2(fmaf(m, L2E, nms)) + (acc[0] + acc[1]);      // m = -inf: factor 0
     m = nm;
   }
   for (int c = (nvec << 3) + threadIdx.x; c < V; c += CE_NT) {  // ragged tail
@@ -86,10 +110,6 @@ __global__ void __launch_bounds__(CE_NT) ce_fwd_kernel(const T* __restrict__ log
   tot = block_sum(tot, red);
   if (threadIdx.x == 0) {
     const float lse = gm + logf(s);
-    const long long lab = labels[row];
-    const long long local = lab - vocab_start;
-    float ll = 0.f;
-    if (lab != ignore_index && local >= 0 && local < V) ll = to_f32<T>(x[local]);
     lse_out[row] = lse;
     if (label_logit_out) label_logit_out[row] = ll;
     if (sum_logits_out) sum_logits_out[row] = tot;

@@ -4,7 +4,7 @@
 //   S  = Q K^T,  dP = dO V^T                      2 x tcgen05.mma -> TMEM   (K-major operands)
 //   P  = exp2(S c - lse),  dS = P (dP - delta) s    registers -> bf16 tiles in swizzled shared memory
 //   dV += P^T dO,  dK += dS^T Q                    accumulate in TMEM across query blocks (MN-major operands)
-//   dQ  = dS K                                      TMEM -> registers -> red.global.add.v4.f32
+//   dQ  = dS K                                      TMEM -> registers -> shared memory -> TMA reduce-add (fp32)
 // A [rows][64] bf16 panel with 128-byte swizzle is at the same time a K-major tile of the matrix and
 // an MN-major tile of its transpose, so P, dS, Q, dO and K are each stored once and read both ways.
 // TMEM: S | dP | dV | dK = 4 x 128 columns; dQ reuses the dP columns.
@@ -18,6 +18,9 @@
 //   element-wise warps meanwhile:                        P(i+1) = exp2(S(i+1) c - lse)   (the exponentials)
 //   then:  dQ(i) out of TMEM (red.add)  ->  tensor core: dP(i+1)  ->  dS(i+1), P(i+1) to shared memory
 // so the exponentials and the loads of the next Q / dO tiles run under the three accumulating products.
+// dQ(i) is staged in the shared memory of P and dS (free between the products of block i and the element-wise
+// results of block i+1) and added to the fp32 accumulation buffer by four cp.reduce.async.bulk.tensor
+// operations of one thread: the 64 KB of atomic adds per query block run in the TMA unit while the warps go on.
 //
 // Masks are per-row key intervals [lo, hi) as in the forward kernel.
 #include "common.cuh"
@@ -53,15 +56,10 @@ struct SmemB {
   static constexpr int P_OFF = V_OFF + TILE;
   static constexpr int DS_OFF = P_OFF + TILE;
   static constexpr int BAR_OFF = DS_OFF + TILE;  // 224 KB
-  static constexpr int NBARS = 12;
+  static constexpr int NBARS = 14;
   static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 64 + 1024;
 };
 static_assert(SmemB::TOTAL <= 232448, "shared memory of the backward kernel exceeds 227 KB");
-
-ATB_DEVICE void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
-               : "memory");
-}
 
 // Row of a query block as the element-wise thread sees it.
 struct RowInfo {
@@ -73,7 +71,8 @@ struct RowInfo {
 
 __global__ void __launch_bounds__(THREADS, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
-                 const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, BwdParams p) {
+                 const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                 const __grid_constant__ CUtensorMap tmdQ, BwdParams p) {
   using L = SmemB;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -94,6 +93,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* pds_full = bars + 9;  // P(i), dS(i) are in shared memory; S(i), dP(i) have been read
   uint64_t* dq_full = bars + 10;  // dV(i), dK(i), dQ(i) are complete
   uint64_t* dp_free = bars + 11;  // dQ(i) has been read out of the dP columns
+  uint64_t* stage_full = bars + 12;  // dQ(i) is staged in shared memory (all element-wise warps)
+  uint64_t* stage_free = bars + 13;  // the TMA unit has read the staged dQ(i): P / dS may be written again
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::NBARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* q_range = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_slot + 2));  // [2]: first, last+1 q block
@@ -120,6 +121,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(pds_full, N_EW / 32);
     mbar_init(dq_full, 1);
     mbar_init(dp_free, N_EW / 32);
+    mbar_init(stage_full, N_EW / 32);
+    mbar_init(stage_free, 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -168,6 +171,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tma_prefetch_desc(&tmdO);
       tma_prefetch_desc(&tmK);
       tma_prefetch_desc(&tmV);
+      tma_prefetch_desc(&tmdQ);
       mbar_expect_tx(kv_full, 2 * TILE);
       tma_load_2d(sK, &tmK, kv_full, hk * HD, (int)k_row);
       tma_load_2d(sK + PANEL, &tmK, kv_full, hk * HD + 64, (int)k_row);
@@ -193,14 +197,22 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       constexpr uint32_t id_km = umma_idesc(128, 128, 1, 1, false, true);
       const uint32_t adO = smem_u32(sdO), aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP), adS = smem_u32(sdS);
       const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdV = tmem_base + 256, tdK = tmem_base + 384;
+      // descriptors of every operand in the form(s) it is read in; the loops below only advance them
+      // (scalars and selects: an array indexed at run time would live in local memory)
+      const uint64_t dQk0 = umma_desc_sw128(smem_u32(sQ), 16, 1024), dQm0 = umma_desc_sw128(smem_u32(sQ), PANEL, 1024);
+      const uint64_t dKk = umma_desc_sw128(aK, 16, 1024), dKm = umma_desc_sw128(aK, PANEL, 1024);
+      const uint64_t dVk = umma_desc_sw128(aV, 16, 1024);
+      const uint64_t dOk = umma_desc_sw128(adO, 16, 1024), dOm = umma_desc_sw128(adO, PANEL, 1024);
+      const uint64_t dPm = umma_desc_sw128(aP, PANEL, 1024);
+      const uint64_t dSk = umma_desc_sw128(adS, 16, 1024), dSm = umma_desc_sw128(adS, PANEL, 1024);
       auto issue_s = [&](int it) -> bool {   // S(it) = Q(it) K^T over d
         if (!mbar_wait(&q_full[it & 1], (it >> 1) & 1, abort_flag, p.status)) return false;
         tc_fence_after();
-        const uint32_t aQ = smem_u32(sQ + (it & 1) * TILE);
+        const uint64_t qd = umma_desc_advance(dQk0, (it & 1) ? TILE : 0);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t off = (k >> 2) * PANEL + (k & 3) * 32;
-          umma_f16<1>(tS, umma_desc_sw128(aQ + off, 16, 1024), umma_desc_sw128(aK + off, 16, 1024), id_kk, k != 0);
+          umma_f16<1>(tS, umma_desc_advance(qd, off), umma_desc_advance(dKk, off), id_kk, k != 0);
         }
         umma_commit(s_full);
         return true;
@@ -211,7 +223,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t off = (k >> 2) * PANEL + (k & 3) * 32;
-          umma_f16<1>(tdP, umma_desc_sw128(adO + off, 16, 1024), umma_desc_sw128(aV + off, 16, 1024), id_kk, k != 0);
+          umma_f16<1>(tdP, umma_desc_advance(dOk, off), umma_desc_advance(dVk, off), id_kk, k != 0);
         }
         umma_commit(dp_full);
         return true;
@@ -222,22 +234,19 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (!mbar_wait(pds_full, it & 1, abort_flag, p.status)) break;
         tc_fence_after();
         if (it + 1 < nblk && !issue_s(it + 1)) break;
-        const uint32_t aQ = smem_u32(sQ + (it & 1) * TILE);
+        const uint64_t qm = umma_desc_advance(dQm0, (it & 1) ? TILE : 0);
 #pragma unroll
         for (int k = 0; k < 8; ++k)  // dV += P^T dO over q
-          umma_f16<1>(tdV, umma_desc_sw128(aP + k * 2048, PANEL, 1024), umma_desc_sw128(adO + k * 2048, PANEL, 1024),
-                      id_mm, (it | k) != 0);
+          umma_f16<1>(tdV, umma_desc_advance(dPm, k * 2048), umma_desc_advance(dOm, k * 2048), id_mm, (it | k) != 0);
         umma_commit(do_free);
 #pragma unroll
         for (int k = 0; k < 8; ++k)  // dK += dS^T Q over q
-          umma_f16<1>(tdK, umma_desc_sw128(adS + k * 2048, PANEL, 1024), umma_desc_sw128(aQ + k * 2048, PANEL, 1024),
-                      id_mm, (it | k) != 0);
+          umma_f16<1>(tdK, umma_desc_advance(dSm, k * 2048), umma_desc_advance(qm, k * 2048), id_mm, (it | k) != 0);
         umma_commit(&q_free[it & 1]);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {  // dQ = dS K over keys (into the dP columns)
           const uint32_t off = (k >> 2) * PANEL + (k & 3) * 32;
-          umma_f16<1>(tdP, umma_desc_sw128(adS + off, 16, 1024), umma_desc_sw128(aK + k * 2048, PANEL, 1024), id_km,
-                      k != 0);
+          umma_f16<1>(tdP, umma_desc_advance(dSk, off), umma_desc_advance(dKm, k * 2048), id_km, k != 0);
         }
         umma_commit(dq_full);
         if (it + 1 < nblk) {
@@ -276,11 +285,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       return ri;
     };
-    // dQ(it) of row `ri` leaves the dP columns for the fp32 accumulation buffer
-    auto drain_dq = [&](int it, const RowInfo& ri) -> bool {
+    // dQ(it) leaves the dP columns: registers -> staging tiles (four [128 x 32] fp32 boxes with the 128-byte
+    // swizzle, in the memory of P and dS) -> reduce-add into the accumulation buffer by the TMA unit. Rows past
+    // the end of the sequence hold zeros (their dS is zero), so whatever the tile covers there is unchanged.
+    uint8_t* stage = sP;
+    const bool reducer = threadIdx.x == 64;     // first element-wise thread issues the TMA operations
+    auto drain_dq = [&](int it) -> bool {
       if (!__all_sync(0xffffffffu, mbar_wait(dq_full, it & 1, abort_flag, p.status))) return false;
       tc_fence_after();
-      float* dqrow = p.dq_acc + (((long long)b * p.Sq + ri.i) * p.Hq + h) * HD + half * 64;
       uint32_t t0[32], t1[32];
       tmem_ld_32x32(tdP, t0);
       tmem_ld_32x32(tdP + 32, t1);
@@ -288,23 +300,37 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(dp_free);
-      if (ri.i < p.Sq && it < nblk) {
+      uint8_t* row0 = stage + (half * 2) * 16384 + r * 128;
 #pragma unroll
-        for (int c = 0; c < 32; c += 4)
-          red_add_v4(dqrow + c, __uint_as_float(t0[c]), __uint_as_float(t0[c + 1]), __uint_as_float(t0[c + 2]),
-                     __uint_as_float(t0[c + 3]));
-#pragma unroll
-        for (int c = 0; c < 32; c += 4)
-          red_add_v4(dqrow + 32 + c, __uint_as_float(t1[c]), __uint_as_float(t1[c + 1]), __uint_as_float(t1[c + 2]),
-                     __uint_as_float(t1[c + 3]));
+      for (int ch = 0; ch < 8; ++ch) {
+        const int slot = (ch ^ (r & 7)) << 4;
+        *reinterpret_cast<uint4*>(row0 + slot) = make_uint4(t0[ch * 4], t0[ch * 4 + 1], t0[ch * 4 + 2], t0[ch * 4 + 3]);
+        *reinterpret_cast<uint4*>(row0 + 16384 + slot) =
+            make_uint4(t1[ch * 4], t1[ch * 4 + 1], t1[ch * 4 + 2], t1[ch * 4 + 3]);
       }
-      return true;
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(stage_full);
+      bool rok = true;
+      if (reducer) {
+        rok = mbar_wait(stage_full, it & 1, abort_flag, p.status);
+        if (rok) {
+          const int qrow = (int)(q_row_base + (long long)(qb0 + it) * BQ);
+#pragma unroll
+          for (int bx = 0; bx < 4; ++bx) tma_reduce_add_2d(&tmdQ, stage + bx * 16384, h * HD + bx * 32, qrow);
+          tma_store_commit();
+          tma_store_wait_read<0>();
+          mbar_arrive(stage_free);
+        }
+      }
+      return __all_sync(0xffffffffu, rok);   // the whole warp leaves the loop together when a wait ran out
     };
 
-    RowInfo cur = row_info(0), prev = cur;
+    RowInfo cur = row_info(0);
     for (int it = 0; it < nblk; ++it) {
       const RowInfo nxt = row_info(it + 1);   // issued early: the loads complete under this block's work
-      const bool row_full = cur.valid && cur.lo <= kv0 && cur.hi >= kv0 + BKV;
+      // warp-uniform, so that the per-element interval tests are a separate path that full tiles never enter
+      const bool row_full = __all_sync(0xffffffffu, cur.valid && cur.lo <= kv0 && cur.hi >= kv0 + BKV);
       // ---- P(it) = exp2(S c - lse): runs while the tensor core accumulates dV, dK and forms dQ of block it-1
       if (!__all_sync(0xffffffffu, mbar_wait(s_full, it & 1, abort_flag, p.status))) { ok = false; break; }
       tc_fence_after();
@@ -315,10 +341,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_ld_32x32(tS + 32, s1);
         tmem_ld_wait();
         const int c0 = kv0 + half * 64;
+        const uint64_t sc2 = f2_pack(p.scale_log2, p.scale_log2), nl2 = f2_pack(-cur.lse2, -cur.lse2);
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          pv[c] = fast_exp2(fmaf(__uint_as_float(s0[c]), p.scale_log2, -cur.lse2));
-          pv[32 + c] = fast_exp2(fmaf(__uint_as_float(s1[c]), p.scale_log2, -cur.lse2));
+        for (int c = 0; c < 32; c += 2) {
+          float a0, a1, b0, b1;
+          f2_unpack(f2_fma(f2_pack_bits(s0[c], s0[c + 1]), sc2, nl2), a0, a1);
+          f2_unpack(f2_fma(f2_pack_bits(s1[c], s1[c + 1]), sc2, nl2), b0, b1);
+          pv[c] = fast_exp2(a0); pv[c + 1] = fast_exp2(a1);
+          pv[32 + c] = fast_exp2(b0); pv[33 + c] = fast_exp2(b1);
         }
         if (!row_full) {
 #pragma unroll
@@ -327,9 +357,14 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
       }
       // ---- dQ(it-1) out of the dP columns, which frees them for dP(it)
-      if (it > 0 && !drain_dq(it - 1, prev)) { ok = false; break; }
+      if (it > 0 && !drain_dq(it - 1)) { ok = false; break; }
       // ---- dS(it) = P (dP - delta) scale; P and dS to shared memory (free: dq_full(it-1) has been waited for)
       if (!__all_sync(0xffffffffu, mbar_wait(dp_full, it & 1, abort_flag, p.status))) { ok = false; break; }
+      // P and dS share their memory with the staged dQ(it-1): wait until the TMA unit has read it
+      if (it > 0 && !__all_sync(0xffffffffu, mbar_wait(stage_free, (it - 1) & 1, abort_flag, p.status))) {
+        ok = false;
+        break;
+      }
       tc_fence_after();
       uint8_t* prow = sP + half * PANEL + r * 128;
       uint8_t* dsrow = sdS + half * PANEL + r * 128;
@@ -338,16 +373,20 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_ld_32x32(tdP, d0);
         tmem_ld_32x32(tdP + 32, d1);
         tmem_ld_wait();
+        const uint64_t nd2 = f2_pack(-cur.delta, -cur.delta), scl2 = f2_pack(p.scale, p.scale);
 #pragma unroll
         for (int c8 = 0; c8 < 8; ++c8) {
           uint32_t pk[4], dk_[4];
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             const int c = c8 * 8 + 2 * q;
-            const float dp0 = __uint_as_float(c < 32 ? d0[c & 31] : d1[c & 31]);
-            const float dp1 = __uint_as_float(c < 32 ? d0[(c + 1) & 31] : d1[(c + 1) & 31]);
+            const uint64_t dp2 = c < 32 ? f2_pack_bits(d0[c & 31], d0[(c + 1) & 31])
+                                        : f2_pack_bits(d1[c & 31], d1[(c + 1) & 31]);
+            const uint64_t p2 = f2_pack(pv[c], pv[c + 1]);
+            float ds0, ds1;
+            f2_unpack(f2_mul(f2_mul(p2, scl2), f2_add(dp2, nd2)), ds0, ds1);   // P (dP - delta) scale
             pk[q] = pack_bf16x2(pv[c], pv[c + 1]);
-            dk_[q] = pack_bf16x2(pv[c] * (dp0 - cur.delta) * p.scale, pv[c + 1] * (dp1 - cur.delta) * p.scale);
+            dk_[q] = pack_bf16x2(ds0, ds1);
           }
           const int slot = (c8 ^ (r & 7)) << 4;
           *reinterpret_cast<uint4*>(prow + slot) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
@@ -358,10 +397,10 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_full);
-      prev = cur;
       cur = nxt;
     }
-    if (ok && nblk > 0) ok = drain_dq(nblk - 1, prev);
+    if (ok && nblk > 0) ok = drain_dq(nblk - 1);
+    if (reducer) tma_store_wait<0>();
     // dV / dK of this key block: TMEM lane = key row. tcgen05.ld is a warp-wide (.sync.aligned)
     // instruction: every lane executes it, only the global stores are predicated per row.
     const int j = kv0 + r;
@@ -463,7 +502,7 @@ extern "C" int atb_flash_bwd(const void* dout, const void* q, const void* k, con
   if (Hq % Hkv) return -1;
   if ((q_stride | k_stride | v_stride | do_stride | dq_stride | dkv_stride) & 7) return -1;
   cudaStream_t st = (cudaStream_t)stream;
-  CUtensorMap tmQ, tmdO, tmK, tmV;
+  CUtensorMap tmQ, tmdO, tmK, tmV, tmdQ;
   if (!make_tmap_2d(&tmQ, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)B * Sq, (uint64_t)Hq * HD, q_stride, BQ, 64,
                     CU_TENSOR_MAP_SWIZZLE_128B))
     return -2;
@@ -475,6 +514,10 @@ extern "C" int atb_flash_bwd(const void* dout, const void* q, const void* k, con
     return -2;
   if (!make_tmap_2d(&tmV, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)B * Sk, (uint64_t)Hkv * HD, v_stride, BKV,
                     64, CU_TENSOR_MAP_SWIZZLE_128B))
+    return -2;
+  // fp32 accumulation buffer as [B*Sq, Hq*HD]; the kernel adds [128 x 32] boxes to it
+  if (!make_tmap_2d(&tmdQ, dq_acc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)B * Sq, (uint64_t)Hq * HD,
+                    (uint64_t)Hq * HD, BQ, 32, CU_TENSOR_MAP_SWIZZLE_128B))
     return -2;
   static bool attr_set = false;
   if (!attr_set) {
@@ -498,7 +541,7 @@ extern "C" int atb_flash_bwd(const void* dout, const void* q, const void* k, con
   p.scale = softmax_scale; p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = status;
   dim3 grid((Sk + BKV - 1) / BKV, Hq, B);
-  flash_bwd_kernel<<<grid, THREADS, SmemB::TOTAL, st>>>(tmQ, tmdO, tmK, tmV, p);
+  flash_bwd_kernel<<<grid, THREADS, SmemB::TOTAL, st>>>(tmQ, tmdO, tmK, tmV, tmdQ, p);
   const long long n4 = (long long)B * Sq * Hq * HD / 4;
   long long g = (n4 + 255) / 256;
   if (g > 148 * 16) g = 148 * 16;

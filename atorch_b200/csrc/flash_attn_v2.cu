@@ -47,6 +47,46 @@ struct L2 {
   static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 64 + 1024;
 };
 
+// P = 2^(S c - m c) for one row: the 128 scores are read back from tensor memory in chunks of 32 (the next
+// chunk's load is in flight while this one is exponentiated) and the packed bf16 result overwrites the first
+// 64 columns of S; each chunk is read before the 16 columns it turns into are written, and those lie below
+// the next chunk. Returns the row sum. MASK: per-element key interval test (tiles that are not fully visible).
+template <bool MASK>
+ATB_DEVICE float softmax_exp_row(uint32_t s_addr, float scale_log2, float neg_ms, int kv0, int lo, int hi) {
+  const uint64_t sc2 = f2_pack(scale_log2, scale_log2), nm2 = f2_pack(neg_ms, neg_ms);
+  uint64_t acc0 = 0ull, acc1 = 0ull;   // (0.f, 0.f)
+  uint32_t xa[32], xb[32];
+  tmem_ld_32x32(s_addr, xa);
+#pragma unroll
+  for (int cc = 0; cc < 4; ++cc) {
+    uint32_t (&x)[32] = (cc & 1) ? xb : xa;
+    uint32_t (&xn)[32] = (cc & 1) ? xa : xb;
+    tmem_ld_wait();
+    if (cc + 1 < 4) tmem_ld_32x32(s_addr + (cc + 1) * 32, xn);
+    uint32_t pk[16];
+#pragma unroll
+    for (int c = 0; c < 32; c += 2) {
+      float t0, t1;
+      f2_unpack(f2_fma(f2_pack_bits(x[c], x[c + 1]), sc2, nm2), t0, t1);
+      float p0 = fast_exp2(t0), p1 = fast_exp2(t1);
+      if (MASK) {
+        const int kk = kv0 + cc * 32 + c;
+        if (kk < lo || kk >= hi) p0 = 0.f;
+        if (kk + 1 < lo || kk + 1 >= hi) p1 = 0.f;
+      }
+      const uint64_t pp = f2_pack(p0, p1);
+      if ((c >> 1) & 1) acc1 = f2_add(acc1, pp);
+      else acc0 = f2_add(acc0, pp);
+      pk[c >> 1] = pack_bf16x2(p0, p1);
+    }
+    tmem_st_32x16(s_addr + cc * 16, pk);
+  }
+  float a, b, c, d;
+  f2_unpack(acc0, a, b);
+  f2_unpack(acc1, c, d);
+  return (a + b) + (c + d);
+}
+
 __global__ void __launch_bounds__(THREADS, 1)
 flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, Params p) {
@@ -151,6 +191,10 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       constexpr uint32_t idesc_s = umma_idesc(BQ, BKV, 1, 1, false, false);
       constexpr uint32_t idesc_o = umma_idesc(BQ, HD, 1, 1, false, true);
       int k_ready = -1, v_ready = -1;   // newest K / V tile whose arrival has been waited for
+      // descriptors of the tiles' first MMA operands; the loops below only advance them
+      // (kept in scalars and picked with selects: an array indexed at run time would live in local memory)
+      const uint64_t q_desc0 = umma_desc_sw128(smem_u32(sQ), 16, 1024), k_desc0 = umma_desc_sw128(smem_u32(sK), 16, 1024),
+                     v_desc0 = umma_desc_sw128(smem_u32(sV), PANEL, 1024);
       // S_T(j) = Q_T K_j^T into the tile's S columns
       auto issue_s = [&](int t, int j) -> bool {
         const int s = j & 1;
@@ -159,12 +203,11 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           k_ready = j;
           tc_fence_after();
         }
-        const uint32_t q_addr = smem_u32(sQ + t * TILE), k_addr = smem_u32(sK + s * TILE);
+        const uint64_t qd = umma_desc_advance(q_desc0, t ? TILE : 0), kd = umma_desc_advance(k_desc0, s ? TILE : 0);
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {
           const uint32_t off = (k >> 2) * PANEL + (k & 3) * 32;
-          umma_f16<1>(tmem_base + t * BKV, umma_desc_sw128(q_addr + off, 16, 1024),
-                      umma_desc_sw128(k_addr + off, 16, 1024), idesc_s, k != 0);
+          umma_f16<1>(tmem_base + t * BKV, umma_desc_advance(qd, off), umma_desc_advance(kd, off), idesc_s, k != 0);
         }
         umma_commit(&s_full[t]);
         return true;
@@ -184,11 +227,11 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
               v_ready = j;
             }
             tc_fence_after();
-            const uint32_t v_addr = smem_u32(sV + s * TILE);
+            const uint64_t vd = umma_desc_advance(v_desc0, s ? TILE : 0);
 #pragma unroll
             for (int k = 0; k < BKV / 16; ++k)   // A = P_T: 16 bf16 keys per step = 8 TMEM columns
               umma_f16_ts(tmem_base + 2 * BKV + t * HD, tmem_base + t * BKV + k * 8,
-                          umma_desc_sw128(v_addr + k * 2048, PANEL, 1024), idesc_o, (j | k) != 0);
+                          umma_desc_advance(vd, k * 2048), idesc_o, (j | k) != 0);
             if (j == nt[t] - 1) umma_commit(&o_full[t]);
           }
           if (t == 1) umma_commit(&v_empty[s]);
@@ -218,7 +261,8 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       const int kv0 = (t0 + j) * BKV;
       if (!__all_sync(0xffffffffu, mbar_wait(&s_full[t], j & 1, abort_flag, p.status))) { ok = false; break; }
       tc_fence_after();
-      const bool full = row_valid && lo <= kv0 && hi >= kv0 + BKV;
+      // the mask tests are compiled into a separate path taken only by warps with a partly visible row
+      const bool full = __all_sync(0xffffffffu, row_valid && lo <= kv0 && hi >= kv0 + BKV);
       // ---- pass 1: row maximum
       float mx;
       {
@@ -266,34 +310,10 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           }
         }
       }
-      // ---- pass 2: P = 2^(S c - m c) as packed bf16 over the first 64 columns of S (each chunk of 32 scores
-      // is read before the 16 columns it turns into are written, and those lie below the next chunk)
+      // ---- pass 2: P = 2^(S c - m c) as packed bf16 over the first 64 columns of S
       const float neg_ms = (m_ref == -INFINITY) ? 0.f : -m_ref * p.scale_log2;
-      float ls4[4] = {0.f, 0.f, 0.f, 0.f};
-      uint32_t xa[32], xb[32];
-      tmem_ld_32x32(s_addr, xa);
-#pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
-        uint32_t (&x)[32] = (cc & 1) ? xb : xa;
-        uint32_t (&xn)[32] = (cc & 1) ? xa : xb;
-        tmem_ld_wait();
-        if (cc + 1 < 4) tmem_ld_32x32(s_addr + (cc + 1) * 32, xn);
-        uint32_t pk[16];
-#pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          float p0 = fast_exp2(fmaf(__uint_as_float(x[c]), p.scale_log2, neg_ms));
-          float p1 = fast_exp2(fmaf(__uint_as_float(x[c + 1]), p.scale_log2, neg_ms));
-          if (!full) {
-            const int kk = kv0 + cc * 32 + c;
-            if (kk < lo || kk >= hi) p0 = 0.f;
-            if (kk + 1 < lo || kk + 1 >= hi) p1 = 0.f;
-          }
-          ls4[(c >> 1) & 3] += p0 + p1;
-          pk[c >> 1] = pack_bf16x2(p0, p1);
-        }
-        tmem_st_32x16(s_addr + cc * 16, pk);
-      }
-      l_run += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+      l_run += full ? softmax_exp_row<false>(s_addr, p.scale_log2, neg_ms, kv0, lo, hi)
+                    : softmax_exp_row<true>(s_addr, p.scale_log2, neg_ms, kv0, lo, hi);
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();

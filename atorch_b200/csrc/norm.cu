@@ -68,12 +68,52 @@ ATB_DEVICE void store8<float>(float* p, const float (&v)[8]) {
   *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
 }
 
+// A row piece as loaded (8 elements, undecoded): what the software pipeline keeps in registers for the
+// row after the current one, so that its loads are in flight during the reductions of this one.
+template <typename T>
+struct Raw8 {
+  uint4 v[sizeof(T) / 2];
+};
+template <typename T>
+ATB_DEVICE Raw8<T> ldraw(const T* p) {
+  Raw8<T> r;
+#pragma unroll
+  for (int k = 0; k < (int)(sizeof(T) / 2); ++k) r.v[k] = reinterpret_cast<const uint4*>(p)[k];
+  return r;
+}
+template <typename T>
+ATB_DEVICE void decode8(const Raw8<T>& r, float (&v)[8]) {
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    float2 a = unpack_bf16x2(r.v[0].x), b = unpack_bf16x2(r.v[0].y), c = unpack_bf16x2(r.v[0].z),
+           d = unpack_bf16x2(r.v[0].w);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+  } else if constexpr (std::is_same<T, __half>::value) {
+    const __half2* h = reinterpret_cast<const __half2*>(&r.v[0]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 f = __half22float2(h[i]);
+      v[2 * i] = f.x; v[2 * i + 1] = f.y;
+    }
+  } else {
+    v[0] = __uint_as_float(r.v[0].x); v[1] = __uint_as_float(r.v[0].y); v[2] = __uint_as_float(r.v[0].z);
+    v[3] = __uint_as_float(r.v[0].w); v[4] = __uint_as_float(r.v[1].x); v[5] = __uint_as_float(r.v[1].y);
+    v[6] = __uint_as_float(r.v[1].z); v[7] = __uint_as_float(r.v[1].w);
+  }
+}
+// value after a round trip through the storage type (what a re-read of a stored tensor would give)
+template <typename T>
+ATB_DEVICE float round_through(float x) {
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) return __bfloat162float(__float2bfloat16_rn(x));
+  else if constexpr (std::is_same<T, __half>::value) return __half2float(__float2half_rn(x));
+  else return x;
+}
+
 // ------------------------------------------------------------------------------------------
 // forward:  y = (x [+ residual]) * rstd * w           (LN: (x - mean) * rstd * w + b)
 // If `residual` is given, the sum x + residual is also written to `sum_out` (pre-norm stream).
 // ------------------------------------------------------------------------------------------
-template <typename T, int VPT, bool LN>
-__global__ void __launch_bounds__(NT) norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ residual,
+template <typename T, int VPT, bool LN, bool RES>
+__global__ void __launch_bounds__(NT, (VPT <= 2 && !LN) ? 4 : 1) norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ residual,
                                                       const T* __restrict__ w, const T* __restrict__ b,
                                                       T* __restrict__ y, T* __restrict__ sum_out,
                                                       float* __restrict__ mean_out, float* __restrict__ rstd_out,
@@ -93,6 +133,18 @@ __global__ void __launch_bounds__(NT) norm_fwd_kernel(const T* __restrict__ x, c
       }
     }
   }
+  Raw8<T> nx[VPT], nr[RES ? VPT : 1];
+  auto fetch = [&](int row) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c = threadIdx.x + i * NT;
+      if (c < nvec) {
+        nx[i] = ldraw<T>(x + (size_t)row * N + c * 8);
+        if constexpr (RES) nr[i] = ldraw<T>(residual + (size_t)row * N + c * 8);
+      }
+    }
+  };
+  if ((int)blockIdx.x < M) fetch(blockIdx.x);
   for (int row = blockIdx.x; row < M; row += gridDim.x) {
     float xv[VPT][8];
     float s = 0.f, ss = 0.f;
@@ -100,15 +152,14 @@ __global__ void __launch_bounds__(NT) norm_fwd_kernel(const T* __restrict__ x, c
     for (int i = 0; i < VPT; ++i) {
       const int c = threadIdx.x + i * NT;
       if (c < nvec) {
-        load8<T>(x + (size_t)row * N + c * 8, xv[i]);
-        if (residual != nullptr) {
+        decode8<T>(nx[i], xv[i]);
+        if constexpr (RES) {
           float rv[8];
-          load8<T>(residual + (size_t)row * N + c * 8, rv);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) xv[i][j] += rv[j];
+          decode8<T>(nr[i], rv);
           // round through the storage type so the normalised value matches a re-read of sum_out
+#pragma unroll
+          for (int j = 0; j < 8; ++j) xv[i][j] = round_through<T>(xv[i][j] + rv[j]);
           store8<T>(sum_out + (size_t)row * N + c * 8, xv[i]);
-          if constexpr (!std::is_same<T, float>::value) load8<T>(sum_out + (size_t)row * N + c * 8, xv[i]);
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -117,6 +168,8 @@ __global__ void __launch_bounds__(NT) norm_fwd_kernel(const T* __restrict__ x, c
         }
       }
     }
+    // the next row's loads are issued before this row's reductions
+    if (row + (int)gridDim.x < M) fetch(row + gridDim.x);
     float mean = 0.f, rstd;
     if (LN) {
       mean = block_sum(s, red) / N;
@@ -178,6 +231,18 @@ __global__ void __launch_bounds__(NT) norm_bwd_kernel(const T* __restrict__ dy, 
   // contiguous row chunk per CTA keeps the partial sums' order independent of the grid stride
   const int rows_per = (M + gridDim.x - 1) / gridDim.x;
   const int r0 = blockIdx.x * rows_per, r1 = min(M, r0 + rows_per);
+  Raw8<T> nx[VPT], ndy[VPT];
+  auto fetch = [&](int row) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c = threadIdx.x + i * NT;
+      if (c < nvec) {
+        nx[i] = ldraw<T>(x + (size_t)row * N + c * 8);
+        ndy[i] = ldraw<T>(dy + (size_t)row * N + c * 8);
+      }
+    }
+  };
+  if (r0 < r1) fetch(r0);
   for (int row = r0; row < r1; ++row) {
     const float rstd = rstd_in[row];
     const float mean = LN ? mean_in[row] : 0.f;
@@ -188,8 +253,8 @@ __global__ void __launch_bounds__(NT) norm_bwd_kernel(const T* __restrict__ dy, 
       const int c = threadIdx.x + i * NT;
       if (c < nvec) {
         float xv[8], dyv[8];
-        load8<T>(x + (size_t)row * N + c * 8, xv);
-        load8<T>(dy + (size_t)row * N + c * 8, dyv);
+        decode8<T>(nx[i], xv);
+        decode8<T>(ndy[i], dyv);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           xh[i][j] = (xv[j] - mean) * rstd;
@@ -201,6 +266,7 @@ __global__ void __launch_bounds__(NT) norm_bwd_kernel(const T* __restrict__ dy, 
         }
       }
     }
+    if (row + 1 < r1) fetch(row + 1);   // in flight during the reductions and the store of this row
     c1 = block_sum(c1, red) / N;
     if (LN) c2 = block_sum(c2, red) / N; else c2 = 0.f;
 #pragma unroll
@@ -248,8 +314,14 @@ int launch_fwd(const void* x, const void* res, const void* w, const void* b, voi
   const int vpt = (nvec + NT - 1) / NT;
   int grid = M < 148 * 8 ? M : 148 * 8;
 #define L(V)                                                                                                       \
-  norm_fwd_kernel<T, V, LN><<<grid, NT, 0, st>>>((const T*)x, (const T*)res, (const T*)w, (const T*)b, (T*)y,     \
-                                                 (T*)sum_out, mean, rstd, M, N, eps)
+  do {                                                                                                             \
+    if (res != nullptr)                                                                                            \
+      norm_fwd_kernel<T, V, LN, true><<<grid, NT, 0, st>>>((const T*)x, (const T*)res, (const T*)w, (const T*)b,   \
+                                                           (T*)y, (T*)sum_out, mean, rstd, M, N, eps);            \
+    else                                                                                                           \
+      norm_fwd_kernel<T, V, LN, false><<<grid, NT, 0, st>>>((const T*)x, (const T*)res, (const T*)w, (const T*)b,  \
+                                                            (T*)y, (T*)sum_out, mean, rstd, M, N, eps);           \
+  } while (0)
   if (vpt <= 1) L(1);
   else if (vpt <= 2) L(2);
   else if (vpt <= 4) L(4);

@@ -92,6 +92,19 @@ struct AgdArgs {
   int first_step, decouple, fixed_decay;
 };
 
+ATB_DEVICE void agd_update(float& p, float& mm, float& vv, float g, const AgdArgs& a, float step_size, float dfloor) {
+  if (a.decouple) p *= a.fixed_decay ? (1.f - a.weight_decay) : (1.f - a.lr * a.weight_decay);
+  else g += a.weight_decay * p;
+  const float m_old = mm;
+  mm = a.beta1 * mm + (1.f - a.beta1) * g;
+  const float s = a.first_step ? mm / a.bc1 : (mm / a.bc1 - m_old / a.bc1_old);
+  vv = a.beta2 * vv + (1.f - a.beta2) * s * s;
+  const float den = fmaxf(sqrtf(vv), dfloor);
+  float u = mm / den;
+  if (a.clip > 0.f) u = fminf(fmaxf(u, -a.clip), a.clip);
+  p -= step_size * u;
+}
+
 template <typename G>
 __global__ void agd_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
                            const G* __restrict__ grad, __nv_bfloat16* __restrict__ param_bf16, long long n, AgdArgs a,
@@ -99,20 +112,31 @@ __global__ void agd_kernel(float* __restrict__ master, float* __restrict__ m, fl
   const float gs = a.grad_scale * (grad_scale_ptr ? *grad_scale_ptr : 1.f);
   const float step_size = a.lr * sqrtf(a.bc2) / a.bc1;
   const float dfloor = a.delta * sqrtf(a.bc2);
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
+  const long long n4 = n >> 2;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4;
        i += (long long)gridDim.x * blockDim.x) {
-    float g = to_f32<G>(grad[i]) * gs;
+    float g[4];
+    ldg4<G>(grad + i * 4, g);
+    float4 p4 = reinterpret_cast<float4*>(master)[i];
+    float4 m4 = reinterpret_cast<float4*>(m)[i];
+    float4 v4 = reinterpret_cast<float4*>(v)[i];
+    float p[4] = {p4.x, p4.y, p4.z, p4.w}, mm[4] = {m4.x, m4.y, m4.z, m4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) agd_update(p[j], mm[j], vv[j], g[j] * gs, a, step_size, dfloor);
+    reinterpret_cast<float4*>(master)[i] = make_float4(p[0], p[1], p[2], p[3]);
+    reinterpret_cast<float4*>(m)[i] = make_float4(mm[0], mm[1], mm[2], mm[3]);
+    reinterpret_cast<float4*>(v)[i] = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    if (param_bf16) {
+      uint2 o;
+      o.x = pack_bf16x2(p[0], p[1]);
+      o.y = pack_bf16x2(p[2], p[3]);
+      reinterpret_cast<uint2*>(param_bf16)[i] = o;
+    }
+  }
+  if (blockIdx.x == 0 && threadIdx.x < (n & 3)) {   // tail (n not a multiple of 4)
+    const long long i = (n4 << 2) + threadIdx.x;
     float p = master[i], mm = m[i], vv = v[i];
-    if (a.decouple) p *= a.fixed_decay ? (1.f - a.weight_decay) : (1.f - a.lr * a.weight_decay);
-    else g += a.weight_decay * p;
-    const float m_old = mm;
-    mm = a.beta1 * mm + (1.f - a.beta1) * g;
-    const float s = a.first_step ? mm / a.bc1 : (mm / a.bc1 - m_old / a.bc1_old);
-    vv = a.beta2 * vv + (1.f - a.beta2) * s * s;
-    const float den = fmaxf(sqrtf(vv), dfloor);
-    float u = mm / den;
-    if (a.clip > 0.f) u = fminf(fmaxf(u, -a.clip), a.clip);
-    p -= step_size * u;
+    agd_update(p, mm, vv, to_f32<G>(grad[i]) * gs, a, step_size, dfloor);
     master[i] = p; m[i] = mm; v[i] = vv;
     if (param_bf16) param_bf16[i] = __float2bfloat16_rn(p);
   }
@@ -138,12 +162,35 @@ __global__ void sumsq_kernel(const G* __restrict__ x, long long n, float* __rest
 __global__ void outer_sgd_kernel(float* __restrict__ synced, float* __restrict__ buf, const float* __restrict__ pg,
                                  float* __restrict__ param_f32, __nv_bfloat16* __restrict__ param_bf16, long long n,
                                  float lr, float mu, int nesterov, int first, float scale) {
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+  const long long n4 = n >> 2;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float4 g4 = reinterpret_cast<const float4*>(pg)[i];
+    const float4 s4 = reinterpret_cast<const float4*>(synced)[i];
+    float4 b4 = first ? make_float4(0.f, 0.f, 0.f, 0.f) : reinterpret_cast<const float4*>(buf)[i];
+    float g[4] = {g4.x * scale, g4.y * scale, g4.z * scale, g4.w * scale};
+    float b[4] = {b4.x, b4.y, b4.z, b4.w}, p[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      b[j] = first ? g[j] : mu * b[j] + g[j];
+      p[j] -= lr * (nesterov ? (g[j] + mu * b[j]) : b[j]);
+    }
+    reinterpret_cast<float4*>(buf)[i] = make_float4(b[0], b[1], b[2], b[3]);
+    reinterpret_cast<float4*>(synced)[i] = make_float4(p[0], p[1], p[2], p[3]);
+    if (param_f32) reinterpret_cast<float4*>(param_f32)[i] = make_float4(p[0], p[1], p[2], p[3]);
+    if (param_bf16) {
+      uint2 o;
+      o.x = pack_bf16x2(p[0], p[1]);
+      o.y = pack_bf16x2(p[2], p[3]);
+      reinterpret_cast<uint2*>(param_bf16)[i] = o;
+    }
+  }
+  if (blockIdx.x == 0 && threadIdx.x < (n & 3)) {
+    const long long i = (n4 << 2) + threadIdx.x;
     const float g = pg[i] * scale;
-    float b = first ? g : mu * buf[i] + g;
+    const float b = first ? g : mu * buf[i] + g;
     buf[i] = b;
-    const float upd = nesterov ? (g + mu * b) : b;
-    const float p = synced[i] - lr * upd;
+    const float p = synced[i] - lr * (nesterov ? (g + mu * b) : b);
     synced[i] = p;
     if (param_f32) param_f32[i] = p;
     if (param_bf16) param_bf16[i] = __float2bfloat16_rn(p);
@@ -181,10 +228,14 @@ extern "C" int atb_agd(float* master, float* m, float* v, const void* grad, void
                        const float* grad_scale_ptr, float clip, int decouple, int fixed_decay, int grad_dtype,
                        void* stream) {
   if (n <= 0) return 0;
+  // 16-byte vectors on the fp32 buffers, 8-byte on bf16 ones
+  if ((((uintptr_t)master | (uintptr_t)m | (uintptr_t)v) & 15) || ((uintptr_t)param_bf16 & 7) ||
+      ((uintptr_t)grad & (grad_dtype == 0 ? 7 : 15)))
+    return -3;
   AgdArgs a{lr, beta1, beta2, delta, weight_decay, 1.f - powf(beta1, (float)step),
             step > 1 ? 1.f - powf(beta1, (float)(step - 1)) : 1.f, 1.f - powf(beta2, (float)step), grad_scale, clip,
             step == 1, decouple, fixed_decay};
-  const int grid = grid_for(n, 256);
+  const int grid = grid_for((n + 3) / 4, 256);
   cudaStream_t st = (cudaStream_t)stream;
   if (grad_dtype == 0)
     agd_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(master, m, v, (const __nv_bfloat16*)grad,
@@ -209,7 +260,10 @@ extern "C" int atb_outer_sgd(float* synced, float* buf, const float* pseudo_grad
                              long long n, float lr, float momentum, int nesterov, int first_step, float scale,
                              void* stream) {
   if (n <= 0) return 0;
-  outer_sgd_kernel<<<grid_for(n, 256), 256, 0, (cudaStream_t)stream>>>(
+  if ((((uintptr_t)synced | (uintptr_t)buf | (uintptr_t)pseudo_grad | (uintptr_t)param_f32) & 15) ||
+      ((uintptr_t)param_bf16 & 7))
+    return -3;
+  outer_sgd_kernel<<<grid_for((n + 3) / 4, 256), 256, 0, (cudaStream_t)stream>>>(
       synced, buf, pseudo_grad, param_f32, (__nv_bfloat16*)param_bf16, n, lr, momentum, nesterov, first_step, scale);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
