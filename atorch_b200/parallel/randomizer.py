@@ -9,6 +9,7 @@ out, like Megatron's RNG tracker.
 from __future__ import annotations
 
 import contextlib
+import zlib
 from typing import Dict, Tuple
 
 import torch
@@ -38,7 +39,8 @@ class MultiDimParallelRandomizer:
                     stride *= size
         elif not self.same_groups:
             offset = D.rank() or 0
-        self.seed = seed + 2718 * (hash(self.same_groups) % 1000) + offset
+        # crc32, not hash(): Python salts string hashes per process, and ranks must agree on the seed
+        self.seed = seed + 2718 * (zlib.crc32(",".join(self.same_groups).encode()) % 1000) + offset
         self.cpu_state = torch.Generator().manual_seed(self.seed).get_state()
         self.cuda_state = None
 
