@@ -18,6 +18,7 @@
 // Masks: per-row key interval [lo, hi) exactly as in flash_attn.cu; each query tile walks only the K/V
 // tiles up to the last one that any of its rows can see.
 #include "common.cuh"
+#include <type_traits>
 
 namespace {
 using namespace atb;
@@ -158,8 +159,8 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const int t0 = kv_range[0];
-  const int nt[2] = {kv_range[1] - t0, kv_range[2] - t0};
-  const int n = max(nt[0], nt[1]);
+  const int n_a = kv_range[1] - t0, n_b = kv_range[2] - t0;   // K/V tiles of query tile A / B
+  const int n = max(n_a, n_b);
   const long long q_row0 = (long long)b * p.Sq + q0;
   const long long k_row0 = (long long)b * p.Sk;
 
@@ -213,32 +214,36 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         return true;
       };
       bool ok = mbar_wait(q_full, 0, abort_flag, p.status);
-      for (int t = 0; t < 2 && ok; ++t)
-        if (nt[t] > 0) ok = issue_s(t, 0);
+      if (ok && n_a > 0) ok = issue_s(0, 0);
+      if (ok && n_b > 0) ok = issue_s(1, 0);
       if (ok) umma_commit(&k_empty[0]);
-      for (int j = 0; ok && j < n; ++j) {
+      // one half-step of the ping-pong for query tile T (compile-time, so that nothing is indexed at run time):
+      // P_T(j) V_j into O_T, then the next scores S_T(j+1)
+      auto half_step = [&](auto tile, int j) -> bool {
+        constexpr int t = decltype(tile)::value;
+        const int n_t = t ? n_b : n_a;
         const int s = j & 1;
-#pragma unroll 1
-        for (int t = 0; t < 2 && ok; ++t) {
-          if (j < nt[t]) {
-            if (!mbar_wait(&p_full[t], j & 1, abort_flag, p.status)) { ok = false; break; }
-            if (v_ready < j) {
-              if (!mbar_wait(&v_full[s], (j >> 1) & 1, abort_flag, p.status)) { ok = false; break; }
-              v_ready = j;
-            }
-            tc_fence_after();
-            const uint64_t vd = umma_desc_advance(v_desc0, s ? TILE : 0);
-#pragma unroll
-            for (int k = 0; k < BKV / 16; ++k)   // A = P_T: 16 bf16 keys per step = 8 TMEM columns
-              umma_f16_ts(tmem_base + 2 * BKV + t * HD, tmem_base + t * BKV + k * 8,
-                          umma_desc_advance(vd, k * 2048), idesc_o, (j | k) != 0);
-            if (j == nt[t] - 1) umma_commit(&o_full[t]);
+        if (j < n_t) {
+          if (!mbar_wait(&p_full[t], j & 1, abort_flag, p.status)) return false;
+          if (v_ready < j) {
+            if (!mbar_wait(&v_full[s], (j >> 1) & 1, abort_flag, p.status)) return false;
+            v_ready = j;
           }
-          if (t == 1) umma_commit(&v_empty[s]);
-          if (j + 1 < nt[t]) ok = issue_s(t, j + 1);
-          if (t == 1 && j + 1 < n) umma_commit(&k_empty[(j + 1) & 1]);
+          tc_fence_after();
+          const uint64_t vd = umma_desc_advance(v_desc0, s ? TILE : 0);
+#pragma unroll
+          for (int k = 0; k < BKV / 16; ++k)   // A = P_T: 16 bf16 keys per step = 8 TMEM columns
+            umma_f16_ts(tmem_base + 2 * BKV + t * HD, tmem_base + t * BKV + k * 8, umma_desc_advance(vd, k * 2048),
+                        idesc_o, (j | k) != 0);
+          if (j == n_t - 1) umma_commit(&o_full[t]);
         }
-      }
+        if (t == 1) umma_commit(&v_empty[s]);
+        if (j + 1 < n_t && !issue_s(t, j + 1)) return false;
+        if (t == 1 && j + 1 < n) umma_commit(&k_empty[(j + 1) & 1]);
+        return true;
+      };
+      for (int j = 0; ok && j < n; ++j)
+        ok = half_step(std::integral_constant<int, 0>{}, j) && half_step(std::integral_constant<int, 1>{}, j);
     }
   } else {
     const int t = (warp - 2) >> 2;            // query tile of this warp
@@ -246,7 +251,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const int r = quarter * 32 + lane;        // row inside the tile
     const int i = q0 + t * BQ + r;            // global query row
     const bool row_valid = i < p.Sq;
-    const int n_t = nt[t];
+    const int n_t = t ? n_b : n_a;
     int lo = 0, hi = 0;
     if (row_valid) {
       lo = p.row_lo ? p.row_lo[(long long)b * p.Sq + i] : 0;
