@@ -1,6 +1,7 @@
 """Micro-benchmark of the sm_100a flash attention (forward, backward) against torch SDPA (cuDNN) and
 flash_attn 2.8 (the kernel behind the reference's FlashAttnModule), when that package is importable.
-The forward is timed for both kernels of this package: one query tile per CTA and two tiles per CTA.
+The forward is timed for both kernels of this package (one query tile per CTA, two tiles per CTA), the
+backward for both forms (key-block kernel + query-block kernel, or one key-block kernel with reduce-adds).
 
     python -m atorch_b200.benchmarks.attn_bench [--iters 10]
 """
@@ -82,9 +83,15 @@ def main(argv=None):
 
             def lib_b():
                 return torch.autograd.grad(o2, (q, k, v), d2, retain_graph=True)
-            tb_o, tb_l = time_fn(ours_b, args.iters, flush), time_fn(lib_b, args.iters, flush)
+            flash.BWD_SPLIT = True
+            tb_o = time_fn(ours_b, args.iters, flush)
+            flash.BWD_SPLIT = False
+            tb_o1 = time_fn(ours_b, args.iters, flush)
+            flash.BWD_SPLIT = True
+            tb_l = time_fn(lib_b, args.iters, flush)
             _lib.check_status(dev)
             line += (f" || bwd: ours {tb_o:8.1f} us {2.5 * flops_f / tb_o / 1e6:7.1f} TF | "
+                     f"ours(one kernel) {tb_o1:8.1f} us {2.5 * flops_f / tb_o1 / 1e6:7.1f} TF | "
                      f"SDPA {tb_l:8.1f} us {2.5 * flops_f / tb_l / 1e6:7.1f} TF")
             if fa is not None:
                 o3 = fa(q, k, v, causal=causal)

@@ -69,6 +69,9 @@ struct RowInfo {
   float lse2, delta;
 };
 
+// WITH_DQ = false: key/value gradients only (the query gradient then comes from flash_attn_bwd_dq.cu): the
+// dQ product, its staging and the reduce-add are compiled out and dP(i+1) follows dK(i) without a hand-shake.
+template <bool WITH_DQ>
 __global__ void __launch_bounds__(THREADS, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                  const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -243,15 +246,19 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int k = 0; k < 8; ++k)  // dK += dS^T Q over q
           umma_f16<1>(tdK, umma_desc_advance(dSm, k * 2048), umma_desc_advance(qm, k * 2048), id_mm, (it | k) != 0);
         umma_commit(&q_free[it & 1]);
+        if constexpr (WITH_DQ) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {  // dQ = dS K over keys (into the dP columns)
-          const uint32_t off = (k >> 2) * PANEL + (k & 3) * 32;
-          umma_f16<1>(tdP, umma_desc_advance(dSk, off), umma_desc_advance(dKm, k * 2048), id_km, k != 0);
+          for (int k = 0; k < 8; ++k) {  // dQ = dS K over keys (into the dP columns)
+            const uint32_t off = (k >> 2) * PANEL + (k & 3) * 32;
+            umma_f16<1>(tdP, umma_desc_advance(dSk, off), umma_desc_advance(dKm, k * 2048), id_km, k != 0);
+          }
         }
         umma_commit(dq_full);
         if (it + 1 < nblk) {
-          if (!mbar_wait(dp_free, it & 1, abort_flag, p.status)) break;
-          tc_fence_after();
+          if constexpr (WITH_DQ) {
+            if (!mbar_wait(dp_free, it & 1, abort_flag, p.status)) break;
+            tc_fence_after();
+          }
           if (!issue_dp(it + 1)) break;
         }
       }
@@ -292,6 +299,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const bool reducer = threadIdx.x == 64;     // first element-wise thread issues the TMA operations
     auto drain_dq = [&](int it) -> bool {
       if (!__all_sync(0xffffffffu, mbar_wait(dq_full, it & 1, abort_flag, p.status))) return false;
+      if constexpr (!WITH_DQ) return true;   // the products that read P and dS have completed: nothing to move
       tc_fence_after();
       uint32_t t0[32], t1[32];
       tmem_ld_32x32(tdP, t0);
@@ -361,7 +369,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       // ---- dS(it) = P (dP - delta) scale; P and dS to shared memory (free: dq_full(it-1) has been waited for)
       if (!__all_sync(0xffffffffu, mbar_wait(dp_full, it & 1, abort_flag, p.status))) { ok = false; break; }
       // P and dS share their memory with the staged dQ(it-1): wait until the TMA unit has read it
-      if (it > 0 && !__all_sync(0xffffffffu, mbar_wait(stage_free, (it - 1) & 1, abort_flag, p.status))) {
+      if (WITH_DQ && it > 0 &&
+          !__all_sync(0xffffffffu, mbar_wait(stage_free, (it - 1) & 1, abort_flag, p.status))) {
         ok = false;
         break;
       }
@@ -400,7 +409,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       cur = nxt;
     }
     if (ok && nblk > 0) ok = drain_dq(nblk - 1);
-    if (reducer) tma_store_wait<0>();
+    if (WITH_DQ && reducer) tma_store_wait<0>();
     // dV / dK of this key block: TMEM lane = key row. tcgen05.ld is a warp-wide (.sync.aligned)
     // instruction: every lane executes it, only the global stores are predicated per row.
     const int j = kv0 + r;
@@ -489,6 +498,16 @@ __global__ void f32_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16*
 
 }  // namespace
 
+extern "C" int atb_flash_bwd_dq(const void* dout, const void* q, const void* k, const void* v, const float* lse,
+                                const float* delta, void* dq, const int* row_lo, const int* row_hi, int B, int Sq,
+                                int Sk, int Hq, int Hkv, long long q_stride, long long k_stride, long long v_stride,
+                                long long do_stride, long long dq_stride, int causal, float softmax_scale,
+                                void* stream, int* status);
+
+// Two forms. dq_acc == nullptr (default of the Python wrapper): the key-block kernel writes dK and dV, the
+// query-block kernel of flash_attn_bwd_dq.cu writes dQ; no atomics, results do not depend on scheduling.
+// dq_acc != nullptr: one key-block kernel for all three; dQ goes through TMA reduce-adds into dq_acc
+// (fp32 [B, Sq, Hq, 128], zero on entry) and a conversion pass.
 // dq_acc must be zero on entry; dq/dk/dv are written as token-major rows of pitch dq_stride / dkv_stride
 // elements (so they may be slices of one fused [tokens, (Hq + 2 Hq) * 128] gradient buffer). dk, dv are per
 // query head; the caller sums head groups for grouped-query attention. `delta` is scratch [B, Hq, Sq].
@@ -516,13 +535,18 @@ extern "C" int atb_flash_bwd(const void* dout, const void* q, const void* k, con
                     64, CU_TENSOR_MAP_SWIZZLE_128B))
     return -2;
   // fp32 accumulation buffer as [B*Sq, Hq*HD]; the kernel adds [128 x 32] boxes to it
-  if (!make_tmap_2d(&tmdQ, dq_acc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)B * Sq, (uint64_t)Hq * HD,
-                    (uint64_t)Hq * HD, BQ, 32, CU_TENSOR_MAP_SWIZZLE_128B))
+  if (dq_acc == nullptr) {
+    tmdQ = tmQ;   // unused by the kernel variant without dQ
+  } else if (!make_tmap_2d(&tmdQ, dq_acc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)B * Sq, (uint64_t)Hq * HD,
+                           (uint64_t)Hq * HD, BQ, 32, CU_TENSOR_MAP_SWIZZLE_128B)) {
     return -2;
+  }
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(flash_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemB::TOTAL) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(flash_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemB::TOTAL) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(flash_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemB::TOTAL) !=
+            cudaSuccess)
       return -4;
     attr_set = true;
   }
@@ -541,7 +565,13 @@ extern "C" int atb_flash_bwd(const void* dout, const void* q, const void* k, con
   p.scale = softmax_scale; p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = status;
   dim3 grid((Sk + BKV - 1) / BKV, Hq, B);
-  flash_bwd_kernel<<<grid, THREADS, SmemB::TOTAL, st>>>(tmQ, tmdO, tmK, tmV, tmdQ, p);
+  if (dq_acc == nullptr) {
+    flash_bwd_kernel<false><<<grid, THREADS, SmemB::TOTAL, st>>>(tmQ, tmdO, tmK, tmV, tmdQ, p);
+    if (cudaGetLastError() != cudaSuccess) return -5;
+    return atb_flash_bwd_dq(dout, q, k, v, lse, delta, dq, row_lo, row_hi, B, Sq, Sk, Hq, Hkv, q_stride, k_stride,
+                            v_stride, do_stride, dq_stride, causal, softmax_scale, stream, status);
+  }
+  flash_bwd_kernel<true><<<grid, THREADS, SmemB::TOTAL, st>>>(tmQ, tmdO, tmK, tmV, tmdQ, p);
   const long long n4 = (long long)B * Sq * Hq * HD / 4;
   long long g = (n4 + 255) / 256;
   if (g > 148 * 16) g = 148 * 16;

@@ -31,6 +31,7 @@ import os
 # default from 256 query rows on (measured 201 us against 256 us for the single-tile kernel at S=4096, H=32,
 # causal); ATB_FLASH_V2=0 keeps the single-tile kernel everywhere
 FWD_TWO_TILES = os.environ.get("ATB_FLASH_V2", "1") == "1"
+BWD_SPLIT = os.environ.get("ATB_FLASH_BWD_SPLIT", "0") == "1"
 
 
 def kernels_built() -> bool:
@@ -132,7 +133,9 @@ def flash_bwd_raw(dout, q, k, v, out, lse, causal, softmax_scale, row_lo, row_hi
     like a fused q|k|v projection output, so the gradient of that projection needs no concatenation."""
     B, Sq, Hq, D = q.shape
     Sk, Hkv = k.shape[1], k.shape[2]
-    dq_acc = torch.zeros(B, Sq, Hq, D, dtype=torch.float32, device=q.device)
+    # two kernels (dK/dV per key block, dQ per query block: no atomics, no fp32 scratch) unless
+    # ATB_FLASH_BWD_SPLIT=0 asks for the single key-block kernel with TMA reduce-adds of dQ
+    dq_acc = None if BWD_SPLIT else torch.zeros(B, Sq, Hq, D, dtype=torch.float32, device=q.device)
     delta = torch.empty(B, Hq, Sq, dtype=torch.float32, device=q.device)
     if fused_out and Hkv == Hq and Sq == Sk:
         fused = torch.empty(B, Sq, 3 * Hq, D, dtype=q.dtype, device=q.device)
