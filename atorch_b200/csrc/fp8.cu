@@ -37,61 +37,101 @@ ATB_DEVICE float from_e4m3(uint8_t b) {
   return __half2float(*reinterpret_cast<__half*>(&h));
 }
 
+// Two e4m3 bytes from two floats in one conversion instruction (low byte = first value).
+ATB_DEVICE uint32_t to_e4m3x2(float a, float b) {
+  return (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+}
+ATB_DEVICE uint32_t to_e4m3x4(float a, float b, float c, float d) { return to_e4m3x2(a, b) | (to_e4m3x2(c, d) << 16); }
+
 // ---------------------------------------------------------------------------------------------
-// 1 x 128 tile quantisation, row-major in, row-major out. One warp per (row, tile); K % 128 == 0.
+// 1 x 128 tile quantisation, row-major in, row-major out; K % 128 == 0. A half-warp owns a tile: every
+// lane loads 16 bytes (8 values) and stores 8; a warp iteration covers four tiles (two per half-warp, both
+// loads issued before the first reduction) so that enough bytes are in flight per SM.
 // ---------------------------------------------------------------------------------------------
 __global__ void tile_quant_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
                                   float* __restrict__ scales, long long M, int K, long long ldx, int pow2) {
   const int tiles = K >> 7;
   const long long total = M * tiles;
-  const int lane = threadIdx.x & 31;
-  for (long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5; w < total;
-       w += ((long long)gridDim.x * blockDim.x) >> 5) {
-    const long long row = w / tiles;
-    const int t = (int)(w - row * tiles);
-    const uint2 u = *reinterpret_cast<const uint2*>(x + row * ldx + t * 128 + lane * 4);
-    const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y);
-    float amax = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y)));
-    amax = warp_max(amax);
-    const float s = make_scale(amax, pow2);
-    const float inv = 1.f / s;
-    uint32_t o = to_e4m3(a.x * inv) | (to_e4m3(a.y * inv) << 8) | (to_e4m3(b.x * inv) << 16) |
-                 ((uint32_t)to_e4m3(b.y * inv) << 24);
-    *reinterpret_cast<uint32_t*>(q + row * K + t * 128 + lane * 4) = o;
-    if (lane == 0) scales[row * tiles + t] = s;
+  const int lane = threadIdx.x & 31, sub = lane & 15, hw = lane >> 4;
+  const long long warp0 = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long w = warp0 * 4; w < total; w += nwarps * 4) {
+    uint4 u[2];
+    long long tix[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      tix[e] = w + e * 2 + hw;
+      u[e] = make_uint4(0u, 0u, 0u, 0u);
+      if (tix[e] < total) {
+        const long long row = tix[e] / tiles;
+        const int t = (int)(tix[e] - row * tiles);
+        u[e] = *reinterpret_cast<const uint4*>(x + row * ldx + t * 128 + sub * 8);
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const float2 a = unpack_bf16x2(u[e].x), b = unpack_bf16x2(u[e].y), c = unpack_bf16x2(u[e].z), d = unpack_bf16x2(u[e].w);
+      float amax = fmaxf(fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y))),
+                         fmaxf(fmaxf(fabsf(c.x), fabsf(c.y)), fmaxf(fabsf(d.x), fabsf(d.y))));
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));   // within the half-warp
+      if (tix[e] < total) {
+        const long long row = tix[e] / tiles;
+        const int t = (int)(tix[e] - row * tiles);
+        const float s = make_scale(amax, pow2);
+        const float inv = 1.f / s;
+        uint2 o;
+        o.x = to_e4m3x4(a.x * inv, a.y * inv, b.x * inv, b.y * inv);
+        o.y = to_e4m3x4(c.x * inv, c.y * inv, d.x * inv, d.y * inv);
+        *reinterpret_cast<uint2*>(q + row * K + t * 128 + sub * 8) = o;
+        if (sub == 0) scales[row * tiles + t] = s;
+      }
+    }
   }
 }
 
 // Transposed form: x [M, K] -> q_t [K, M] quantised in strips of 128 along M; scales_t [K, M/128].
-// One CTA per [128 (M) x 64 (K)] tile; M % 128 == 0, K % 64 == 0.
+// One CTA per [128 (M) x 64 (K)] tile; M % 128 == 0, K % 64 == 0. Four threads per output row; thread `part`
+// writes bytes [16 part, 16 part + 16) and [64 + 16 part, ...) of the row's 128, so that the four stores of a
+// row are one contiguous 64-byte piece each.
 __global__ void __launch_bounds__(256)
 tile_quant_t_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ qt, float* __restrict__ scales_t,
                     long long M, int K, long long ldx, int pow2) {
   __shared__ float tile[64][129];
   const long long m0 = (long long)blockIdx.y * 128;
   const int k0 = blockIdx.x * 64;
-  for (int i = threadIdx.x; i < 128 * 32; i += 256) {  // 128 rows x 32 bf16 pairs
-    const int r = i >> 5, c2 = i & 31;
-    const float2 v = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(x + (m0 + r) * ldx + k0 + c2 * 2));
-    tile[c2 * 2][r] = v.x;
-    tile[c2 * 2 + 1][r] = v.y;
+  for (int i = threadIdx.x; i < 128 * 8; i += 256) {  // 128 rows x 8 chunks of 8 bf16 (16 bytes)
+    const int r = i >> 3, c8 = i & 7;
+    const uint4 u = *reinterpret_cast<const uint4*>(x + (m0 + r) * ldx + k0 + c8 * 8);
+    const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+    float* col = &tile[c8 * 8][r];
+    col[0] = a.x; col[129] = a.y; col[2 * 129] = b.x; col[3 * 129] = b.y;
+    col[4 * 129] = c.x; col[5 * 129] = c.y; col[6 * 129] = d.x; col[7 * 129] = d.y;
   }
   __syncthreads();
-  const int k = threadIdx.x >> 2, part = threadIdx.x & 3;  // 4 threads per output row, 32 values each
+  const int k = threadIdx.x >> 2, part = threadIdx.x & 3;
+  float v[32];
   float amax = 0.f;
 #pragma unroll
-  for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(tile[k][part * 32 + j]));
+  for (int j = 0; j < 16; ++j) {
+    v[j] = tile[k][part * 16 + j];
+    v[16 + j] = tile[k][64 + part * 16 + j];
+    amax = fmaxf(amax, fmaxf(fabsf(v[j]), fabsf(v[16 + j])));
+  }
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
   const float s = make_scale(amax, pow2);
   const float inv = 1.f / s;
-  uint8_t* dst = qt + (long long)(k0 + k) * M + m0 + part * 32;
+  uint8_t* dst = qt + (long long)(k0 + k) * M + m0;
 #pragma unroll
-  for (int j = 0; j < 32; j += 4) {
-    const uint32_t o = to_e4m3(tile[k][part * 32 + j] * inv) | (to_e4m3(tile[k][part * 32 + j + 1] * inv) << 8) |
-                       (to_e4m3(tile[k][part * 32 + j + 2] * inv) << 16) |
-                       ((uint32_t)to_e4m3(tile[k][part * 32 + j + 3] * inv) << 24);
-    *reinterpret_cast<uint32_t*>(dst + j) = o;
+  for (int hlf = 0; hlf < 2; ++hlf) {
+    const float* w = v + hlf * 16;
+    uint4 o;
+    o.x = to_e4m3x4(w[0] * inv, w[1] * inv, w[2] * inv, w[3] * inv);
+    o.y = to_e4m3x4(w[4] * inv, w[5] * inv, w[6] * inv, w[7] * inv);
+    o.z = to_e4m3x4(w[8] * inv, w[9] * inv, w[10] * inv, w[11] * inv);
+    o.w = to_e4m3x4(w[12] * inv, w[13] * inv, w[14] * inv, w[15] * inv);
+    *reinterpret_cast<uint4*>(dst + hlf * 64 + part * 16) = o;
   }
   if (part == 0) scales_t[(long long)(k0 + k) * (M >> 7) + blockIdx.y] = s;
 }
@@ -333,15 +373,15 @@ inline int grid_cap(long long work, int threads, int cap_mult) {
 extern "C" int atb_fp8_tile_quant(const void* x, void* q, float* scales, long long M, int K, long long ldx, int pow2,
                                   void* stream) {
   if (M <= 0) return 0;
-  if ((K & 127) || (ldx & 3)) return -1;
-  tile_quant_kernel<<<grid_cap(M * (K >> 7) * 32, 256, 16), 256, 0, (cudaStream_t)stream>>>(
+  if ((K & 127) || (ldx & 7) || ((uintptr_t)x & 15) || ((uintptr_t)q & 7)) return -1;   // 16-byte loads, 8-byte stores
+  tile_quant_kernel<<<grid_cap(M * (K >> 7) * 8, 256, 16), 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)x, (uint8_t*)q, scales, M, K, ldx, pow2);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 extern "C" int atb_fp8_tile_quant_t(const void* x, void* qt, float* scales_t, long long M, int K, long long ldx,
                                     int pow2, void* stream) {
   if (M <= 0) return 0;
-  if ((M & 127) || (K & 63) || (ldx & 1)) return -1;
+  if ((M & 127) || (K & 63) || (ldx & 7) || ((uintptr_t)x & 15) || ((uintptr_t)qt & 15)) return -1;
   dim3 grid(K / 64, (unsigned)(M / 128));
   tile_quant_t_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, (uint8_t*)qt, scales_t, M, K,
                                                              ldx, pow2);
