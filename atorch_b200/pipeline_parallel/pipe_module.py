@@ -99,10 +99,14 @@ class PipeModule(nn.Module):
 def make_pipe_module(meta_model=None, model_provider=None, loss_func=None, strategy=None, distributed_context=None,
                      config: Optional[PipeModuleConfig] = None) -> PipeModule:
     assert config is not None, "config is required"
-    if model_provider is None:
-        raise NotImplementedError("partitioning from a meta model needs a model_provider")
     ctx = distributed_context or D
-    modules, stage_ids, tie = partition_model_from_model_provider(model_provider, ctx, config)
+    if model_provider is not None:
+        modules, stage_ids, tie = partition_model_from_model_provider(model_provider, ctx, config)
+    else:
+        assert meta_model is not None, "give a model_provider or a (meta) model"
+        from .pipe_partition import partition_model_from_meta_model
+
+        modules, stage_ids, tie = partition_model_from_meta_model(meta_model, ctx, config)
     total = (ctx.parallel_group_size("pipe") or 1) * (config.virtual_pp_size or 1)
     return PipeModule(modules, stage_ids, total, config.input_output_mapping, loss_func, tie, strategy,
                       config.auto_ddp)

@@ -111,3 +111,56 @@ def test_schedules_match_single_process(tmp_path):
             for (sid, i), g in d["grads"].items():
                 assert torch.allclose(g, ref_grads[sid * per + i], atol=1e-5), (sche, sid, i)
         assert seen_loss
+
+
+class _Chain(nn.Module):
+    """embed -> 4 layers -> norm -> head, the shape `partition_model_from_meta_model` understands."""
+
+    def __init__(self):
+        super().__init__()
+        self.embed = nn.Linear(8, 8)
+        self.layers = nn.ModuleList([nn.Linear(8, 8) for _ in range(4)])
+        self.norm = nn.LayerNorm(8)
+        self.head = nn.Linear(8, 8)
+
+    def forward(self, x):
+        x = self.embed(x)
+        for l in self.layers:
+            x = l(x)
+        return self.head(self.norm(x))
+
+
+def _run_meta_pipe(rank, world, out_file):
+    from atorch_b200.distributed import distributed as D
+    from atorch_b200.pipeline_parallel.pipe_module import PipeModuleConfig, make_pipe_module
+    from atorch_b200.pipeline_parallel.pipe_schedule import make_pipe_schedule_from_pipe_module
+
+    D.create_parallel_group(([("pipe", world)], None))
+    with torch.device("meta"):
+        meta = _Chain()
+    cfg = PipeModuleConfig(total_layer_num=4, sche_name="Schedule1F1B", n_microbatches=2, auto_ddp=False)
+    pm = make_pipe_module(meta_model=meta, loss_func=lambda o, t: ((o - t) ** 2).mean(), config=cfg)
+    st = pm.stage_modules[0]
+    assert not any(p.is_meta for p in st.parameters())
+    if rank == 0:
+        assert len(st.pre) == 1 and len(st.layers) == 2 and len(st.post) == 0
+    else:
+        assert len(st.pre) == 0 and len(st.layers) == 2 and len(st.post) == 2
+    # load known weights so that the result can be compared with the unpartitioned model
+    torch.manual_seed(5)
+    full = _Chain()
+    mine = {0: [full.embed, full.layers[0], full.layers[1]], 1: [full.layers[2], full.layers[3], full.norm, full.head]}[rank]
+    for dst, src in zip(list(st.pre) + list(st.layers) + list(st.post), mine):
+        dst.load_state_dict(src.state_dict())
+    g = torch.Generator().manual_seed(3)
+    x, y = torch.randn(4, 8, generator=g), torch.randn(4, 8, generator=g)
+    sched = make_pipe_schedule_from_pipe_module(pm, cfg)
+    loss = sched.step(x) if rank == 0 else sched.step(target=y)
+    if rank == 1:
+        ref = sum(((full(xm) - ym) ** 2).mean() for xm, ym in zip(x.chunk(2), y.chunk(2))) / 2
+        assert abs(loss.item() - ref.item()) < 1e-5, (loss.item(), ref.item())
+    torch.save(True, f"{out_file}.{rank}")
+
+
+def test_pipe_module_from_meta_model(tmp_path):
+    run_distributed(_run_meta_pipe, world=2, args=(str(tmp_path / "m"),))
