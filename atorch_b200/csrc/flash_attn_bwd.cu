@@ -504,6 +504,17 @@ extern "C" int atb_flash_bwd_dq(const void* dout, const void* q, const void* k, 
                                 long long do_stride, long long dq_stride, int causal, float softmax_scale,
                                 void* stream, int* status);
 
+extern "C" int atb_flash_bwd_dkv(const void* dout, const void* q, const void* k, const void* v, const float* lse,
+                                 const float* delta, void* dk, void* dv, const int* row_lo, const int* row_hi, int B,
+                                 int Sq, int Sk, int Hq, int Hkv, long long q_stride, long long k_stride,
+                                 long long v_stride, long long do_stride, long long dkv_stride, int causal,
+                                 float softmax_scale, void* stream, int* status);
+
+// Which key-block kernel the two-kernel form uses: 1 = flash_attn_bwd_dkv.cu (transposed products, P and dS kept
+// in tensor memory; default), 0 = this file's kernel without its dQ part (P and dS through shared memory).
+static int g_dkv_transposed = 1;
+extern "C" void atb_flash_bwd_set_dkv(int transposed) { g_dkv_transposed = transposed; }
+
 // Two forms. dq_acc == nullptr (default of the Python wrapper): the key-block kernel writes dK and dV, the
 // query-block kernel of flash_attn_bwd_dq.cu writes dQ; no atomics, results do not depend on scheduling.
 // dq_acc != nullptr: one key-block kernel for all three; dQ goes through TMA reduce-adds into dq_acc
@@ -566,8 +577,14 @@ extern "C" int atb_flash_bwd(const void* dout, const void* q, const void* k, con
   p.status = status;
   dim3 grid((Sk + BKV - 1) / BKV, Hq, B);
   if (dq_acc == nullptr) {
-    flash_bwd_kernel<false><<<grid, THREADS, SmemB::TOTAL, st>>>(tmQ, tmdO, tmK, tmV, tmdQ, p);
-    if (cudaGetLastError() != cudaSuccess) return -5;
+    if (g_dkv_transposed) {
+      const int rc = atb_flash_bwd_dkv(dout, q, k, v, lse, delta, dk, dv, row_lo, row_hi, B, Sq, Sk, Hq, Hkv, q_stride,
+                                       k_stride, v_stride, do_stride, dkv_stride, causal, softmax_scale, stream, status);
+      if (rc != 0) return rc;
+    } else {
+      flash_bwd_kernel<false><<<grid, THREADS, SmemB::TOTAL, st>>>(tmQ, tmdO, tmK, tmV, tmdQ, p);
+      if (cudaGetLastError() != cudaSuccess) return -5;
+    }
     return atb_flash_bwd_dq(dout, q, k, v, lse, delta, dq, row_lo, row_hi, B, Sq, Sk, Hq, Hkv, q_stride, k_stride,
                             v_stride, do_stride, dq_stride, causal, softmax_scale, stream, status);
   }

@@ -32,6 +32,7 @@ import os
 # causal); ATB_FLASH_V2=0 keeps the single-tile kernel everywhere
 FWD_TWO_TILES = os.environ.get("ATB_FLASH_V2", "1") == "1"
 BWD_SPLIT = os.environ.get("ATB_FLASH_BWD_SPLIT", "0") == "1"
+_DKV_SET = False   # ATB_FLASH_BWD_DKV=0 picks the shared-memory key-block kernel of the two-kernel backward
 
 
 def kernels_built() -> bool:
@@ -133,6 +134,11 @@ def flash_bwd_raw(dout, q, k, v, out, lse, causal, softmax_scale, row_lo, row_hi
     like a fused q|k|v projection output, so the gradient of that projection needs no concatenation."""
     B, Sq, Hq, D = q.shape
     Sk, Hkv = k.shape[1], k.shape[2]
+    global _DKV_SET
+    if not _DKV_SET:
+        _DKV_SET = True
+        if os.environ.get("ATB_FLASH_BWD_DKV", "1") == "0":
+            _lib.lib().atb_flash_bwd_set_dkv(ctypes.c_int(0))
     # two kernels (dK/dV per key block, dQ per query block: no atomics, no fp32 scratch) unless
     # ATB_FLASH_BWD_SPLIT=0 asks for the single key-block kernel with TMA reduce-adds of dQ
     dq_acc = None if BWD_SPLIT else torch.zeros(B, Sq, Hq, D, dtype=torch.float32, device=q.device)
