@@ -256,22 +256,28 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       // tiles inside the intersection of the rows' intervals run without per-element tests
       const bool tile_full = (kv0 >= full_lo) && (kv0 + BKV <= full_hi);
       const int c0 = kv0 + half * 64;
-      uint32_t ds[32];
+      float pa[32], pb[32];   // P for keys c0 .. c0+31 and c0+32 .. c0+63
 #pragma unroll
       for (int c = 0; c < 32; c += 2) {
         float a0, a1, b0, b1;
         f2_unpack(f2_fma(f2_pack_bits(s0[c], s0[c + 1]), sc2, nl2), a0, a1);
         f2_unpack(f2_fma(f2_pack_bits(s1[c], s1[c + 1]), sc2, nl2), b0, b1);
-        float pa0 = fast_exp2(a0), pa1 = fast_exp2(a1), pb0 = fast_exp2(b0), pb1 = fast_exp2(b1);
-        if (!tile_full) {
-          if (!valid || c0 + c < lo || c0 + c >= hi) pa0 = 0.f;
-          if (!valid || c0 + c + 1 < lo || c0 + c + 1 >= hi) pa1 = 0.f;
-          if (!valid || c0 + 32 + c < lo || c0 + 32 + c >= hi) pb0 = 0.f;
-          if (!valid || c0 + 33 + c < lo || c0 + 33 + c >= hi) pb1 = 0.f;
+        pa[c] = fast_exp2(a0); pa[c + 1] = fast_exp2(a1);
+        pb[c] = fast_exp2(b0); pb[c + 1] = fast_exp2(b1);
+      }
+      if (!tile_full) {   // a separate pass, so that fully visible tiles execute no interval tests at all
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          if (!valid || c0 + c < lo || c0 + c >= hi) pa[c] = 0.f;
+          if (!valid || c0 + 32 + c < lo || c0 + 32 + c >= hi) pb[c] = 0.f;
         }
+      }
+      uint32_t ds[32];
+#pragma unroll
+      for (int c = 0; c < 32; c += 2) {
         float x0, x1, y0, y1;   // dS = P (dP - delta) scale
-        f2_unpack(f2_mul(f2_mul(f2_pack(pa0, pa1), scl2), f2_add(f2_pack_bits(d0[c], d0[c + 1]), nd2)), x0, x1);
-        f2_unpack(f2_mul(f2_mul(f2_pack(pb0, pb1), scl2), f2_add(f2_pack_bits(d1[c], d1[c + 1]), nd2)), y0, y1);
+        f2_unpack(f2_mul(f2_mul(f2_pack(pa[c], pa[c + 1]), scl2), f2_add(f2_pack_bits(d0[c], d0[c + 1]), nd2)), x0, x1);
+        f2_unpack(f2_mul(f2_mul(f2_pack(pb[c], pb[c + 1]), scl2), f2_add(f2_pack_bits(d1[c], d1[c + 1]), nd2)), y0, y1);
         ds[c >> 1] = pack_bf16x2(x0, x1);
         ds[16 + (c >> 1)] = pack_bf16x2(y0, y1);
       }
