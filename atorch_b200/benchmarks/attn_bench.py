@@ -86,17 +86,18 @@ def main(argv=None):
             saved = flash.BWD_SPLIT
             L = _lib.lib()
             flash.BWD_SPLIT = True
-            tb_o = time_fn(ours_b, args.iters, flush)            # dK/dV kernel (transposed) + dQ kernel
-            L.atb_flash_bwd_set_dkv(0)
-            tb_o2 = time_fn(ours_b, args.iters, flush)           # dK/dV kernel through shared memory + dQ kernel
+            L.atb_flash_bwd_set_dkv(-1)
+            tb_o = time_fn(ours_b, args.iters, flush)            # default: dK/dV kernel chosen by shape + dQ kernel
             L.atb_flash_bwd_set_dkv(1)
+            tb_o2 = time_fn(ours_b, args.iters, flush)           # transposed dK/dV kernel + dQ kernel
+            L.atb_flash_bwd_set_dkv(-1)
             flash.BWD_SPLIT = False
             tb_o1 = time_fn(ours_b, args.iters, flush)           # one key-block kernel, dQ by TMA reduce-adds
             flash.BWD_SPLIT = saved
             tb_l = time_fn(lib_b, args.iters, flush)
             _lib.check_status(dev)
             line += (f" || bwd: ours {tb_o:8.1f} us {2.5 * flops_f / tb_o / 1e6:7.1f} TF | "
-                     f"ours(smem dK/dV) {tb_o2:8.1f} us | ours(one kernel) {tb_o1:8.1f} us | "
+                     f"ours(transposed dK/dV) {tb_o2:8.1f} us | ours(one kernel) {tb_o1:8.1f} us | "
                      f"SDPA {tb_l:8.1f} us {2.5 * flops_f / tb_l / 1e6:7.1f} TF")
             if fa is not None:
                 o3 = fa(q, k, v, causal=causal)

@@ -296,15 +296,34 @@ __global__ void __launch_bounds__(NT) norm_bwd_kernel(const T* __restrict__ dy, 
   }
 }
 
-// out[c] (+)= sum_p partial[p][c]; fixed summation order.
+// out[c] (+)= sum_p partial[p][c]; fixed summation order. A CTA owns 32 columns; its 8 row groups (thread
+// group g takes rows g, g+8, ...) each keep two running sums and are combined through shared memory in a
+// fixed order, so the result does not depend on scheduling while 8 x more loads are in flight per column
+// than with one thread per column.
+constexpr int CS_COLS = 32, CS_GROUPS = 8;
 template <typename TO>
-__global__ void colsum_kernel(const float* __restrict__ partial, TO* __restrict__ out, int P, int N, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= N) return;
-  float s = 0.f;
-  for (int p = 0; p < P; ++p) s += partial[(size_t)p * N + c];
-  if (accumulate) s += to_f32<TO>(out[c]);
-  out[c] = from_f32<TO>(s);
+__global__ void __launch_bounds__(CS_COLS * CS_GROUPS)
+colsum_kernel(const float* __restrict__ partial, TO* __restrict__ out, int P, int N, int accumulate) {
+  __shared__ float part[CS_GROUPS][CS_COLS];
+  const int cl = threadIdx.x % CS_COLS, g = threadIdx.x / CS_COLS;
+  const int c = blockIdx.x * CS_COLS + cl;
+  float s0 = 0.f, s1 = 0.f;
+  if (c < N) {
+    int p = g;
+    for (; p + CS_GROUPS < P; p += 2 * CS_GROUPS) {
+      s0 += partial[(size_t)p * N + c];
+      s1 += partial[(size_t)(p + CS_GROUPS) * N + c];
+    }
+    if (p < P) s0 += partial[(size_t)p * N + c];
+  }
+  part[g][cl] = s0 + s1;
+  __syncthreads();
+  if (g == 0 && c < N) {
+    float s = ((part[0][cl] + part[1][cl]) + (part[2][cl] + part[3][cl])) +
+              ((part[4][cl] + part[5][cl]) + (part[6][cl] + part[7][cl]));
+    if (accumulate) s += to_f32<TO>(out[c]);
+    out[c] = from_f32<TO>(s);
+  }
 }
 
 template <typename T, bool LN>
@@ -391,10 +410,10 @@ extern "C" int atb_norm_bwd(const void* dy, const void* x, const void* w, const 
 // out[N] (+)= column sums of partial[P, N].  out_dtype: 0 bf16, 1 fp16, 2 fp32.
 extern "C" int atb_colsum(const float* partial, void* out, int P, int N, int out_dtype, int accumulate, void* stream) {
   cudaStream_t st = (cudaStream_t)stream;
-  const int grid = (N + 255) / 256;
-  if (out_dtype == 0) colsum_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(partial, (__nv_bfloat16*)out, P, N, accumulate);
-  else if (out_dtype == 1) colsum_kernel<__half><<<grid, 256, 0, st>>>(partial, (__half*)out, P, N, accumulate);
-  else colsum_kernel<float><<<grid, 256, 0, st>>>(partial, (float*)out, P, N, accumulate);
+  const int grid = (N + CS_COLS - 1) / CS_COLS, threads = CS_COLS * CS_GROUPS;
+  if (out_dtype == 0) colsum_kernel<__nv_bfloat16><<<grid, threads, 0, st>>>(partial, (__nv_bfloat16*)out, P, N, accumulate);
+  else if (out_dtype == 1) colsum_kernel<__half><<<grid, threads, 0, st>>>(partial, (__half*)out, P, N, accumulate);
+  else colsum_kernel<float><<<grid, threads, 0, st>>>(partial, (float*)out, P, N, accumulate);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

@@ -145,7 +145,7 @@ class LlamaDecoderLayer(nn.Module):
         x = self.input_layernorm(h)
         qkv = self._proj(self.qkv_proj, x)
         S = qkv.shape[1]      # the projection may have gathered a sequence-sharded input (sequence parallelism)
-        qkv = ops.rope(qkv, cos, sin, self.n_q + self.n_kv, d, positions)
+        qkv = ops.rope(qkv, cos, sin, self.n_q + self.n_kv, d, positions, inplace=True)   # qkv is read by nothing else
         qkv = qkv.view(B, S, self.n_q + 2 * self.n_kv, d)
         q = qkv[:, :, : self.n_q]
         k = qkv[:, :, self.n_q: self.n_q + self.n_kv]

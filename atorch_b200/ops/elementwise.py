@@ -50,29 +50,44 @@ def _rope_launch(dst2, src2, cos, sin, positions, nheads, head_dim, backward):
 
 class _Rope(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, cos, sin, positions, nheads, head_dim):
+    def forward(ctx, x, cos, sin, positions, nheads, head_dim, inplace):
+        ctx.save_for_backward(cos, sin, positions)
+        ctx.cfg = (nheads, head_dim, inplace)
+        if inplace and x.stride(-1) == 1 and x.is_contiguous():
+            # rotate the q / k heads where they are: the untouched columns (v heads) cost no traffic
+            ctx.mark_dirty(x)
+            x2 = x.view(-1, x.shape[-1])
+            _rope_launch(x2, x2, cos, sin, positions, nheads, head_dim, False)
+            return x
         src = x.reshape(-1, x.shape[-1])
         src = src if src.stride(-1) == 1 else src.contiguous()
         out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
-        ctx.save_for_backward(cos, sin, positions)
-        ctx.cfg = (nheads, head_dim)
         _rope_launch(out.view(-1, out.shape[-1]), src, cos, sin, positions, nheads, head_dim, False)
         return out
 
     @staticmethod
     def backward(ctx, dy):
         cos, sin, positions = ctx.saved_tensors
-        nheads, head_dim = ctx.cfg
+        nheads, head_dim, inplace = ctx.cfg
+        if inplace and dy.is_contiguous():
+            # the incoming gradient is a temporary of the attention backward: rotate it back in place
+            d2 = dy.view(-1, dy.shape[-1])
+            _rope_launch(d2, d2, cos, sin, positions, nheads, head_dim, True)
+            return dy, None, None, None, None, None, None
         src = dy.reshape(-1, dy.shape[-1])
         src = src if src.stride(-1) == 1 else src.contiguous()
         dx = torch.empty(dy.shape, dtype=dy.dtype, device=dy.device)
         _rope_launch(dx.view(-1, dx.shape[-1]), src, cos, sin, positions, nheads, head_dim, True)
-        return dx, None, None, None, None, None
+        return dx, None, None, None, None, None, None
 
 
 def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, nheads: int, head_dim: int,
-         positions: Optional[torch.Tensor] = None) -> torch.Tensor:
+         positions: Optional[torch.Tensor] = None, inplace: bool = False) -> torch.Tensor:
     """Rotate the first ``nheads`` heads of the last dim of ``x`` ([..., W], W >= nheads*head_dim).
+
+    ``inplace``: overwrite ``x`` (and, in the backward pass, the incoming gradient) instead of writing a new
+    tensor; only for an ``x`` that nothing else reads in its unrotated form, e.g. the output of the fused
+    q|k|v projection. The columns that are not rotated then cost no memory traffic.
 
     Used on the fused q|k|v projection output: passing ``nheads = n_q + n_kv`` rotates q and k and
     leaves v untouched. Token position = ``positions`` (int32, one per row) or row index mod S.
@@ -83,7 +98,7 @@ def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, nheads: int, hea
         return _RopeRef.apply(x, cos, sin, positions, nheads, head_dim)
     if positions is not None and positions.dtype != torch.int32:
         positions = positions.to(torch.int32)
-    return _Rope.apply(x, cos, sin, positions, nheads, head_dim)
+    return _Rope.apply(x, cos, sin, positions, nheads, head_dim, bool(inplace) and not x.is_leaf)
 
 
 class _RopeRef(torch.autograd.Function):

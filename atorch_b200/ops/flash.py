@@ -31,8 +31,10 @@ import os
 # default from 256 query rows on (measured 201 us against 256 us for the single-tile kernel at S=4096, H=32,
 # causal); ATB_FLASH_V2=0 keeps the single-tile kernel everywhere
 FWD_TWO_TILES = os.environ.get("ATB_FLASH_V2", "1") == "1"
-BWD_SPLIT = os.environ.get("ATB_FLASH_BWD_SPLIT", "0") == "1"
-_DKV_SET = False   # ATB_FLASH_BWD_DKV=0 picks the shared-memory key-block kernel of the two-kernel backward
+# backward as two kernels (dK/dV per key block + dQ per query block; no atomics, no fp32 scratch): measured 667 us
+# against 696 us for the single key-block kernel at S=4096, H=32, causal. ATB_FLASH_BWD_SPLIT=0 selects the latter.
+BWD_SPLIT = os.environ.get("ATB_FLASH_BWD_SPLIT", "1") == "1"
+_DKV_SET = False   # ATB_FLASH_BWD_DKV=0 / 1 forces the shared-memory / transposed key-block kernel (default: by shape)
 
 
 def kernels_built() -> bool:
@@ -137,8 +139,8 @@ def flash_bwd_raw(dout, q, k, v, out, lse, causal, softmax_scale, row_lo, row_hi
     global _DKV_SET
     if not _DKV_SET:
         _DKV_SET = True
-        if os.environ.get("ATB_FLASH_BWD_DKV", "1") == "0":
-            _lib.lib().atb_flash_bwd_set_dkv(ctypes.c_int(0))
+        if os.environ.get("ATB_FLASH_BWD_DKV", "") in ("0", "1"):
+            _lib.lib().atb_flash_bwd_set_dkv(ctypes.c_int(int(os.environ["ATB_FLASH_BWD_DKV"])))
     # two kernels (dK/dV per key block, dQ per query block: no atomics, no fp32 scratch) unless
     # ATB_FLASH_BWD_SPLIT=0 asks for the single key-block kernel with TMA reduce-adds of dQ
     dq_acc = None if BWD_SPLIT else torch.zeros(B, Sq, Hq, D, dtype=torch.float32, device=q.device)

@@ -88,6 +88,27 @@ def test_rope_matches_reference_and_is_orthogonal():
     _close(y2, ops.rope_reference(x.detach(), cos, sin, nq, d, positions=pos), 1e-2, 1e-2)
 
 
+def test_rope_in_place_matches_out_of_place():
+    torch.manual_seed(5)
+    B, S, nq, nkv, d = 2, 128, 4, 4, 128
+    W = (nq + 2 * nkv) * d
+    x = torch.randn(B, S, W, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    cos, sin = ops.rope_tables(S, d, device="cuda")
+    ref = ops.rope(x, cos, sin, nq + nkv, d)
+    dy = torch.randn_like(ref)
+    ref.backward(dy.clone())
+    g_ref, x.grad = x.grad.clone(), None
+    h = x * 1.0                                  # a non-leaf that nothing else reads
+    y = ops.rope(h, cos, sin, nq + nkv, d, inplace=True)
+    assert y.data_ptr() == h.data_ptr()          # rotated where it is
+    assert torch.equal(y, ref)
+    y.backward(dy.clone())
+    assert torch.equal(x.grad, g_ref)
+    # a leaf is never overwritten
+    z = ops.rope(x, cos, sin, nq + nkv, d, inplace=True)
+    assert z.data_ptr() != x.data_ptr()
+
+
 def test_swiglu_fwd_bwd():
     torch.manual_seed(4)
     gu = torch.randn(300, 2 * 1376, device="cuda", dtype=torch.bfloat16, requires_grad=True)
