@@ -143,3 +143,45 @@ def test_dcp_format_checkpoint_reshards_across_world_sizes(tmp_path):
         a2, a1, a3 = (torch.load(path + f"/after_{w}.pt") for w in (2, 1, 3))
         for k in a2:
             assert torch.allclose(a2[k], a1[k], atol=1e-6) and torch.allclose(a2[k], a3[k], atol=1e-6), k
+
+
+def test_reference_reader_loads_flat_checkpoint_written_here(tmp_path):
+    """The flat sharded files written by this package at world size 2 (with optimizer state) are read back by the
+    reference's own ``ShardTensorUtil`` / ``ShardOptim`` (run in a clean interpreter whose only ``atorch`` is the
+    unmodified reference installed under baseline/_ref)."""
+    import os
+    import subprocess
+    import sys
+
+    import pytest
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ref = os.path.join(root, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "atorch")):
+        pytest.skip("the reference is not installed under baseline/_ref")
+    path = str(tmp_path / "flat")
+    run_distributed(_save, world=2, args=(path, False))
+    script = r"""
+import sys, torch
+if not torch.cuda.is_available():      # the reader ends with a device synchronise; there is no device here
+    torch.cuda.synchronize = lambda *a, **k: None
+    torch.cuda.current_device = lambda: 0
+from atorch.utils.fsdp_save_util import ShardTensorUtil
+import atorch
+assert "baseline/_ref" in atorch.__file__.replace("\\", "/"), atorch.__file__
+path = sys.argv[1]
+ref = torch.load(path + "/full_ref.pt")
+util = ShardTensorUtil(path, 0, 1, device="cpu")
+bad = []
+for k, v in ref.items():
+    t = util.load_tensor_by_name(k)
+    if t is None or not torch.equal(t.reshape(v.shape).to(v.dtype), v):
+        bad.append(k)
+print("params", len(ref), "bad", bad)
+assert not bad, bad
+"""
+    env = dict(os.environ, PYTHONPATH=ref)
+    res = subprocess.run([sys.executable, "-c", script, path], cwd=str(tmp_path), env=env, capture_output=True, text=True,
+                         timeout=300)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
+    assert "bad []" in res.stdout
