@@ -68,7 +68,7 @@ def main(argv=None):
         qkv = torch.randn(4, 4096, 96, 128, device=dev, dtype=torch.bfloat16, requires_grad=True)
         cos, sin = ops.rope_tables(4096, 128, 10000.0, dev)
         for _ in range(n):
-            ops.rope(qkv.view(4, 4096, -1), cos, sin, 64, 128).backward(torch.ones(4, 4096, 96 * 128, device=dev,
+            ops.rope(qkv.view(4, 4096, -1), cos, sin, 64, 128, inplace=True).backward(torch.ones(4, 4096, 96 * 128, device=dev,
                                                                                    dtype=torch.bfloat16))
     elif case == "swiglu":
         x = torch.randn(16384, 22016, device=dev, dtype=torch.bfloat16, requires_grad=True)

@@ -13,6 +13,7 @@
 #include <stdint.h>
 
 #define ATB_DEVICE __device__ __forceinline__
+#define ATB_HOST_DEVICE __host__ __device__ __forceinline__
 
 #ifndef ATB_WAIT_LIMIT_NS
 #define ATB_WAIT_LIMIT_NS 2000000000ull  // 2 s: far above any legal wait in these kernels
@@ -377,6 +378,28 @@ ATB_DEVICE uint64_t f2_mul(uint64_t a, uint64_t b) {
   uint64_t d;
   asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
+}
+
+// Attention dropout: a counter-based keep decision per (batch*head, query row, key column), the same in the
+// forward and the backward kernels and reproducible on the host (ops/flash.py: dropout_keep_mask). One hash
+// serves two neighbouring columns: the low 16 bits decide the even column, the high 16 bits the odd one;
+// an element is kept when its 16 bits are >= thr16 = round(p * 65536).
+struct DropParams {
+  uint32_t thr16;      // 0: no dropout
+  uint32_t seed_lo, seed_hi;
+  float keep_scale;    // 65536 / (65536 - thr16)
+};
+ATB_HOST_DEVICE uint32_t hash32(uint32_t x) {
+  x ^= x >> 16; x *= 0x7feb352dU; x ^= x >> 15; x *= 0x846ca68bU; x ^= x >> 16;
+  return x;
+}
+ATB_HOST_DEVICE uint32_t drop_row_key(const DropParams& d, uint32_t bh, uint32_t row) {
+  const uint32_t base = hash32(d.seed_lo ^ (bh * 0x9E3779B1U)) ^ d.seed_hi;
+  return hash32(base + row * 0x85EBCA77U);
+}
+// bits for columns (col, col + 1), col even
+ATB_HOST_DEVICE uint32_t drop_pair_bits(uint32_t row_key, uint32_t col) {
+  return hash32(row_key ^ ((col >> 1) * 0xC2B2AE3DU));
 }
 
 // 2^x on the special-function unit (ex2.approx.ftz): -inf -> 0, relative error ~2^-22

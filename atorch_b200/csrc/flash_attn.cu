@@ -44,6 +44,7 @@ struct FwdParams {
   int causal;         // analytic causal bound when row_hi is null
   float scale_log2;   // softmax scale * log2(e)
   int* status;
+  DropParams drop;    // attention dropout (thr16 == 0: none)
 };
 
 struct SmemLayout {
@@ -59,6 +60,7 @@ struct SmemLayout {
   static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 64 + 1024;
 };
 
+template <bool DROP>
 __global__ void __launch_bounds__(THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, FwdParams p) {
@@ -239,6 +241,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       hi = min(hi, p.Sk);
     }
     float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
+    const uint32_t drop_key = DROP ? drop_row_key(p.drop, (uint32_t)(b * p.Hq + h), (uint32_t)i) : 0u;
     float o_acc[64];
 #pragma unroll
     for (int c = 0; c < 64; ++c) o_acc[c] = 0.f;
@@ -307,12 +310,26 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const float neg_ms = -m_use * p.scale_log2;
       float ls4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t pk[32];
+      if constexpr (!DROP) {
 #pragma unroll
-      for (int c = 0; c < 64; c += 2) {
-        const float p0 = fast_exp2(fmaf(sv[c], p.scale_log2, neg_ms));
-        const float p1 = fast_exp2(fmaf(sv[c + 1], p.scale_log2, neg_ms));
-        ls4[(c >> 1) & 3] += p0 + p1;
-        pk[c >> 1] = pack_bf16x2(p0, p1);
+        for (int c = 0; c < 64; c += 2) {
+          const float p0 = fast_exp2(fmaf(sv[c], p.scale_log2, neg_ms));
+          const float p1 = fast_exp2(fmaf(sv[c + 1], p.scale_log2, neg_ms));
+          ls4[(c >> 1) & 3] += p0 + p1;
+          pk[c >> 1] = pack_bf16x2(p0, p1);
+        }
+      } else {
+        // the row sum (and lse) is that of the full softmax; dropped elements only leave the P V product,
+        // and the 1 / (1 - p) factor is applied once, to the finished row
+        const uint32_t cbase = (uint32_t)(kv0 + half * 64);
+#pragma unroll
+        for (int c = 0; c < 64; c += 2) {
+          const float p0 = fast_exp2(fmaf(sv[c], p.scale_log2, neg_ms));
+          const float p1 = fast_exp2(fmaf(sv[c + 1], p.scale_log2, neg_ms));
+          ls4[(c >> 1) & 3] += p0 + p1;
+          const uint32_t w = drop_pair_bits(drop_key, cbase + c);
+          pk[c >> 1] = pack_bf16x2((w & 0xffffu) >= p.drop.thr16 ? p0 : 0.f, (w >> 16) >= p.drop.thr16 ? p1 : 0.f);
+        }
       }
       l_run = l_run * alpha + ((ls4[0] + ls4[1]) + (ls4[2] + ls4[3]));
       m_run = m_new;
@@ -342,7 +359,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     ok = ok && mbar_wait(x_bar, ntiles & 1, abort_flag, p.status);
     const float l_tot = l_run + s_rowsum[(half ^ 1) * 128 + r];
     if (ok && row_valid) {
-      const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+      const float inv = l_tot > 0.f ? (DROP ? p.drop.keep_scale : 1.f) / l_tot : 0.f;
       __nv_bfloat16* orow = p.O + (((long long)b * p.Sq + i) * p.Hq + h) * HD + half * 64;
 #pragma unroll
       for (int c = 0; c < 64; c += 8) {
@@ -376,10 +393,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 // q: rows = B*Sq tokens with pitch q_stride elements, head h at columns [h*128, h*128+128);
 // k, v likewise with B*Sk rows. O: [B, Sq, Hq, 128] contiguous bf16; lse: [B, Hq, Sq] fp32.
 // row_lo / row_hi: optional int32 [B, Sq] key intervals (see file header).
-extern "C" int atb_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* row_lo,
-                             const int* row_hi, int B, int Sq, int Sk, int Hq, int Hkv, long long q_stride,
-                             long long k_stride, long long v_stride, int causal, float softmax_scale, void* stream,
-                             int* status) {
+static int flash_fwd_launch(const void* q, const void* k, const void* v, void* o, float* lse, const int* row_lo,
+                            const int* row_hi, int B, int Sq, int Sk, int Hq, int Hkv, long long q_stride,
+                            long long k_stride, long long v_stride, int causal, float softmax_scale, void* stream,
+                            int* status, DropParams drop) {
   if (B <= 0 || Sq <= 0 || Sk <= 0) return 0;
   if (Hq % Hkv) return -1;
   if ((q_stride | k_stride | v_stride) & 7) return -1;
@@ -395,8 +412,10 @@ extern "C" int atb_flash_fwd(const void* q, const void* k, const void* v, void* 
     return -2;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(flash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemLayout::TOTAL) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(flash_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SmemLayout::TOTAL) != cudaSuccess ||
+        cudaFuncSetAttribute(flash_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SmemLayout::TOTAL) != cudaSuccess)
       return -4;
     attr_set = true;
   }
@@ -405,7 +424,32 @@ extern "C" int atb_flash_fwd(const void* q, const void* k, const void* v, void* 
   p.B = B; p.Sq = Sq; p.Sk = Sk; p.Hq = Hq; p.Hkv = Hkv; p.causal = causal;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = status;
+  p.drop = drop;
   dim3 grid((Sq + BQ - 1) / BQ, Hq, B);
-  flash_fwd_kernel<<<grid, THREADS, SmemLayout::TOTAL, (cudaStream_t)stream>>>(tmQ, tmK, tmV, p);
+  if (drop.thr16 != 0)
+    flash_fwd_kernel<true><<<grid, THREADS, SmemLayout::TOTAL, (cudaStream_t)stream>>>(tmQ, tmK, tmV, p);
+  else
+    flash_fwd_kernel<false><<<grid, THREADS, SmemLayout::TOTAL, (cudaStream_t)stream>>>(tmQ, tmK, tmV, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+extern "C" int atb_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* row_lo,
+                             const int* row_hi, int B, int Sq, int Sk, int Hq, int Hkv, long long q_stride,
+                             long long k_stride, long long v_stride, int causal, float softmax_scale, void* stream,
+                             int* status) {
+  return flash_fwd_launch(q, k, v, o, lse, row_lo, row_hi, B, Sq, Sk, Hq, Hkv, q_stride, k_stride, v_stride, causal,
+                          softmax_scale, stream, status, DropParams{0u, 0u, 0u, 1.f});
+}
+
+// The same with attention dropout: probability thr16 / 65536 (0 < thr16 < 65536), mask defined by the seed pair
+// (common.cuh: drop_row_key / drop_pair_bits); the backward must be given the same three numbers.
+extern "C" int atb_flash_fwd_dropout(const void* q, const void* k, const void* v, void* o, float* lse,
+                                     const int* row_lo, const int* row_hi, int B, int Sq, int Sk, int Hq, int Hkv,
+                                     long long q_stride, long long k_stride, long long v_stride, int causal,
+                                     float softmax_scale, void* stream, int* status, unsigned thr16,
+                                     unsigned seed_lo, unsigned seed_hi) {
+  if (thr16 == 0 || thr16 >= 65536u) return -1;
+  return flash_fwd_launch(q, k, v, o, lse, row_lo, row_hi, B, Sq, Sk, Hq, Hkv, q_stride, k_stride, v_stride, causal,
+                          softmax_scale, stream, status,
+                          DropParams{thr16, seed_lo, seed_hi, 65536.f / (float)(65536u - thr16)});
 }

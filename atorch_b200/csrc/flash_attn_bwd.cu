@@ -46,6 +46,7 @@ struct BwdParams {
   int B, Sq, Sk, Hq, Hkv, causal;
   float scale, scale_log2;
   int* status;
+  DropParams drop;     // attention dropout of the forward pass (thr16 == 0: none)
 };
 
 struct SmemB {
@@ -71,7 +72,7 @@ struct RowInfo {
 
 // WITH_DQ = false: key/value gradients only (the query gradient then comes from flash_attn_bwd_dq.cu): the
 // dQ product, its staging and the reduce-add are compiled out and dP(i+1) follows dK(i) without a hand-shake.
-template <bool WITH_DQ>
+template <bool WITH_DQ, bool DROP = false>
 __global__ void __launch_bounds__(THREADS, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                  const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -383,23 +384,52 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_ld_32x32(tdP + 32, d1);
         tmem_ld_wait();
         const uint64_t nd2 = f2_pack(-cur.delta, -cur.delta), scl2 = f2_pack(p.scale, p.scale);
+        if constexpr (!DROP) {
 #pragma unroll
-        for (int c8 = 0; c8 < 8; ++c8) {
-          uint32_t pk[4], dk_[4];
+          for (int c8 = 0; c8 < 8; ++c8) {
+            uint32_t pk[4], dk_[4];
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const int c = c8 * 8 + 2 * q;
-            const uint64_t dp2 = c < 32 ? f2_pack_bits(d0[c & 31], d0[(c + 1) & 31])
-                                        : f2_pack_bits(d1[c & 31], d1[(c + 1) & 31]);
-            const uint64_t p2 = f2_pack(pv[c], pv[c + 1]);
-            float ds0, ds1;
-            f2_unpack(f2_mul(f2_mul(p2, scl2), f2_add(dp2, nd2)), ds0, ds1);   // P (dP - delta) scale
-            pk[q] = pack_bf16x2(pv[c], pv[c + 1]);
-            dk_[q] = pack_bf16x2(ds0, ds1);
+            for (int q = 0; q < 4; ++q) {
+              const int c = c8 * 8 + 2 * q;
+              const uint64_t dp2 = c < 32 ? f2_pack_bits(d0[c & 31], d0[(c + 1) & 31])
+                                          : f2_pack_bits(d1[c & 31], d1[(c + 1) & 31]);
+              const uint64_t p2 = f2_pack(pv[c], pv[c + 1]);
+              float ds0, ds1;
+              f2_unpack(f2_mul(f2_mul(p2, scl2), f2_add(dp2, nd2)), ds0, ds1);   // P (dP - delta) scale
+              pk[q] = pack_bf16x2(pv[c], pv[c + 1]);
+              dk_[q] = pack_bf16x2(ds0, ds1);
+            }
+            const int slot = (c8 ^ (r & 7)) << 4;
+            *reinterpret_cast<uint4*>(prow + slot) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            *reinterpret_cast<uint4*>(dsrow + slot) = make_uint4(dk_[0], dk_[1], dk_[2], dk_[3]);
           }
-          const int slot = (c8 ^ (r & 7)) << 4;
-          *reinterpret_cast<uint4*>(prow + slot) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-          *reinterpret_cast<uint4*>(dsrow + slot) = make_uint4(dk_[0], dk_[1], dk_[2], dk_[3]);
+        } else {
+          // dropout: with m = keep / (1 - p) per element, the tile for dV is P m and dS = P (m dP - delta) scale
+          const uint32_t dkey = drop_row_key(p.drop, (uint32_t)(b * p.Hq + h), (uint32_t)cur.i);
+          const uint32_t cbase = (uint32_t)(kv0 + half * 64);
+#pragma unroll
+          for (int c8 = 0; c8 < 8; ++c8) {
+            uint32_t pk[4], dk_[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int c = c8 * 8 + 2 * q;
+              const uint32_t w = drop_pair_bits(dkey, cbase + c);
+              const float m0 = (w & 0xffffu) >= p.drop.thr16 ? p.drop.keep_scale : 0.f;
+              const float m1 = (w >> 16) >= p.drop.thr16 ? p.drop.keep_scale : 0.f;
+              const uint64_t m2 = f2_pack(m0, m1);
+              const uint64_t dp2 = c < 32 ? f2_pack_bits(d0[c & 31], d0[(c + 1) & 31])
+                                          : f2_pack_bits(d1[c & 31], d1[(c + 1) & 31]);
+              const uint64_t p2 = f2_pack(pv[c], pv[c + 1]);
+              float ds0, ds1, pm0, pm1;
+              f2_unpack(f2_mul(f2_mul(p2, scl2), f2_fma(dp2, m2, nd2)), ds0, ds1);
+              f2_unpack(f2_mul(p2, m2), pm0, pm1);
+              pk[q] = pack_bf16x2(pm0, pm1);
+              dk_[q] = pack_bf16x2(ds0, ds1);
+            }
+            const int slot = (c8 ^ (r & 7)) << 4;
+            *reinterpret_cast<uint4*>(prow + slot) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            *reinterpret_cast<uint4*>(dsrow + slot) = make_uint4(dk_[0], dk_[1], dk_[2], dk_[3]);
+          }
         }
       }
       fence_proxy_async_smem();
@@ -524,13 +554,14 @@ extern "C" void atb_flash_bwd_set_dkv(int transposed) { g_dkv_transposed = trans
 // dq_acc must be zero on entry; dq/dk/dv are written as token-major rows of pitch dq_stride / dkv_stride
 // elements (so they may be slices of one fused [tokens, (Hq + 2 Hq) * 128] gradient buffer). dk, dv are per
 // query head; the caller sums head groups for grouped-query attention. `delta` is scratch [B, Hq, Sq].
-extern "C" int atb_flash_bwd(const void* dout, const void* q, const void* k, const void* v, const void* out,
-                             const float* lse, float* delta, float* dq_acc, void* dq, void* dk, void* dv,
-                             const int* row_lo, const int* row_hi, int B, int Sq, int Sk, int Hq, int Hkv,
-                             long long q_stride, long long k_stride, long long v_stride, long long do_stride,
-                             long long dq_stride, long long dkv_stride, int causal, float softmax_scale, void* stream,
-                             int* status) {
+static int flash_bwd_launch(const void* dout, const void* q, const void* k, const void* v, const void* out,
+                            const float* lse, float* delta, float* dq_acc, void* dq, void* dk, void* dv,
+                            const int* row_lo, const int* row_hi, int B, int Sq, int Sk, int Hq, int Hkv,
+                            long long q_stride, long long k_stride, long long v_stride, long long do_stride,
+                            long long dq_stride, long long dkv_stride, int causal, float softmax_scale, void* stream,
+                            int* status, DropParams drop) {
   if (B <= 0 || Sq <= 0 || Sk <= 0) return 0;
+  if (drop.thr16 != 0 && dq_acc == nullptr) return -1;   // dropout is implemented in the one-kernel form only
   if (Hq % Hkv) return -1;
   if ((q_stride | k_stride | v_stride | do_stride | dq_stride | dkv_stride) & 7) return -1;
   cudaStream_t st = (cudaStream_t)stream;
@@ -559,7 +590,9 @@ extern "C" int atb_flash_bwd(const void* dout, const void* q, const void* k, con
     if (cudaFuncSetAttribute(flash_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemB::TOTAL) !=
             cudaSuccess ||
         cudaFuncSetAttribute(flash_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemB::TOTAL) !=
-            cudaSuccess)
+            cudaSuccess ||
+        cudaFuncSetAttribute(flash_bwd_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SmemB::TOTAL) != cudaSuccess)
       return -4;
     attr_set = true;
   }
@@ -577,6 +610,7 @@ extern "C" int atb_flash_bwd(const void* dout, const void* q, const void* k, con
   p.B = B; p.Sq = Sq; p.Sk = Sk; p.Hq = Hq; p.Hkv = Hkv; p.causal = causal;
   p.scale = softmax_scale; p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = status;
+  p.drop = drop;
   dim3 grid((Sk + BKV - 1) / BKV, Hq, B);
   if (dq_acc == nullptr) {
     if (g_dkv_transposed > 0 || (g_dkv_transposed < 0 && causal && Sk >= 8192)) {
@@ -590,10 +624,37 @@ extern "C" int atb_flash_bwd(const void* dout, const void* q, const void* k, con
     return atb_flash_bwd_dq(dout, q, k, v, lse, delta, dq, row_lo, row_hi, B, Sq, Sk, Hq, Hkv, q_stride, k_stride,
                             v_stride, do_stride, dq_stride, causal, softmax_scale, stream, status);
   }
-  flash_bwd_kernel<true><<<grid, THREADS, SmemB::TOTAL, st>>>(tmQ, tmdO, tmK, tmV, tmdQ, p);
+  if (drop.thr16 != 0)
+    flash_bwd_kernel<true, true><<<grid, THREADS, SmemB::TOTAL, st>>>(tmQ, tmdO, tmK, tmV, tmdQ, p);
+  else
+    flash_bwd_kernel<true><<<grid, THREADS, SmemB::TOTAL, st>>>(tmQ, tmdO, tmK, tmV, tmdQ, p);
   const long long n4 = (long long)B * Sq * Hq * HD / 4;
   long long g = (n4 + 255) / 256;
   if (g > 148 * 16) g = 148 * 16;
   f32_to_bf16_kernel<<<(unsigned)g, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dq, n4, Hq * HD / 4, dq_stride);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+extern "C" int atb_flash_bwd(const void* dout, const void* q, const void* k, const void* v, const void* out,
+                             const float* lse, float* delta, float* dq_acc, void* dq, void* dk, void* dv,
+                             const int* row_lo, const int* row_hi, int B, int Sq, int Sk, int Hq, int Hkv,
+                             long long q_stride, long long k_stride, long long v_stride, long long do_stride,
+                             long long dq_stride, long long dkv_stride, int causal, float softmax_scale, void* stream,
+                             int* status) {
+  return flash_bwd_launch(dout, q, k, v, out, lse, delta, dq_acc, dq, dk, dv, row_lo, row_hi, B, Sq, Sk, Hq, Hkv,
+                          q_stride, k_stride, v_stride, do_stride, dq_stride, dkv_stride, causal, softmax_scale, stream,
+                          status, DropParams{0u, 0u, 0u, 1.f});
+}
+
+// Backward of atb_flash_fwd_dropout: same thr16 and seed pair as the forward; one-kernel form (dq_acc required).
+extern "C" int atb_flash_bwd_dropout(const void* dout, const void* q, const void* k, const void* v, const void* out,
+                                     const float* lse, float* delta, float* dq_acc, void* dq, void* dk, void* dv,
+                                     const int* row_lo, const int* row_hi, int B, int Sq, int Sk, int Hq, int Hkv,
+                                     long long q_stride, long long k_stride, long long v_stride, long long do_stride,
+                                     long long dq_stride, long long dkv_stride, int causal, float softmax_scale,
+                                     void* stream, int* status, unsigned thr16, unsigned seed_lo, unsigned seed_hi) {
+  if (thr16 == 0 || thr16 >= 65536u) return -1;
+  return flash_bwd_launch(dout, q, k, v, out, lse, delta, dq_acc, dq, dk, dv, row_lo, row_hi, B, Sq, Sk, Hq, Hkv,
+                          q_stride, k_stride, v_stride, do_stride, dq_stride, dkv_stride, causal, softmax_scale, stream,
+                          status, DropParams{thr16, seed_lo, seed_hi, 65536.f / (float)(65536u - thr16)});
 }

@@ -45,46 +45,50 @@ ATB_DEVICE uint32_t to_e4m3x4(float a, float b, float c, float d) { return to_e4
 
 // ---------------------------------------------------------------------------------------------
 // 1 x 128 tile quantisation, row-major in, row-major out; K % 128 == 0. A half-warp owns a tile: every
-// lane loads 16 bytes (8 values) and stores 8; a warp iteration covers four tiles (two per half-warp, both
-// loads issued before the first reduction) so that enough bytes are in flight per SM.
+// lane loads 16 bytes (8 values) and stores 8; a warp iteration covers eight tiles (four per half-warp, all
+// loads issued before the first reduction) so that enough bytes are in flight per SM. Output and scales are
+// dense, so tile t lives at byte 128 t of q; only a pitched input needs the row of a tile.
 // ---------------------------------------------------------------------------------------------
+constexpr int TQ_E = 4;
 __global__ void tile_quant_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
                                   float* __restrict__ scales, long long M, int K, long long ldx, int pow2) {
   const int tiles = K >> 7;
   const long long total = M * tiles;
+  const bool dense = ldx == K;
   const int lane = threadIdx.x & 31, sub = lane & 15, hw = lane >> 4;
   const long long warp0 = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
-  for (long long w = warp0 * 4; w < total; w += nwarps * 4) {
-    uint4 u[2];
-    long long tix[2];
+  for (long long w = warp0 * (2 * TQ_E); w < total; w += nwarps * (2 * TQ_E)) {
+    uint4 u[TQ_E];
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      tix[e] = w + e * 2 + hw;
+    for (int e = 0; e < TQ_E; ++e) {
+      const long long tix = w + e * 2 + hw;
       u[e] = make_uint4(0u, 0u, 0u, 0u);
-      if (tix[e] < total) {
-        const long long row = tix[e] / tiles;
-        const int t = (int)(tix[e] - row * tiles);
-        u[e] = *reinterpret_cast<const uint4*>(x + row * ldx + t * 128 + sub * 8);
+      if (tix < total) {
+        long long off = tix * 128;
+        if (!dense) {
+          const long long row = tix / tiles;
+          off = row * ldx + (tix - row * tiles) * 128;
+        }
+        u[e] = *reinterpret_cast<const uint4*>(x + off + sub * 8);
       }
     }
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
+    for (int e = 0; e < TQ_E; ++e) {
+      const long long tix = w + e * 2 + hw;
       const float2 a = unpack_bf16x2(u[e].x), b = unpack_bf16x2(u[e].y), c = unpack_bf16x2(u[e].z), d = unpack_bf16x2(u[e].w);
       float amax = fmaxf(fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y))),
                          fmaxf(fmaxf(fabsf(c.x), fabsf(c.y)), fmaxf(fabsf(d.x), fabsf(d.y))));
 #pragma unroll
       for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));   // within the half-warp
-      if (tix[e] < total) {
-        const long long row = tix[e] / tiles;
-        const int t = (int)(tix[e] - row * tiles);
+      if (tix < total) {
         const float s = make_scale(amax, pow2);
         const float inv = 1.f / s;
         uint2 o;
         o.x = to_e4m3x4(a.x * inv, a.y * inv, b.x * inv, b.y * inv);
         o.y = to_e4m3x4(c.x * inv, c.y * inv, d.x * inv, d.y * inv);
-        *reinterpret_cast<uint2*>(q + row * K + t * 128 + sub * 8) = o;
-        if (sub == 0) scales[row * tiles + t] = s;
+        *reinterpret_cast<uint2*>(q + tix * 128 + sub * 8) = o;
+        if (sub == 0) scales[tix] = s;
       }
     }
   }
@@ -374,7 +378,7 @@ extern "C" int atb_fp8_tile_quant(const void* x, void* q, float* scales, long lo
                                   void* stream) {
   if (M <= 0) return 0;
   if ((K & 127) || (ldx & 7) || ((uintptr_t)x & 15) || ((uintptr_t)q & 7)) return -1;   // 16-byte loads, 8-byte stores
-  tile_quant_kernel<<<grid_cap(M * (K >> 7) * 8, 256, 16), 256, 0, (cudaStream_t)stream>>>(
+  tile_quant_kernel<<<grid_cap(M * (K >> 7) * (16 / TQ_E), 256, 16), 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)x, (uint8_t*)q, scales, M, K, ldx, pow2);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

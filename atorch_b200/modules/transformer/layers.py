@@ -87,7 +87,8 @@ class FlashAttnModule(nn.Module):
         lo, hi = lengths_to_intervals(mask_in_length, kw["causal"])
         if flash.supported(q, k, v, kw["dropout_p"]):
             scale = kw["softmax_scale"] or 1.0 / math.sqrt(q.shape[-1])
-            return flash._FlashAttn.apply(q, k, v, False, float(scale), lo, hi)
+            drop = flash.dropout_config(kw["dropout_p"]) if kw["dropout_p"] > 0.0 else None
+            return flash._FlashAttn.apply(q, k, v, False, float(scale), lo, hi, drop)
         B, S = mask_in_length.shape
         j = torch.arange(S, device=q.device)
         vis = (j[None, None, :] >= lo[:, :, None]) & (j[None, None, :] < hi[:, :, None])

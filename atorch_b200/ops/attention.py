@@ -93,7 +93,7 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = 
     if flash.supported(q, k, v, dropout_p, additive_mask, additive_bias, key_padding_mask):
         return flash.flash_attention(q, k, v, causal=causal, softmax_scale=softmax_scale, glm_mask=glm_mask,
                                      pack_glm_mask=pack_glm_mask, key_padding_mask=key_padding_mask,
-                                     cu_seqlens=cu_seqlens)
+                                     cu_seqlens=cu_seqlens, dropout_p=dropout_p)
     if q.is_cuda and glm_mask is None and pack_glm_mask is None and key_padding_mask is None and cu_seqlens is None \
             and additive_mask is None and additive_bias is None and q.shape[1] == k.shape[1]:
         # library path (torch SDPA) for shapes the sm_100a kernels do not cover

@@ -54,11 +54,14 @@ class _Rope(torch.autograd.Function):
         ctx.save_for_backward(cos, sin, positions)
         ctx.cfg = (nheads, head_dim, inplace)
         if inplace and x.stride(-1) == 1 and x.is_contiguous():
-            # rotate the q / k heads where they are: the untouched columns (v heads) cost no traffic
-            ctx.mark_dirty(x)
+            # rotate the q / k heads where they are: the untouched columns (v heads) cost no traffic. The result
+            # is a second tensor over x's storage rather than x marked dirty: x is usually a view made inside the
+            # projection's autograd function, which autograd refuses to modify in place, and the projection's
+            # backward needs its inputs, not this output.
             x2 = x.view(-1, x.shape[-1])
             _rope_launch(x2, x2, cos, sin, positions, nheads, head_dim, False)
-            return x
+            return torch.empty(0, dtype=x.dtype, device=x.device).set_(x.untyped_storage(), x.storage_offset(),
+                                                                       x.shape, x.stride())
         src = x.reshape(-1, x.shape[-1])
         src = src if src.stride(-1) == 1 else src.contiguous()
         out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
@@ -93,8 +96,6 @@ def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, nheads: int, hea
     leaves v untouched. Token position = ``positions`` (int32, one per row) or row index mod S.
     """
     if not (_lib.use_kernels(x, cos) and x.dtype == torch.bfloat16 and head_dim % 16 == 0 and x.shape[-1] % 8 == 0):
-        if x.requires_grad and False:
-            pass
         return _RopeRef.apply(x, cos, sin, positions, nheads, head_dim)
     if positions is not None and positions.dtype != torch.int32:
         positions = positions.to(torch.int32)

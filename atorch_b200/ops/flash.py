@@ -50,7 +50,9 @@ def backward_built() -> bool:
 def supported(q, k, v, dropout_p=0.0, additive_mask=None, additive_bias=None, key_padding_mask=None) -> bool:
     if not _lib.use_kernels(q, k, v) or not kernels_built():
         return False
-    if dropout_p != 0.0 or additive_mask is not None or additive_bias is not None:
+    if additive_mask is not None or additive_bias is not None:
+        return False
+    if dropout_p != 0.0 and not (0.0 < dropout_p < 1.0 and _lib.lib().has("atb_flash_fwd_dropout")):
         return False
     if (q.requires_grad or k.requires_grad or v.requires_grad) and torch.is_grad_enabled() and not backward_built():
         return False
@@ -111,26 +113,69 @@ def _token_stride(t: torch.Tensor) -> int:
     return t.stride(1)
 
 
-def flash_fwd_raw(q, k, v, causal, softmax_scale, row_lo, row_hi):
-    """Launch the forward kernel. Returns (out [B,Sq,Hq,D] bf16, lse [B,Hq,Sq] fp32)."""
+def dropout_config(dropout_p: float, seed=None) -> Tuple[int, int, int]:
+    """``(thr16, seed_lo, seed_hi)`` for the dropout kernels: an element is dropped when its 16 hash bits are below
+    ``thr16 = round(p * 65536)`` (so the effective probability is ``thr16 / 65536``). The seed pair is drawn from
+    torch's CPU generator (restored by activation checkpointing, so a recomputed forward draws the same mask)
+    unless given."""
+    thr = min(max(int(round(dropout_p * 65536.0)), 1), 65535)
+    if seed is None:
+        lo, hi = torch.randint(0, 2 ** 31 - 1, (2,)).tolist()
+    else:
+        lo, hi = int(seed) & 0xFFFFFFFF, (int(seed) >> 32) & 0xFFFFFFFF
+    return thr, lo, hi
+
+
+def _hash32(x: torch.Tensor) -> torch.Tensor:
+    m = 0xFFFFFFFF
+    x = x ^ (x >> 16)
+    x = (x * 0x7FEB352D) & m
+    x = x ^ (x >> 15)
+    x = (x * 0x846CA68B) & m
+    return x ^ (x >> 16)
+
+
+def dropout_keep_mask(B: int, Hq: int, Sq: int, Sk: int, drop: Tuple[int, int, int], device="cpu") -> torch.Tensor:
+    """The keep mask ``[B, Hq, Sq, Sk]`` (bool) the kernels use for ``drop = (thr16, seed_lo, seed_hi)``: the
+    host restatement of ``drop_row_key`` / ``drop_pair_bits`` (csrc/common.cuh), used by the tests."""
+    thr, lo, hi = drop
+    m = 0xFFFFFFFF
+    bh = torch.arange(B * Hq, dtype=torch.int64, device=device)
+    base = _hash32(lo ^ ((bh * 0x9E3779B1) & m)) ^ hi                               # [B*Hq]
+    rows = torch.arange(Sq, dtype=torch.int64, device=device)
+    key = _hash32((base[:, None] + ((rows * 0x85EBCA77) & m)[None]) & m)             # [B*Hq, Sq]
+    pairs = torch.arange((Sk + 1) // 2, dtype=torch.int64, device=device)
+    w = _hash32(key[:, :, None] ^ ((pairs * 0xC2B2AE3D) & m)[None, None])            # [B*Hq, Sq, Sk/2]
+    bits = torch.stack([w & 0xFFFF, w >> 16], dim=-1).reshape(B * Hq, Sq, -1)[:, :, :Sk]
+    return (bits >= thr).view(B, Hq, Sq, Sk)
+
+
+def flash_fwd_raw(q, k, v, causal, softmax_scale, row_lo, row_hi, drop=None):
+    """Launch the forward kernel. Returns (out [B,Sq,Hq,D] bf16, lse [B,Hq,Sq] fp32). ``drop``: see
+    ``dropout_config``; dropout runs in the single-tile kernel."""
     B, Sq, Hq, D = q.shape
     Sk, Hkv = k.shape[1], k.shape[2]
     out = torch.empty(B, Sq, Hq, D, dtype=q.dtype, device=q.device)
     lse = torch.empty(B, Hq, Sq, dtype=torch.float32, device=q.device)
     L = _lib.lib()
     # two-query-tile kernel (flash_attn_v2.cu) for long enough sequences; the single-tile kernel otherwise
-    fwd = L.atb_flash_fwd_v2 if (FWD_TWO_TILES and Sq >= 256 and L.has("atb_flash_fwd_v2")) else L.atb_flash_fwd
+    if drop is not None:
+        fwd, extra = L.atb_flash_fwd_dropout, tuple(ctypes.c_uint(x) for x in drop)
+    else:
+        fwd = L.atb_flash_fwd_v2 if (FWD_TWO_TILES and Sq >= 256 and L.has("atb_flash_fwd_v2")) else L.atb_flash_fwd
+        extra = ()
     rc = fwd(
         _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(lse), _lib.ptr(row_lo), _lib.ptr(row_hi),
         ctypes.c_int(B), ctypes.c_int(Sq), ctypes.c_int(Sk), ctypes.c_int(Hq), ctypes.c_int(Hkv),
         ctypes.c_longlong(_token_stride(q)), ctypes.c_longlong(_token_stride(k)), ctypes.c_longlong(_token_stride(v)),
         ctypes.c_int(int(causal)), ctypes.c_float(softmax_scale), _lib.stream_ptr(),
-        _lib.ptr(_lib.status_word(q.device)))
+        _lib.ptr(_lib.status_word(q.device)), *extra)
     _lib.check(rc, "atb_flash_fwd")
     return out, lse
 
 
-def flash_bwd_raw(dout, q, k, v, out, lse, causal, softmax_scale, row_lo, row_hi, fused_out: bool = False):
+def flash_bwd_raw(dout, q, k, v, out, lse, causal, softmax_scale, row_lo, row_hi, fused_out: bool = False,
+                  drop=None):
     """Launch the backward kernels. Returns (dq, dk, dv) shaped like q, k, v. With ``fused_out`` (and
     equal query / key-value head counts) the three are slices of ONE ``[B, S, 3*H, D]`` buffer laid out
     like a fused q|k|v projection output, so the gradient of that projection needs no concatenation."""
@@ -143,7 +188,7 @@ def flash_bwd_raw(dout, q, k, v, out, lse, causal, softmax_scale, row_lo, row_hi
             _lib.lib().atb_flash_bwd_set_dkv(ctypes.c_int(int(os.environ["ATB_FLASH_BWD_DKV"])))
     # two kernels (dK/dV per key block, dQ per query block: no atomics, no fp32 scratch) unless
     # ATB_FLASH_BWD_SPLIT=0 asks for the single key-block kernel with TMA reduce-adds of dQ
-    dq_acc = None if BWD_SPLIT else torch.zeros(B, Sq, Hq, D, dtype=torch.float32, device=q.device)
+    dq_acc = None if (BWD_SPLIT and drop is None) else torch.zeros(B, Sq, Hq, D, dtype=torch.float32, device=q.device)
     delta = torch.empty(B, Hq, Sq, dtype=torch.float32, device=q.device)
     if fused_out and Hkv == Hq and Sq == Sk:
         fused = torch.empty(B, Sq, 3 * Hq, D, dtype=q.dtype, device=q.device)
@@ -155,14 +200,16 @@ def flash_bwd_raw(dout, q, k, v, out, lse, causal, softmax_scale, row_lo, row_hi
         dv = torch.empty(B, Sk, Hq, D, dtype=q.dtype, device=q.device)
     dout = dout if (dout.stride(-1) == 1 and dout.stride(2) == D and dout.stride(0) == dout.stride(1) * Sq) \
         else dout.contiguous()
-    rc = _lib.lib().atb_flash_bwd(
+    bwd = _lib.lib().atb_flash_bwd if drop is None else _lib.lib().atb_flash_bwd_dropout
+    extra = () if drop is None else tuple(ctypes.c_uint(x) for x in drop)
+    rc = bwd(
         _lib.ptr(dout), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(lse), _lib.ptr(delta),
         _lib.ptr(dq_acc), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(row_lo), _lib.ptr(row_hi),
         ctypes.c_int(B), ctypes.c_int(Sq), ctypes.c_int(Sk), ctypes.c_int(Hq), ctypes.c_int(Hkv),
         ctypes.c_longlong(_token_stride(q)), ctypes.c_longlong(_token_stride(k)), ctypes.c_longlong(_token_stride(v)),
         ctypes.c_longlong(_token_stride(dout)), ctypes.c_longlong(_token_stride(dq)),
         ctypes.c_longlong(_token_stride(dk)), ctypes.c_int(int(causal)), ctypes.c_float(softmax_scale),
-        _lib.stream_ptr(), _lib.ptr(_lib.status_word(q.device)))
+        _lib.stream_ptr(), _lib.ptr(_lib.status_word(q.device)), *extra)
     _lib.check(rc, "atb_flash_bwd")
     if Hkv != Hq:
         g = Hq // Hkv
@@ -175,22 +222,25 @@ def flash_bwd_raw(dout, q, k, v, out, lse, causal, softmax_scale, row_lo, row_hi
 
 class _FlashAttn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, causal, scale, row_lo, row_hi):
-        out, lse = flash_fwd_raw(q, k, v, causal, scale, row_lo, row_hi)
+    def forward(ctx, q, k, v, causal, scale, row_lo, row_hi, drop=None):
+        out, lse = flash_fwd_raw(q, k, v, causal, scale, row_lo, row_hi, drop)
         ctx.save_for_backward(q, k, v, out, lse, row_lo, row_hi)
-        ctx.cfg = (causal, scale)
+        ctx.cfg = (causal, scale, drop)
         return out
 
     @staticmethod
     def backward(ctx, dout):
         q, k, v, out, lse, row_lo, row_hi = ctx.saved_tensors
-        causal, scale = ctx.cfg
-        dq, dk, dv = flash_bwd_raw(dout, q, k, v, out, lse, causal, scale, row_lo, row_hi)
-        return dq, dk, dv, None, None, None, None
+        causal, scale, drop = ctx.cfg
+        dq, dk, dv = flash_bwd_raw(dout, q, k, v, out, lse, causal, scale, row_lo, row_hi, drop=drop)
+        return dq, dk, dv, None, None, None, None, None
 
 
 def flash_attention(q, k, v, causal=False, softmax_scale=None, glm_mask=None, pack_glm_mask=None,
-                    key_padding_mask=None, cu_seqlens=None):
+                    key_padding_mask=None, cu_seqlens=None, dropout_p=0.0, dropout_seed=None):
+    """``dropout_p``: attention dropout inside the kernels (the mask is a counter-based hash of batch, head, row
+    and column, see ``dropout_keep_mask``); ``dropout_seed`` fixes the mask, otherwise torch's CPU generator
+    supplies the seed."""
     B, Sq, Hq, D = q.shape
     Sk = k.shape[1]
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(D)
@@ -199,11 +249,14 @@ def flash_attention(q, k, v, causal=False, softmax_scale=None, glm_mask=None, pa
     try:
         lo, hi = row_intervals(B, Sq, Sk, q.device, causal, glm_mask, pack_glm_mask, key_padding_mask, cu_seqlens)
     except NonContiguousKeyMask:
-        return _unpadded_attention(q, k, v, key_padding_mask, causal, scale, glm_mask, pack_glm_mask, cu_seqlens)
-    return _FlashAttn.apply(q, k, v, bool(causal), float(scale), lo, hi)
+        return _unpadded_attention(q, k, v, key_padding_mask, causal, scale, glm_mask, pack_glm_mask, cu_seqlens,
+                                   dropout_p, dropout_seed)
+    drop = dropout_config(dropout_p, dropout_seed) if dropout_p > 0.0 else None
+    return _FlashAttn.apply(q, k, v, bool(causal), float(scale), lo, hi, drop)
 
 
-def _unpadded_attention(q, k, v, key_padding_mask, causal, scale, glm_mask, pack_glm_mask, cu_seqlens):
+def _unpadded_attention(q, k, v, key_padding_mask, causal, scale, glm_mask, pack_glm_mask, cu_seqlens,
+                        dropout_p=0.0, dropout_seed=None):
     """Key-padding mask with holes (self-attention): drop the padded tokens, run the batch as packed
     sequences, put the results back (padded positions get zeros). Mirrors the reference's unpad / pad
     path (atorch/modules/transformer/layers.py:76-95,1363-1408)."""
@@ -211,13 +264,15 @@ def _unpadded_attention(q, k, v, key_padding_mask, causal, scale, glm_mask, pack
     if k.shape[1] != S or glm_mask is not None or pack_glm_mask is not None or cu_seqlens is not None:
         from .attention import attention_reference
 
-        return attention_reference(q, k, v, causal, scale, glm_mask, pack_glm_mask, key_padding_mask, cu_seqlens)
+        return attention_reference(q, k, v, causal, scale, glm_mask, pack_glm_mask, key_padding_mask, cu_seqlens,
+                                   dropout_p=dropout_p)
     kp = key_padding_mask.to(q.device).bool()
     idx = kp.reshape(-1).nonzero(as_tuple=False)[:, 0]
     cu = torch.zeros(B + 1, dtype=torch.int32, device=q.device)
     cu[1:] = kp.sum(1).cumsum(0)
     pick = lambda t: t.reshape(B * S, t.shape[2], D).index_select(0, idx).unsqueeze(0)
-    out_p = flash_attention(pick(q), pick(k), pick(v), causal=causal, softmax_scale=scale, cu_seqlens=cu)
+    out_p = flash_attention(pick(q), pick(k), pick(v), causal=causal, softmax_scale=scale, cu_seqlens=cu,
+                            dropout_p=dropout_p, dropout_seed=dropout_seed)
     out = torch.zeros(B * S, H, D, dtype=q.dtype, device=q.device)
     out = out.index_copy(0, idx, out_p[0])
     return out.view(B, S, H, D)

@@ -1,0 +1,64 @@
+"""Host-side parts of the attention operator: mask lowering to key intervals and the dropout-mask restatement."""
+import torch
+
+from atorch_b200.ops import attention_reference, flash
+from atorch_b200.ops.attention import build_dense_mask
+
+
+def test_row_intervals_agree_with_the_dense_masks():
+    B, S = 2, 48
+    dev = torch.device("cpu")
+    cases = [
+        dict(causal=True),
+        dict(causal=True, glm_mask=torch.tensor([7, 30], dtype=torch.int32)),
+        dict(causal=True, pack_glm_mask=torch.tensor([[[0, 20, -1], [5, 30, -1]], [[3, 16, 40], [8, 24, 48]]],
+                                                      dtype=torch.int32)),
+        dict(causal=True, cu_seqlens=torch.tensor([0, 10, 25, 48], dtype=torch.int32)),
+        dict(causal=False, cu_seqlens=torch.tensor([0, 10, 25, 48], dtype=torch.int32)),
+    ]
+    kp = torch.ones(B, S, dtype=torch.bool)
+    kp[0, 30:] = False
+    kp[1, :5] = False
+    cases.append(dict(causal=False, key_padding_mask=kp))
+    j = torch.arange(S)
+    for kw in cases:
+        causal = kw.pop("causal")
+        lo, hi = flash.row_intervals(B, S, S, dev, causal, kw.get("glm_mask"), kw.get("pack_glm_mask"),
+                                     kw.get("key_padding_mask"), kw.get("cu_seqlens"))
+        if lo is None:       # analytic causal form inside the kernel
+            lo = torch.zeros(B, S, dtype=torch.int32)
+            hi = (torch.arange(S, dtype=torch.int32) + 1)[None].expand(B, S)
+        vis = (j[None, None] >= lo[:, :, None]) & (j[None, None] < hi[:, :, None])
+        dense = build_dense_mask(B, S, S, dev, causal, kw.get("glm_mask"), kw.get("pack_glm_mask"),
+                                 kw.get("key_padding_mask"), kw.get("cu_seqlens"))
+        assert torch.equal(vis, dense.expand(B, -1, S, S)[:, 0]), kw
+
+
+def test_flash_dropout_mask_restatement_statistics():
+    """Host restatement of the kernels' dropout hash: keep rate, determinism, independence of rows and heads."""
+    drop = flash.dropout_config(0.1, seed=42)
+    assert drop[0] == round(0.1 * 65536)
+    keep = flash.dropout_keep_mask(2, 3, 64, 257, drop)
+    assert keep.shape == (2, 3, 64, 257)
+    assert abs(keep.float().mean().item() - 0.9) < 0.01
+    assert torch.equal(keep, flash.dropout_keep_mask(2, 3, 64, 257, drop))
+    assert not torch.equal(keep[0, 0], keep[0, 1]) and not torch.equal(keep[0, 0, 0], keep[0, 0, 1])
+    other = flash.dropout_keep_mask(2, 3, 64, 257, flash.dropout_config(0.1, seed=43))
+    assert 0.15 < (keep ^ other).float().mean().item() < 0.21       # 2 p (1 - p) = 0.18 for independent masks
+    # without a seed, torch's CPU generator supplies it (so checkpoint recomputation replays it)
+    torch.manual_seed(5)
+    a = flash.dropout_config(0.1)
+    torch.manual_seed(5)
+    b = flash.dropout_config(0.1)
+    assert a == b
+
+
+def test_attention_reference_dropout_keeps_expectation():
+    torch.manual_seed(0)
+    q, k, v = (torch.randn(1, 64, 2, 16) for _ in range(3))
+    base = attention_reference(q, k, v, causal=True)
+    acc = torch.zeros_like(base)
+    n = 200
+    for _ in range(n):
+        acc += attention_reference(q, k, v, causal=True, dropout_p=0.3)
+    assert (acc / n - base).abs().mean().item() < 0.05

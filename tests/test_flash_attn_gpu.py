@@ -218,3 +218,43 @@ def test_flash_left_padded_and_holed_key_masks():
             tol = 5e-2 * max(1.0, b.abs().max().item())
             assert (a.float() - b).abs().max().item() < tol, (name, causal, kp is holes)
     _lib.check_status(q.device)
+
+
+@pytest.mark.parametrize("B,Sq,Sk,Hq,Hkv,causal", [(2, 384, 384, 4, 4, True), (1, 200, 330, 4, 2, False)])
+def test_flash_dropout_matches_reference_with_the_same_mask(B, Sq, Sk, Hq, Hkv, causal):
+    """Forward and backward with dropout inside the kernels against dense fp32 attention that applies the keep
+    mask restated on the host (flash.dropout_keep_mask)."""
+    torch.manual_seed(21)
+    p_drop, seed = 0.2, 0x1234_5678_9ABC
+    q, k, v = _qkv(B, Sq, Sk, Hq, Hkv)
+    qs = [t.detach().clone().requires_grad_() for t in (q, k, v)]
+    out = flash.flash_attention(*qs, causal=causal, dropout_p=p_drop, dropout_seed=seed)
+    dout = torch.randn_like(out)
+    out.backward(dout)
+    torch.cuda.synchronize()
+    _lib.check_status(q.device)
+
+    drop = flash.dropout_config(p_drop, seed)
+    keep = flash.dropout_keep_mask(B, Hq, Sq, Sk, drop, device="cuda")
+    frac = keep.float().mean().item()
+    assert abs(frac - (1 - p_drop)) < 0.01, frac
+    rs = [t.detach().float().requires_grad_() for t in (q, k, v)]
+    qf, kf, vf = (t.transpose(1, 2) for t in rs)
+    if Hkv != Hq:
+        kf, vf = kf.repeat_interleave(Hq // Hkv, dim=1), vf.repeat_interleave(Hq // Hkv, dim=1)
+    s = qf @ kf.transpose(-1, -2) / math.sqrt(q.shape[-1])
+    if causal:
+        i, j = torch.arange(Sq, device="cuda")[:, None], torch.arange(Sk, device="cuda")[None]
+        s = s.masked_fill(j > i + (Sk - Sq), float("-inf"))
+    pm = torch.softmax(s, -1) * keep * (65536.0 / (65536 - drop[0]))
+    ref = (pm @ vf).transpose(1, 2)
+    ref.backward(dout.float())
+    assert torch.allclose(out.float(), ref, rtol=2e-2, atol=2e-2)
+    for name, a, b in zip("qkv", qs, rs):
+        err = (a.grad.float() - b.grad).abs().max().item()
+        scale = b.grad.abs().max().item() + 1e-6
+        assert err / scale < 3e-2, f"d{name}: max err {err} vs scale {scale}"
+    # a different seed gives a different result, the same seed the same one
+    again = flash.flash_attention(q, k, v, causal=causal, dropout_p=p_drop, dropout_seed=seed)
+    other = flash.flash_attention(q, k, v, causal=causal, dropout_p=p_drop, dropout_seed=seed + 1)
+    assert torch.equal(again, out.detach()) and not torch.equal(other, out.detach())
