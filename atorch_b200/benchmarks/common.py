@@ -58,3 +58,9 @@ def timed_steps(step: Callable[[int], object], steps: int, warmup: int, device) 
 def report(rank: int, record: Dict) -> None:
     if rank == 0:
         print(json.dumps(record), flush=True)
+
+
+def reference_unavailable(why: str) -> None:
+    """The line a benchmark prints (rank 0) when its reference arm cannot run in this environment."""
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)

@@ -15,7 +15,7 @@ import torch
 import torch.nn as nn
 
 from atorch_b200 import ops
-from atorch_b200.benchmarks.common import report, setup, timed_steps
+from atorch_b200.benchmarks.common import reference_unavailable, report, setup, timed_steps
 from atorch_b200.distributed import distributed as D
 from atorch_b200.models.llama import LlamaConfig, LlamaDecoderLayer, RMSNorm, causal_lm_loss
 from atorch_b200.parallel.fsdp import FSDP, FusedShardedOptimizer
@@ -78,7 +78,11 @@ def main(argv=None):
     ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=2)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     a = ap.parse_args(argv)
+    if a.impl == "reference":
+        reference_unavailable("not wired: the reference has no single entry point for TP2 + sequence parallel + PP2 + DP2; its nearest runnable piece (PP x DDP with AGD through make_pipe_module, examples/llama2/train_llama2_with_pp.py) was not brought up on this image")
+        return
     rank, world, dev = setup()
     dp = world // (a.tp * a.pp)
     D.create_parallel_group(([("tensor", a.tp), ("pipe", a.pp), ("data", dp)], None))

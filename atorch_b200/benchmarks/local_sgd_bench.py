@@ -13,7 +13,7 @@ import argparse
 import torch
 
 from atorch_b200.auto import auto_accelerate
-from atorch_b200.benchmarks.common import report, setup, timed_steps
+from atorch_b200.benchmarks.common import reference_unavailable, report, setup, timed_steps
 from atorch_b200.local_sgd import (LocalSGDConfig, OuterOptimizerConfig, OuterOptimPeriodicModelAverager,
                                    StatefulPostLocalSGDOptimizer)
 from atorch_b200.models.llama import LlamaConfig, LlamaDecoderLayer, LlamaModel
@@ -24,7 +24,11 @@ def main(argv=None):
     ap.add_argument("--H", type=int, default=32)
     ap.add_argument("--tiny", action="store_true")
     ap.add_argument("--windows", type=int, default=2)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     a = ap.parse_args(argv)
+    if a.impl == "reference":
+        reference_unavailable("the reference's FSDP local-SGD patch rewrites torch 2.1 / 2.4 FSDP internals (atorch/local_sgd/FSDP/__init__.py) and has not been validated against the torch 2.11 of this image")
+        return
     rank, world, dev = setup()
     cfg = LlamaConfig.tiny() if a.tiny else LlamaConfig.llama_1p3b()
     seq, mbs = (64, 2) if a.tiny else (2048, 4)

@@ -14,7 +14,7 @@ import argparse
 import torch
 
 from atorch_b200.auto import auto_accelerate
-from atorch_b200.benchmarks.common import report, setup, timed_steps
+from atorch_b200.benchmarks.common import reference_unavailable, report, setup, timed_steps
 from atorch_b200.distributed import distributed as D
 from atorch_b200.models.mixtral import MixtralConfig, MixtralDecoderLayer, MixtralModel
 from atorch_b200.modules.moe import Grouped_GEMM_MoE
@@ -30,7 +30,11 @@ def main(argv=None):
     ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--dispatcher", default="auto", choices=["auto", "PeerMemory", "AllToAll", "AllGather"],
                     help="auto: PeerMemory (capacity factor 1.25, own kernels over NVLink) on GPUs, AllToAll elsewhere")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     a = ap.parse_args(argv)
+    if a.impl == "reference":
+        reference_unavailable("the reference's FP8 grouped linear imports the `kitchen` package and its bf16 Grouped_GEMM_MoE imports `grouped_gemm`; neither is installed and no index is reachable")
+        return
     rank, world, dev = setup()
     if world > 1:
         D.create_parallel_group(([("expert", world)], None))

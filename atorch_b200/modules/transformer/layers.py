@@ -244,3 +244,50 @@ class CLIPAttentionFA(nn.Module):
         out = core(self.q_proj(hidden_states).view(shp), self.k_proj(hidden_states).view(shp),
                    self.v_proj(hidden_states).view(shp)).reshape(B, S, E)
         return self.out_proj(out), None
+
+
+class HFGLMSelfAttentionFA(nn.Module):
+    """Self-attention of the Hugging Face GLM models (``modeling_glm.py`` of THUDM/glm-10b: fused
+    ``query_key_value`` projection, ``dense`` output projection, attention and output dropout) with the flash
+    kernels. Built from a config or from an existing GLM ``SelfAttention`` module, whose parameters it keeps.
+
+    ``forward(hidden_states [b, s, h], ltor_mask [b, 1, s, s] (1 = visible), mem=None)``: the left-to-right mask
+    of GLM (bidirectional prefix, causal tail, per-sample separators) has one run of visible keys per row, so it is
+    lowered to key intervals (``ops.flash.intervals_from_additive_mask``) instead of being added to the scores;
+    any other mask takes the dense path. (Reference: atorch/modules/transformer/layers.py:1513-1632.)"""
+
+    def __init__(self, config=None, src_module: Optional[nn.Module] = None):
+        super().__init__()
+        if src_module is not None:
+            self.hidden_size = src_module.hidden_size
+            self.num_attention_heads = src_module.num_attention_heads
+            self.attention_scale = getattr(src_module, "attention_scale", 1.0)
+            self.query_key_value, self.dense = src_module.query_key_value, src_module.dense
+            self.attention_dropout = nn.Dropout(src_module.attention_dropout.p)
+            self.output_dropout = nn.Dropout(src_module.output_dropout.p)
+        else:
+            self.hidden_size = getattr(config, "hidden_size", 4096)
+            self.num_attention_heads = getattr(config, "num_attention_heads", 64)
+            self.attention_scale = getattr(config, "attention_scale", 1.0)
+            self.query_key_value = nn.Linear(self.hidden_size, 3 * self.hidden_size)
+            self.dense = nn.Linear(self.hidden_size, self.hidden_size)
+            self.attention_dropout = nn.Dropout(getattr(config, "attention_dropout_prob", 0.1))
+            self.output_dropout = nn.Dropout(getattr(config, "output_dropout_prob", 0.1))
+        assert self.hidden_size % self.num_attention_heads == 0
+        self.hidden_size_per_attention_head = self.hidden_size // self.num_attention_heads
+
+    @classmethod
+    def from_module(cls, src: nn.Module, **kwargs):
+        return cls(src_module=src)
+
+    def forward(self, hidden_states, ltor_mask, mem=None):
+        B, S, _ = hidden_states.shape
+        x = hidden_states if mem is None else torch.cat((mem, hidden_states), 1)
+        q, k, v = self.query_key_value(x).chunk(3, dim=-1)
+        if mem is not None:
+            q = q[:, -S:]
+        heads = lambda t: t.reshape(B, t.shape[1], self.num_attention_heads, self.hidden_size_per_attention_head)
+        p = self.attention_dropout.p if self.training else 0.0
+        ctx = ops.attention(heads(q), heads(k), heads(v), additive_mask=ltor_mask > 0.5 if ltor_mask.dtype != torch.bool
+                            else ltor_mask, dropout_p=p)
+        return self.output_dropout(self.dense(ctx.reshape(B, S, self.hidden_size)))

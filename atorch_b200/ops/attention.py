@@ -11,7 +11,9 @@ atorch/npu/layers.py:9-45):
   pair (s, e) each row ``i >= s`` sees every column ``j < e``.
 * ``key_padding_mask`` ``[B, S_k]``: True/1 = valid key.
 * ``cu_seqlens`` (packed sequences): tokens only see keys of their own sequence.
-* ``additive_mask`` / ``additive_bias``: added to the scaled scores before the softmax.
+* ``additive_mask`` / ``additive_bias``: added to the scaled scores before the softmax (a boolean
+  ``additive_mask`` means True = visible). A 0 / -inf mask shared by all heads with one run of visible keys per
+  row is lowered to key intervals and runs in the flash kernels; soft biases take the dense path.
 
 ``attention`` dispatches to the sm_100a flash-attention kernels when they are built and the
 problem fits them, and evaluates the dense PyTorch reference otherwise (CPU, unusual shapes).
@@ -70,7 +72,8 @@ def attention_reference(q, k, v, causal=False, softmax_scale=None, glm_mask=None
     if additive_bias is not None:
         s = s + additive_bias.float()
     if additive_mask is not None:
-        s = s + additive_mask.float()
+        s = s.masked_fill(~additive_mask, float("-inf")) if additive_mask.dtype == torch.bool \
+            else s + additive_mask.float()
     vis = build_dense_mask(B, Sq, Sk, q.device, causal, glm_mask, pack_glm_mask, key_padding_mask, cu_seqlens)
     if vis is not None:
         s = s.masked_fill(~vis, float("-inf"))
@@ -90,6 +93,14 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = 
     """Attention over ``[B, S, H, D]`` tensors with the mask options described in the module docstring."""
     from . import flash
 
+    if additive_mask is not None and additive_bias is None and glm_mask is None and pack_glm_mask is None \
+            and key_padding_mask is None and cu_seqlens is None and flash.supported(q, k, v, dropout_p):
+        # a dense 0 / -inf (or boolean) mask that is one run of visible keys per row runs in the flash kernels
+        iv = flash.intervals_from_additive_mask(additive_mask, q.shape[0], q.shape[1], k.shape[1], causal)
+        if iv is not None:
+            scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(q.shape[-1])
+            drop = flash.dropout_config(dropout_p) if dropout_p > 0.0 else None
+            return flash._FlashAttn.apply(q, k, v, False, float(scale), iv[0], iv[1], drop)
     if flash.supported(q, k, v, dropout_p, additive_mask, additive_bias, key_padding_mask):
         return flash.flash_attention(q, k, v, causal=causal, softmax_scale=softmax_scale, glm_mask=glm_mask,
                                      pack_glm_mask=pack_glm_mask, key_padding_mask=key_padding_mask,

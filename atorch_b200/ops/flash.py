@@ -105,6 +105,44 @@ def row_intervals(B: int, Sq: int, Sk: int, device, causal: bool = False, glm_ma
     return lo.to(torch.int32).contiguous(), hi.to(torch.int32).contiguous()
 
 
+def intervals_from_additive_mask(additive_mask: torch.Tensor, B: int, Sq: int, Sk: int, causal: bool = False):
+    """Lower a dense mask to per-row key intervals, or return ``None`` when it is not of that form.
+
+    ``additive_mask``: broadcastable to ``[B, 1, Sq, Sk]`` (the same for every head), either boolean (True =
+    visible) or additive with entries that are 0 (visible) or <= -1e4 (hidden) — the ``-65504 * (1 - ltor_mask)``
+    and ``-inf`` conventions. Causal, GLM prefix, packed-sequence and padding masks all have one contiguous run of
+    visible keys per row, which is what the kernels take; a mask with soft biases or holes is left to the dense
+    path. Costs one pass over the mask and one host synchronisation."""
+    m = additive_mask
+    if m.dim() == 4:
+        if m.shape[1] != 1:
+            return None
+        m = m[:, 0]
+    elif m.dim() == 2:
+        m = m[None]
+    if m.dim() != 3 or m.shape[-2:] != (Sq, Sk) or m.shape[0] not in (1, B):
+        return None
+    if m.dtype == torch.bool:
+        vis, binary = m, None
+    else:
+        vis = m > -1e4
+        binary = ((m == 0) | ~vis).all()
+    cnt = vis.sum(-1)
+    first = vis.int().argmax(-1)
+    last = Sk - 1 - vis.flip(-1).int().argmax(-1)
+    ok = ((cnt == 0) | (last - first + 1 == cnt)).all()
+    if binary is not None:
+        ok = ok & binary
+    if not bool(ok):
+        return None
+    lo = torch.where(cnt > 0, first, torch.zeros_like(first)).expand(B, Sq)
+    hi = torch.where(cnt > 0, last + 1, torch.zeros_like(last)).expand(B, Sq)
+    if causal:
+        i = torch.arange(Sq, device=m.device)
+        hi = torch.minimum(hi, (i + 1 + (Sk - Sq)).clamp(min=0)[None])
+    return lo.to(torch.int32).contiguous(), hi.to(torch.int32).contiguous()
+
+
 class NonContiguousKeyMask(ValueError):
     """The valid keys of some row are not contiguous: no per-row interval describes the mask."""
 

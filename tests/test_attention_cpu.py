@@ -62,3 +62,61 @@ def test_attention_reference_dropout_keeps_expectation():
     for _ in range(n):
         acc += attention_reference(q, k, v, causal=True, dropout_p=0.3)
     assert (acc / n - base).abs().mean().item() < 0.05
+
+
+def _glm_ltor_mask(B, S, seps):
+    m = torch.tril(torch.ones(S, S))[None].repeat(B, 1, 1)
+    for b, sep in enumerate(seps):
+        m[b, :, :sep] = 1
+    return m[:, None]                                  # [B, 1, S, S], 1 = visible
+
+
+def test_dense_binary_masks_lower_to_intervals():
+    B, S = 2, 40
+    ltor = _glm_ltor_mask(B, S, [7, 19])
+    for mask in (ltor > 0.5, -65504.0 * (1.0 - ltor), torch.where(ltor > 0.5, 0.0, float("-inf"))):
+        lo, hi = flash.intervals_from_additive_mask(mask, B, S, S)
+        j = torch.arange(S)
+        vis = (j[None, None] >= lo[:, :, None]) & (j[None, None] < hi[:, :, None])
+        assert torch.equal(vis, ltor[:, 0] > 0.5)
+    # with causal=True the upper end is clamped to the diagonal
+    lo, hi = flash.intervals_from_additive_mask(ltor > 0.5, B, S, S, causal=True)
+    assert torch.equal(hi, (torch.arange(S, dtype=torch.int32) + 1)[None].expand(B, S))
+    # a soft bias, a per-head mask and a mask with holes are not intervals
+    assert flash.intervals_from_additive_mask(torch.randn(B, 1, S, S), B, S, S) is None
+    assert flash.intervals_from_additive_mask(torch.zeros(B, 3, S, S), B, S, S) is None
+    holed = (ltor > 0.5).clone()
+    holed[0, 0, 20, 3] = False
+    assert flash.intervals_from_additive_mask(holed, B, S, S) is None
+    # fully hidden rows become empty intervals
+    hidden = (ltor > 0.5).clone()
+    hidden[1, 0, 5] = False
+    lo, hi = flash.intervals_from_additive_mask(hidden, B, S, S)
+    assert lo[1, 5] == 0 and hi[1, 5] == 0
+
+
+def test_glm_self_attention_module_matches_plain_math():
+    from types import SimpleNamespace
+
+    from atorch_b200.modules.transformer.layers import HFGLMSelfAttentionFA
+
+    torch.manual_seed(3)
+    cfg = SimpleNamespace(hidden_size=64, num_attention_heads=4, attention_dropout_prob=0.0, output_dropout_prob=0.0)
+    m = HFGLMSelfAttentionFA(cfg).eval()
+    B, S = 2, 24
+    x = torch.randn(B, S, 64)
+    ltor = _glm_ltor_mask(B, S, [5, 11])
+    out = m(x, ltor)
+    q, k, v = m.query_key_value(x).chunk(3, -1)
+    h = lambda t: t.view(B, S, 4, 16).transpose(1, 2)
+    s = h(q) @ h(k).transpose(-1, -2) / 4.0 + (-65504.0) * (1.0 - ltor)
+    ref = m.dense((torch.softmax(s, -1) @ h(v)).transpose(1, 2).reshape(B, S, 64))
+    assert torch.allclose(out, ref, atol=1e-5)
+    # with memory of earlier tokens the keys are longer than the queries
+    mem = torch.randn(B, 6, 64)
+    ltor2 = torch.cat([torch.ones(B, 1, S, 6), ltor], -1)
+    out2 = m(x, ltor2, mem=mem)
+    assert out2.shape == (B, S, 64)
+    # building from an existing module keeps its parameters
+    m2 = HFGLMSelfAttentionFA(src_module=m)
+    assert m2.query_key_value is m.query_key_value and torch.equal(m2(x, ltor), out)

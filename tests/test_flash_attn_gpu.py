@@ -258,3 +258,34 @@ def test_flash_dropout_matches_reference_with_the_same_mask(B, Sq, Sk, Hq, Hkv, 
     again = flash.flash_attention(q, k, v, causal=causal, dropout_p=p_drop, dropout_seed=seed)
     other = flash.flash_attention(q, k, v, causal=causal, dropout_p=p_drop, dropout_seed=seed + 1)
     assert torch.equal(again, out.detach()) and not torch.equal(other, out.detach())
+
+
+def test_dense_glm_mask_runs_in_the_flash_kernels():
+    """A [B, 1, S, S] left-to-right GLM mask (0 / -65504 additive form) is lowered to key intervals: the result
+    equals dense attention with the mask added to the scores, and no library or dense path is taken."""
+    from atorch_b200.ops import attention
+    import atorch_b200.ops.attention as A
+
+    torch.manual_seed(13)
+    B, S, H = 2, 384, 4
+    q, k, v = _qkv(B, S, S, H, H)
+    ltor = torch.tril(torch.ones(S, S, device="cuda"))[None].repeat(B, 1, 1)
+    ltor[0, :, :100] = 1
+    ltor[1, :, :257] = 1
+    add = (-65504.0 * (1.0 - ltor))[:, None].to(torch.bfloat16)
+    assert flash.intervals_from_additive_mask(add, B, S, S) is not None
+    before = A.library_calls
+    qs = [t.detach().clone().requires_grad_() for t in (q, k, v)]
+    out = attention(*qs, additive_mask=add)
+    dout = torch.randn_like(out)
+    out.backward(dout)
+    torch.cuda.synchronize()
+    _lib.check_status(q.device)
+    assert A.library_calls == before and type(out.grad_fn).__name__ == "_FlashAttnBackward"
+    rs = [t.detach().float().requires_grad_() for t in (q, k, v)]
+    ref = attention_reference(*rs, additive_mask=add.float())
+    ref.backward(dout.float())
+    assert torch.allclose(out.float(), ref, rtol=2e-2, atol=2e-2)
+    for name, a, b in zip("qkv", qs, rs):
+        err = (a.grad.float() - b.grad).abs().max().item()
+        assert err / (b.grad.abs().max().item() + 1e-6) < 3e-2, name
