@@ -264,7 +264,9 @@ def test_dense_glm_mask_runs_in_the_flash_kernels():
     """A [B, 1, S, S] left-to-right GLM mask (0 / -65504 additive form) is lowered to key intervals: the result
     equals dense attention with the mask added to the scores, and no library or dense path is taken."""
     from atorch_b200.ops import attention
-    import atorch_b200.ops.attention as A
+    import sys
+
+    A = sys.modules["atorch_b200.ops.attention"]      # the module (ops.attention is the function)
 
     torch.manual_seed(13)
     B, S, H = 2, 384, 4
