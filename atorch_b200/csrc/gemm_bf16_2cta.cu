@@ -58,6 +58,13 @@ struct Epi {
   // rs_base[rank] + (r % rs_rows) * ldc + column; C is not written
   float* rs_base[8];
   int rs_rows;
+  // gated (SwiGLU) epilogue: B is the fused gate|up weight [2 N, K] (K-major); a tile pairs gate rows
+  // [f0, f0 + BN/2) (CTA 0's half of B) with up rows [N + f0, ...) (CTA 1's half), so that accumulator columns c
+  // and BN/2 + c belong to the same output feature, and C[:, f0 + c] = silu(gate) * up is written as bf16. With
+  // gu_out != null the bf16 gate and up values are stored too ([M, 2 N], pitch ldgu) for the backward pass.
+  int gated;
+  void* gu_out;
+  long long ldgu;
 };
 
 // Arrival flags of the A operand (all-gather -> GEMM): rows [g * rows, (g + 1) * rows) are in place once
@@ -161,7 +168,8 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   const bool skip = status != nullptr && *reinterpret_cast<volatile int*>(status) != 0;
 
   const int tiles_m = (M + 2 * BM - 1) / (2 * BM);
-  const int tiles_n = (N + BN - 1) / BN;
+  const int tile_cols = ep.gated ? BN / 2 : BN;      // output columns per tile
+  const int tiles_n = (N + tile_cols - 1) / tile_cols;
   const int num_tiles = skip ? 0 : tiles_m * tiles_n;
   const int num_kb = (K + BK - 1) / BK;
   const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
@@ -225,7 +233,7 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       if (tm >= tiles_m) tm -= tiles_m;
     }
     m0 = tm * 2 * BM;
-    n0 = tn * BN;
+    n0 = tn * tile_cols;
   };
 
   if (warp == 0) {
@@ -237,7 +245,8 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         if (!tile_active(m0)) continue;
         const int am0 = m0 + (int)rank * BM;   // this CTA's rows of A
         const int bshift = grp.b_rows > 0 ? (m0 / grp.bm_rows) * grp.b_rows : 0;   // this expert's own B
-        const int bn0 = n0 + (int)rank * BNH + (B_MN ? 0 : bshift);   // this CTA's rows of B
+        // this CTA's rows of B (gated: CTA 0 takes gate rows, CTA 1 the up rows of the same features)
+        const int bn0 = ep.gated ? n0 + (int)rank * N : n0 + (int)rank * BNH + (B_MN ? 0 : bshift);
         const int bk0 = B_MN ? bshift : 0;
         if (gate.flags != nullptr && !gate_wait(gate, am0, min(am0 + BM, M), abort_flag, status)) goto producer_done;
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -342,6 +351,45 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       tc_fence_after();
       const int row = m0 + (int)rank * BM + q * 32 + lane;
       const uint32_t t_addr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+      if (ep.gated) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t g[32], u[32];
+          tmem_ld_32x32(t_addr + c * 32, g);
+          tmem_ld_32x32(t_addr + BN / 2 + c * 32, u);
+          tmem_ld_wait();
+          const int col0 = n0 + c * 32;
+          if (row < M && col0 < N) {
+            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(ep.C) + (long long)row * ep.ldc + col0;
+            __nv_bfloat16* grow = ep.gu_out == nullptr ? nullptr
+                : reinterpret_cast<__nv_bfloat16*>(ep.gu_out) + (long long)row * ep.ldgu + col0;
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              if (col0 + i < N) {
+                uint32_t gp[4], up[4], op[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  // round to bf16 first: the same values and the same formula as the separate SwiGLU kernel
+                  gp[j] = pack_bf16x2(__uint_as_float(g[i + 2 * j]), __uint_as_float(g[i + 2 * j + 1]));
+                  up[j] = pack_bf16x2(__uint_as_float(u[i + 2 * j]), __uint_as_float(u[i + 2 * j + 1]));
+                  const float2 a = unpack_bf16x2(gp[j]), b = unpack_bf16x2(up[j]);
+                  op[j] = pack_bf16x2(a.x / (1.f + __expf(-a.x)) * b.x, a.y / (1.f + __expf(-a.y)) * b.y);
+                }
+                *reinterpret_cast<uint4*>(crow + i) = make_uint4(op[0], op[1], op[2], op[3]);
+                if (grow != nullptr) {
+                  *reinterpret_cast<uint4*>(grow + i) = make_uint4(gp[0], gp[1], gp[2], gp[3]);
+                  *reinterpret_cast<uint4*>(grow + N + i) = make_uint4(up[0], up[1], up[2], up[3]);
+                }
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_remote(tempty_leader[acc]);
+        ++local;
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -470,7 +518,8 @@ int launch(const void* A, const void* B, const Epi& ep, int M, int N, int K, lon
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL) != cudaSuccess) return -4;
     attr_set = true;
   }
-  const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+  const int tile_cols = ep.gated ? BN / 2 : BN;
+  const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + tile_cols - 1) / tile_cols);
   int clusters = sm_count() / 2;
   if (tiles < clusters) clusters = tiles;
   if (max_ctas > 0 && clusters > max_ctas / 2) clusters = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
@@ -532,7 +581,7 @@ extern "C" int atb_gemm_bf16_2cta_grouped(const void* A, const void* B, void* C,
     grp.bm_rows = bm_group_rows;
     b_extent = n_b * b_group_rows;
   }
-  Epi ep{C, bias, ldc, alpha, out_fp32, accumulate, residual, ldr, {nullptr}, 0};
+  Epi ep{C, bias, ldc, alpha, out_fp32, accumulate, residual, ldr, {nullptr}, 0, 0, nullptr, 0};
   Gate gate{nullptr, 0u, 1, 0};
   if (g_fused_args.active) {   // set by atb_gemm_bf16_2cta_fused for this one launch
     gate = g_fused_args.gate;
@@ -566,6 +615,24 @@ extern "C" int atb_gemm_bf16_2cta(const void* A, const void* B, void* C, const v
   return atb_gemm_bf16_2cta_grouped(A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn_major, b_mn_major, out_fp32,
                                     accumulate, alpha, tile_n, max_ctas, residual, ldr, nullptr, 0, 0, 0, 0, 0, stream,
                                     status);
+}
+
+// act[M, F] = silu(x Wg^T) * (x Wu^T) for the fused weight W = [Wg; Wu] ([2 F, K], K-major, pitch ldb): the GEMM with
+// the gated epilogue (see Epi). gu_out (optional, [M, 2 F] bf16, pitch ldgu) receives the gate and up values the
+// backward pass needs. F % 8 == 0; x is [M, K] K-major with pitch lda.
+extern "C" int atb_gemm_bf16_2cta_swiglu(const void* A, const void* B, void* act, void* gu_out, int M, int F, int K,
+                                         long long lda, long long ldb, long long ld_act, long long ldgu, void* stream,
+                                         int* status) {
+  if (M <= 0 || F <= 0 || K <= 0) return 0;
+  if ((F & 7) || (lda & 7) || (ldb & 7) || (ld_act & 7) || (gu_out != nullptr && (ldgu & 7))) return -1;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(act) |
+       reinterpret_cast<uintptr_t>(gu_out)) & 15)
+    return -1;
+  Epi ep{act, nullptr, ld_act, 1.f, 0, 0, nullptr, 0, {nullptr}, 0, 1, gu_out, ldgu};
+  Groups grp{nullptr, 0, 0, 0, 0};
+  Gate gate{nullptr, 0u, 1, 0};
+  return launch<256, false, false>(A, B, ep, M, F, K, lda, ldb, 0, grp, 2 * F, gate,
+                                   reinterpret_cast<cudaStream_t>(stream), status);
 }
 
 // Upper bound of the arrival-flag waits of the all-gather -> GEMM form, in nanoseconds (default 2 s).

@@ -104,8 +104,8 @@ class RMSNorm(nn.Module):
     def reset_parameters(self):
         nn.init.ones_(self.weight)
 
-    def forward(self, x, residual=None):
-        return ops.rms_norm(x, self.weight, self.eps, residual)
+    def forward(self, x, residual=None, carry=False):
+        return ops.rms_norm(x, self.weight, self.eps, residual, carry)
 
 
 class LlamaDecoderLayer(nn.Module):
@@ -142,7 +142,10 @@ class LlamaDecoderLayer(nn.Module):
                 positions: Optional[torch.Tensor] = None, attn_kwargs: Optional[dict] = None) -> torch.Tensor:
         B, S, _ = h.shape
         d = self.config.head_dim
-        x = self.input_layernorm(h)
+        # carry=True: h comes back as a second output, so that its two gradients (norm path, residual path)
+        # are added inside the norm's backward kernel
+        pre = type(self.input_layernorm) is RMSNorm and type(self.post_attention_layernorm) is RMSNorm
+        x, h = self.input_layernorm(h, carry=True) if pre else (self.input_layernorm(h), h)
         qkv = self._proj(self.qkv_proj, x)
         S = qkv.shape[1]      # the projection may have gathered a sequence-sharded input (sequence parallelism)
         qkv = ops.rope(qkv, cos, sin, self.n_q + self.n_kv, d, positions, inplace=True)   # qkv is read by nothing else
@@ -158,8 +161,11 @@ class LlamaDecoderLayer(nn.Module):
         else:
             a = ops.attention(q, k, v, **kw)
         h = self._proj(self.o_proj, a.reshape(B, S, self.n_q * d), h)
-        x = self.post_attention_layernorm(h)
-        act = ops.swiglu(self._proj(self.gate_up_proj, x))
+        x, h = self.post_attention_layernorm(h, carry=True) if pre else (self.post_attention_layernorm(h), h)
+        if type(self.gate_up_proj) is nn.Linear and self.gate_up_proj.bias is None:
+            act = ops.linear_swiglu(x, self.gate_up_proj.weight)      # SwiGLU in the GEMM epilogue
+        else:
+            act = ops.swiglu(self._proj(self.gate_up_proj, x))
         h = self._proj(self.down_proj, act, h)
         return h
 

@@ -3,7 +3,7 @@
 Every op has a PyTorch reference implementation (``*_reference``) that is both the CPU path and the
 oracle the GPU numerics tests compare against.
 """
-from .gemm import gemm, gemm_reference, linear
+from .gemm import gemm, gemm_reference, linear, linear_swiglu
 from .norm import rms_norm, rms_norm_reference, layer_norm, layer_norm_reference
 from .elementwise import (rope, rope_reference, rope_tables, swiglu, swiglu_reference, bias_gather_add,
                           bias_gather_add_reference)

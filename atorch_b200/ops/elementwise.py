@@ -140,17 +140,21 @@ class _SwiGLU(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dout):
         (gu2,) = ctx.saved_tensors
-        F = gu2.shape[1] // 2
-        d2 = dout.reshape(-1, F)
-        d2 = d2 if d2.is_contiguous() else d2.contiguous()
-        dgu = torch.empty(gu2.shape[0], 2 * F, dtype=gu2.dtype, device=gu2.device)
-        # dgu is written with the pitch of gu2; a contiguous gu2 is the common case
-        src = gu2 if gu2.is_contiguous() else gu2.contiguous()
-        rc = _lib.lib().atb_swiglu_bwd(_lib.ptr(src), _lib.ptr(d2), _lib.ptr(dgu), ctypes.c_longlong(src.shape[0]),
-                                       ctypes.c_int(F), ctypes.c_longlong(2 * F), ctypes.c_longlong(F),
-                                       _lib.stream_ptr())
-        _lib.check(rc, "atb_swiglu_bwd")
-        return dgu.view(ctx.shp)
+        return swiglu_backward(gu2, dout.reshape(-1, gu2.shape[1] // 2)).view(ctx.shp)
+
+
+def swiglu_backward(gu2: torch.Tensor, d2: torch.Tensor) -> torch.Tensor:
+    """Gradient of ``silu(gate) * up`` with respect to the fused ``[T, 2F]`` gate|up tensor (kernel launch)."""
+    F = gu2.shape[1] // 2
+    d2 = d2 if d2.is_contiguous() else d2.contiguous()
+    dgu = torch.empty(gu2.shape[0], 2 * F, dtype=gu2.dtype, device=gu2.device)
+    # dgu is written with the pitch of gu2; a contiguous gu2 is the common case
+    src = gu2 if gu2.is_contiguous() else gu2.contiguous()
+    rc = _lib.lib().atb_swiglu_bwd(_lib.ptr(src), _lib.ptr(d2), _lib.ptr(dgu), ctypes.c_longlong(src.shape[0]),
+                                   ctypes.c_int(F), ctypes.c_longlong(2 * F), ctypes.c_longlong(F),
+                                   _lib.stream_ptr())
+    _lib.check(rc, "atb_swiglu_bwd")
+    return dgu
 
 
 def swiglu(gate_up: torch.Tensor) -> torch.Tensor:

@@ -148,6 +148,77 @@ def gemm(
     return out
 
 
+def _linear_grads(ctx, dy2, x2, weight, need_dx, need_dw):
+    """dx and dW of ``y = x W^T`` from ``dy``; dW goes straight into ``weight.main_grad`` when there is one."""
+    dx = dw = None
+    if need_dx:
+        dx = gemm(dy2, weight, b_mn=True, out_dtype=x2.dtype).view(ctx.x_shape)
+    if need_dw:
+        mg = getattr(ctx.weight_ref, "main_grad", None)
+        if mg is not None:
+            first = getattr(ctx.weight_ref, "_atb_first", False)     # untouched buffer: overwrite, no zero fill
+            gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, accumulate=not first)
+            ctx.weight_ref._atb_first = False
+            ctx.weight_ref.grad_added_to_main_grad = True
+        else:
+            dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=weight.dtype)
+    return dx, dw
+
+
+def gemm_swiglu(x2: torch.Tensor, weight: torch.Tensor, keep_gate_up: bool):
+    """``act = silu(x Wg^T) * (x Wu^T)`` for the fused weight ``[Wg; Wu]`` in one kernel (gated epilogue of the
+    CTA-pair GEMM); with ``keep_gate_up`` also the bf16 gate|up tensor ``[T, 2F]`` that the backward needs."""
+    T, K = x2.shape
+    F = weight.shape[0] // 2
+    act = torch.empty(T, F, dtype=x2.dtype, device=x2.device)
+    gu = torch.empty(T, 2 * F, dtype=x2.dtype, device=x2.device) if keep_gate_up else None
+    rc = _lib.lib().atb_gemm_bf16_2cta_swiglu(
+        _lib.ptr(x2), _lib.ptr(weight), _lib.ptr(act), _lib.ptr(gu), ctypes.c_int(T), ctypes.c_int(F), ctypes.c_int(K),
+        ctypes.c_longlong(_pitch(x2)), ctypes.c_longlong(_pitch(weight)), ctypes.c_longlong(F),
+        ctypes.c_longlong(2 * F), _lib.stream_ptr(), _lib.ptr(_lib.status_word(x2.device)))
+    _lib.check(rc, f"atb_gemm_bf16_2cta_swiglu T={T} F={F} K={K}")
+    return act, gu
+
+
+class _LinearSwiGLU(torch.autograd.Function):
+    """``swiglu(x @ W^T)`` with the activation computed in the GEMM epilogue. A pass that needs no gradient (the
+    first pass of an activation-checkpointed block) never writes the ``[T, 2F]`` pre-activation; a pass that does
+    writes it from the same epilogue, so the separate SwiGLU kernel and its read of that tensor disappear."""
+
+    @staticmethod
+    def forward(ctx, x, weight):
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1])
+        x2 = x2 if x2.stride(-1) == 1 else x2.contiguous()
+        need = ctx.needs_input_grad[0] or ctx.needs_input_grad[1]
+        act, gu = gemm_swiglu(x2, weight, need)
+        if need:
+            ctx.save_for_backward(x2, weight, gu)
+        ctx.x_shape, ctx.weight_ref = shp, weight
+        return act.view(*shp[:-1], act.shape[-1])
+
+    @staticmethod
+    def backward(ctx, dact):
+        from .elementwise import swiglu_backward
+
+        x2, weight, gu = ctx.saved_tensors
+        dgu = swiglu_backward(gu, dact.reshape(-1, dact.shape[-1]))
+        dx, dw = _linear_grads(ctx, dgu, x2, weight, ctx.needs_input_grad[0], ctx.needs_input_grad[1])
+        return dx, dw
+
+
+def linear_swiglu(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """``silu(x @ Wg.T) * (x @ Wu.T)`` for ``weight = [Wg; Wu]`` (``[2F, K]``), the gated MLP's first half."""
+    from .elementwise import swiglu
+
+    F = weight.shape[0] // 2
+    if not (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and _lib.use_kernels(x, weight)
+            and _lib.lib().has("atb_gemm_bf16_2cta_swiglu") and F % 8 == 0 and x.shape[-1] % 8 == 0
+            and weight.stride(-1) == 1 and PAIR_KERNEL_DEFAULT):
+        return swiglu(linear(x, weight))
+    return _LinearSwiGLU.apply(x, weight)
+
+
 class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias, residual):
@@ -173,18 +244,8 @@ class _Linear(torch.autograd.Function):
         dy2 = dy.reshape(-1, dy.shape[-1])
         if dy2.stride(-1) != 1:
             dy2 = dy2.contiguous()
-        dx = dw = db = dres = None
-        if ctx.needs_input_grad[0]:
-            dx = gemm(dy2, weight, b_mn=True, out_dtype=x2.dtype).view(ctx.x_shape)
-        if ctx.needs_input_grad[1]:
-            mg = getattr(ctx.weight_ref, "main_grad", None)
-            if mg is not None:
-                first = getattr(ctx.weight_ref, "_atb_first", False)     # untouched buffer: overwrite, no zero fill
-                gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, accumulate=not first)
-                ctx.weight_ref._atb_first = False
-                ctx.weight_ref.grad_added_to_main_grad = True
-            else:
-                dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=weight.dtype)
+        db = dres = None
+        dx, dw = _linear_grads(ctx, dy2, x2, weight, ctx.needs_input_grad[0], ctx.needs_input_grad[1])
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dy2.sum(0)
         if ctx.has_res and ctx.needs_input_grad[3]:

@@ -78,7 +78,7 @@ def _param_grad(param, partial, parts):
 
 class _Norm(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, residual, weight, bias, eps, ln):
+    def forward(ctx, x, residual, weight, bias, eps, ln, carry=False):
         shp = x.shape
         x2 = x.reshape(-1, shp[-1])
         x2 = x2 if x2.is_contiguous() else x2.contiguous()
@@ -92,6 +92,11 @@ class _Norm(torch.autograd.Function):
         ctx.w_ref, ctx.b_ref = weight, bias
         if residual is not None:
             return y.view(shp), s.view(shp)
+        if carry:
+            # second output: x itself (a second tensor over the same storage, no copy) for the residual path, so
+            # that the gradient arriving through it is added inside the backward kernel
+            return y.view(shp), torch.empty(0, dtype=x.dtype, device=x.device).set_(
+                x.untyped_storage(), x.storage_offset(), x.shape, x.stride())
         return y.view(shp)
 
     @staticmethod
@@ -108,7 +113,7 @@ class _Norm(torch.autograd.Function):
         dw = _param_grad(ctx.w_ref, pdw, parts) if ctx.needs_input_grad[2] else None
         db = _param_grad(ctx.b_ref, pdb, parts) if (need_db and ctx.needs_input_grad[3]) else None
         dx = dx.view(ctx.shp)
-        return dx, (dx if ctx.has_res else None), dw, db, None, None
+        return dx, (dx if ctx.has_res else None), dw, db, None, None, None
 
 
 def _kernel_ok(x, weight):
@@ -117,10 +122,18 @@ def _kernel_ok(x, weight):
 
 
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6,
-             residual: Optional[torch.Tensor] = None):
-    """``y = rmsnorm(x [+ residual]) * weight``; with ``residual`` also returns the sum ``x + residual``."""
+             residual: Optional[torch.Tensor] = None, carry: bool = False):
+    """``y = rmsnorm(x [+ residual]) * weight``; with ``residual`` also returns the sum ``x + residual``.
+
+    ``carry`` (without ``residual``): also return ``x`` for the residual branch of a pre-norm block. Using that
+    second output instead of ``x`` itself makes both gradients of ``x`` (through the norm and through the
+    residual path) arrive in one backward call, whose kernel adds them, instead of autograd summing them with a
+    separate pass over the activations."""
     if not _kernel_ok(x, weight):
-        return rms_norm_reference(x, weight, eps, residual)
+        y = rms_norm_reference(x, weight, eps, residual)
+        return (y, x) if (carry and residual is None) else y
+    if carry and residual is None:
+        return _Norm.apply(x, None, weight, None, eps, False, True)
     return _Norm.apply(x, residual, weight, None, eps, False)
 
 

@@ -194,3 +194,24 @@ def test_bias_gather_add():
     out.sum().backward()
     cnt = torch.bincount(idx, minlength=8).float()
     _close(bias.grad, cnt[:, None].expand(8, 256), 1e-2, 1e-2)
+
+
+def test_rmsnorm_carry_adds_the_residual_gradient_in_the_kernel():
+    """``carry=True`` hands x back for the residual path: no copy, and the gradient through it is added inside the
+    backward kernel. Same numbers as the plain form plus autograd's own add."""
+    torch.manual_seed(8)
+    x = torch.randn(512, 4096, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(4096, device="cuda", dtype=torch.bfloat16)
+    dy, dres = torch.randn_like(x), torch.randn_like(x)
+    xa, wa = x.clone().requires_grad_(), w.clone().requires_grad_()
+    h = xa * 1.0
+    y, carried = ops.rms_norm(h, wa, 1e-5, carry=True)
+    assert carried.data_ptr() == h.data_ptr() and torch.equal(carried, h)
+    torch.autograd.backward([y, carried], [dy, dres])
+    xb, wb = x.clone().requires_grad_(), w.clone().requires_grad_()
+    y2 = ops.rms_norm(xb, wb, 1e-5)
+    assert torch.equal(y, y2)
+    y2.backward(dy)
+    ref = xb.grad.float() + dres.float()
+    _close(xa.grad, ref, 2e-2, 2e-2)
+    assert torch.equal(wa.grad, wb.grad)

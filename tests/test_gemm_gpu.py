@@ -156,3 +156,35 @@ def test_grouped_gemm_with_device_counts():
     dw = torch.full((N, K), 3.0, device="cuda", dtype=torch.bfloat16)
     ops.gemm(dy[:W * cap], x[:W * cap], a_mn=True, b_mn=True, out=dw, groups={"counts": zc, "k_rows": cap})
     assert (dw == 0).all()
+
+
+@pytest.mark.parametrize("T,H,F", [(512, 1024, 1408), (1000, 512, 2752), (4096, 4096, 11008)])
+def test_linear_swiglu_epilogue_matches_separate_kernels(T, H, F):
+    """SwiGLU in the GEMM epilogue: the activation and the kept gate|up tensor are bit-identical to the GEMM
+    followed by the SwiGLU kernel, with and without gradients; gradients agree with the two-op form."""
+    from atorch_b200 import ops
+
+    torch.manual_seed(T + F)
+    x = _mk(T, H)
+    w = (_mk(2 * F, H) * 0.1).to(torch.bfloat16)
+    with torch.no_grad():
+        ref = ops.swiglu(ops.linear(x, w))
+        out = ops.linear_swiglu(x, w)
+    torch.cuda.synchronize()
+    _lib.check_status(x.device)
+    assert torch.equal(out, ref)
+    xa, wa = x.clone().requires_grad_(), w.clone().requires_grad_()
+    xb, wb = x.clone().requires_grad_(), w.clone().requires_grad_()
+    ya = ops.linear_swiglu(xa, wa)
+    yb = ops.swiglu(ops.linear(xb, wb))
+    assert type(ya.grad_fn).__name__ == "_LinearSwiGLUBackward" and torch.equal(ya, yb)
+    dy = _mk(T, F)
+    ya.backward(dy)
+    yb.backward(dy)
+    torch.cuda.synchronize()
+    _lib.check_status(x.device)
+    assert torch.equal(xa.grad, xb.grad) and torch.equal(wa.grad, wb.grad)
+    # against fp32 math
+    g = x.float() @ w.float().t()
+    full = torch.nn.functional.silu(g[:, :F]) * g[:, F:]
+    _check(out, full, H)
