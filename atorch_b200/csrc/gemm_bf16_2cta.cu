@@ -69,10 +69,13 @@ struct Epi {
 
 // Arrival flags of the A operand (all-gather -> GEMM): rows [g * rows, (g + 1) * rows) are in place once
 // flags[g] >= epoch (wrap-safe). rot = first tile row to visit (this rank's own shard).
+// on_b: the flags describe rows of B (a weight gathered from row shards) instead of rows of A; rot then counts
+// tile columns.
 struct Gate {
   const unsigned int* flags;
   unsigned int epoch;
   int rows, rot;
+  int on_b;
 };
 
 __device__ unsigned long long g_gate_wait_ns = ATB_WAIT_LIMIT_NS;
@@ -226,11 +229,16 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const int band = tile / band_tiles;
     const int rem = tile - band * band_tiles;
     const int rows_in_band = min(BAND, tiles_m - band * BAND);
-    const int tn = rem / rows_in_band;
+    int tn = rem / rows_in_band;
     int tm = band * BAND + (rem - tn * rows_in_band);
     if (gate.rot > 0) {          // start with the rows that are already here
-      tm += gate.rot;
-      if (tm >= tiles_m) tm -= tiles_m;
+      if (gate.on_b) {
+        tn += gate.rot;
+        if (tn >= tiles_n) tn -= tiles_n;
+      } else {
+        tm += gate.rot;
+        if (tm >= tiles_m) tm -= tiles_m;
+      }
     }
     m0 = tm * 2 * BM;
     n0 = tn * tile_cols;
@@ -248,7 +256,11 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         // this CTA's rows of B (gated: CTA 0 takes gate rows, CTA 1 the up rows of the same features)
         const int bn0 = ep.gated ? n0 + (int)rank * N : n0 + (int)rank * BNH + (B_MN ? 0 : bshift);
         const int bk0 = B_MN ? bshift : 0;
-        if (gate.flags != nullptr && !gate_wait(gate, am0, min(am0 + BM, M), abort_flag, status)) goto producer_done;
+        if (gate.flags != nullptr) {
+          const bool here = gate.on_b ? gate_wait(gate, min(bn0, N - 1), min(bn0 + BNH, N), abort_flag, status)
+                                      : gate_wait(gate, am0, min(am0 + BM, M), abort_flag, status);
+          if (!here) goto producer_done;
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!kb_active(kb)) continue;
           const int s = it % STAGES;
@@ -633,6 +645,23 @@ extern "C" int atb_gemm_bf16_2cta_swiglu(const void* A, const void* B, void* act
   Gate gate{nullptr, 0u, 1, 0};
   return launch<256, false, false>(A, B, ep, M, F, K, lda, ldb, 0, grp, 2 * F, gate,
                                    reinterpret_cast<cudaStream_t>(stream), status);
+}
+
+// Weight all-gather -> GEMM (a linear layer whose weight is sharded by rows over the ranks): C = A B^T with
+// B [N, K] K-major arriving in shards of gate_rows rows (a multiple of 128); shard g is in place once
+// gate_flags[g] >= gate_epoch. Tiles start at column gate_first_row (a multiple of 256: this rank's own shard).
+extern "C" int atb_gemm_bf16_2cta_wgather(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                                          long long ldb, long long ldc, const unsigned int* gate_flags,
+                                          unsigned int gate_epoch, int gate_rows, int gate_first_row, void* stream,
+                                          int* status) {
+  if (gate_flags == nullptr || gate_rows <= 0 || (gate_rows % 128) || gate_first_row < 0 || (gate_first_row % 256))
+    return -1;
+  FusedArgs fa = {true, {gate_flags, gate_epoch, gate_rows, gate_first_row / 256, 1}, {nullptr}, 0};
+  g_fused_args = fa;
+  const int rc = atb_gemm_bf16_2cta_grouped(A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0, 0, 0, 0, 1.f, 0, 0, nullptr, 0,
+                                            nullptr, 0, 0, 0, 0, 0, stream, status);
+  g_fused_args.active = false;
+  return rc;
 }
 
 // Upper bound of the arrival-flag waits of the all-gather -> GEMM form, in nanoseconds (default 2 s).

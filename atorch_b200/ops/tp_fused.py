@@ -120,11 +120,12 @@ def _ag_gemm(x_local: torch.Tensor, b: torch.Tensor, b_mn: bool, group) -> Tuple
     return y, x_full
 
 
-def _gemm_rs(a: torch.Tensor, b: torch.Tensor, b_mn: bool, group) -> torch.Tensor:
-    """``reduce_scatter(a[S, K] @ op(b))`` -> y_local [S/W, N] (bf16)."""
+def _gemm_rs(a: torch.Tensor, b: torch.Tensor, b_mn: bool, group, a_mn: bool = False,
+             out_dtype=torch.bfloat16) -> torch.Tensor:
+    """``reduce_scatter(op(a)[S, K] @ op(b))`` -> y_local [S/W, N]; ``a_mn``: a is stored ``[K, S]``."""
     from ..parallel.symm import CH_ARRIVE, CH_READY
 
-    S, K = a.shape
+    K, S = a.shape if a_mn else a.shape[::-1]
     N = b.shape[1] if b_mn else b.shape[0]
     W = dist.get_world_size(group)
     rows = S // W
@@ -135,13 +136,13 @@ def _gemm_rs(a: torch.Tensor, b: torch.Tensor, b_mn: bool, group) -> torch.Tenso
     a = a if a.stride(-1) == 1 else a.contiguous()
     rc = _lib.lib().atb_gemm_bf16_2cta_fused(
         _lib.ptr(a), _lib.ptr(b), None, ctypes.c_int(S), ctypes.c_int(N), ctypes.c_int(K),
-        ctypes.c_longlong(a.stride(0)), ctypes.c_longlong(b.stride(0)), ctypes.c_longlong(N), ctypes.c_int(0),
-        ctypes.c_int(int(b_mn)), ctypes.c_float(1.0), None, ctypes.c_uint(0), ctypes.c_int(0), ctypes.c_int(0),
-        c._acc_ptrs, ctypes.c_int(W), ctypes.c_int(rows), _lib.stream_ptr(), _lib.ptr(_lib.status_word(a.device)))
+        ctypes.c_longlong(a.stride(0)), ctypes.c_longlong(b.stride(0)), ctypes.c_longlong(N),
+        ctypes.c_int(int(a_mn)), ctypes.c_int(int(b_mn)), ctypes.c_float(1.0), None, ctypes.c_uint(0), ctypes.c_int(0),
+        ctypes.c_int(0), c._acc_ptrs, ctypes.c_int(W), ctypes.c_int(rows), _lib.stream_ptr(), _lib.ptr(_lib.status_word(a.device)))
     _lib.check(rc, "atb_gemm_bf16_2cta_fused (GEMM -> reduce-scatter)")
     c.acc.signal(CH_ARRIVE, c.acc.seq)       # my contributions are out
     c.acc.wait(CH_ARRIVE, c.acc.seq)         # ... and everybody's are in
-    y = c.acc.tensor.view(rows, N).to(torch.bfloat16)
+    y = c.acc.tensor.view(rows, N).to(out_dtype, copy=True)
     c.acc.tensor.zero_()
     c.acc.signal(CH_READY, c.acc.seq)
     return y
@@ -214,3 +215,134 @@ def linear_reduce_scatter(x: torch.Tensor, weight: torch.Tensor, group) -> torch
     x2 = x.reshape(-1, x.shape[-1])
     y = _LinearReduceScatter.apply(x2, weight, group)
     return y.view(*lead, y.shape[0], y.shape[1])
+
+
+# ------------------------------------------------------------------------------------------------------
+# Row-sharded weight (per-parameter ZeRO-3 / FSDP sharding along dim 0): the all-gather of the weight is fused
+# into the GEMM that consumes it, the reduce-scatter of its gradient into the GEMM that produces it.
+# ------------------------------------------------------------------------------------------------------
+def _gather_rows(w_shard: torch.Tensor, group, wait: bool):
+    """Copy-engine all-gather of ``w_shard [N/W, K]`` into a full ``[N, K]`` tensor, one arrival flag per shard.
+    Returns (w_full, context, event); with ``wait`` the current stream waits for all shards."""
+    from ..parallel.symm import CH_DONE, CH_READY
+
+    rows, K = w_shard.shape
+    c = _ctx(group, rows, K, w_shard.device)
+    W, r = c.world, c.rank
+    cur = torch.cuda.current_stream(w_shard.device)
+    if c.x.seq > 0:
+        c.x.wait(CH_DONE, c.x.seq)
+    c.x.tensor.view(rows, K).copy_(w_shard)
+    c.x.seq += 1
+    c.x.signal(CH_READY, c.x.seq)
+    w_full = torch.empty(W * rows, K, dtype=torch.bfloat16, device=w_shard.device)
+    c.epoch += 1
+    c.copy_stream.wait_stream(cur)
+    with torch.cuda.stream(c.copy_stream):
+        w_full[r * rows: (r + 1) * rows].copy_(c.x.tensor.view(rows, K))
+        c.flags[r: r + 1].fill_(c.epoch)
+        c.x.wait(CH_READY, c.x.seq)
+        for k in range(1, W):
+            p = (r + k) % W
+            w_full[p * rows: (p + 1) * rows].copy_(c.x.peer_view(p).view(rows, K), non_blocking=True)
+            c.flags[p: p + 1].fill_(c.epoch)
+        c.x.signal(CH_DONE, c.x.seq)
+        ev = torch.cuda.Event()
+        ev.record(c.copy_stream)
+    w_full.record_stream(c.copy_stream)
+    if wait:
+        cur.wait_event(ev)
+    return w_full, c, ev
+
+
+class _ShardedWeightLinear(torch.autograd.Function):
+    """``y = x @ all_gather(w_shard)^T``. Forward: the GEMM starts with this rank's own rows of the weight and its
+    TMA producer waits (bounded) on the arrival flag of the shard a tile's weight rows come from. Backward: the
+    weight is gathered again (it is not kept between the passes, as with reshard-after-forward), ``dx`` is a
+    plain GEMM and the weight gradient ``dy^T x``, summed over the ranks, is added row by row into its owner's
+    fp32 buffer by the GEMM epilogue, so each rank ends with the gradient of its own shard."""
+
+    @staticmethod
+    def forward(ctx, x, w_shard, group):
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1])
+        x2 = x2 if x2.stride(-1) == 1 else x2.contiguous()
+        w_full, c, ev = _gather_rows(w_shard, group, wait=False)
+        M, K = x2.shape
+        N = w_full.shape[0]
+        y = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+        rc = _lib.lib().atb_gemm_bf16_2cta_wgather(
+            _lib.ptr(x2), _lib.ptr(w_full), _lib.ptr(y), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
+            ctypes.c_longlong(x2.stride(0)), ctypes.c_longlong(K), ctypes.c_longlong(N), _lib.ptr(c.flags),
+            ctypes.c_uint(c.epoch), ctypes.c_int(c.rows), ctypes.c_int(c.rank * c.rows), _lib.stream_ptr(),
+            _lib.ptr(_lib.status_word(x.device)))
+        _lib.check(rc, "atb_gemm_bf16_2cta_wgather (weight all-gather -> GEMM)")
+        torch.cuda.current_stream(x.device).wait_event(ev)     # w_full is freed after this call
+        ctx.save_for_backward(x2, w_shard)
+        ctx.group, ctx.x_shape, ctx.w_ref = group, shp, w_shard
+        return y.view(*shp[:-1], N)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w_shard = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        dy2 = dy2 if dy2.is_contiguous() else dy2.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            w_full, _, _ = _gather_rows(w_shard, ctx.group, wait=True)
+            dx = gemm(dy2, w_full, b_mn=True, out_dtype=x2.dtype).view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            # dW [N, K] = dy^T x, reduce-scattered over its rows: both operands are read as stored
+            g = _gemm_rs(dy2, x2, True, ctx.group, a_mn=True, out_dtype=torch.float32)
+            mg = getattr(ctx.w_ref, "main_grad", None)
+            if mg is not None:
+                mg.add_(g) if mg.dtype == g.dtype else mg.add_(g.to(mg.dtype))
+                ctx.w_ref.grad_added_to_main_grad = True
+            else:
+                dw = g.to(w_shard.dtype)
+        return dx, dw, None
+
+
+def sharded_weight_available(group, rows_local: int, n_total: int, k: int) -> bool:
+    L = _lib.lib()
+    return (available(group) and L.has("atb_gemm_bf16_2cta_wgather") and rows_local % 256 == 0 and k % 8 == 0
+            and n_total % 8 == 0)
+
+
+def sharded_weight_linear(x: torch.Tensor, w_shard: torch.Tensor, group) -> torch.Tensor:
+    """Linear layer whose weight ``[N, K]`` is sharded by rows over ``group`` (``w_shard [N/W, K]`` on each rank),
+    every rank with its own ``x``: the data-parallel ZeRO-3 case. The weight gradient returned (or added to
+    ``w_shard.main_grad``) is the SUM over the ranks of the gradient rows this rank owns."""
+    W = dist.get_world_size(group)
+    if x.dtype == torch.bfloat16 and w_shard.dtype == torch.bfloat16 and x.is_cuda and \
+            sharded_weight_available(group, w_shard.shape[0], w_shard.shape[0] * W, w_shard.shape[1]):
+        return _ShardedWeightLinear.apply(x, w_shard, group)
+    return _ShardedWeightLinearRef.apply(x, w_shard, group)
+
+
+class _ShardedWeightLinearRef(torch.autograd.Function):
+    """The same contract with ``torch.distributed`` collectives around plain matmuls (CPU / gloo, odd shapes)."""
+
+    @staticmethod
+    def forward(ctx, x, w_shard, group):
+        W = dist.get_world_size(group)
+        parts = [torch.empty_like(w_shard) for _ in range(W)]
+        dist.all_gather(parts, w_shard.contiguous(), group=group)
+        w_full = torch.cat(parts, 0)
+        ctx.save_for_backward(x, w_shard)
+        ctx.group = group
+        return x @ w_full.t()
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w_shard = ctx.saved_tensors
+        W = dist.get_world_size(ctx.group)
+        parts = [torch.empty_like(w_shard) for _ in range(W)]
+        dist.all_gather(parts, w_shard.contiguous(), group=ctx.group)
+        w_full = torch.cat(parts, 0)
+        dx = dy @ w_full
+        dw_full = (dy.reshape(-1, dy.shape[-1]).float().t() @ x.reshape(-1, x.shape[-1]).float())
+        dist.all_reduce(dw_full, group=ctx.group)
+        r = dist.get_rank(ctx.group)
+        rows = w_shard.shape[0]
+        return dx, dw_full[r * rows: (r + 1) * rows].to(w_shard.dtype), None

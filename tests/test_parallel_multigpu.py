@@ -333,3 +333,43 @@ def test_allgather_gemm_gate_times_out_cleanly():
     torch.cuda.synchronize()
     _lib.check_status(dev)
     assert torch.allclose(out.float(), ref, rtol=2e-2, atol=2e-1)
+
+
+# --------------------------------------------- row-sharded weight: all-gather fused into the consuming GEMM
+def _sharded_weight(rank, world):
+    """ops.tp_fused.sharded_weight_linear (weight all-gather -> GEMM, weight-gradient GEMM -> reduce-scatter)
+    against the torch.distributed form, twice in a row; every rank has its own input (data parallel)."""
+    import torch.distributed as dist
+
+    from atorch_b200 import _lib
+    from atorch_b200.ops import tp_fused
+
+    dev = torch.device("cuda", rank)
+    rows, K, M = 256, 384, 640
+    N = rows * world
+    assert tp_fused.sharded_weight_available(dist.group.WORLD, rows, N, K)
+    for it in range(2):
+        gw = torch.Generator().manual_seed(500 + it)
+        w_full = (0.05 * torch.randn(N, K, generator=gw)).bfloat16()
+        w_shard = w_full[rank * rows:(rank + 1) * rows].to(dev).requires_grad_()
+        g = torch.Generator().manual_seed(11 + 17 * rank + it)
+        x = (0.5 * torch.randn(M, K, generator=g)).to(dev).bfloat16().requires_grad_()
+        y = tp_fused.sharded_weight_linear(x, w_shard, dist.group.WORLD)
+        assert type(y.grad_fn).__name__ == "_ShardedWeightLinearBackward"
+        ref = x.detach().float() @ w_full.to(dev).float().t()
+        assert torch.allclose(y.float(), ref, rtol=2e-2, atol=2e-2), (it, (y.float() - ref).abs().max())
+        gy = torch.randn(M, N, generator=g).to(dev).bfloat16()
+        y.backward(gy)
+        dx_ref = gy.float() @ w_full.to(dev).float()
+        assert torch.allclose(x.grad.float(), dx_ref, rtol=3e-2, atol=3e-2 * dx_ref.abs().max().item()), it
+        dw = gy.float().t() @ x.detach().float()
+        dist.all_reduce(dw)
+        dw_ref = dw[rank * rows:(rank + 1) * rows]
+        assert torch.allclose(w_shard.grad.float(), dw_ref, rtol=3e-2, atol=3e-2 * dw_ref.abs().max().item()), it
+    torch.cuda.synchronize()
+    _lib.check_status(dev)
+
+
+@pytest.mark.skipif(NGPU < 2, reason="needs 2 GPUs")
+def test_sharded_weight_linear_fused_with_collectives():
+    run_distributed(_sharded_weight, world=min(NGPU, 4) if NGPU != 3 else 2, backend="nccl", timeout=300)

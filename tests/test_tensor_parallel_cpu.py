@@ -220,3 +220,32 @@ def _megatron_blocks(rank, world):
 
 def test_megatron_style_blocks_match_hf_layers_gloo():
     run_distributed(_megatron_blocks, world=2)
+
+
+def _sharded_weight_ref(rank, world):
+    import torch.distributed as dist
+
+    from atorch_b200.ops import tp_fused
+
+    rows, K, M = 6, 10, 7
+    torch.manual_seed(3)
+    w_full = torch.randn(rows * world, K)
+    w_shard = w_full[rank * rows:(rank + 1) * rows].clone().requires_grad_()
+    torch.manual_seed(20 + rank)
+    x = torch.randn(M, K, requires_grad=True)
+    y = tp_fused.sharded_weight_linear(x, w_shard, dist.group.WORLD)
+    assert torch.allclose(y, x.detach() @ w_full.t(), atol=1e-5)
+    gy = torch.randn(M, rows * world)
+    y.backward(gy)
+    assert torch.allclose(x.grad, gy @ w_full, atol=1e-5)
+    dw = gy.t() @ x.detach()
+    dist.all_reduce(dw)
+    assert torch.allclose(w_shard.grad, dw[rank * rows:(rank + 1) * rows], atol=1e-4)
+
+
+def test_sharded_weight_linear_reference_form_gloo():
+    """Row-sharded weight, every rank its own input: output from the gathered weight, weight gradient summed over
+    the ranks and scattered by rows (the contract the fused GPU form is tested against)."""
+    from tests.dist_utils import run_distributed
+
+    run_distributed(_sharded_weight_ref, world=2, backend="gloo", timeout=120)
