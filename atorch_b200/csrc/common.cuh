@@ -389,6 +389,13 @@ struct DropParams {
   uint32_t seed_lo, seed_hi;
   float keep_scale;    // 65536 / (65536 - thr16)
 };
+// Additive attention bias (bf16), added to the scaled scores: element (b, h, i, j) at ptr[b sb + h sh + i sq + j];
+// sb / sh = 0 broadcast over batch / heads. Rows are read in 16-byte pieces: sq, sb, sh and the key count are
+// multiples of 8 and ptr is 16-byte aligned. ptr == nullptr: none.
+struct BiasParams {
+  const __nv_bfloat16* ptr;
+  long long sb, sh, sq;
+};
 ATB_HOST_DEVICE uint32_t hash32(uint32_t x) {
   x ^= x >> 16; x *= 0x7feb352dU; x ^= x >> 15; x *= 0x846ca68bU; x ^= x >> 16;
   return x;

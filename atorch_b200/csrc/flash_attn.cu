@@ -45,6 +45,8 @@ struct FwdParams {
   float scale_log2;   // softmax scale * log2(e)
   int* status;
   DropParams drop;    // attention dropout (thr16 == 0: none)
+  BiasParams bias;    // additive bias on the scaled scores (ptr == nullptr: none)
+  float inv_scale;    // 1 / softmax scale: the bias is folded into the raw scores
 };
 
 struct SmemLayout {
@@ -60,7 +62,7 @@ struct SmemLayout {
   static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 64 + 1024;
 };
 
-template <bool DROP>
+template <bool DROP, bool BIAS>
 __global__ void __launch_bounds__(THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, FwdParams p) {
@@ -279,6 +281,27 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_free[sb]);
+      if constexpr (BIAS) {
+        // s + bias / scale, so that the scale folded into the exponent leaves the bias as given
+        if (row_valid) {
+          const int cb = kv0 + half * 64;
+          const __nv_bfloat16* bp = p.bias.ptr + (long long)b * p.bias.sb + (long long)h * p.bias.sh +
+                                    (long long)i * p.bias.sq + cb;
+#pragma unroll
+          for (int c8 = 0; c8 < 8; ++c8) {
+            if (cb + c8 * 8 < p.Sk) {
+              const uint4 u = *reinterpret_cast<const uint4*>(bp + c8 * 8);
+              const float2 b0 = unpack_bf16x2(u.x), b1 = unpack_bf16x2(u.y), b2 = unpack_bf16x2(u.z),
+                           b3 = unpack_bf16x2(u.w);
+              float* d = sv + c8 * 8;
+              d[0] = fmaf(b0.x, p.inv_scale, d[0]); d[1] = fmaf(b0.y, p.inv_scale, d[1]);
+              d[2] = fmaf(b1.x, p.inv_scale, d[2]); d[3] = fmaf(b1.y, p.inv_scale, d[3]);
+              d[4] = fmaf(b2.x, p.inv_scale, d[4]); d[5] = fmaf(b2.y, p.inv_scale, d[5]);
+              d[6] = fmaf(b3.x, p.inv_scale, d[6]); d[7] = fmaf(b3.y, p.inv_scale, d[7]);
+            }
+          }
+        }
+      }
       const bool tile_full = (kv0 >= full_lo) && (kv0 + BKV <= full_hi);
       if (!tile_full) {
         const int c0 = kv0 + half * 64;
@@ -396,7 +419,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 static int flash_fwd_launch(const void* q, const void* k, const void* v, void* o, float* lse, const int* row_lo,
                             const int* row_hi, int B, int Sq, int Sk, int Hq, int Hkv, long long q_stride,
                             long long k_stride, long long v_stride, int causal, float softmax_scale, void* stream,
-                            int* status, DropParams drop) {
+                            int* status, DropParams drop, BiasParams bias = BiasParams{nullptr, 0, 0, 0}) {
   if (B <= 0 || Sq <= 0 || Sk <= 0) return 0;
   if (Hq % Hkv) return -1;
   if ((q_stride | k_stride | v_stride) & 7) return -1;
@@ -412,11 +435,15 @@ static int flash_fwd_launch(const void* q, const void* k, const void* v, void* o
     return -2;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(flash_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             SmemLayout::TOTAL) != cudaSuccess ||
-        cudaFuncSetAttribute(flash_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             SmemLayout::TOTAL) != cudaSuccess)
-      return -4;
+    const bool ok = cudaFuncSetAttribute(flash_fwd_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         SmemLayout::TOTAL) == cudaSuccess &&
+                    cudaFuncSetAttribute(flash_fwd_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         SmemLayout::TOTAL) == cudaSuccess &&
+                    cudaFuncSetAttribute(flash_fwd_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         SmemLayout::TOTAL) == cudaSuccess &&
+                    cudaFuncSetAttribute(flash_fwd_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         SmemLayout::TOTAL) == cudaSuccess;
+    if (!ok) return -4;
     attr_set = true;
   }
   FwdParams p;
@@ -425,11 +452,22 @@ static int flash_fwd_launch(const void* q, const void* k, const void* v, void* o
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = status;
   p.drop = drop;
+  p.bias = bias;
+  p.inv_scale = 1.f / softmax_scale;
+  if (bias.ptr != nullptr &&
+      ((Sk & 7) || ((bias.sb | bias.sh | bias.sq) & 7) || (reinterpret_cast<uintptr_t>(bias.ptr) & 15) ||
+       !(softmax_scale > 0.f)))
+    return -1;
   dim3 grid((Sq + BQ - 1) / BQ, Hq, B);
-  if (drop.thr16 != 0)
-    flash_fwd_kernel<true><<<grid, THREADS, SmemLayout::TOTAL, (cudaStream_t)stream>>>(tmQ, tmK, tmV, p);
+  const cudaStream_t st = (cudaStream_t)stream;
+  if (drop.thr16 != 0 && bias.ptr != nullptr)
+    flash_fwd_kernel<true, true><<<grid, THREADS, SmemLayout::TOTAL, st>>>(tmQ, tmK, tmV, p);
+  else if (drop.thr16 != 0)
+    flash_fwd_kernel<true, false><<<grid, THREADS, SmemLayout::TOTAL, st>>>(tmQ, tmK, tmV, p);
+  else if (bias.ptr != nullptr)
+    flash_fwd_kernel<false, true><<<grid, THREADS, SmemLayout::TOTAL, st>>>(tmQ, tmK, tmV, p);
   else
-    flash_fwd_kernel<false><<<grid, THREADS, SmemLayout::TOTAL, (cudaStream_t)stream>>>(tmQ, tmK, tmV, p);
+    flash_fwd_kernel<false, false><<<grid, THREADS, SmemLayout::TOTAL, st>>>(tmQ, tmK, tmV, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
@@ -452,4 +490,18 @@ extern "C" int atb_flash_fwd_dropout(const void* q, const void* k, const void* v
   return flash_fwd_launch(q, k, v, o, lse, row_lo, row_hi, B, Sq, Sk, Hq, Hkv, q_stride, k_stride, v_stride, causal,
                           softmax_scale, stream, status,
                           DropParams{thr16, seed_lo, seed_hi, 65536.f / (float)(65536u - thr16)});
+}
+
+// With an additive bias on the scaled scores (see BiasParams in common.cuh) and, if thr16 != 0, dropout.
+extern "C" int atb_flash_fwd_bias(const void* q, const void* k, const void* v, void* o, float* lse, const int* row_lo,
+                                  const int* row_hi, int B, int Sq, int Sk, int Hq, int Hkv, long long q_stride,
+                                  long long k_stride, long long v_stride, int causal, float softmax_scale,
+                                  void* stream, int* status, unsigned thr16, unsigned seed_lo, unsigned seed_hi,
+                                  const void* bias, long long bias_sb, long long bias_sh, long long bias_sq) {
+  if (thr16 >= 65536u || bias == nullptr) return -1;
+  const DropParams drop = thr16 ? DropParams{thr16, seed_lo, seed_hi, 65536.f / (float)(65536u - thr16)}
+                                : DropParams{0u, 0u, 0u, 1.f};
+  return flash_fwd_launch(q, k, v, o, lse, row_lo, row_hi, B, Sq, Sk, Hq, Hkv, q_stride, k_stride, v_stride, causal,
+                          softmax_scale, stream, status, drop,
+                          BiasParams{(const __nv_bfloat16*)bias, bias_sb, bias_sh, bias_sq});
 }

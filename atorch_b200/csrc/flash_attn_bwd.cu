@@ -47,6 +47,8 @@ struct BwdParams {
   float scale, scale_log2;
   int* status;
   DropParams drop;     // attention dropout of the forward pass (thr16 == 0: none)
+  BiasParams bias;     // additive bias of the forward pass (ptr == nullptr: none); not differentiated
+  float inv_scale;
 };
 
 struct SmemB {
@@ -72,7 +74,7 @@ struct RowInfo {
 
 // WITH_DQ = false: key/value gradients only (the query gradient then comes from flash_attn_bwd_dq.cu): the
 // dQ product, its staging and the reduce-add are compiled out and dP(i+1) follows dK(i) without a hand-shake.
-template <bool WITH_DQ, bool DROP = false>
+template <bool WITH_DQ, bool DROP = false, bool BIAS = false>
 __global__ void __launch_bounds__(THREADS, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                  const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -350,6 +352,26 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_ld_32x32(tS + 32, s1);
         tmem_ld_wait();
         const int c0 = kv0 + half * 64;
+        if constexpr (BIAS) {
+          if (cur.valid) {     // s + bias / scale, exactly as the forward pass formed it
+            const __nv_bfloat16* bp = p.bias.ptr + (long long)b * p.bias.sb + (long long)h * p.bias.sh +
+                                      (long long)cur.i * p.bias.sq + c0;
+#pragma unroll
+            for (int c8 = 0; c8 < 8; ++c8) {
+              if (c0 + c8 * 8 < p.Sk) {
+                const uint4 u = *reinterpret_cast<const uint4*>(bp + c8 * 8);
+                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+                uint32_t* d = (c8 < 4 ? s0 : s1) + (c8 & 3) * 8;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 bv = unpack_bf16x2(w[j]);
+                  d[2 * j] = __float_as_uint(fmaf(bv.x, p.inv_scale, __uint_as_float(d[2 * j])));
+                  d[2 * j + 1] = __float_as_uint(fmaf(bv.y, p.inv_scale, __uint_as_float(d[2 * j + 1])));
+                }
+              }
+            }
+          }
+        }
         const uint64_t sc2 = f2_pack(p.scale_log2, p.scale_log2), nl2 = f2_pack(-cur.lse2, -cur.lse2);
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
@@ -559,9 +581,14 @@ static int flash_bwd_launch(const void* dout, const void* q, const void* k, cons
                             const int* row_lo, const int* row_hi, int B, int Sq, int Sk, int Hq, int Hkv,
                             long long q_stride, long long k_stride, long long v_stride, long long do_stride,
                             long long dq_stride, long long dkv_stride, int causal, float softmax_scale, void* stream,
-                            int* status, DropParams drop) {
+                            int* status, DropParams drop, BiasParams bias = BiasParams{nullptr, 0, 0, 0}) {
   if (B <= 0 || Sq <= 0 || Sk <= 0) return 0;
-  if (drop.thr16 != 0 && dq_acc == nullptr) return -1;   // dropout is implemented in the one-kernel form only
+  // dropout and the additive bias are implemented in the one-kernel form only
+  if ((drop.thr16 != 0 || bias.ptr != nullptr) && dq_acc == nullptr) return -1;
+  if (bias.ptr != nullptr &&
+      ((Sk & 7) || ((bias.sb | bias.sh | bias.sq) & 7) || (reinterpret_cast<uintptr_t>(bias.ptr) & 15) ||
+       !(softmax_scale > 0.f)))
+    return -1;
   if (Hq % Hkv) return -1;
   if ((q_stride | k_stride | v_stride | do_stride | dq_stride | dkv_stride) & 7) return -1;
   cudaStream_t st = (cudaStream_t)stream;
@@ -592,6 +619,10 @@ static int flash_bwd_launch(const void* dout, const void* q, const void* k, cons
         cudaFuncSetAttribute(flash_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemB::TOTAL) !=
             cudaSuccess ||
         cudaFuncSetAttribute(flash_bwd_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SmemB::TOTAL) != cudaSuccess ||
+        cudaFuncSetAttribute(flash_bwd_kernel<true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SmemB::TOTAL) != cudaSuccess ||
+        cudaFuncSetAttribute(flash_bwd_kernel<true, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              SmemB::TOTAL) != cudaSuccess)
       return -4;
     attr_set = true;
@@ -611,6 +642,8 @@ static int flash_bwd_launch(const void* dout, const void* q, const void* k, cons
   p.scale = softmax_scale; p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = status;
   p.drop = drop;
+  p.bias = bias;
+  p.inv_scale = 1.f / softmax_scale;
   dim3 grid((Sk + BKV - 1) / BKV, Hq, B);
   if (dq_acc == nullptr) {
     if (g_dkv_transposed > 0 || (g_dkv_transposed < 0 && causal && Sk >= 8192)) {
@@ -624,8 +657,12 @@ static int flash_bwd_launch(const void* dout, const void* q, const void* k, cons
     return atb_flash_bwd_dq(dout, q, k, v, lse, delta, dq, row_lo, row_hi, B, Sq, Sk, Hq, Hkv, q_stride, k_stride,
                             v_stride, do_stride, dq_stride, causal, softmax_scale, stream, status);
   }
-  if (drop.thr16 != 0)
+  if (drop.thr16 != 0 && bias.ptr != nullptr)
+    flash_bwd_kernel<true, true, true><<<grid, THREADS, SmemB::TOTAL, st>>>(tmQ, tmdO, tmK, tmV, tmdQ, p);
+  else if (drop.thr16 != 0)
     flash_bwd_kernel<true, true><<<grid, THREADS, SmemB::TOTAL, st>>>(tmQ, tmdO, tmK, tmV, tmdQ, p);
+  else if (bias.ptr != nullptr)
+    flash_bwd_kernel<true, false, true><<<grid, THREADS, SmemB::TOTAL, st>>>(tmQ, tmdO, tmK, tmV, tmdQ, p);
   else
     flash_bwd_kernel<true><<<grid, THREADS, SmemB::TOTAL, st>>>(tmQ, tmdO, tmK, tmV, tmdQ, p);
   const long long n4 = (long long)B * Sq * Hq * HD / 4;
@@ -657,4 +694,20 @@ extern "C" int atb_flash_bwd_dropout(const void* dout, const void* q, const void
   return flash_bwd_launch(dout, q, k, v, out, lse, delta, dq_acc, dq, dk, dv, row_lo, row_hi, B, Sq, Sk, Hq, Hkv,
                           q_stride, k_stride, v_stride, do_stride, dq_stride, dkv_stride, causal, softmax_scale, stream,
                           status, DropParams{thr16, seed_lo, seed_hi, 65536.f / (float)(65536u - thr16)});
+}
+
+// Backward of atb_flash_fwd_bias: the same bias (it gets no gradient) and, if thr16 != 0, the same dropout.
+extern "C" int atb_flash_bwd_bias(const void* dout, const void* q, const void* k, const void* v, const void* out,
+                                  const float* lse, float* delta, float* dq_acc, void* dq, void* dk, void* dv,
+                                  const int* row_lo, const int* row_hi, int B, int Sq, int Sk, int Hq, int Hkv,
+                                  long long q_stride, long long k_stride, long long v_stride, long long do_stride,
+                                  long long dq_stride, long long dkv_stride, int causal, float softmax_scale,
+                                  void* stream, int* status, unsigned thr16, unsigned seed_lo, unsigned seed_hi,
+                                  const void* bias, long long bias_sb, long long bias_sh, long long bias_sq) {
+  if (thr16 >= 65536u || bias == nullptr) return -1;
+  const DropParams drop = thr16 ? DropParams{thr16, seed_lo, seed_hi, 65536.f / (float)(65536u - thr16)}
+                                : DropParams{0u, 0u, 0u, 1.f};
+  return flash_bwd_launch(dout, q, k, v, out, lse, delta, dq_acc, dq, dk, dv, row_lo, row_hi, B, Sq, Sk, Hq, Hkv,
+                          q_stride, k_stride, v_stride, do_stride, dq_stride, dkv_stride, causal, softmax_scale, stream,
+                          status, drop, BiasParams{(const __nv_bfloat16*)bias, bias_sb, bias_sh, bias_sq});
 }

@@ -13,7 +13,8 @@ atorch/npu/layers.py:9-45):
 * ``cu_seqlens`` (packed sequences): tokens only see keys of their own sequence.
 * ``additive_mask`` / ``additive_bias``: added to the scaled scores before the softmax (a boolean
   ``additive_mask`` means True = visible). A 0 / -inf mask shared by all heads with one run of visible keys per
-  row is lowered to key intervals and runs in the flash kernels; soft biases take the dense path.
+  row is lowered to key intervals; any other mask or bias without a gradient is added to the scores inside the
+  flash kernels as one bf16 tensor (S_k a multiple of 8); a bias that needs a gradient takes the dense path.
 
 ``attention`` dispatches to the sm_100a flash-attention kernels when they are built and the
 problem fits them, and evaluates the dense PyTorch reference otherwise (CPU, unusual shapes).
@@ -104,7 +105,8 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool = 
     if flash.supported(q, k, v, dropout_p, additive_mask, additive_bias, key_padding_mask):
         return flash.flash_attention(q, k, v, causal=causal, softmax_scale=softmax_scale, glm_mask=glm_mask,
                                      pack_glm_mask=pack_glm_mask, key_padding_mask=key_padding_mask,
-                                     cu_seqlens=cu_seqlens, dropout_p=dropout_p)
+                                     cu_seqlens=cu_seqlens, dropout_p=dropout_p, additive_mask=additive_mask,
+                                     additive_bias=additive_bias)
     if q.is_cuda and glm_mask is None and pack_glm_mask is None and key_padding_mask is None and cu_seqlens is None \
             and additive_mask is None and additive_bias is None and q.shape[1] == k.shape[1]:
         # library path (torch SDPA) for shapes the sm_100a kernels do not cover

@@ -51,7 +51,13 @@ def supported(q, k, v, dropout_p=0.0, additive_mask=None, additive_bias=None, ke
     if not _lib.use_kernels(q, k, v) or not kernels_built():
         return False
     if additive_mask is not None or additive_bias is not None:
-        return False
+        # soft masks / biases run in the kernels when they can be read as one bf16 tensor without a gradient
+        if not _lib.lib().has("atb_flash_fwd_bias") or k.shape[1] % 8 != 0:
+            return False
+        for t in (additive_mask, additive_bias):
+            if t is not None and (t.requires_grad or t.dim() < 2 or t.dim() > 4 or t.shape[-1] != k.shape[1]
+                                  or t.shape[-2] not in (1, q.shape[1])):
+                return False
     if dropout_p != 0.0 and not (0.0 < dropout_p < 1.0 and _lib.lib().has("atb_flash_fwd_dropout")):
         return False
     if (q.requires_grad or k.requires_grad or v.requires_grad) and torch.is_grad_enabled() and not backward_built():
@@ -151,6 +157,23 @@ def _token_stride(t: torch.Tensor) -> int:
     return t.stride(1)
 
 
+def bias_config(B: int, Hq: int, Sq: int, Sk: int, additive_mask=None, additive_bias=None):
+    """``(tensor, stride_b, stride_h, stride_q)`` for the bias kernels: mask and bias summed into one bf16 tensor
+    of shape ``[1|B, 1|H, 1|Sq, Sk]`` (2-D = ``[Sq, Sk]``, 3-D = ``[B, Sq, Sk]``), broadcast dims with stride 0."""
+    t = None
+    for x in (additive_mask, additive_bias):
+        if x is None:
+            continue
+        if x.dtype == torch.bool:
+            x = torch.zeros(x.shape, dtype=torch.float32, device=x.device).masked_fill(~x, float("-inf"))
+        x = x[None, None] if x.dim() == 2 else x[:, None] if x.dim() == 3 else x
+        t = x.float() if t is None else t + x.float()
+    t = t.to(torch.bfloat16).contiguous()
+    b, h, sq, sk = t.shape
+    assert b in (1, B) and h in (1, Hq) and sq in (1, Sq) and sk == Sk, (t.shape, (B, Hq, Sq, Sk))
+    return t, (0 if b == 1 else h * sq * sk), (0 if h == 1 else sq * sk), (0 if sq == 1 else sk)
+
+
 def dropout_config(dropout_p: float, seed=None) -> Tuple[int, int, int]:
     """``(thr16, seed_lo, seed_hi)`` for the dropout kernels: an element is dropped when its 16 hash bits are below
     ``thr16 = round(p * 65536)`` (so the effective probability is ``thr16 / 65536``). The seed pair is drawn from
@@ -188,7 +211,15 @@ def dropout_keep_mask(B: int, Hq: int, Sq: int, Sk: int, drop: Tuple[int, int, i
     return (bits >= thr).view(B, Hq, Sq, Sk)
 
 
-def flash_fwd_raw(q, k, v, causal, softmax_scale, row_lo, row_hi, drop=None):
+def _extra_args(drop, bias):
+    d = drop if drop is not None else (0, 0, 0)
+    extra = tuple(ctypes.c_uint(x) for x in d)
+    if bias is not None:
+        extra += (_lib.ptr(bias[0]),) + tuple(ctypes.c_longlong(x) for x in bias[1:])
+    return extra
+
+
+def flash_fwd_raw(q, k, v, causal, softmax_scale, row_lo, row_hi, drop=None, bias=None):
     """Launch the forward kernel. Returns (out [B,Sq,Hq,D] bf16, lse [B,Hq,Sq] fp32). ``drop``: see
     ``dropout_config``; dropout runs in the single-tile kernel."""
     B, Sq, Hq, D = q.shape
@@ -197,8 +228,10 @@ def flash_fwd_raw(q, k, v, causal, softmax_scale, row_lo, row_hi, drop=None):
     lse = torch.empty(B, Hq, Sq, dtype=torch.float32, device=q.device)
     L = _lib.lib()
     # two-query-tile kernel (flash_attn_v2.cu) for long enough sequences; the single-tile kernel otherwise
-    if drop is not None:
-        fwd, extra = L.atb_flash_fwd_dropout, tuple(ctypes.c_uint(x) for x in drop)
+    if bias is not None:
+        fwd, extra = L.atb_flash_fwd_bias, _extra_args(drop, bias)
+    elif drop is not None:
+        fwd, extra = L.atb_flash_fwd_dropout, _extra_args(drop, None)
     else:
         fwd = L.atb_flash_fwd_v2 if (FWD_TWO_TILES and Sq >= 256 and L.has("atb_flash_fwd_v2")) else L.atb_flash_fwd
         extra = ()
@@ -213,7 +246,7 @@ def flash_fwd_raw(q, k, v, causal, softmax_scale, row_lo, row_hi, drop=None):
 
 
 def flash_bwd_raw(dout, q, k, v, out, lse, causal, softmax_scale, row_lo, row_hi, fused_out: bool = False,
-                  drop=None):
+                  drop=None, bias=None):
     """Launch the backward kernels. Returns (dq, dk, dv) shaped like q, k, v. With ``fused_out`` (and
     equal query / key-value head counts) the three are slices of ONE ``[B, S, 3*H, D]`` buffer laid out
     like a fused q|k|v projection output, so the gradient of that projection needs no concatenation."""
@@ -226,7 +259,8 @@ def flash_bwd_raw(dout, q, k, v, out, lse, causal, softmax_scale, row_lo, row_hi
             _lib.lib().atb_flash_bwd_set_dkv(ctypes.c_int(int(os.environ["ATB_FLASH_BWD_DKV"])))
     # two kernels (dK/dV per key block, dQ per query block: no atomics, no fp32 scratch) unless
     # ATB_FLASH_BWD_SPLIT=0 asks for the single key-block kernel with TMA reduce-adds of dQ
-    dq_acc = None if (BWD_SPLIT and drop is None) else torch.zeros(B, Sq, Hq, D, dtype=torch.float32, device=q.device)
+    dq_acc = None if (BWD_SPLIT and drop is None and bias is None) else \
+        torch.zeros(B, Sq, Hq, D, dtype=torch.float32, device=q.device)
     delta = torch.empty(B, Hq, Sq, dtype=torch.float32, device=q.device)
     if fused_out and Hkv == Hq and Sq == Sk:
         fused = torch.empty(B, Sq, 3 * Hq, D, dtype=q.dtype, device=q.device)
@@ -238,8 +272,12 @@ def flash_bwd_raw(dout, q, k, v, out, lse, causal, softmax_scale, row_lo, row_hi
         dv = torch.empty(B, Sk, Hq, D, dtype=q.dtype, device=q.device)
     dout = dout if (dout.stride(-1) == 1 and dout.stride(2) == D and dout.stride(0) == dout.stride(1) * Sq) \
         else dout.contiguous()
-    bwd = _lib.lib().atb_flash_bwd if drop is None else _lib.lib().atb_flash_bwd_dropout
-    extra = () if drop is None else tuple(ctypes.c_uint(x) for x in drop)
+    if bias is not None:
+        bwd, extra = _lib.lib().atb_flash_bwd_bias, _extra_args(drop, bias)
+    elif drop is not None:
+        bwd, extra = _lib.lib().atb_flash_bwd_dropout, _extra_args(drop, None)
+    else:
+        bwd, extra = _lib.lib().atb_flash_bwd, ()
     rc = bwd(
         _lib.ptr(dout), _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(lse), _lib.ptr(delta),
         _lib.ptr(dq_acc), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv), _lib.ptr(row_lo), _lib.ptr(row_hi),
@@ -260,22 +298,23 @@ def flash_bwd_raw(dout, q, k, v, out, lse, causal, softmax_scale, row_lo, row_hi
 
 class _FlashAttn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, causal, scale, row_lo, row_hi, drop=None):
-        out, lse = flash_fwd_raw(q, k, v, causal, scale, row_lo, row_hi, drop)
+    def forward(ctx, q, k, v, causal, scale, row_lo, row_hi, drop=None, bias=None):
+        out, lse = flash_fwd_raw(q, k, v, causal, scale, row_lo, row_hi, drop, bias)
         ctx.save_for_backward(q, k, v, out, lse, row_lo, row_hi)
-        ctx.cfg = (causal, scale, drop)
+        ctx.cfg = (causal, scale, drop, bias)       # bias: (bf16 tensor, strides), not differentiated
         return out
 
     @staticmethod
     def backward(ctx, dout):
         q, k, v, out, lse, row_lo, row_hi = ctx.saved_tensors
-        causal, scale, drop = ctx.cfg
-        dq, dk, dv = flash_bwd_raw(dout, q, k, v, out, lse, causal, scale, row_lo, row_hi, drop=drop)
-        return dq, dk, dv, None, None, None, None, None
+        causal, scale, drop, bias = ctx.cfg
+        dq, dk, dv = flash_bwd_raw(dout, q, k, v, out, lse, causal, scale, row_lo, row_hi, drop=drop, bias=bias)
+        return dq, dk, dv, None, None, None, None, None, None
 
 
 def flash_attention(q, k, v, causal=False, softmax_scale=None, glm_mask=None, pack_glm_mask=None,
-                    key_padding_mask=None, cu_seqlens=None, dropout_p=0.0, dropout_seed=None):
+                    key_padding_mask=None, cu_seqlens=None, dropout_p=0.0, dropout_seed=None,
+                    additive_mask=None, additive_bias=None):
     """``dropout_p``: attention dropout inside the kernels (the mask is a counter-based hash of batch, head, row
     and column, see ``dropout_keep_mask``); ``dropout_seed`` fixes the mask, otherwise torch's CPU generator
     supplies the seed."""
@@ -287,10 +326,18 @@ def flash_attention(q, k, v, causal=False, softmax_scale=None, glm_mask=None, pa
     try:
         lo, hi = row_intervals(B, Sq, Sk, q.device, causal, glm_mask, pack_glm_mask, key_padding_mask, cu_seqlens)
     except NonContiguousKeyMask:
+        if additive_mask is not None or additive_bias is not None:
+            from .attention import attention_reference
+
+            return attention_reference(q, k, v, causal, scale, glm_mask, pack_glm_mask, key_padding_mask, cu_seqlens,
+                                       additive_mask, additive_bias, dropout_p)
         return _unpadded_attention(q, k, v, key_padding_mask, causal, scale, glm_mask, pack_glm_mask, cu_seqlens,
                                    dropout_p, dropout_seed)
     drop = dropout_config(dropout_p, dropout_seed) if dropout_p > 0.0 else None
-    return _FlashAttn.apply(q, k, v, bool(causal), float(scale), lo, hi, drop)
+    bias = None
+    if additive_mask is not None or additive_bias is not None:
+        bias = bias_config(B, Hq, Sq, Sk, additive_mask, additive_bias)
+    return _FlashAttn.apply(q, k, v, bool(causal), float(scale), lo, hi, drop, bias)
 
 
 def _unpadded_attention(q, k, v, key_padding_mask, causal, scale, glm_mask, pack_glm_mask, cu_seqlens,

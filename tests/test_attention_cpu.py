@@ -120,3 +120,19 @@ def test_glm_self_attention_module_matches_plain_math():
     # building from an existing module keeps its parameters
     m2 = HFGLMSelfAttentionFA(src_module=m)
     assert m2.query_key_value is m.query_key_value and torch.equal(m2(x, ltor), out)
+
+
+def test_bias_config_sums_mask_and_bias_and_reports_broadcast_strides():
+    B, H, Sq, Sk = 2, 3, 4, 8
+    alibi = torch.randn(1, H, Sq, Sk)
+    pad = torch.zeros(B, 1, 1, Sk)
+    pad[1, 0, 0, 5:] = float("-inf")
+    t, sb, sh, sq = flash.bias_config(B, H, Sq, Sk, pad, alibi)
+    assert t.dtype == torch.bfloat16 and t.shape == (B, H, Sq, Sk) and (sb, sh, sq) == (H * Sq * Sk, Sq * Sk, Sk)
+    assert torch.allclose(t.float(), (pad + alibi).to(torch.bfloat16).float(), atol=2e-2, equal_nan=True)
+    t, sb, sh, sq = flash.bias_config(B, H, Sq, Sk, None, alibi)
+    assert (sb, sh, sq) == (0, Sq * Sk, Sk)
+    t, sb, sh, sq = flash.bias_config(B, H, Sq, Sk, pad, None)
+    assert t.shape == (B, 1, 1, Sk) and (sb, sh, sq) == (Sk, 0, 0)
+    t, *_ = flash.bias_config(B, H, Sq, Sk, torch.ones(Sq, Sk, dtype=torch.bool).tril(), None)
+    assert t.shape == (1, 1, Sq, Sk) and t[0, 0, 0, 1] == float("-inf") and t[0, 0, 1, 1] == 0

@@ -291,3 +291,49 @@ def test_dense_glm_mask_runs_in_the_flash_kernels():
     for name, a, b in zip("qkv", qs, rs):
         err = (a.grad.float() - b.grad).abs().max().item()
         assert err / (b.grad.abs().max().item() + 1e-6) < 3e-2, name
+
+
+@pytest.mark.parametrize("kind", ["alibi", "soft_padding", "alibi+dropout"])
+def test_additive_bias_inside_the_flash_kernels(kind):
+    """A soft additive bias (per-head ALiBi slopes, or a per-batch key bias with -inf entries) is added to the
+    scores inside the forward and backward kernels; compared with dense fp32 attention."""
+    from atorch_b200.ops import attention
+
+    torch.manual_seed(17)
+    B, Sq, Sk, H = 2, 320, 320, 4
+    q, k, v = _qkv(B, Sq, Sk, H, H)
+    i, j = torch.arange(Sq, device="cuda")[:, None], torch.arange(Sk, device="cuda")[None]
+    if kind.startswith("alibi"):
+        slopes = torch.tensor([0.5, 0.25, 0.125, 0.0625], device="cuda")
+        bias = (-(i - j).abs().float())[None, None] * slopes[None, :, None, None]          # [1, H, Sq, Sk]
+        kw = dict(additive_bias=bias, causal=True)
+    else:
+        bias = 0.3 * torch.randn(B, 1, 1, Sk, device="cuda")
+        bias[1, 0, 0, 200:] = float("-inf")
+        kw = dict(additive_mask=bias)
+    p_drop, seed = (0.15, 99) if kind.endswith("dropout") else (0.0, None)
+    qs = [t.detach().clone().requires_grad_() for t in (q, k, v)]
+    if p_drop:
+        out = flash.flash_attention(*qs, dropout_p=p_drop, dropout_seed=seed, **kw)
+    else:
+        out = attention(*qs, **kw)
+    assert type(out.grad_fn).__name__ == "_FlashAttnBackward"
+    dout = torch.randn_like(out)
+    out.backward(dout)
+    torch.cuda.synchronize()
+    _lib.check_status(q.device)
+    rs = [t.detach().float().requires_grad_() for t in (q, k, v)]
+    s = rs[0].transpose(1, 2) @ rs[1].transpose(1, 2).transpose(-1, -2) / math.sqrt(128)
+    s = s + bias.to(torch.bfloat16).float()
+    if kw.get("causal"):
+        s = s.masked_fill(j > i, float("-inf"))
+    pm = torch.softmax(s, -1)
+    if p_drop:
+        drop = flash.dropout_config(p_drop, seed)
+        pm = pm * flash.dropout_keep_mask(B, H, Sq, Sk, drop, device="cuda") * (65536.0 / (65536 - drop[0]))
+    ref = (pm @ rs[2].transpose(1, 2)).transpose(1, 2)
+    ref.backward(dout.float())
+    assert torch.allclose(out.float(), ref, rtol=2e-2, atol=2e-2), (out.float() - ref).abs().max()
+    for name, a, b_ in zip("qkv", qs, rs):
+        err = (a.grad.float() - b_.grad).abs().max().item()
+        assert err / (b_.grad.abs().max().item() + 1e-6) < 3e-2, (name, err)
