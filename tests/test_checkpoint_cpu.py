@@ -185,3 +185,115 @@ assert not bad, bad
                          timeout=300)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
     assert "bad []" in res.stdout
+
+
+_REF_WRITER = r"""
+import os, sys, torch, torch.nn as nn, torch.distributed as dist, torch.multiprocessing as mp
+
+
+def make_mlp():
+    torch.manual_seed(0)
+    m = nn.Sequential(nn.Linear(256, 512), nn.ReLU(), nn.Linear(512, 512), nn.ReLU(), nn.Linear(512, 512), nn.ReLU(),
+                      nn.Linear(512, 10))
+    for p in m.parameters():
+        if p.dim() > 1:
+            nn.init.normal_(p, std=0.02)
+    return m
+
+
+def run(rank, world, path, port):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.cuda.synchronize = lambda *a, **k: None      # the writer ends with a device synchronise; no device here
+    torch.cuda.current_device = lambda: 0
+    from torch.distributed.fsdp import FullyShardedDataParallel as FSDP
+    from torch.distributed.fsdp.wrap import ModuleWrapPolicy
+    import atorch
+    from atorch.utils.fsdp_save_util import save_fsdp_flat_param, save_fsdp_optim_param
+    assert "baseline/_ref" in atorch.__file__.replace("\\", "/"), atorch.__file__
+    f = FSDP(make_mlp(), auto_wrap_policy=ModuleWrapPolicy({nn.Linear}), use_orig_params=True,
+             device_id=torch.device("cpu"))
+    opt = torch.optim.AdamW(f.parameters(), lr=1e-3)
+    g = torch.Generator().manual_seed(7 + rank)
+    for _ in range(2):
+        opt.zero_grad()
+        f(torch.randn(4, 256, generator=g)).sum().backward()
+        opt.step()
+    save_fsdp_flat_param(f, path)
+    save_fsdp_optim_param(f, opt, path)
+    with FSDP.summon_full_params(f, writeback=False):
+        full = {k.replace("_fsdp_wrapped_module.", ""): v.detach().clone() for k, v in f.named_parameters()}
+    if rank == 0:
+        torch.save(full, path + "/full_ref.pt")
+        # the optimizer state to expect: the same two steps on an unsharded copy with the ranks' gradients averaged
+        plain = make_mlp()
+        popt = torch.optim.AdamW(plain.parameters(), lr=1e-3)
+        gens = [torch.Generator().manual_seed(7 + r) for r in range(world)]
+        for _ in range(2):
+            popt.zero_grad()
+            (sum(plain(torch.randn(4, 256, generator=g_)).sum() for g_ in gens) / world).backward()
+            popt.step()
+        torch.save({n: {k: v for k, v in popt.state[p_].items() if k != "step"} for n, p_ in plain.named_parameters()},
+                   path + "/full_opt_ref.pt")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    os.makedirs(sys.argv[1], exist_ok=True)
+    mp.spawn(run, args=(2, sys.argv[1], int(sys.argv[2])), nprocs=2)
+"""
+
+
+def _load_reference_ckpt(rank, world, path):
+    from atorch_b200.parallel.fsdp import FSDP, ShardedOptimizer
+    from atorch_b200.utils.fsdp_save_util import ShardOptim, load_fsdp_flat_param
+
+    m = make_mlp()
+    with torch.no_grad():
+        for p in m.parameters():
+            p.add_(1.0)
+    f = FSDP(m, wrap_cls=(nn.Linear,))
+    load_fsdp_flat_param(f, path)
+    sd = f.state_dict()
+    ref = torch.load(path + "/full_ref.pt")
+    assert set(ref) == set(sd), (sorted(ref), sorted(sd))
+    for k, v in ref.items():
+        assert torch.equal(sd[k], v), k
+    opt = ShardedOptimizer(torch.optim.AdamW(f.parameters(), lr=1e-3), f.engine)
+    ShardOptim(path).load_into(f, opt)
+    ref_opt = torch.load(path + "/full_opt_ref.pt")
+    so = ShardOptim(path)
+    for name, st in ref_opt.items():
+        n = st["exp_avg"].numel()
+        for key in ("exp_avg", "exp_avg_sq"):
+            got = so.load_state_slice(name, key, 0, n)
+            assert got is not None and torch.allclose(got, st[key].reshape(-1), rtol=1e-4, atol=1e-9), (name, key)
+
+
+def test_flat_checkpoint_written_by_the_reference_loads_here(tmp_path):
+    """The unmodified reference (torch FSDP on two gloo ranks, its own ``save_fsdp_flat_param`` /
+    ``save_fsdp_optim_param``) writes a flat checkpoint; this package's loader restores it into its own sharded
+    engine at world size 1 and 4: parameters bit-exact against the reference run's gathered parameters, optimizer
+    state against the same two steps on an unsharded copy."""
+    import os
+    import subprocess
+    import sys
+
+    import pytest
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ref = os.path.join(root, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "atorch")):
+        pytest.skip("the reference is not installed under baseline/_ref")
+    path = str(tmp_path / "ref_flat")
+    script = tmp_path / "ref_writer.py"
+    script.write_text(_REF_WRITER)
+    env = dict(os.environ, PYTHONPATH=ref)
+    res = subprocess.run([sys.executable, str(script), path, "29643"], cwd=str(tmp_path), env=env, capture_output=True,
+                         text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
+    assert os.path.exists(path + "/flat_param.00001-00002") and os.path.exists(path + "/optim_param.00000-00002")
+    for w in (1, 4):
+        run_distributed(_load_reference_ckpt, world=w, args=(path,))
