@@ -1,4 +1,4 @@
-// Flash attention forward for sm_100a (head dim 128, bf16), tcgen05 + TMEM + TMA.
+// Flash attention forward for sm_100a (head dim 128 or 64, bf16), tcgen05 + TMEM + TMA.
 //
 // One CTA per (128 query rows, head, batch). Warp 0 = TMA producer, warp 1 = MMA issuer and TMEM
 // owner, warps 2..9 = softmax: two warps per TMEM lane quarter, thread (row r, half h) owns
@@ -62,7 +62,9 @@ struct SmemLayout {
   static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 64 + 1024;
 };
 
-template <bool DROP, bool BIAS>
+// HDIM = 128 or 64: with 64 the Q / K / V tiles are one 64-column panel (in the same shared-memory slots), the
+// score product runs over four k-steps and the output tile has 64 columns, 32 per thread.
+template <bool DROP, bool BIAS, int HDIM = 128>
 __global__ void __launch_bounds__(THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, FwdParams p) {
@@ -168,27 +170,28 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tma_prefetch_desc(&tmQ);
       tma_prefetch_desc(&tmK);
       tma_prefetch_desc(&tmV);
-      mbar_expect_tx(q_full, TILE);
-      tma_load_2d(sQ, &tmQ, q_full, h * HD, (int)q_row0);
-      tma_load_2d(sQ + PANEL, &tmQ, q_full, h * HD + 64, (int)q_row0);
+      constexpr int TILE_B = (HDIM / 64) * PANEL;   // bytes of a [128 x HDIM] tile
+      mbar_expect_tx(q_full, TILE_B);
+      tma_load_2d(sQ, &tmQ, q_full, h * HDIM, (int)q_row0);
+      if (HDIM == 128) tma_load_2d(sQ + PANEL, &tmQ, q_full, h * HDIM + 64, (int)q_row0);
       for (int j = 0; j < ntiles; ++j) {
         const int s = j % KV_STAGES;
         const uint32_t ph = (j / KV_STAGES) & 1;
         const int krow = (int)(k_row0 + (long long)(t0 + j) * BKV);
         if (!mbar_wait(&k_empty[s], ph ^ 1, abort_flag, p.status)) break;
-        mbar_expect_tx(&k_full[s], TILE);
-        tma_load_2d(sK + s * TILE, &tmK, &k_full[s], hk * HD, krow);
-        tma_load_2d(sK + s * TILE + PANEL, &tmK, &k_full[s], hk * HD + 64, krow);
+        mbar_expect_tx(&k_full[s], TILE_B);
+        tma_load_2d(sK + s * TILE, &tmK, &k_full[s], hk * HDIM, krow);
+        if (HDIM == 128) tma_load_2d(sK + s * TILE + PANEL, &tmK, &k_full[s], hk * HDIM + 64, krow);
         if (!mbar_wait(&v_empty[s], ph ^ 1, abort_flag, p.status)) break;
-        mbar_expect_tx(&v_full[s], TILE);
-        tma_load_2d(sV + s * TILE, &tmV, &v_full[s], hk * HD, krow);
-        tma_load_2d(sV + s * TILE + PANEL, &tmV, &v_full[s], hk * HD + 64, krow);
+        mbar_expect_tx(&v_full[s], TILE_B);
+        tma_load_2d(sV + s * TILE, &tmV, &v_full[s], hk * HDIM, krow);
+        if (HDIM == 128) tma_load_2d(sV + s * TILE + PANEL, &tmV, &v_full[s], hk * HDIM + 64, krow);
       }
     }
   } else if (warp == 1) {
     if (lane == 0 && ntiles > 0) {
       constexpr uint32_t idesc_s = umma_idesc(BQ, BKV, 1, 1, false, false);
-      constexpr uint32_t idesc_o = umma_idesc(BQ, HD, 1, 1, false, true);
+      constexpr uint32_t idesc_o = umma_idesc(BQ, HDIM, 1, 1, false, true);
       const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
       auto issue_s = [&](int j) -> bool {
         const int s = j % KV_STAGES, sb = j & 1;
@@ -197,7 +200,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tc_fence_after();
         const uint32_t k_addr = smem_u32(sK + s * TILE);
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k) {
+        for (int k = 0; k < HDIM / 16; ++k) {
           const uint32_t off = (k >> 2) * PANEL + (k & 3) * 32;
           umma_f16<1>(tmem_base + sb * BKV, umma_desc_sw128(q_addr + off, 16, 1024),
                       umma_desc_sw128(k_addr + off, 16, 1024), idesc_s, k != 0);
@@ -254,9 +257,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (!__all_sync(0xffffffffu, mbar_wait(o_full, j & 1, abort_flag, p.status))) return false;
       tc_fence_after();
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
+      for (int cc = 0; cc < HDIM / 64; ++cc) {
         uint32_t t[32];
-        tmem_ld_32x32(lane_addr + 2 * BKV + half * 64 + cc * 32, t);
+        tmem_ld_32x32(lane_addr + 2 * BKV + half * (HDIM / 2) + cc * 32, t);
         tmem_ld_wait();
 #pragma unroll
         for (int c = 0; c < 32; ++c) o_acc[cc * 32 + c] = o_acc[cc * 32 + c] * alpha_prev + __uint_as_float(t[c]);
@@ -383,9 +386,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const float l_tot = l_run + s_rowsum[(half ^ 1) * 128 + r];
     if (ok && row_valid) {
       const float inv = l_tot > 0.f ? (DROP ? p.drop.keep_scale : 1.f) / l_tot : 0.f;
-      __nv_bfloat16* orow = p.O + (((long long)b * p.Sq + i) * p.Hq + h) * HD + half * 64;
+      __nv_bfloat16* orow = p.O + (((long long)b * p.Sq + i) * p.Hq + h) * HDIM + half * (HDIM / 2);
 #pragma unroll
-      for (int c = 0; c < 64; c += 8) {
+      for (int c = 0; c < HDIM / 2; c += 8) {
         uint4 v;
         v.x = pack_bf16x2(o_acc[c] * inv, o_acc[c + 1] * inv);
         v.y = pack_bf16x2(o_acc[c + 2] * inv, o_acc[c + 3] * inv);
@@ -414,38 +417,42 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 }  // namespace
 
 // q: rows = B*Sq tokens with pitch q_stride elements, head h at columns [h*128, h*128+128);
-// k, v likewise with B*Sk rows. O: [B, Sq, Hq, 128] contiguous bf16; lse: [B, Hq, Sq] fp32.
+// k, v likewise with B*Sk rows. O: [B, Sq, Hq, head_dim] contiguous bf16; lse: [B, Hq, Sq] fp32.
 // row_lo / row_hi: optional int32 [B, Sq] key intervals (see file header).
+template <bool DROP, bool BIAS, int HDIM>
+static int fwd_variant(dim3 grid, cudaStream_t st, const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap& tmV,
+                       const FwdParams& p) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(flash_fwd_kernel<DROP, BIAS, HDIM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SmemLayout::TOTAL) != cudaSuccess)
+      return -4;
+    attr_set = true;
+  }
+  flash_fwd_kernel<DROP, BIAS, HDIM><<<grid, THREADS, SmemLayout::TOTAL, st>>>(tmQ, tmK, tmV, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
 static int flash_fwd_launch(const void* q, const void* k, const void* v, void* o, float* lse, const int* row_lo,
                             const int* row_hi, int B, int Sq, int Sk, int Hq, int Hkv, long long q_stride,
                             long long k_stride, long long v_stride, int causal, float softmax_scale, void* stream,
-                            int* status, DropParams drop, BiasParams bias = BiasParams{nullptr, 0, 0, 0}) {
+                            int* status, DropParams drop, BiasParams bias = BiasParams{nullptr, 0, 0, 0},
+                            int head_dim = 128) {
   if (B <= 0 || Sq <= 0 || Sk <= 0) return 0;
+  if (head_dim != 128 && head_dim != 64) return -1;
+  const int HDv = head_dim;
   if (Hq % Hkv) return -1;
   if ((q_stride | k_stride | v_stride) & 7) return -1;
   CUtensorMap tmQ, tmK, tmV;
-  if (!make_tmap_2d(&tmQ, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)B * Sq, (uint64_t)Hq * HD, q_stride, BQ,
+  if (!make_tmap_2d(&tmQ, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)B * Sq, (uint64_t)Hq * HDv, q_stride, BQ,
                     64, CU_TENSOR_MAP_SWIZZLE_128B))
     return -2;
-  if (!make_tmap_2d(&tmK, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)B * Sk, (uint64_t)Hkv * HD, k_stride,
+  if (!make_tmap_2d(&tmK, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)B * Sk, (uint64_t)Hkv * HDv, k_stride,
                     BKV, 64, CU_TENSOR_MAP_SWIZZLE_128B))
     return -2;
-  if (!make_tmap_2d(&tmV, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)B * Sk, (uint64_t)Hkv * HD, v_stride,
+  if (!make_tmap_2d(&tmV, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)B * Sk, (uint64_t)Hkv * HDv, v_stride,
                     BKV, 64, CU_TENSOR_MAP_SWIZZLE_128B))
     return -2;
-  static bool attr_set = false;
-  if (!attr_set) {
-    const bool ok = cudaFuncSetAttribute(flash_fwd_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         SmemLayout::TOTAL) == cudaSuccess &&
-                    cudaFuncSetAttribute(flash_fwd_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         SmemLayout::TOTAL) == cudaSuccess &&
-                    cudaFuncSetAttribute(flash_fwd_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         SmemLayout::TOTAL) == cudaSuccess &&
-                    cudaFuncSetAttribute(flash_fwd_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         SmemLayout::TOTAL) == cudaSuccess;
-    if (!ok) return -4;
-    attr_set = true;
-  }
   FwdParams p;
   p.O = (__nv_bfloat16*)o; p.lse = lse; p.row_lo = row_lo; p.row_hi = row_hi;
   p.B = B; p.Sq = Sq; p.Sk = Sk; p.Hq = Hq; p.Hkv = Hkv; p.causal = causal;
@@ -460,15 +467,17 @@ static int flash_fwd_launch(const void* q, const void* k, const void* v, void* o
     return -1;
   dim3 grid((Sq + BQ - 1) / BQ, Hq, B);
   const cudaStream_t st = (cudaStream_t)stream;
-  if (drop.thr16 != 0 && bias.ptr != nullptr)
-    flash_fwd_kernel<true, true><<<grid, THREADS, SmemLayout::TOTAL, st>>>(tmQ, tmK, tmV, p);
-  else if (drop.thr16 != 0)
-    flash_fwd_kernel<true, false><<<grid, THREADS, SmemLayout::TOTAL, st>>>(tmQ, tmK, tmV, p);
-  else if (bias.ptr != nullptr)
-    flash_fwd_kernel<false, true><<<grid, THREADS, SmemLayout::TOTAL, st>>>(tmQ, tmK, tmV, p);
-  else
-    flash_fwd_kernel<false, false><<<grid, THREADS, SmemLayout::TOTAL, st>>>(tmQ, tmK, tmV, p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+  const bool dr = drop.thr16 != 0, bi = bias.ptr != nullptr;
+#define ATB_FWD_PICK(HD_)                                                             \
+  do {                                                                                \
+    if (dr && bi) return fwd_variant<true, true, HD_>(grid, st, tmQ, tmK, tmV, p);     \
+    if (dr) return fwd_variant<true, false, HD_>(grid, st, tmQ, tmK, tmV, p);          \
+    if (bi) return fwd_variant<false, true, HD_>(grid, st, tmQ, tmK, tmV, p);          \
+    return fwd_variant<false, false, HD_>(grid, st, tmQ, tmK, tmV, p);                 \
+  } while (0)
+  if (head_dim == 64) ATB_FWD_PICK(64);
+  ATB_FWD_PICK(128);
+#undef ATB_FWD_PICK
 }
 
 extern "C" int atb_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* row_lo,
@@ -504,4 +513,18 @@ extern "C" int atb_flash_fwd_bias(const void* q, const void* k, const void* v, v
   return flash_fwd_launch(q, k, v, o, lse, row_lo, row_hi, B, Sq, Sk, Hq, Hkv, q_stride, k_stride, v_stride, causal,
                           softmax_scale, stream, status, drop,
                           BiasParams{(const __nv_bfloat16*)bias, bias_sb, bias_sh, bias_sq});
+}
+
+// The general entry point: head dim 128 or 64, optional dropout (thr16 != 0) and additive bias (bias != null).
+extern "C" int atb_flash_fwd_ex(const void* q, const void* k, const void* v, void* o, float* lse, const int* row_lo,
+                                const int* row_hi, int B, int Sq, int Sk, int Hq, int Hkv, long long q_stride,
+                                long long k_stride, long long v_stride, int causal, float softmax_scale, void* stream,
+                                int* status, unsigned thr16, unsigned seed_lo, unsigned seed_hi, const void* bias,
+                                long long bias_sb, long long bias_sh, long long bias_sq, int head_dim) {
+  if (thr16 >= 65536u) return -1;
+  const DropParams drop = thr16 ? DropParams{thr16, seed_lo, seed_hi, 65536.f / (float)(65536u - thr16)}
+                                : DropParams{0u, 0u, 0u, 1.f};
+  return flash_fwd_launch(q, k, v, o, lse, row_lo, row_hi, B, Sq, Sk, Hq, Hkv, q_stride, k_stride, v_stride, causal,
+                          softmax_scale, stream, status, drop,
+                          BiasParams{(const __nv_bfloat16*)bias, bias_sb, bias_sh, bias_sq}, head_dim);
 }

@@ -74,7 +74,8 @@ struct RowInfo {
 
 // WITH_DQ = false: key/value gradients only (the query gradient then comes from flash_attn_bwd_dq.cu): the
 // dQ product, its staging and the reduce-add are compiled out and dP(i+1) follows dK(i) without a hand-shake.
-template <bool WITH_DQ, bool DROP = false, bool BIAS = false>
+// HDIM = 128 or 64 (64: one 64-column panel per Q / dO / K / V tile, 64-column dV / dK / dQ accumulators).
+template <bool WITH_DQ, bool DROP = false, bool BIAS = false, int HDIM = 128>
 __global__ void __launch_bounds__(THREADS, 1)
 flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                  const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -178,29 +179,30 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tma_prefetch_desc(&tmK);
       tma_prefetch_desc(&tmV);
       tma_prefetch_desc(&tmdQ);
-      mbar_expect_tx(kv_full, 2 * TILE);
-      tma_load_2d(sK, &tmK, kv_full, hk * HD, (int)k_row);
-      tma_load_2d(sK + PANEL, &tmK, kv_full, hk * HD + 64, (int)k_row);
-      tma_load_2d(sV, &tmV, kv_full, hk * HD, (int)k_row);
-      tma_load_2d(sV + PANEL, &tmV, kv_full, hk * HD + 64, (int)k_row);
+      constexpr int TILE_B = (HDIM / 64) * PANEL;   // bytes of a [128 x HDIM] tile
+      mbar_expect_tx(kv_full, 2 * TILE_B);
+      tma_load_2d(sK, &tmK, kv_full, hk * HDIM, (int)k_row);
+      if (HDIM == 128) tma_load_2d(sK + PANEL, &tmK, kv_full, hk * HDIM + 64, (int)k_row);
+      tma_load_2d(sV, &tmV, kv_full, hk * HDIM, (int)k_row);
+      if (HDIM == 128) tma_load_2d(sV + PANEL, &tmV, kv_full, hk * HDIM + 64, (int)k_row);
       for (int it = 0; it < nblk; ++it) {
         const int qs = it & 1;
         const int qrow = (int)(q_row_base + (long long)(qb0 + it) * BQ);
         if (!mbar_wait(&q_free[qs], ((it >> 1) & 1) ^ 1, abort_flag, p.status)) break;
-        mbar_expect_tx(&q_full[qs], TILE);
-        tma_load_2d(sQ + qs * TILE, &tmQ, &q_full[qs], h * HD, qrow);
-        tma_load_2d(sQ + qs * TILE + PANEL, &tmQ, &q_full[qs], h * HD + 64, qrow);
+        mbar_expect_tx(&q_full[qs], TILE_B);
+        tma_load_2d(sQ + qs * TILE, &tmQ, &q_full[qs], h * HDIM, qrow);
+        if (HDIM == 128) tma_load_2d(sQ + qs * TILE + PANEL, &tmQ, &q_full[qs], h * HDIM + 64, qrow);
         if (!mbar_wait(do_free, (it & 1) ^ 1, abort_flag, p.status)) break;
-        mbar_expect_tx(do_full, TILE);
-        tma_load_2d(sdO, &tmdO, do_full, h * HD, qrow);
-        tma_load_2d(sdO + PANEL, &tmdO, do_full, h * HD + 64, qrow);
+        mbar_expect_tx(do_full, TILE_B);
+        tma_load_2d(sdO, &tmdO, do_full, h * HDIM, qrow);
+        if (HDIM == 128) tma_load_2d(sdO + PANEL, &tmdO, do_full, h * HDIM + 64, qrow);
       }
     }
   } else if (warp == 1) {
     if (lane == 0 && nblk > 0) {
       constexpr uint32_t id_kk = umma_idesc(128, 128, 1, 1, false, false);
-      constexpr uint32_t id_mm = umma_idesc(128, 128, 1, 1, true, true);
-      constexpr uint32_t id_km = umma_idesc(128, 128, 1, 1, false, true);
+      constexpr uint32_t id_mm = umma_idesc(128, HDIM, 1, 1, true, true);     // dV, dK: [keys x d]
+      constexpr uint32_t id_km = umma_idesc(128, HDIM, 1, 1, false, true);    // dQ: [queries x d]
       const uint32_t adO = smem_u32(sdO), aK = smem_u32(sK), aV = smem_u32(sV), aP = smem_u32(sP), adS = smem_u32(sdS);
       const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdV = tmem_base + 256, tdK = tmem_base + 384;
       // descriptors of every operand in the form(s) it is read in; the loops below only advance them
@@ -216,7 +218,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tc_fence_after();
         const uint64_t qd = umma_desc_advance(dQk0, (it & 1) ? TILE : 0);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
+        for (int k = 0; k < HDIM / 16; ++k) {
           const uint32_t off = (k >> 2) * PANEL + (k & 3) * 32;
           umma_f16<1>(tS, umma_desc_advance(qd, off), umma_desc_advance(dKk, off), id_kk, k != 0);
         }
@@ -227,7 +229,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (!mbar_wait(do_full, it & 1, abort_flag, p.status)) return false;
         tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
+        for (int k = 0; k < HDIM / 16; ++k) {
           const uint32_t off = (k >> 2) * PANEL + (k & 3) * 32;
           umma_f16<1>(tdP, umma_desc_advance(dOk, off), umma_desc_advance(dVk, off), id_kk, k != 0);
         }
@@ -304,20 +306,23 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (!__all_sync(0xffffffffu, mbar_wait(dq_full, it & 1, abort_flag, p.status))) return false;
       if constexpr (!WITH_DQ) return true;   // the products that read P and dS have completed: nothing to move
       tc_fence_after();
+      // this thread's HDIM / 2 columns of dQ: boxes (2 half, 2 half + 1) for 128, box `half` for 64
       uint32_t t0[32], t1[32];
-      tmem_ld_32x32(tdP, t0);
-      tmem_ld_32x32(tdP + 32, t1);
+      const uint32_t dq_addr = lane_addr + 128 + half * (HDIM / 2);
+      tmem_ld_32x32(dq_addr, t0);
+      if (HDIM == 128) tmem_ld_32x32(dq_addr + 32, t1);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(dp_free);
-      uint8_t* row0 = stage + (half * 2) * 16384 + r * 128;
+      uint8_t* row0 = stage + (half * (HDIM / 64)) * 16384 + r * 128;
 #pragma unroll
       for (int ch = 0; ch < 8; ++ch) {
         const int slot = (ch ^ (r & 7)) << 4;
         *reinterpret_cast<uint4*>(row0 + slot) = make_uint4(t0[ch * 4], t0[ch * 4 + 1], t0[ch * 4 + 2], t0[ch * 4 + 3]);
-        *reinterpret_cast<uint4*>(row0 + 16384 + slot) =
-            make_uint4(t1[ch * 4], t1[ch * 4 + 1], t1[ch * 4 + 2], t1[ch * 4 + 3]);
+        if (HDIM == 128)
+          *reinterpret_cast<uint4*>(row0 + 16384 + slot) =
+              make_uint4(t1[ch * 4], t1[ch * 4 + 1], t1[ch * 4 + 2], t1[ch * 4 + 3]);
       }
       fence_proxy_async_smem();
       __syncwarp();
@@ -328,7 +333,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (rok) {
           const int qrow = (int)(q_row_base + (long long)(qb0 + it) * BQ);
 #pragma unroll
-          for (int bx = 0; bx < 4; ++bx) tma_reduce_add_2d(&tmdQ, stage + bx * 16384, h * HD + bx * 32, qrow);
+          for (int bx = 0; bx < HDIM / 32; ++bx)
+            tma_reduce_add_2d(&tmdQ, stage + bx * 16384, h * HDIM + bx * 32, qrow);
           tma_store_commit();
           tma_store_wait_read<0>();
           mbar_arrive(stage_free);
@@ -468,15 +474,15 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       const bool store = j < p.Sk;
-      __nv_bfloat16* dvrow = p.dv + ((long long)b * p.Sk + j) * p.dkv_stride + h * HD + half * 64;
-      __nv_bfloat16* dkrow = p.dk + ((long long)b * p.Sk + j) * p.dkv_stride + h * HD + half * 64;
+      __nv_bfloat16* dvrow = p.dv + ((long long)b * p.Sk + j) * p.dkv_stride + h * HDIM + half * (HDIM / 2);
+      __nv_bfloat16* dkrow = p.dk + ((long long)b * p.Sk + j) * p.dkv_stride + h * HDIM + half * (HDIM / 2);
       if (nblk > 0) tc_fence_after();
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
+      for (int cc = 0; cc < HDIM / 64; ++cc) {
         uint32_t tv[32], tk[32];
         if (nblk > 0) {
-          tmem_ld_32x32(lane_addr + 256 + half * 64 + cc * 32, tv);
-          tmem_ld_32x32(lane_addr + 384 + half * 64 + cc * 32, tk);
+          tmem_ld_32x32(lane_addr + 256 + half * (HDIM / 2) + cc * 32, tv);
+          tmem_ld_32x32(lane_addr + 384 + half * (HDIM / 2) + cc * 32, tk);
           tmem_ld_wait();
         } else {
 #pragma unroll
@@ -514,19 +520,22 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 }
 
-// delta[b, h, i] = sum_d dO[b, i, h, d] * O[b, i, h, d]; one warp per (b, i, h) row of 128 elements.
+// delta[b, h, i] = sum_d dO[b, i, h, d] * O[b, i, h, d]; one warp per (b, i, h) row of hd (128 or 64) elements.
 __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
-                                   float* __restrict__ delta, int B, int Sq, int Hq, long long do_stride) {
+                                   float* __restrict__ delta, int B, int Sq, int Hq, long long do_stride, int hd) {
   const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const long long total = (long long)B * Sq * Hq;
   if (w >= total) return;
   const int hh = (int)(w % Hq);
   const long long tok = w / Hq;  // b * Sq + i
-  const uint2 a = *reinterpret_cast<const uint2*>(dO + tok * do_stride + hh * HD + lane * 4);
-  const uint2 o = *reinterpret_cast<const uint2*>(O + (tok * Hq + hh) * HD + lane * 4);
-  const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), o0 = unpack_bf16x2(o.x), o1 = unpack_bf16x2(o.y);
-  float s = a0.x * o0.x + a0.y * o0.y + a1.x * o1.x + a1.y * o1.y;
+  float s = 0.f;
+  if (lane * 4 < hd) {
+    const uint2 a = *reinterpret_cast<const uint2*>(dO + tok * do_stride + hh * hd + lane * 4);
+    const uint2 o = *reinterpret_cast<const uint2*>(O + (tok * Hq + hh) * hd + lane * 4);
+    const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), o0 = unpack_bf16x2(o.x), o1 = unpack_bf16x2(o.y);
+    s = a0.x * o0.x + a0.y * o0.y + a1.x * o1.x + a1.y * o1.y;
+  }
   s = warp_sum(s);
   if (lane == 0) {
     const long long bb = tok / Sq, i = tok % Sq;
@@ -576,15 +585,33 @@ extern "C" void atb_flash_bwd_set_dkv(int transposed) { g_dkv_transposed = trans
 // dq_acc must be zero on entry; dq/dk/dv are written as token-major rows of pitch dq_stride / dkv_stride
 // elements (so they may be slices of one fused [tokens, (Hq + 2 Hq) * 128] gradient buffer). dk, dv are per
 // query head; the caller sums head groups for grouped-query attention. `delta` is scratch [B, Hq, Sq].
+// One-kernel form (dQ through the fp32 buffer) for a given dropout / bias / head-dim combination.
+template <bool DROP, bool BIAS, int HDIM>
+static int bwd_variant(dim3 grid, cudaStream_t st, const CUtensorMap& tmQ, const CUtensorMap& tmdO, const CUtensorMap& tmK,
+                       const CUtensorMap& tmV, const CUtensorMap& tmdQ, const BwdParams& p) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(flash_bwd_kernel<true, DROP, BIAS, HDIM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SmemB::TOTAL) != cudaSuccess)
+      return -4;
+    attr_set = true;
+  }
+  flash_bwd_kernel<true, DROP, BIAS, HDIM><<<grid, THREADS, SmemB::TOTAL, st>>>(tmQ, tmdO, tmK, tmV, tmdQ, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
 static int flash_bwd_launch(const void* dout, const void* q, const void* k, const void* v, const void* out,
                             const float* lse, float* delta, float* dq_acc, void* dq, void* dk, void* dv,
                             const int* row_lo, const int* row_hi, int B, int Sq, int Sk, int Hq, int Hkv,
                             long long q_stride, long long k_stride, long long v_stride, long long do_stride,
                             long long dq_stride, long long dkv_stride, int causal, float softmax_scale, void* stream,
-                            int* status, DropParams drop, BiasParams bias = BiasParams{nullptr, 0, 0, 0}) {
+                            int* status, DropParams drop, BiasParams bias = BiasParams{nullptr, 0, 0, 0},
+                            int head_dim = 128) {
   if (B <= 0 || Sq <= 0 || Sk <= 0) return 0;
-  // dropout and the additive bias are implemented in the one-kernel form only
-  if ((drop.thr16 != 0 || bias.ptr != nullptr) && dq_acc == nullptr) return -1;
+  // dropout, the additive bias and head dim 64 are implemented in the one-kernel form only
+  if (head_dim != 128 && head_dim != 64) return -1;
+  const int HDv = head_dim;
+  if ((drop.thr16 != 0 || bias.ptr != nullptr || HDv != 128) && dq_acc == nullptr) return -1;
   if (bias.ptr != nullptr &&
       ((Sk & 7) || ((bias.sb | bias.sh | bias.sq) & 7) || (reinterpret_cast<uintptr_t>(bias.ptr) & 15) ||
        !(softmax_scale > 0.f)))
@@ -593,37 +620,29 @@ static int flash_bwd_launch(const void* dout, const void* q, const void* k, cons
   if ((q_stride | k_stride | v_stride | do_stride | dq_stride | dkv_stride) & 7) return -1;
   cudaStream_t st = (cudaStream_t)stream;
   CUtensorMap tmQ, tmdO, tmK, tmV, tmdQ;
-  if (!make_tmap_2d(&tmQ, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)B * Sq, (uint64_t)Hq * HD, q_stride, BQ, 64,
+  if (!make_tmap_2d(&tmQ, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)B * Sq, (uint64_t)Hq * HDv, q_stride, BQ, 64,
                     CU_TENSOR_MAP_SWIZZLE_128B))
     return -2;
-  if (!make_tmap_2d(&tmdO, dout, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)B * Sq, (uint64_t)Hq * HD, do_stride,
+  if (!make_tmap_2d(&tmdO, dout, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)B * Sq, (uint64_t)Hq * HDv, do_stride,
                     BQ, 64, CU_TENSOR_MAP_SWIZZLE_128B))
     return -2;
-  if (!make_tmap_2d(&tmK, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)B * Sk, (uint64_t)Hkv * HD, k_stride, BKV,
+  if (!make_tmap_2d(&tmK, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)B * Sk, (uint64_t)Hkv * HDv, k_stride, BKV,
                     64, CU_TENSOR_MAP_SWIZZLE_128B))
     return -2;
-  if (!make_tmap_2d(&tmV, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)B * Sk, (uint64_t)Hkv * HD, v_stride, BKV,
+  if (!make_tmap_2d(&tmV, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)B * Sk, (uint64_t)Hkv * HDv, v_stride, BKV,
                     64, CU_TENSOR_MAP_SWIZZLE_128B))
     return -2;
   // fp32 accumulation buffer as [B*Sq, Hq*HD]; the kernel adds [128 x 32] boxes to it
   if (dq_acc == nullptr) {
     tmdQ = tmQ;   // unused by the kernel variant without dQ
-  } else if (!make_tmap_2d(&tmdQ, dq_acc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)B * Sq, (uint64_t)Hq * HD,
-                           (uint64_t)Hq * HD, BQ, 32, CU_TENSOR_MAP_SWIZZLE_128B)) {
+  } else if (!make_tmap_2d(&tmdQ, dq_acc, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)B * Sq, (uint64_t)Hq * HDv,
+                           (uint64_t)Hq * HDv, BQ, 32, CU_TENSOR_MAP_SWIZZLE_128B)) {
     return -2;
   }
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(flash_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemB::TOTAL) !=
-            cudaSuccess ||
-        cudaFuncSetAttribute(flash_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemB::TOTAL) !=
-            cudaSuccess ||
-        cudaFuncSetAttribute(flash_bwd_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             SmemB::TOTAL) != cudaSuccess ||
-        cudaFuncSetAttribute(flash_bwd_kernel<true, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             SmemB::TOTAL) != cudaSuccess ||
-        cudaFuncSetAttribute(flash_bwd_kernel<true, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             SmemB::TOTAL) != cudaSuccess)
+    if (cudaFuncSetAttribute(flash_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SmemB::TOTAL) !=
+        cudaSuccess)
       return -4;
     attr_set = true;
   }
@@ -632,7 +651,7 @@ static int flash_bwd_launch(const void* dout, const void* q, const void* k, cons
     const int threads = 256;
     const long long blocks = (warps * 32 + threads - 1) / threads;
     flash_delta_kernel<<<(unsigned)blocks, threads, 0, st>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out,
-                                                             delta, B, Sq, Hq, do_stride);
+                                                             delta, B, Sq, Hq, do_stride, HDv);
   }
   BwdParams p;
   p.lse = lse; p.delta = delta; p.dq_acc = dq_acc; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv;
@@ -657,18 +676,22 @@ static int flash_bwd_launch(const void* dout, const void* q, const void* k, cons
     return atb_flash_bwd_dq(dout, q, k, v, lse, delta, dq, row_lo, row_hi, B, Sq, Sk, Hq, Hkv, q_stride, k_stride,
                             v_stride, do_stride, dq_stride, causal, softmax_scale, stream, status);
   }
-  if (drop.thr16 != 0 && bias.ptr != nullptr)
-    flash_bwd_kernel<true, true, true><<<grid, THREADS, SmemB::TOTAL, st>>>(tmQ, tmdO, tmK, tmV, tmdQ, p);
-  else if (drop.thr16 != 0)
-    flash_bwd_kernel<true, true><<<grid, THREADS, SmemB::TOTAL, st>>>(tmQ, tmdO, tmK, tmV, tmdQ, p);
-  else if (bias.ptr != nullptr)
-    flash_bwd_kernel<true, false, true><<<grid, THREADS, SmemB::TOTAL, st>>>(tmQ, tmdO, tmK, tmV, tmdQ, p);
-  else
-    flash_bwd_kernel<true><<<grid, THREADS, SmemB::TOTAL, st>>>(tmQ, tmdO, tmK, tmV, tmdQ, p);
-  const long long n4 = (long long)B * Sq * Hq * HD / 4;
+  {
+    const bool dr = drop.thr16 != 0, bi = bias.ptr != nullptr;
+    int rc;
+#define ATB_BWD_PICK(HD_)                                                                          \
+  rc = (dr && bi) ? bwd_variant<true, true, HD_>(grid, st, tmQ, tmdO, tmK, tmV, tmdQ, p)            \
+       : dr       ? bwd_variant<true, false, HD_>(grid, st, tmQ, tmdO, tmK, tmV, tmdQ, p)           \
+       : bi       ? bwd_variant<false, true, HD_>(grid, st, tmQ, tmdO, tmK, tmV, tmdQ, p)           \
+                  : bwd_variant<false, false, HD_>(grid, st, tmQ, tmdO, tmK, tmV, tmdQ, p)
+    if (HDv == 64) ATB_BWD_PICK(64); else ATB_BWD_PICK(128);
+#undef ATB_BWD_PICK
+    if (rc != 0) return rc;
+  }
+  const long long n4 = (long long)B * Sq * Hq * HDv / 4;
   long long g = (n4 + 255) / 256;
   if (g > 148 * 16) g = 148 * 16;
-  f32_to_bf16_kernel<<<(unsigned)g, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dq, n4, Hq * HD / 4, dq_stride);
+  f32_to_bf16_kernel<<<(unsigned)g, 256, 0, st>>>(dq_acc, (__nv_bfloat16*)dq, n4, Hq * HDv / 4, dq_stride);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 
@@ -710,4 +733,22 @@ extern "C" int atb_flash_bwd_bias(const void* dout, const void* q, const void* k
   return flash_bwd_launch(dout, q, k, v, out, lse, delta, dq_acc, dq, dk, dv, row_lo, row_hi, B, Sq, Sk, Hq, Hkv,
                           q_stride, k_stride, v_stride, do_stride, dq_stride, dkv_stride, causal, softmax_scale, stream,
                           status, drop, BiasParams{(const __nv_bfloat16*)bias, bias_sb, bias_sh, bias_sq});
+}
+
+// The general entry point: head dim 128 or 64, optional dropout (thr16 != 0) and additive bias (bias != null).
+// Anything but the plain head-dim-128 case needs dq_acc (one-kernel form).
+extern "C" int atb_flash_bwd_ex(const void* dout, const void* q, const void* k, const void* v, const void* out,
+                                const float* lse, float* delta, float* dq_acc, void* dq, void* dk, void* dv,
+                                const int* row_lo, const int* row_hi, int B, int Sq, int Sk, int Hq, int Hkv,
+                                long long q_stride, long long k_stride, long long v_stride, long long do_stride,
+                                long long dq_stride, long long dkv_stride, int causal, float softmax_scale,
+                                void* stream, int* status, unsigned thr16, unsigned seed_lo, unsigned seed_hi,
+                                const void* bias, long long bias_sb, long long bias_sh, long long bias_sq,
+                                int head_dim) {
+  if (thr16 >= 65536u) return -1;
+  const DropParams drop = thr16 ? DropParams{thr16, seed_lo, seed_hi, 65536.f / (float)(65536u - thr16)}
+                                : DropParams{0u, 0u, 0u, 1.f};
+  return flash_bwd_launch(dout, q, k, v, out, lse, delta, dq_acc, dq, dk, dv, row_lo, row_hi, B, Sq, Sk, Hq, Hkv,
+                          q_stride, k_stride, v_stride, do_stride, dq_stride, dkv_stride, causal, softmax_scale, stream,
+                          status, drop, BiasParams{(const __nv_bfloat16*)bias, bias_sb, bias_sh, bias_sq}, head_dim);
 }

@@ -63,7 +63,8 @@ def supported(q, k, v, dropout_p=0.0, additive_mask=None, additive_bias=None, ke
     if (q.requires_grad or k.requires_grad or v.requires_grad) and torch.is_grad_enabled() and not backward_built():
         return False
     B, Sq, Hq, D = q.shape
-    ok = q.dtype == torch.bfloat16 and D == 128 and Hq % k.shape[2] == 0
+    ok = q.dtype == torch.bfloat16 and Hq % k.shape[2] == 0 and \
+        (D == 128 or (D == 64 and _lib.lib().has("atb_flash_fwd_ex")))
     ok = ok and all(t.stride(-1) == 1 and t.stride(2) == D and t.stride(1) % 8 == 0 for t in (q, k, v))
     ok = ok and all(t.stride(0) == t.stride(1) * t.shape[1] for t in (q, k, v))
     return ok
@@ -211,11 +212,15 @@ def dropout_keep_mask(B: int, Hq: int, Sq: int, Sk: int, drop: Tuple[int, int, i
     return (bits >= thr).view(B, Hq, Sq, Sk)
 
 
-def _extra_args(drop, bias):
+def _extra_args(drop, bias, head_dim=None):
     d = drop if drop is not None else (0, 0, 0)
     extra = tuple(ctypes.c_uint(x) for x in d)
     if bias is not None:
         extra += (_lib.ptr(bias[0]),) + tuple(ctypes.c_longlong(x) for x in bias[1:])
+    elif head_dim is not None:
+        extra += (None, ctypes.c_longlong(0), ctypes.c_longlong(0), ctypes.c_longlong(0))
+    if head_dim is not None:
+        extra += (ctypes.c_int(head_dim),)
     return extra
 
 
@@ -228,7 +233,9 @@ def flash_fwd_raw(q, k, v, causal, softmax_scale, row_lo, row_hi, drop=None, bia
     lse = torch.empty(B, Hq, Sq, dtype=torch.float32, device=q.device)
     L = _lib.lib()
     # two-query-tile kernel (flash_attn_v2.cu) for long enough sequences; the single-tile kernel otherwise
-    if bias is not None:
+    if D != 128:
+        fwd, extra = L.atb_flash_fwd_ex, _extra_args(drop, bias, D)      # single-tile kernel, head dim 64
+    elif bias is not None:
         fwd, extra = L.atb_flash_fwd_bias, _extra_args(drop, bias)
     elif drop is not None:
         fwd, extra = L.atb_flash_fwd_dropout, _extra_args(drop, None)
@@ -259,7 +266,7 @@ def flash_bwd_raw(dout, q, k, v, out, lse, causal, softmax_scale, row_lo, row_hi
             _lib.lib().atb_flash_bwd_set_dkv(ctypes.c_int(int(os.environ["ATB_FLASH_BWD_DKV"])))
     # two kernels (dK/dV per key block, dQ per query block: no atomics, no fp32 scratch) unless
     # ATB_FLASH_BWD_SPLIT=0 asks for the single key-block kernel with TMA reduce-adds of dQ
-    dq_acc = None if (BWD_SPLIT and drop is None and bias is None) else \
+    dq_acc = None if (BWD_SPLIT and drop is None and bias is None and D == 128) else \
         torch.zeros(B, Sq, Hq, D, dtype=torch.float32, device=q.device)
     delta = torch.empty(B, Hq, Sq, dtype=torch.float32, device=q.device)
     if fused_out and Hkv == Hq and Sq == Sk:
@@ -272,7 +279,9 @@ def flash_bwd_raw(dout, q, k, v, out, lse, causal, softmax_scale, row_lo, row_hi
         dv = torch.empty(B, Sk, Hq, D, dtype=q.dtype, device=q.device)
     dout = dout if (dout.stride(-1) == 1 and dout.stride(2) == D and dout.stride(0) == dout.stride(1) * Sq) \
         else dout.contiguous()
-    if bias is not None:
+    if D != 128:
+        bwd, extra = _lib.lib().atb_flash_bwd_ex, _extra_args(drop, bias, D)
+    elif bias is not None:
         bwd, extra = _lib.lib().atb_flash_bwd_bias, _extra_args(drop, bias)
     elif drop is not None:
         bwd, extra = _lib.lib().atb_flash_bwd_dropout, _extra_args(drop, None)

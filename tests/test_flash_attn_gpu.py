@@ -337,3 +337,47 @@ def test_additive_bias_inside_the_flash_kernels(kind):
     for name, a, b_ in zip("qkv", qs, rs):
         err = (a.grad.float() - b_.grad).abs().max().item()
         assert err / (b_.grad.abs().max().item() + 1e-6) < 3e-2, (name, err)
+
+
+@pytest.mark.parametrize("B,Sq,Sk,Hq,Hkv,causal", [(2, 256, 256, 4, 4, True), (1, 200, 200, 12, 12, False),
+                                                   (1, 384, 640, 4, 2, True), (2, 1024, 1024, 8, 8, True)])
+def test_flash_head_dim_64(B, Sq, Sk, Hq, Hkv, causal):
+    """Head dim 64 (GPT-2, BERT, CLIP): the single-tile forward and the one-kernel backward with one 64-column
+    panel per tile, against dense fp32 attention; no library path."""
+    A = __import__("sys").modules["atorch_b200.ops.attention"]
+    torch.manual_seed(B * 10 + Sq)
+    q, k, v = _qkv(B, Sq, Sk, Hq, Hkv, D=64)
+    assert flash.supported(q, k, v)
+    before = A.library_calls
+    _bwd_check(q, k, v, causal=causal)
+    assert A.library_calls == before
+
+
+def test_flash_head_dim_64_masks_and_dropout():
+    torch.manual_seed(31)
+    B, S, H = 2, 512, 4
+    q, k, v = _qkv(B, S, S, H, H, D=64)
+    _bwd_check(q, k, v, causal=True, glm_mask=torch.tensor([100, 333], device="cuda", dtype=torch.int32))
+    kp = torch.ones(B, S, dtype=torch.bool, device="cuda")
+    kp[0, 300:] = False
+    _bwd_check(q, k, v, causal=False, key_padding_mask=kp)
+    # dropout with the host restatement of the mask
+    p_drop, seed = 0.1, 4242
+    qs = [t.detach().clone().requires_grad_() for t in (q, k, v)]
+    out = flash.flash_attention(*qs, causal=True, dropout_p=p_drop, dropout_seed=seed)
+    dout = torch.randn_like(out)
+    out.backward(dout)
+    torch.cuda.synchronize()
+    _lib.check_status(q.device)
+    drop = flash.dropout_config(p_drop, seed)
+    keep = flash.dropout_keep_mask(B, H, S, S, drop, device="cuda")
+    rs = [t.detach().float().requires_grad_() for t in (q, k, v)]
+    s = rs[0].transpose(1, 2) @ rs[1].transpose(1, 2).transpose(-1, -2) / math.sqrt(64)
+    i, j = torch.arange(S, device="cuda")[:, None], torch.arange(S, device="cuda")[None]
+    pm = torch.softmax(s.masked_fill(j > i, float("-inf")), -1) * keep * (65536.0 / (65536 - drop[0]))
+    ref = (pm @ rs[2].transpose(1, 2)).transpose(1, 2)
+    ref.backward(dout.float())
+    assert torch.allclose(out.float(), ref, rtol=2e-2, atol=2e-2)
+    for name, a, b_ in zip("qkv", qs, rs):
+        err = (a.grad.float() - b_.grad).abs().max().item()
+        assert err / (b_.grad.abs().max().item() + 1e-6) < 3e-2, (name, err)
