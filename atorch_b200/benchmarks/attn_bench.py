@@ -39,9 +39,11 @@ def main(argv=None):
     args = ap.parse_args(argv)
     dev = torch.device("cuda")
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-    for (B, S, H, Hkv, causal) in [(1, 4096, 32, 32, True), (1, 4096, 32, 32, False), (4, 2048, 16, 16, True),
-                                   (1, 4096, 32, 8, True), (1, 8192, 32, 32, True)]:
-        D = 128
+    # the last two: head dim 64 (GPT-2 medium / BERT-large like); the others: head dim 128
+    for (B, S, H, Hkv, causal, D) in [(1, 4096, 32, 32, True, 128), (1, 4096, 32, 32, False, 128),
+                                      (4, 2048, 16, 16, True, 128), (1, 4096, 32, 8, True, 128),
+                                      (1, 8192, 32, 32, True, 128), (8, 1024, 16, 16, True, 64),
+                                      (16, 512, 16, 16, False, 64)]:
         q = torch.randn(B, S, H, D, device=dev, dtype=torch.bfloat16, requires_grad=True)
         k = torch.randn(B, S, Hkv, D, device=dev, dtype=torch.bfloat16, requires_grad=True)
         v = torch.randn(B, S, Hkv, D, device=dev, dtype=torch.bfloat16, requires_grad=True)
@@ -61,7 +63,7 @@ def main(argv=None):
         flash.FWD_TWO_TILES = False
         t_l = time_fn(lib_f, args.iters, flush)
         _lib.check_status(dev)
-        line = (f"B{B} S{S} H{H}/{Hkv} causal={int(causal)} fwd: ours {t_o:8.1f} us {flops_f / t_o / 1e6:7.1f} TF | "
+        line = (f"B{B} S{S} H{H}/{Hkv} D{D} causal={int(causal)} fwd: ours {t_o:8.1f} us {flops_f / t_o / 1e6:7.1f} TF | "
                 f"ours(2 tiles) {t_o2:8.1f} us {flops_f / t_o2 / 1e6:7.1f} TF | "
                 f"SDPA {t_l:8.1f} us {flops_f / t_l / 1e6:7.1f} TF")
         fa = None

@@ -220,7 +220,9 @@ def run_ours(args):
                   "sync_module_states": False,
                   "fused_comm": {"0": False, "1": True}.get(os.environ.get("ATB_FUSED_COMM", ""), None),
                   "optimizer_in_backward": os.environ.get("ATB_OPT_IN_BACKWARD", "0") == "1",
-                  "prefetch_depth": int(os.environ.get("ATB_PREFETCH_DEPTH", "2"))}),
+                  "prefetch_depth": int(os.environ.get("ATB_PREFETCH_DEPTH", "2")),
+                  # ATB_RESHARD=0: keep the gathered bf16 parameters between forward and backward (13.5 GB for 7B)
+                  "reshard_after_forward": os.environ.get("ATB_RESHARD", "1") != "0"}),
         ("amp_native", {"dtype": torch.bfloat16}),
         ("checkpoint", {"wrap_class": (LlamaDecoderLayer,), "no_reentrant": True}),
     ]
@@ -341,6 +343,7 @@ def run_ours(args):
                        "attention_recompute": "skipped (attention output + lse of the first pass are kept)"
                                               if reuse else "executed",
                        "collective": comm,
+                       "reshard_after_forward": os.environ.get("ATB_RESHARD", "1") != "0",
                        "l2": "not flushed: 13.5 GB of bf16 weights and 108 GB of optimizer state stream per step "
                              "(inputs larger than the 126 MB L2)"},
             "hw_tflops_per_gpu": round(value / world * flops / 1e12, 1),
