@@ -203,10 +203,13 @@ class BertAttentionFA(nn.Module):
         v = s.value(hidden_states).view(B, S, self.num_heads, self.head_dim)
         kp = None
         if attention_mask is not None:
-            # HF passes an additive [B, 1, 1, S] mask: 0 = keep, large negative = drop
-            kp = (attention_mask.reshape(B, -1)[:, -S:] >= 0)
+            # HF passes [B, 1, 1, S] (or [B, 1, S, S] whose rows agree for a padding mask): additive (0 = keep, large
+            # negative = drop) or boolean (True = keep)
+            m = attention_mask[:, 0, -1] if attention_mask.dim() == 4 else attention_mask.reshape(B, -1)[:, -S:]
+            kp = m if m.dtype == torch.bool else (m >= 0)
         ctx = self.attn(q, k, v, key_padding_mask=kp).reshape(B, S, -1)
-        return (self.output(ctx, hidden_states),)
+        # (output, attention weights): recent transformers versions unpack two values
+        return self.output(ctx, hidden_states), None
 
 
 class GPT2AttentionFA(nn.Module):
