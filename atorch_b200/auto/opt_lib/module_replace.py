@@ -37,7 +37,7 @@ def _register_defaults() -> None:
     if REPLACEMENT_PAIRS:
         return
     from ...modules.normalization import AtorchLayerNorm
-    from ...modules.transformer.layers import (BertAttentionFA, GPT2AttentionFA, LlamaAttentionFA,
+    from ...modules.transformer.layers import (BertAttentionFA, CLIPAttentionFA, GPT2AttentionFA, LlamaAttentionFA,
                                                MultiheadAttentionFA, hf_classes)
 
     half = {torch.float16, torch.bfloat16}
@@ -47,7 +47,8 @@ def _register_defaults() -> None:
     hf = hf_classes()
     for nm, src, tgt in (("HF_LlamaAttention_FA", hf.get("LlamaAttention"), LlamaAttentionFA),
                          ("HF_BertAttention_FA", hf.get("BertAttention"), BertAttentionFA),
-                         ("HF_GPT2Attention_FA", hf.get("GPT2Attention"), GPT2AttentionFA)):
+                         ("HF_GPT2Attention_FA", hf.get("GPT2Attention"), GPT2AttentionFA),
+                         ("HF_CLIPAttention_FA", hf.get("CLIPAttention"), CLIPAttentionFA)):
         if src is not None:
             register_replace_pair(nm, supported_dtypes=half, pair_cls=(src, tgt))
 

@@ -240,12 +240,25 @@ class CLIPAttentionFA(nn.Module):
         self.attn = FlashAttnModule(causal=False, attention_dropout=getattr(src, "dropout", 0.0))
 
     def forward(self, hidden_states, attention_mask=None, causal_attention_mask=None, **kwargs):
+        # the text tower passes its causal (and padding) mask as a [B, 1, S, S] tensor, additive or boolean, in
+        # ``attention_mask`` (older transformers: a second ``causal_attention_mask``); the vision tower passes none.
+        # A mask with one run of visible keys per row becomes key intervals inside ops.attention.
         B, S, E = hidden_states.shape
         shp = (B, S, self.num_heads, self.head_dim)
+        mask = None
+        for m in (attention_mask, causal_attention_mask):
+            if m is None:
+                continue
+            if mask is None:
+                mask = m
+            else:
+                to_add = lambda t: torch.zeros(t.shape, device=t.device).masked_fill(~t, float("-inf")) \
+                    if t.dtype == torch.bool else t.float()
+                mask = to_add(mask) + to_add(m)
         core = self.attn
-        core.causal = causal_attention_mask is not None
+        core.causal = False
         out = core(self.q_proj(hidden_states).view(shp), self.k_proj(hidden_states).view(shp),
-                   self.v_proj(hidden_states).view(shp)).reshape(B, S, E)
+                   self.v_proj(hidden_states).view(shp), additive_mask=mask).reshape(B, S, E)
         return self.out_proj(out), None
 
 

@@ -50,3 +50,24 @@ def test_gpt2_bert_llama_replacements_match_the_stock_modules():
     assert torch.allclose(ref(input_ids=ids).logits, out.logits, atol=1e-4)
     out.loss.backward()
     assert all(p.grad is not None for n, p in new.named_parameters() if "self_attn" in n)
+
+
+def test_clip_text_and_vision_replacements():
+    from transformers import CLIPTextConfig, CLIPTextModel, CLIPVisionConfig, CLIPVisionModel
+
+    cfg = CLIPTextConfig(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                         num_attention_heads=4, max_position_embeddings=64)
+    cfg._attn_implementation = "eager"
+    ref, new = _pair(lambda: CLIPTextModel(cfg))
+    ids = torch.randint(0, 512, (2, 32))
+    am = torch.ones(2, 32, dtype=torch.long)
+    am[1, 20:] = 0
+    a = ref(input_ids=ids, attention_mask=am).last_hidden_state      # causal + padding, one [B, 1, S, S] mask
+    b = new(input_ids=ids, attention_mask=am).last_hidden_state
+    assert torch.allclose(a[am.bool()], b[am.bool()], atol=1e-4)
+    vc = CLIPVisionConfig(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4,
+                          image_size=32, patch_size=8)
+    vc._attn_implementation = "eager"
+    ref, new = _pair(lambda: CLIPVisionModel(vc))
+    x = torch.randn(2, 3, 32, 32)
+    assert torch.allclose(ref(pixel_values=x).last_hidden_state, new(pixel_values=x).last_hidden_state, atol=1e-4)
