@@ -97,6 +97,19 @@ class FlashAttnModule(nn.Module):
                                        dropout_p=kw["dropout_p"])
 
 
+def _causal_attention(core: "FlashAttnModule", q, k, v, attention_mask):
+    """Causal self-attention as the Hugging Face decoder layers call it: ``attention_mask`` is None, a ``[B, S]``
+    key-padding mask, or the ``[B, 1, S, S]`` causal-plus-padding mask (additive or boolean) that the model builds
+    once per forward; the 4-D form already contains the causal structure and is lowered to key intervals once per
+    mask tensor (ops.flash.intervals_from_additive_mask)."""
+    if attention_mask is not None and attention_mask.dim() == 4:
+        p = core.attention_dropout if core.training else 0.0
+        return ops.attention(q, k, v, causal=False, softmax_scale=core.softmax_scale, additive_mask=attention_mask,
+                             dropout_p=p)
+    kp = attention_mask if (attention_mask is not None and attention_mask.dim() == 2) else None
+    return core(q, k, v, key_padding_mask=kp)
+
+
 def hf_classes() -> dict:
     """Hugging Face attention classes that can be replaced, if transformers is importable."""
     out = {}
@@ -153,8 +166,7 @@ class LlamaAttentionFA(nn.Module):
             cos, sin = cos.unsqueeze(2), sin.unsqueeze(2)
             q = q * cos + _rotate_half(q) * sin
             k = k * cos + _rotate_half(k) * sin
-        kp = attention_mask if (attention_mask is not None and attention_mask.dim() == 2) else None
-        out = self.attn(q.contiguous(), k.contiguous(), v.contiguous(), key_padding_mask=kp)
+        out = _causal_attention(self.attn, q.contiguous(), k.contiguous(), v.contiguous(), attention_mask)
         return self.o_proj(out.reshape(B, S, -1)), None
 
 
@@ -226,8 +238,10 @@ class GPT2AttentionFA(nn.Module):
         B, S, E = hidden_states.shape
         q, k, v = self.c_attn(hidden_states).split(E, dim=2)
         shp = (B, S, self.num_heads, self.head_dim)
-        out = self.attn(q.reshape(shp), k.reshape(shp), v.reshape(shp)).reshape(B, S, E)
-        return self.resid_dropout(self.c_proj(out)), None
+        if attention_mask is None and len(args) >= 2 and torch.is_tensor(args[1]):
+            attention_mask = args[1]          # (hidden_states, past_key_values, attention_mask, ...) given by position
+        out = _causal_attention(self.attn, q.reshape(shp), k.reshape(shp), v.reshape(shp), attention_mask)
+        return self.resid_dropout(self.c_proj(out.reshape(B, S, E))), None
 
 
 class CLIPAttentionFA(nn.Module):

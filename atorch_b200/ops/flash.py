@@ -16,6 +16,7 @@ packed sequences       ``lo = start of the row's sequence`` (``cu_seqlens``)
 """
 from __future__ import annotations
 
+import collections
 import ctypes
 import math
 from typing import Optional, Tuple
@@ -26,6 +27,7 @@ from .. import _lib
 
 
 import os
+import weakref
 
 # forward kernel with two 128-row query tiles per CTA that share every K/V tile (csrc/flash_attn_v2.cu): the
 # default from 256 query rows on (measured 201 us against 256 us for the single-tile kernel at S=4096, H=32,
@@ -112,7 +114,28 @@ def row_intervals(B: int, Sq: int, Sk: int, device, causal: bool = False, glm_ma
     return lo.to(torch.int32).contiguous(), hi.to(torch.int32).contiguous()
 
 
+_INTERVAL_CACHE: "collections.OrderedDict" = collections.OrderedDict()   # the layers of one forward share one mask
+
+
 def intervals_from_additive_mask(additive_mask: torch.Tensor, B: int, Sq: int, Sk: int, causal: bool = False):
+    """Cached front of ``_intervals_from_additive_mask``: every layer of a forward pass is given the same mask
+    tensor, so the lowering (one pass over the mask and one host synchronisation) runs once per mask, not per layer."""
+    key = (additive_mask.data_ptr(), tuple(additive_mask.shape), additive_mask.dtype, additive_mask._version,
+           str(additive_mask.device), B, Sq, Sk, bool(causal))
+    hit = _INTERVAL_CACHE.get(key)
+    if hit is not None and hit[0]() is additive_mask:
+        return hit[1]
+    out = _intervals_from_additive_mask(additive_mask, B, Sq, Sk, causal)
+    try:
+        _INTERVAL_CACHE[key] = (weakref.ref(additive_mask), out)
+    except TypeError:
+        return out
+    while len(_INTERVAL_CACHE) > 8:
+        _INTERVAL_CACHE.popitem(last=False)
+    return out
+
+
+def _intervals_from_additive_mask(additive_mask: torch.Tensor, B: int, Sq: int, Sk: int, causal: bool = False):
     """Lower a dense mask to per-row key intervals, or return ``None`` when it is not of that form.
 
     ``additive_mask``: broadcastable to ``[B, 1, Sq, Sk]`` (the same for every head), either boolean (True =

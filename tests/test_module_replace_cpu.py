@@ -71,3 +71,24 @@ def test_clip_text_and_vision_replacements():
     ref, new = _pair(lambda: CLIPVisionModel(vc))
     x = torch.randn(2, 3, 32, 32)
     assert torch.allclose(ref(pixel_values=x).last_hidden_state, new(pixel_values=x).last_hidden_state, atol=1e-4)
+
+
+def test_decoder_replacements_honour_padding_in_the_4d_mask():
+    """GPT-2 and Llama with a left-padded batch: the model hands every layer one [B, 1, S, S] causal + padding mask."""
+    from transformers import GPT2Config, GPT2LMHeadModel, LlamaConfig, LlamaForCausalLM
+
+    ids = torch.randint(0, 512, (2, 40))
+    am = torch.ones(2, 40, dtype=torch.long)
+    am[1, :13] = 0
+    cfg = GPT2Config(vocab_size=512, n_positions=256, n_embd=256, n_layer=2, n_head=4, resid_pdrop=0.0, embd_pdrop=0.0,
+                     attn_pdrop=0.0)
+    cfg._attn_implementation = "eager"
+    ref, new = _pair(lambda: GPT2LMHeadModel(cfg))
+    a, b = ref(input_ids=ids, attention_mask=am).logits, new(input_ids=ids, attention_mask=am).logits
+    assert torch.allclose(a[am.bool()], b[am.bool()], atol=1e-4)
+    cfg = LlamaConfig(vocab_size=512, hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=512)
+    cfg._attn_implementation = "eager"
+    ref, new = _pair(lambda: LlamaForCausalLM(cfg))
+    a, b = ref(input_ids=ids, attention_mask=am).logits, new(input_ids=ids, attention_mask=am).logits
+    assert torch.allclose(a[am.bool()], b[am.bool()], atol=1e-4)
