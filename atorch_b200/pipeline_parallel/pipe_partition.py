@@ -10,6 +10,8 @@ from __future__ import annotations
 
 from typing import Dict, List, Optional, Sequence, Tuple, Union
 
+import torch.nn as nn
+
 
 def layers_per_stage(total_layer_num: int, total_stages: int,
                      manual: Union[None, Sequence[int], Dict[int, int]] = None) -> List[int]:
@@ -65,12 +67,10 @@ def partition_model_from_model_provider(model_provider, distributed_context, con
     return modules, stage_ids, None
 
 
-class _SequentialStage(__import__("torch").nn.Module):
+class _SequentialStage(nn.Module):
     """One pipeline stage cut out of a model that is a chain ``pre -> layers[i] ... -> post``."""
 
     def __init__(self, pre, layers, post):
-        import torch.nn as nn
-
         super().__init__()
         self.pre, self.layers, self.post = nn.ModuleList(pre), nn.ModuleList(layers), nn.ModuleList(post)
 
@@ -89,9 +89,6 @@ def partition_model_from_meta_model(meta_model, distributed_context, config):
     ``reset_parameters``), so a model that does not fit one device can still be partitioned. Models whose data
     flow is not a chain need a ``model_provider`` instead. (The reference declares this entry point and leaves it
     unimplemented: atorch/pipeline_parallel/pipe_partition.py:127-129.)"""
-    import torch
-    import torch.nn as nn
-
     lists = [(n, m) for n, m in meta_model.named_modules() if isinstance(m, nn.ModuleList)]
     assert lists, "no nn.ModuleList of layers found; pass a model_provider"
     lname, layers = max(lists, key=lambda t: len(t[1]))
@@ -129,5 +126,4 @@ def partition_model_from_meta_model(meta_model, distributed_context, config):
                     m.reset_parameters()
         modules.append(stage)
         stage_ids.append(sid)
-    del torch
     return modules, stage_ids, None
