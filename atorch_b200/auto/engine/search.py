@@ -17,6 +17,7 @@ does: rank 0 hosts the engine (:mod:`atorch_b200.auto.engine.service`, task queu
 """
 from __future__ import annotations
 
+import random
 import itertools
 import logging
 import time
@@ -86,7 +87,7 @@ class BayesianGenerator:
         self.max_iter, self.patience, self.random_sample = max_iter, patience, random_sample
         self.space = list(itertools.product(*self.GROUPS.values()))
         self.X, self.y, self.tried = [], [], set()
-        self.rng = __import__("random").Random(seed)
+        self.rng = random.Random(seed)
 
     def _encode(self, combo):
         v = []

@@ -9,6 +9,7 @@ by the sharded engine over the ``data`` group with per-layer recomputation, and 
 """
 from __future__ import annotations
 
+import json
 import argparse
 
 import torch
@@ -146,7 +147,7 @@ def main(argv=None):
                       "micro_batches": a.micro_batches, "schedule": "1F1B", "optimizer": "AGD lr 3e-4"}}
     if last and (D.parallel_rank("tensor") or 0) == 0 and (D.parallel_rank("data") or 0) == 0:
         rec["losses"] = [round(x, 4) for x in losses]
-        print("LAST_STAGE " + __import__("json").dumps(rec), flush=True)
+        print("LAST_STAGE " + json.dumps(rec), flush=True)
     report(rank, rec)
     return losses
 

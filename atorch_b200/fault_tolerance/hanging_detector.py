@@ -10,6 +10,7 @@ the host: the store is a ``torch.distributed.TCPStore`` (address from
 """
 from __future__ import annotations
 
+import datetime
 import os
 import threading
 import time
@@ -37,7 +38,7 @@ class RelaunchStatus:
             return None
         from torch.distributed import TCPStore
 
-        return TCPStore(addr, int(port), is_master=False, timeout=__import__("datetime").timedelta(seconds=30))
+        return TCPStore(addr, int(port), is_master=False, timeout=datetime.timedelta(seconds=30))
 
     def _set(self, key: str, value: int) -> None:
         self.store.set(self.PREFIX + key, str(value))

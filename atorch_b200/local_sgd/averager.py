@@ -24,6 +24,7 @@ stateful_post_localSGD_optimizer.py:6-20.)
 """
 from __future__ import annotations
 
+import time
 from typing import Dict, Iterable, List, Optional, Union
 
 import torch
@@ -79,7 +80,7 @@ class OuterOptimPeriodicModelAverager:
         self.last_sync_timestamp: Optional[float] = None
         self.last_total_global_step = 0
         self._step_at_last_sync = 0
-        self._clock = __import__("time").time      # replaceable in tests
+        self._clock = time.time      # replaceable in tests
 
     # ------------------------------------------------------------------------------- state
     def state_dict(self) -> Dict:
