@@ -473,6 +473,22 @@ p2p_allgather_kernel(Peers pr, long long shard_vec16, uint4* __restrict__ out, i
 }
 
 // Stream-ordered flags: one block.
+// dst[i] += src[i] for a bf16 source in this GPU's memory and an fp32 destination that may live on a peer (its
+// address in the symmetric buffer): vector red.add through NVLink, no read of the destination. n % 8 == 0.
+__global__ void peer_add_bf16_kernel(float* __restrict__ dst, const __nv_bfloat16* __restrict__ src, long long n8) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    const uint4 u = reinterpret_cast<const uint4*>(src)[i];
+    const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+    float* o = dst + i * 8;
+    asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o), "f"(a.x), "f"(a.y), "f"(b.x),
+                 "f"(b.y)
+                 : "memory");
+    asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(o + 4), "f"(c.x), "f"(c.y), "f"(d.x),
+                 "f"(d.y)
+                 : "memory");
+  }
+}
+
 __global__ void pad_signal_kernel(Peers pr, int ch) {
   __syncthreads();
   signal_all(pr, ch);
@@ -643,5 +659,18 @@ extern "C" int atb_pad_wait(const unsigned long long* pad_ptrs, int rank, int wo
   Peers pr;
   if (channel < 0 || channel > 3 || !fill_peers(pr, nullptr, pad_ptrs, 0, nullptr, rank, world, seq)) return -1;
   pad_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(pr, channel * 8, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+// dst (fp32, this GPU's or a peer's address inside a symmetric buffer) += src (bf16, local). n % 8 == 0; both 16-byte
+// aligned. Completion is ordered with the stream; pair it with a pad signal so that the owner knows when to read.
+extern "C" int atb_peer_add_bf16(unsigned long long dst, const void* src, long long n, void* stream) {
+  if (n <= 0) return 0;
+  if ((n & 7) || (dst & 15) || (reinterpret_cast<uintptr_t>(src) & 15)) return -1;
+  const long long n8 = n >> 3;
+  long long g = (n8 + 255) / 256;
+  if (g > 148 * 8) g = 148 * 8;
+  peer_add_bf16_kernel<<<(unsigned)g, 256, 0, (cudaStream_t)stream>>>(reinterpret_cast<float*>(dst),
+                                                                      (const __nv_bfloat16*)src, n8);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

@@ -4,7 +4,9 @@
   the full sequence with ``H / sp`` heads, attention runs locally (flash kernels), a second
   all-to-all swaps back. ``set_sp(sp_size, sp_rank, sp_group)`` is the hook called by the
   ``sequence_parallel`` optimisation.
-* ``ring_attention``: K/V stay sequence-sharded and travel round the ring (``sp - 1`` send/recv steps);
+* ``ring_attention``: on GPUs of one NVLink domain the flash kernels run per chunk and the copy engines pull the
+  peers' K/V chunks out of symmetric memory (``ops/ring_flash.py``); elsewhere (CPU / gloo, odd shapes) K/V stay
+  sequence-sharded and travel round the ring with dense attention per step (``sp - 1`` send/recv steps);
   each step's partial output is merged with the running one through the log-sum-exp rule
   ``o = (o1 e^{l1} + o2 e^{l2}) / (e^{l1} + e^{l2})``. Causal masking uses contiguous chunks: a rank
   skips chunks from higher ranks and runs the diagonal chunk causally. Differentiable through autograd.
@@ -93,6 +95,12 @@ def ring_attention(q, k, v, group=None, causal: bool = True, softmax_scale: Opti
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     rank = dist.get_rank(group) if dist.is_initialized() else 0
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if world > 1 and q.is_cuda:
+        from ..ops import ring_flash
+
+        grp = group if group is not None else dist.group.WORLD
+        if ring_flash.available(q, k, v, grp):      # flash kernels per chunk, chunks pulled over peer memory
+            return ring_flash.ring_flash_attention(q, k, v, grp, causal, scale)
     out, lse = None, None
     kv = torch.stack([k, v])
     for step in range(world):

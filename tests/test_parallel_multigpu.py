@@ -373,3 +373,49 @@ def _sharded_weight(rank, world):
 @pytest.mark.skipif(NGPU < 2, reason="needs 2 GPUs")
 def test_sharded_weight_linear_fused_with_collectives():
     run_distributed(_sharded_weight, world=min(NGPU, 4) if NGPU != 3 else 2, backend="nccl", timeout=300)
+
+
+# ------------------------------------------------- sequence parallel attention on the flash kernels (ring, Ulysses)
+def _ring_flash(rank, world):
+    """Ring attention with the flash kernels per chunk and K/V chunks pulled over peer memory, causal and full,
+    forward and backward, twice in a row (buffers are reused), against dense attention on the whole sequence."""
+    import torch.distributed as dist
+
+    from atorch_b200 import _lib
+    from atorch_b200.ops import attention_reference, ring_flash
+    from atorch_b200.parallel.sequence_parallel import UlyssesAttention, ring_attention
+
+    dev = torch.device("cuda", rank)
+    B, S_loc, H, D = 2, 256, 4, 128
+    S = S_loc * world
+    for it, causal in enumerate((True, False, True)):
+        g = torch.Generator().manual_seed(40 + it)
+        full = [(0.5 * torch.randn(B, S, H, D, generator=g)).to(dev).bfloat16() for _ in range(3)]
+        gy = torch.randn(B, S, H, D, generator=g).to(dev).bfloat16()
+        sl = slice(rank * S_loc, (rank + 1) * S_loc)
+        q, k, v = (t[:, sl].clone().requires_grad_() for t in full)
+        assert ring_flash.available(q, k, v, dist.group.WORLD)
+        out = ring_attention(q, k, v, dist.group.WORLD, causal=causal)
+        assert type(out.grad_fn).__name__ == "_RingFlashBackward"
+        out.backward(gy[:, sl])
+        rq, rk, rv = (t.float().requires_grad_() for t in full)
+        ref = attention_reference(rq, rk, rv, causal=causal)
+        ref.backward(gy.float())
+        torch.cuda.synchronize()
+        _lib.check_status(dev)
+        assert torch.allclose(out.float(), ref[:, sl], rtol=2e-2, atol=2e-2), (it, (out.float() - ref[:, sl]).abs().max())
+        for name, a, b in (("q", q, rq), ("k", k, rk), ("v", v, rv)):
+            gb = b.grad[:, sl]
+            err = (a.grad.float() - gb).abs().max().item()
+            assert err < 3e-2 * (gb.abs().max().item() + 1e-6), (it, name, err)
+        # Ulysses on the same data: heads scattered, sequence gathered, flash kernels locally
+        ul = UlyssesAttention(causal=causal)
+        ul.set_sp(world, rank, dist.group.WORLD)
+        q2, k2, v2 = (t[:, sl].clone().requires_grad_() for t in full)
+        o2 = ul(q2, k2, v2)
+        assert torch.allclose(o2.float(), ref[:, sl], rtol=2e-2, atol=2e-2), it
+
+
+@pytest.mark.skipif(NGPU < 2, reason="needs 2 GPUs")
+def test_ring_attention_on_flash_kernels_over_peer_memory():
+    run_distributed(_ring_flash, world=min(NGPU, 4) if NGPU != 3 else 2, backend="nccl", timeout=300)
