@@ -433,6 +433,13 @@ class _SeqAllToAll(torch.autograd.Function):
             return x
         # [.., scatter, ..] -> [sp, .., scatter/sp, ..] contiguous chunks, one per destination
         send = torch.stack([c for c in torch.tensor_split(x, sp_size, scatter_idx)]).contiguous()
+        grp = group if group is not None else dist.group.WORLD
+        if send.is_cuda and os.environ.get("ATB_FUSED_COMM", "1") != "0":
+            from ..parallel import symm
+
+            if sp_size == dist.get_world_size(grp) and symm.all_to_all_available(send, grp):
+                recv = symm.all_to_all_pull(send, grp)      # copy-engine pulls out of symmetric memory
+                return torch.cat(list(recv.unbind(0)), dim=gather_idx).contiguous()
         recv = torch.empty_like(send)
         dist.all_to_all_single(recv, send, group=group)
         return torch.cat(list(recv.unbind(0)), dim=gather_idx).contiguous()

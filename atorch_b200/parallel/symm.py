@@ -209,3 +209,40 @@ class SymmetricBuffer:
         for k in range(self.world):
             p = (self.rank + 1 + k) % self.world
             out[p * n: (p + 1) * n].copy_(self.peer_view(p)[offset: offset + n], non_blocking=True)
+
+
+# ----------------------------------------------------------------------------------------------
+# all-to-all by pulls: every rank publishes ``send [W, chunk]`` in symmetric memory and copies, with the copy
+# engines, chunk ``rank`` of every peer's buffer into ``recv [W, chunk]`` (what dist.all_to_all_single does, without
+# a collective kernel on the SMs). Used by the Ulysses head <-> sequence exchange.
+# ----------------------------------------------------------------------------------------------
+_a2a_buffers: dict = {}
+
+
+def all_to_all_available(x: torch.Tensor, group) -> bool:
+    return (x.is_cuda and available() and 1 < dist.get_world_size(group) <= SymmetricBuffer.MAX_RANKS
+            and (x.numel() * x.element_size()) % 16 == 0)
+
+
+def all_to_all_pull(send: torch.Tensor, group) -> torch.Tensor:
+    """``recv[p] = rank p's send[rank]`` for ``send`` of shape ``[W, ...]`` (contiguous)."""
+    W, r = dist.get_world_size(group), dist.get_rank(group)
+    assert send.shape[0] == W and send.is_contiguous()
+    key = (id(group), send.numel(), send.dtype, send.device.index)
+    buf = _a2a_buffers.get(key)
+    if buf is None:
+        buf = _a2a_buffers[key] = SymmetricBuffer(send.numel(), send.dtype, group, send.device)
+    if buf.seq > 0:
+        buf.wait(CH_DONE, buf.seq)                 # every peer has read the previous contents
+    buf.tensor.copy_(send.reshape(-1))
+    buf.seq += 1
+    buf.signal(CH_READY, buf.seq)
+    buf.wait(CH_READY, buf.seq)                    # every rank has published
+    recv = torch.empty_like(send)
+    n = send.numel() // W
+    flat = recv.view(W, n)
+    for k in range(W):
+        p = (r + k) % W
+        flat[p].copy_(buf.peer_view(p)[r * n: (r + 1) * n], non_blocking=True)
+    buf.signal(CH_DONE, buf.seq)
+    return recv

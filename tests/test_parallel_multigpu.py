@@ -414,6 +414,10 @@ def _ring_flash(rank, world):
         q2, k2, v2 = (t[:, sl].clone().requires_grad_() for t in full)
         o2 = ul(q2, k2, v2)
         assert torch.allclose(o2.float(), ref[:, sl], rtol=2e-2, atol=2e-2), it
+        o2.backward(gy[:, sl])
+        for name, a, b in (("q", q2, rq), ("k", k2, rk), ("v", v2, rv)):
+            gb = b.grad[:, sl]
+            assert (a.grad.float() - gb).abs().max().item() < 3e-2 * (gb.abs().max().item() + 1e-6), (it, name)
 
 
 @pytest.mark.skipif(NGPU < 2, reason="needs 2 GPUs")
