@@ -118,28 +118,61 @@ def _visit_chunks(c: _Ctx, k: torch.Tensor, v: torch.Tensor, causal: bool, fn) -
         t.record_stream(c.copy_stream)
 
 
+def zigzag_shard(x: torch.Tensor, rank: int, world: int, dim: int = 1) -> torch.Tensor:
+    """This rank's part of ``x`` in the load-balanced layout for causal ring attention: the sequence is cut into
+    ``2 W`` pieces and rank r holds pieces ``r`` and ``2 W - 1 - r`` (in that order)."""
+    pieces = x.chunk(2 * world, dim)
+    return torch.cat([pieces[rank], pieces[2 * world - 1 - rank]], dim)
+
+
+def zigzag_unshard(parts, dim: int = 1) -> torch.Tensor:
+    """Inverse of ``zigzag_shard`` for the list of all ranks' parts."""
+    world = len(parts)
+    lo = [p.chunk(2, dim)[0] for p in parts]
+    hi = [p.chunk(2, dim)[1] for p in parts]
+    return torch.cat(lo + hi[::-1], dim)
+
+
+def _plan(owner: int, rank: int, causal: bool, zigzag: bool, S: int):
+    """Which (query rows, key rows, causal?) products this rank computes against ``owner``'s chunk. Contiguous
+    layout: everything against an earlier (or, without a mask, any) chunk. Zigzag layout with a causal mask: both
+    query halves against the first key half of an earlier rank, the second query half against both key halves of a
+    later rank - two half-by-half products per peer on every rank."""
+    full = slice(0, S)
+    if owner == rank:
+        return [(full, full, causal)]
+    if not (causal and zigzag):
+        return [(full, full, False)]
+    h = S // 2
+    return [(full, slice(0, h), False)] if owner < rank else [(slice(h, S), full, False)]
+
+
 class _RingFlash(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, group, causal, scale):
+    def forward(ctx, q, k, v, group, causal, scale, zigzag):
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         c = _ctx(group, k.shape, k.device)
-        state = {"out": None, "lse": None}
+        B, S, H, _ = q.shape
+        out = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+        lse = torch.full((B, H, S), float("-inf"), dtype=torch.float32, device=q.device)
 
         def step(owner, kc, vc, is_own):
-            o_i, lse_i = flash.flash_fwd_raw(q, kc, vc, bool(causal and is_own), scale, None, None)
-            if state["out"] is None:
-                state["out"], state["lse"] = o_i.float(), lse_i
-                return
-            lse = torch.logaddexp(state["lse"], lse_i)                       # [B, H, S]
-            w_old = torch.exp(state["lse"] - lse).transpose(1, 2).unsqueeze(-1)
-            w_new = torch.exp(lse_i - lse).transpose(1, 2).unsqueeze(-1)
-            state["out"] = state["out"] * w_old + o_i.float() * w_new
-            state["lse"] = lse
+            for qs, ks, cz in _plan(owner, c.rank, causal, zigzag, S):
+                whole_q = qs.stop - qs.start == S
+                qq = q if whole_q else q[:, qs].contiguous()
+                kk, vv = (kc, vc) if ks.stop - ks.start == S else (kc[:, ks].contiguous(), vc[:, ks].contiguous())
+                o_i, lse_i = flash.flash_fwd_raw(qq, kk, vv, cz, scale, None, None)
+                old = lse[:, :, qs]
+                new = torch.logaddexp(old, lse_i)                            # [B, H, rows]; the own chunk comes first,
+                w_old = torch.exp(old - new).transpose(1, 2).unsqueeze(-1)   # so `new` is finite from then on
+                w_new = torch.exp(lse_i - new).transpose(1, 2).unsqueeze(-1)
+                out[:, qs] = out[:, qs] * w_old + o_i.float() * w_new
+                lse[:, :, qs] = new
 
-        _visit_chunks(c, k, v, causal, step)
-        out = state["out"].to(q.dtype)
-        ctx.save_for_backward(q, k, v, out, state["lse"])
-        ctx.cfg = (group, causal, scale)
+        _visit_chunks(c, k, v, causal and not zigzag, step)
+        out = out.to(q.dtype)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.cfg = (group, causal, scale, zigzag)
         return out
 
     @staticmethod
@@ -147,7 +180,8 @@ class _RingFlash(torch.autograd.Function):
         from ..parallel.symm import CH_ARRIVE, CH_READY
 
         q, k, v, out, lse = ctx.saved_tensors
-        group, causal, scale = ctx.cfg
+        group, causal, scale, zigzag = ctx.cfg
+        S = q.shape[1]
         c = _ctx(group, k.shape, k.device)
         dout = dout.contiguous()
         if c.acc.seq > 0:
@@ -157,15 +191,26 @@ class _RingFlash(torch.autograd.Function):
         keep = []
 
         def step(owner, kc, vc, is_own):
-            dq_i, dk_i, dv_i = flash.flash_bwd_raw(dout, q, kc, vc, out, lse, bool(causal and is_own), scale, None, None)
-            dq.add_(dq_i)
-            dkv = torch.cat([dk_i.reshape(-1), dv_i.reshape(-1)])
-            rc = _lib.lib().atb_peer_add_bf16(ctypes.c_ulonglong(c.acc_ptrs[owner]), _lib.ptr(dkv),
-                                              ctypes.c_longlong(dkv.numel()), _lib.stream_ptr())
-            _lib.check(rc, "atb_peer_add_bf16")
-            keep.append(dkv)
+            for qs, ks, cz in _plan(owner, c.rank, causal, zigzag, S):
+                whole_q, whole_k = qs.stop - qs.start == S, ks.stop - ks.start == S
+                sub = (lambda t: t) if whole_q else (lambda t: t[:, qs].contiguous())
+                kk, vv = (kc, vc) if whole_k else (kc[:, ks].contiguous(), vc[:, ks].contiguous())
+                lse_q = lse if whole_q else lse[:, :, qs].contiguous()
+                dq_i, dk_i, dv_i = flash.flash_bwd_raw(sub(dout), sub(q), kk, vv, sub(out), lse_q, cz, scale, None, None)
+                dq[:, qs] += dq_i
+                if whole_k:
+                    dkv = torch.cat([dk_i.reshape(-1), dv_i.reshape(-1)])
+                else:                        # a key half: the other half of the owner's gradient gets zeros
+                    full = torch.zeros((2,) + tuple(kc.shape), dtype=dk_i.dtype, device=dk_i.device)
+                    full[0][:, ks] = dk_i
+                    full[1][:, ks] = dv_i
+                    dkv = full.reshape(-1)
+                rc = _lib.lib().atb_peer_add_bf16(ctypes.c_ulonglong(c.acc_ptrs[owner]), _lib.ptr(dkv),
+                                                  ctypes.c_longlong(dkv.numel()), _lib.stream_ptr())
+                _lib.check(rc, "atb_peer_add_bf16")
+                keep.append(dkv)
 
-        _visit_chunks(c, k, v, causal, step)
+        _visit_chunks(c, k, v, causal and not zigzag, step)
         c.acc.signal(CH_ARRIVE, c.acc.seq)           # my contributions are out
         c.acc.wait(CH_ARRIVE, c.acc.seq)             # ... and everybody's are in
         half = c.n // 2
@@ -173,11 +218,16 @@ class _RingFlash(torch.autograd.Function):
         dv = c.acc.tensor[half:].view(v.shape).to(v.dtype)
         c.acc.tensor.zero_()
         c.acc.signal(CH_READY, c.acc.seq)
-        return dq.to(q.dtype), dk, dv, None, None, None
+        return dq.to(q.dtype), dk, dv, None, None, None, None
 
 
-def ring_flash_attention(q, k, v, group, causal: bool = True, softmax_scale=None) -> torch.Tensor:
-    """q, k, v: this rank's ``[B, S / W, H, D]`` chunk (chunks in rank order); returns the attention output of the
-    local queries over the whole sequence."""
+def ring_flash_attention(q, k, v, group, causal: bool = True, softmax_scale=None, layout: str = "contiguous"):
+    """q, k, v: this rank's ``[B, S / W, H, D]`` part of the sequence; returns the attention output of the local
+    queries over the whole sequence. ``layout="contiguous"``: parts are consecutive chunks in rank order (with a
+    causal mask rank r then works on r + 1 chunks). ``layout="zigzag"``: parts made by ``zigzag_shard`` (pieces r
+    and 2 W - 1 - r), which gives every rank the same amount of causal work."""
+    assert layout in ("contiguous", "zigzag"), layout
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(q.shape[-1])
-    return _RingFlash.apply(q, k, v, group, bool(causal), float(scale))
+    zigzag = layout == "zigzag" and causal
+    assert not zigzag or q.shape[1] % 2 == 0
+    return _RingFlash.apply(q, k, v, group, bool(causal), float(scale), zigzag)

@@ -90,8 +90,11 @@ def _ring_pass(x, group, direction: int):
     return out
 
 
-def ring_attention(q, k, v, group=None, causal: bool = True, softmax_scale: Optional[float] = None):
-    """q, k, v are this rank's contiguous sequence chunk ``[B, S/sp, H, D]``; returns the chunk's output."""
+def ring_attention(q, k, v, group=None, causal: bool = True, softmax_scale: Optional[float] = None,
+                   layout: str = "contiguous"):
+    """q, k, v are this rank's part of the sequence ``[B, S/sp, H, D]``; returns that part's output.
+    ``layout="contiguous"``: consecutive chunks in rank order. ``layout="zigzag"`` (GPU form only): parts made by
+    ``ops.ring_flash.zigzag_shard``, which balances the causal work over the ranks."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     rank = dist.get_rank(group) if dist.is_initialized() else 0
     scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(q.shape[-1])
@@ -100,7 +103,9 @@ def ring_attention(q, k, v, group=None, causal: bool = True, softmax_scale: Opti
 
         grp = group if group is not None else dist.group.WORLD
         if ring_flash.available(q, k, v, grp):      # flash kernels per chunk, chunks pulled over peer memory
-            return ring_flash.ring_flash_attention(q, k, v, grp, causal, scale)
+            return ring_flash.ring_flash_attention(q, k, v, grp, causal, scale, layout)
+    if layout != "contiguous" and causal and world > 1:
+        raise NotImplementedError("the zigzag layout needs the flash / peer-memory form (CUDA, bf16, head dim 64 or 128)")
     out, lse = None, None
     kv = torch.stack([k, v])
     for step in range(world):

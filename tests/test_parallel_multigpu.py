@@ -408,6 +408,19 @@ def _ring_flash(rank, world):
             gb = b.grad[:, sl]
             err = (a.grad.float() - gb).abs().max().item()
             assert err < 3e-2 * (gb.abs().max().item() + 1e-6), (it, name, err)
+        if causal:
+            # load-balanced layout: rank r holds pieces r and 2W-1-r of the sequence
+            zq, zk, zv = (ring_flash.zigzag_shard(t, rank, world).clone().requires_grad_() for t in full)
+            zo = ring_attention(zq, zk, zv, dist.group.WORLD, causal=True, layout="zigzag")
+            zo.backward(ring_flash.zigzag_shard(gy, rank, world))
+            torch.cuda.synchronize()
+            _lib.check_status(dev)
+            zref = ring_flash.zigzag_shard(ref, rank, world)
+            assert torch.allclose(zo.float(), zref, rtol=2e-2, atol=2e-2), (it, (zo.float() - zref).abs().max())
+            for name, a, b in (("q", zq, rq), ("k", zk, rk), ("v", zv, rv)):
+                gb = ring_flash.zigzag_shard(b.grad, rank, world)
+                err = (a.grad.float() - gb).abs().max().item()
+                assert err < 3e-2 * (gb.abs().max().item() + 1e-6), (it, "zigzag", name, err)
         # Ulysses on the same data: heads scattered, sequence gathered, flash kernels locally
         ul = UlyssesAttention(causal=causal)
         ul.set_sp(world, rank, dist.group.WORLD)
