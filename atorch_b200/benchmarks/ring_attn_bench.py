@@ -45,7 +45,10 @@ def main(argv=None):
     S = S_loc * world
     flops = 3.5 * 4.0 * S * S * H * D * 0.5          # forward + backward, causal
     res = {}
-    for name, fn in (("ring", lambda: ring_attention(q, k, v, group, causal=True)), ("ulysses", lambda: ul(q, k, v))):
+    cases = [("ring", lambda: ring_attention(q, k, v, group, causal=True)), ("ulysses", lambda: ul(q, k, v))]
+    if dev.type == "cuda" and world > 1:     # the same tensors read as the load-balanced layout (timing only)
+        cases.insert(1, ("ring_zigzag", lambda: ring_attention(q, k, v, group, causal=True, layout="zigzag")))
+    for name, fn in cases:
         if name == "ulysses" and H % world:
             continue
         ms = run(fn)
