@@ -167,7 +167,7 @@ class _UnitFn(torch.autograd.Function):
         ctx.proto = [None if isinstance(t, torch.Tensor) else t for t in flat]
         ctx.autocast = (torch.is_autocast_enabled(eng.device.type), torch.get_autocast_dtype(eng.device.type)) \
             if hasattr(torch, "get_autocast_dtype") else (False, None)
-        eng._pre_forward(unit)
+        eng._pre_forward(unit, will_backward=True)
         if unit.checkpoint:
             ctx.save_for_backward(*[flat[i] for i in ctx.tensor_idx])
             ctx.token = new_pass_token()
@@ -511,10 +511,12 @@ class FSDPEngine:
             u.gather_event = None
 
     # ------------------------------------------------------------------------------- schedule
-    def _pre_forward(self, u: FlatUnit) -> None:
+    def _pre_forward(self, u: FlatUnit, will_backward: bool = False) -> None:
+        """``will_backward``: this forward is an autograd node, so the unit goes on the list the backward prefetch
+        walks in reverse (grad mode cannot tell: it is off inside an autograd function's forward)."""
         self._unshard(u)
         self._wait_unshard(u)
-        if torch.is_grad_enabled():
+        if will_backward or torch.is_grad_enabled():
             self.exec_order.append(u)
         if self.cfg.forward_prefetch and self.world > 1:
             for nxt in self._next_in_order(u):
