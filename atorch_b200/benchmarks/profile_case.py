@@ -1,6 +1,6 @@
 """Runs one kernel a few times on a case sized for an ncu capture (inputs above the 126 MB L2, well
 under a few GB): ``python -m atorch_b200.benchmarks.profile_case <case>`` with case one of
-gemm | gemm1 | gemm_grouped | flash_fwd | flash_bwd | rmsnorm | layernorm | rope | swiglu | ce | adamw | agd |
+gemm | gemm1 | gemm_swiglu | gemm_grouped | flash_hd64 | flash_fwd | flash_bwd | rmsnorm | layernorm | rope | swiglu | ce | adamw | agd |
 fp8_quant | fp8_gemm | quant | moe | reduce_scatter. The last two run the peer-memory kernels on a process
 group of one rank (the "peers" are this GPU), which exercises the same code without a second GPU.
 """
@@ -51,6 +51,18 @@ def main(argv=None):
         lp = torch.empty(m, device=dev, dtype=torch.bfloat16)
         for i in range(n):
             ops.adamw_step(master, a, b, g, lp, 1e-3, 0.9, 0.999, 1e-8, 0.01, i + 1)
+    elif case == "gemm_swiglu":          # gate|up projection with SwiGLU in the epilogue, Llama-2 7B shape
+        from atorch_b200.ops.gemm import gemm_swiglu
+
+        x = torch.randn(4096, 4096, device=dev, dtype=torch.bfloat16)
+        w = torch.randn(2 * 11008, 4096, device=dev, dtype=torch.bfloat16) * 0.02
+        for i in range(n):
+            gemm_swiglu(x, w, keep_gate_up=bool(i & 1))        # without / with the pre-activation output
+    elif case == "flash_hd64":           # head dim 64: single-tile forward, one-kernel backward
+        q, k, v = (torch.randn(8, 1024, 16, 64, device=dev, dtype=torch.bfloat16) for _ in range(3))
+        for _ in range(n):
+            out, lse = flash.flash_fwd_raw(q, k, v, True, 0.125, None, None)
+            flash.flash_bwd_raw(torch.ones_like(out), q, k, v, out, lse, True, 0.125, None, None)
     elif case == "gemm_grouped":
         E, W, cap, K, N = 1, 8, 1280, 4096, 4096
         x = torch.randn(E * W * cap, K, device=dev, dtype=torch.bfloat16)
