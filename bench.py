@@ -222,7 +222,8 @@ def run_ours(args):
                   "optimizer_in_backward": os.environ.get("ATB_OPT_IN_BACKWARD", "0") == "1",
                   "prefetch_depth": int(os.environ.get("ATB_PREFETCH_DEPTH", "2")),
                   # ATB_RESHARD=0: keep the gathered bf16 parameters between forward and backward (13.5 GB for 7B)
-                  "reshard_after_forward": os.environ.get("ATB_RESHARD", "1") != "0"}),
+                  "reshard_after_forward": os.environ.get("ATB_RESHARD", "1") != "0",
+                  "backward_prefetch": os.environ.get("ATB_BWD_PREFETCH", "1") != "0"}),
         ("amp_native", {"dtype": torch.bfloat16}),
         ("checkpoint", {"wrap_class": (LlamaDecoderLayer,), "no_reentrant": True}),
     ]
