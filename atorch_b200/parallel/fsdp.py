@@ -40,6 +40,7 @@ from torch.utils._pytree import tree_flatten, tree_unflatten
 from .. import ops
 from ..utils.checkpoint import checkpoint_pass, new_pass_token
 
+_RS_PREWAIT = os.environ.get("ATB_RS_PREWAIT", "0") == "1"   # see _reduce_grads_fused
 ALIGN = 8  # elements: 16 bytes in bf16, so every parameter can be a TMA operand
 
 
@@ -699,6 +700,13 @@ class FSDPEngine:
             if opt is not None and opt.in_backward_ready(u):
                 opt.fused_unit_step(buf, u, u.shard_offset)
             else:
+                if _RS_PREWAIT:
+                    # One warp waits until every rank's gradients of this unit are complete; only then does the
+                    # multi-CTA kernel start. Its own arrival wait would otherwise keep its CTAs resident (and the
+                    # persistent GEMM CTAs that share their SMs slow) for as long as the slowest rank is behind.
+                    from . import symm
+
+                    buf.wait(symm.CH_READY, buf.signal(symm.CH_READY))
                 buf.reduce_scatter_into(dst, scale=scale, accumulate=not u.fresh, numel=u.padded_numel,
                                         max_blocks=self.cfg.comm_blocks)
             if u._gbuf_idx >= 0:
