@@ -77,7 +77,7 @@ ATB_DEVICE void signal_all(const Peers& pr, int ch) {
 }
 
 // Every rank has signalled `seq` on channel `ch`? Polled by the first `world` threads of the block;
-// the verdict is shared by the whole block. Returns false when the wait ran out.
+// the outcome is shared by the whole block. Returns false when the wait ran out.
 ATB_DEVICE bool wait_all(const Peers& pr, int ch, int* status) {
   int bad = 0;
   if ((int)threadIdx.x < pr.world) {
