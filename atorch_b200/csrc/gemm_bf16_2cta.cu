@@ -25,6 +25,9 @@
 //   GEMM -> reduce-scatter  the epilogue adds every output row into the fp32 accumulation buffer of the
 //                        rank that owns the row (`red.add.f32` on peer pointers): no partial-sum tensor, no
 //                        separate collective, the reduction traffic overlaps the remaining tiles
+#include <cstdlib>
+#include <mutex>
+
 #include "common.cuh"
 
 namespace {
@@ -43,7 +46,8 @@ struct Cfg {
   static constexpr int STAGES = BN == 256 ? 6 : 8;
   static constexpr int B_BYTES = BNH * BK * 2;
   static constexpr int BAR_OFF = STAGES * (A_BYTES + B_BYTES);
-  static constexpr int SMEM_TOTAL = BAR_OFF + (2 * STAGES + 4) * 8 + 16 + 1024;
+  static constexpr int TQ = 4;                     // tile-id ring of the dynamic scheduler
+  static constexpr int SMEM_TOTAL = BAR_OFF + (2 * STAGES + 4 + 2 * TQ) * 8 + 16 + TQ * 4 + 1024;
 };
 
 struct Epi {
@@ -143,6 +147,45 @@ ATB_DEVICE void tma_load_2d_pair(void* smem_dst, const CUtensorMap* tm, uint32_t
       "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar_cluster_addr), "r"(x), "r"(y)
       : "memory");
 }
+// Dynamic tile scheduling: tiles are handed out by an atomic counter instead of a fixed stride, so that a CTA pair
+// that shares its SMs with another kernel (a reduce-scatter or copy kernel of the communication streams takes part
+// of the SM's path to L2, on which this kernel's operand loads depend) simply takes fewer tiles, instead of making
+// the whole launch wait for it. counters[0] = next tile, counters[1] = pairs that have finished; both are zero
+// between launches (the pair that finishes last clears them).
+struct Sched {
+  int* counters;   // nullptr: static schedule (tile = pair + i * pairs)
+};
+
+ATB_DEVICE void st_remote_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+// Wait on a barrier whose phase is completed by an arrive of another CTA of the cluster that published data with it.
+ATB_DEVICE bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
+  uint64_t t0 = 0;
+  uint32_t spins = 0;
+  while (true) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((++spins & 0x3ff) == 0) {
+      if (t0 == 0) t0 = globaltimer_ns();
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > ATB_WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        if (status) atomicCAS(status, 0, (int)ATB_ERR_WAIT_TIMEOUT);
+        return false;
+      }
+    }
+  }
+}
 ATB_DEVICE void mbar_arrive_remote(uint32_t bar_cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
@@ -150,7 +193,7 @@ ATB_DEVICE void mbar_arrive_remote(uint32_t bar_cluster_addr) {
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(192, 1)
 gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Epi ep, int M,
-                      int N, int K, Groups grp, Gate gate, int* status) {
+                      int N, int K, Groups grp, Gate gate, Sched sched, int* status) {
   constexpr int BNH = Cfg<BN>::BNH, STAGES = Cfg<BN>::STAGES, B_BYTES = Cfg<BN>::B_BYTES,
                 BAR_OFF = Cfg<BN>::BAR_OFF;
   extern __shared__ uint8_t smem_raw[];
@@ -161,8 +204,12 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   uint64_t* empty = full + STAGES;
   uint64_t* tfull = empty + STAGES;
   uint64_t* tempty = tfull + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  constexpr int TQ = Cfg<BN>::TQ;
+  uint64_t* tq_full = tempty + 2;
+  uint64_t* tq_empty = tq_full + TQ;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tq_empty + TQ);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* tq_tile = reinterpret_cast<volatile int*>(tmem_slot + 4);   // [TQ] tile ids (-1: no more tiles)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -187,6 +234,10 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     mbar_init(&tfull[1], 1);
     mbar_init(&tempty[0], 8);
     mbar_init(&tempty[1], 8);
+    for (int i = 0; i < TQ; ++i) {
+      mbar_init(&tq_full[i], 1);
+      mbar_init(&tq_empty[i], 10);   // leader: MMA thread + 4 epilogue warps; partner: producer + 4 epilogue warps
+    }
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -244,10 +295,55 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     n0 = tn * tile_cols;
   };
 
+  // The idx-th tile of this pair, the same number in every role of both CTAs. Static: a fixed stride. Dynamic: the
+  // leader's producer thread draws it from the global counter and publishes it through a ring of tile ids in the
+  // shared memory of both CTAs; every other role reads it there and frees the slot.
+  const bool dyn = sched.counters != nullptr;
+  auto static_tile = [&](int idx) -> int {
+    const int t = cluster_id + idx * num_clusters;
+    return t < num_tiles ? t : -1;
+  };
+  auto publish_tile = [&](int idx, int t) -> bool {          // leader's producer thread
+    const int slot = idx % TQ;
+    if (!mbar_wait(&tq_empty[slot], ((idx / TQ) & 1) ^ 1, abort_flag, status)) return false;
+    tq_tile[slot] = t;
+    st_remote_u32(map_to_cta(const_cast<int*>(&tq_tile[slot]), 1), (uint32_t)t);
+    mbar_arrive(&tq_full[slot]);
+    mbar_arrive_remote(map_to_cta(&tq_full[slot], 1));       // release.cluster: orders the store above
+    return true;
+  };
+  auto read_tile = [&](int idx) -> int {                      // any other role (one thread, or all lanes of a warp)
+    if (!dyn) return static_tile(idx);
+    const int slot = idx % TQ;
+    if (!mbar_wait_cluster(&tq_full[slot], (idx / TQ) & 1, abort_flag, status)) return -1;
+    return tq_tile[slot];
+  };
+  auto free_tile_slot = [&](int idx) {                        // one thread per consumer, after read_tile
+    if (dyn) mbar_arrive_remote(map_to_cta(&tq_empty[idx % TQ], 0));
+  };
+
   if (warp == 0) {
     if (lane == 0) {
       uint32_t it = 0;
-      for (int tile = cluster_id; tile < num_tiles; tile += num_clusters) {
+      int drawn = (dyn && leader) ? atomicAdd(&sched.counters[0], 1) : 0;
+      for (int idx = 0;; ++idx) {
+        int tile;
+        if (dyn && leader) {
+          tile = drawn < num_tiles ? drawn : -1;
+          if (tile >= 0) drawn = atomicAdd(&sched.counters[0], 1);     // the next one, fetched under this tile's loads
+          if (!publish_tile(idx, tile)) goto producer_done;
+          if (tile < 0) {      // every pair draws exactly one number past the end; the last pair to do so resets
+            if (atomicAdd(&sched.counters[1], 1) == num_clusters - 1) {
+              sched.counters[0] = 0;
+              sched.counters[1] = 0;
+              __threadfence();
+            }
+          }
+        } else {
+          tile = read_tile(idx);
+          free_tile_slot(idx);
+        }
+        if (tile < 0) break;
         int m0, n0;
         tile_coords(tile, m0, n0);
         if (!tile_active(m0)) continue;
@@ -293,7 +389,10 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       constexpr uint32_t idesc = umma_idesc(2 * BM, BN, 1, 1, A_MN, B_MN);
       uint32_t it = 0;
       int local = 0;
-      for (int tile = cluster_id; tile < num_tiles; tile += num_clusters) {
+      for (int idx = 0;; ++idx) {
+        const int tile = read_tile(idx);
+        free_tile_slot(idx);
+        if (tile < 0) break;
         {
           int m0, n0;
           tile_coords(tile, m0, n0);
@@ -336,7 +435,11 @@ gemm_bf16_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const int q = warp & 3;
     int local = 0;
     const uint32_t tempty_leader[2] = {map_to_cta(&tempty[0], 0), map_to_cta(&tempty[1], 0)};
-    for (int tile = cluster_id; tile < num_tiles; tile += num_clusters) {
+    for (int idx = 0;; ++idx) {
+      const int tile = __shfl_sync(0xffffffffu, read_tile(idx), 0);
+      __syncwarp();
+      if (lane == 0) free_tile_slot(idx);
+      if (tile < 0) break;
       int m0, n0;
       tile_coords(tile, m0, n0);
       if (!tile_active(m0)) {
@@ -505,6 +608,45 @@ int sm_count() {
   return g_sms;
 }
 
+// Counters of the dynamic tile scheduler: one pair per (device, stream), because launches on different streams can
+// overlap. Allocated and zeroed on first use (never during a stream capture: such launches use the static schedule).
+struct SchedWs {
+  int dev;
+  cudaStream_t stream;
+  int* counters;
+};
+constexpr int SCHED_MAX_STREAMS = 16;
+SchedWs g_sched_ws[SCHED_MAX_STREAMS];
+int g_sched_n = 0;
+int g_dynamic = -1;      // -1: read ATB_GEMM_DYNAMIC on first use (default on)
+std::mutex g_sched_mu;
+
+int* sched_counters(cudaStream_t stream) {
+  std::lock_guard<std::mutex> lock(g_sched_mu);
+  int dev = 0;
+  cudaGetDevice(&dev);
+  for (int i = 0; i < g_sched_n; ++i)
+    if (g_sched_ws[i].dev == dev && g_sched_ws[i].stream == stream) return g_sched_ws[i].counters;
+  if (g_sched_n >= SCHED_MAX_STREAMS) return nullptr;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  void* p = nullptr;
+  if (cudaMalloc(&p, 256) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  if (cudaMemsetAsync(p, 0, 256, stream) != cudaSuccess) {
+    cudaGetLastError();
+    cudaFree(p);
+    return nullptr;
+  }
+  g_sched_ws[g_sched_n++] = SchedWs{dev, stream, reinterpret_cast<int*>(p)};
+  return reinterpret_cast<int*>(p);
+}
+
 template <int BN, bool A_MN, bool B_MN>
 int launch(const void* A, const void* B, const Epi& ep, int M, int N, int K, long long lda, long long ldb,
            int max_ctas, const Groups& grp, int b_extent_rows, const Gate& gate, cudaStream_t stream, int* status) {
@@ -535,6 +677,14 @@ int launch(const void* A, const void* B, const Epi& ep, int M, int N, int K, lon
   int clusters = sm_count() / 2;
   if (tiles < clusters) clusters = tiles;
   if (max_ctas > 0 && clusters > max_ctas / 2) clusters = max_ctas / 2 > 0 ? max_ctas / 2 : 1;
+  // dynamic tile scheduling for plain launches with more tiles than CTA pairs (see Sched)
+  Sched sched{nullptr};
+  if (g_dynamic < 0) {
+    const char* e = getenv("ATB_GEMM_DYNAMIC");
+    g_dynamic = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  if (g_dynamic > 0 && tiles > clusters && grp.counts == nullptr && grp.b_rows == 0 && gate.flags == nullptr)
+    sched.counters = sched_counters(stream);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * clusters, 1, 1);
   cfg.blockDim = dim3(192, 1, 1);
@@ -547,7 +697,7 @@ int launch(const void* A, const void* B, const Epi& ep, int M, int N, int K, lon
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, ep, M, N, K, grp, gate, status);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tmA, tmB, ep, M, N, K, grp, gate, sched, status);
   return e == cudaSuccess ? 0 : -5;
 }
 
@@ -663,6 +813,9 @@ extern "C" int atb_gemm_bf16_2cta_wgather(const void* A, const void* B, void* C,
   g_fused_args.active = false;
   return rc;
 }
+
+// 1 / 0: hand tiles out dynamically or by a fixed stride (default: dynamic unless ATB_GEMM_DYNAMIC=0).
+extern "C" void atb_gemm_set_dynamic(int on) { g_dynamic = on ? 1 : 0; }
 
 // Upper bound of the arrival-flag waits of the all-gather -> GEMM form, in nanoseconds (default 2 s).
 extern "C" int atb_set_gate_wait_ns(unsigned long long ns) {
