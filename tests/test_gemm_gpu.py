@@ -188,3 +188,33 @@ def test_linear_swiglu_epilogue_matches_separate_kernels(T, H, F):
     g = x.float() @ w.float().t()
     full = torch.nn.functional.silu(g[:, :F]) * g[:, F:]
     _check(out, full, H)
+
+
+def test_dynamic_tile_schedule_matches_static():
+    """Tiles handed out by the atomic counter give bit-identical results to the fixed-stride schedule, launch after
+    launch (the counters are left at zero), on two streams at once, and while another kernel shares the SMs."""
+    L = _lib.lib()
+    torch.manual_seed(11)
+    side = torch.cuda.Stream()
+    try:
+        for M, N, K, a_mn, b_mn in [(4096, 4096, 1024, False, False), (4096, 11008, 512, False, True),
+                                    (2048 + 72, 4096 + 8, 1024 + 40, True, True), (8192, 8192, 256, False, False)]:
+            a = _mk(K, M) if a_mn else _mk(M, K)
+            b = _mk(K, N) if b_mn else _mk(N, K)
+            L.atb_gemm_set_dynamic(0)
+            ref = gemm(a, b, a_mn=a_mn, b_mn=b_mn, kernel="2cta")
+            L.atb_gemm_set_dynamic(1)
+            outs = [gemm(a, b, a_mn=a_mn, b_mn=b_mn, kernel="2cta") for _ in range(3)]
+            filler = torch.empty(64 << 20, device="cuda")
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):                       # a second stream has counters of its own
+                for _ in range(4):
+                    filler.normal_()
+                other = gemm(a, b, a_mn=a_mn, b_mn=b_mn, kernel="2cta")
+            busy = gemm(a, b, a_mn=a_mn, b_mn=b_mn, kernel="2cta")
+            torch.cuda.synchronize()
+            _lib.check_status(ref.device)
+            for o in outs + [other, busy]:
+                assert torch.equal(o, ref)
+    finally:
+        L.atb_gemm_set_dynamic(1)
