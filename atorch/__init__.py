@@ -30,6 +30,12 @@ _RENAMES = {
     "atorch.trainer.atorch_trainer_v2": "atorch_b200.trainer.atorch_trainer_v2",
     "atorch.trainer.fsdp.fsdp_shard_async_saver": "atorch_b200.trainer.fsdp.fsdp_ckpt_saver",
     "atorch.trainer.fsdp.fsdp_shard_dcp_loader": "atorch_b200.trainer.fsdp.fsdp_ckpt_saver",
+    "atorch.trainer.base": "atorch_b200.trainer",
+    "atorch.trainer.base.dist_checkpointing": "atorch_b200.trainer",
+    "atorch.trainer.base.dist_checkpointing.strategies": "atorch_b200.trainer",
+    "atorch.trainer.base.dist_checkpointing.strategies.async_utils": "atorch_b200.trainer.async_calls",
+    "atorch.trainer.megatron": "atorch_b200.trainer",
+    "atorch.trainer.megatron.megatron_async_save": "atorch_b200.trainer.async_calls",
     "atorch.utils.numberic_checker": "atorch_b200.utils.numeric_checker",
     "atorch.utils.dynamic_profiler": "atorch_b200.utils.dynamic_profiler",
     "atorch.utils.inspector": "atorch_b200.utils.inspector",
