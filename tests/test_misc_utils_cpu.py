@@ -1,0 +1,150 @@
+"""Small utilities: topology-aware node ranks, memory estimation, sparse all-reduce, module-level numeric checker,
+per-stage pipeline checkpoints, dynamic gradient scalers."""
+import os
+from types import SimpleNamespace
+
+import torch
+import torch.nn as nn
+
+from tests.dist_utils import run_distributed
+
+
+def test_rank_reorder_groups_nodes_of_one_switch():
+    from atorch_b200.utils.rank_reorder import new_node_rank, reorder_nodes_by_topology
+
+    labels = [{"rack": "r2", "switch": "s1"}, {"rack": "r1", "switch": "s9"}, {"rack": "r2", "switch": "s0"},
+              {"rack": "r1", "switch": "s9"}, {}]
+    order = reorder_nodes_by_topology(labels)
+    assert order == [4, 1, 3, 2, 0]                    # unlabeled first, then rack r1 (stable), then r2 by switch
+    assert [new_node_rank(i, labels) for i in range(5)] == [4, 1, 3, 2, 0]
+    assert sorted(order) == list(range(5))
+
+
+def test_estimate_training_memory_scales_with_the_layout():
+    from atorch_b200.utils.virtual_optimizer import estimate_training_memory
+
+    m = nn.Linear(1000, 1000, bias=False)               # 1e6 parameters
+    one = estimate_training_memory(m)
+    assert one == {"params": 2e6, "grads": 4e6, "optimizer_state": 12e6, "total": 18e6}
+    eight = estimate_training_memory(m, data=8)
+    assert eight["total"] == one["total"] / 8
+    zero1 = estimate_training_memory(m, data=8, shard_params=False)
+    assert zero1["params"] == 2e6 and zero1["optimizer_state"] == 12e6 / 8
+    tp_pp = estimate_training_memory(m, tensor=2, pipe=2)
+    assert tp_pp["total"] == one["total"] / 4
+
+
+def _sparse(rank, world):
+    from atorch_b200.utils.sparse import all_reduce_sparse
+
+    idx = torch.tensor([[0, 2], [1, 1]]) if rank == 0 else torch.tensor([[2, 3, 3], [1, 0, 0]])
+    val = torch.tensor([1.0, 2.0]) if rank == 0 else torch.tensor([10.0, 5.0, 6.0])
+    out = all_reduce_sparse(torch.sparse_coo_tensor(idx, val, (4, 2)))
+    dense = torch.zeros(4, 2)
+    dense[0, 1], dense[2, 1], dense[3, 0] = 1.0, 12.0, 11.0
+    assert torch.equal(out.to_dense(), dense)
+
+
+def test_all_reduce_sparse_sums_ragged_index_sets():
+    run_distributed(_sparse, world=2)
+
+
+def test_module_numeric_checker_reports_the_module_that_differs(tmp_path):
+    from atorch_b200.utils.numeric_checker import module_numeric_checker
+
+    torch.manual_seed(0)
+    m = nn.Sequential(nn.Linear(8, 8), nn.ReLU(), nn.Linear(8, 4))
+    x = torch.randn(3, 8)
+    with module_numeric_checker(m, str(tmp_path), "save"):
+        m(x)
+    with module_numeric_checker(m, str(tmp_path), "compare") as same:
+        m(x)
+    assert same.mismatches == []
+    with torch.no_grad():
+        m[2].weight.add_(0.5)
+    with module_numeric_checker(m, str(tmp_path), "compare") as diff:
+        m(x)
+    names = {d["module"] if "module" in d else d.get("name") for d in diff.mismatches}
+    assert names and all(n in ("2", "root") for n in names), diff.mismatches
+
+
+def _param_with_grad(values):
+    p = nn.Parameter(torch.zeros(len(values)))
+    p.grad = torch.tensor(values, dtype=torch.float32)
+    return p
+
+
+def test_dynamic_grad_scaler_backs_off_on_overflow_and_grows_after_good_steps():
+    from atorch_b200.utils.grad_scaler import BF16GradScaler, DynamicGradScaler
+
+    p = _param_with_grad([8.0, -4.0])
+    opt = torch.optim.SGD([p], lr=1.0)
+    s = DynamicGradScaler(init_scale=4.0, growth_interval=2)
+    assert s.scale(torch.tensor(2.0)).item() == 8.0
+    s.step(opt)                                     # gradients are divided by the scale before the update
+    assert torch.equal(p.detach(), torch.tensor([-2.0, 1.0])) and not s.has_overflow()
+    s.update()
+    assert s.get_scale() == 4.0
+    p.grad = torch.tensor([1.0, 1.0])
+    s.step(opt)
+    s.update()
+    assert s.get_scale() == 8.0                     # two good steps: the scale grows
+    before = p.detach().clone()
+    p.grad = torch.tensor([float("inf"), 1.0])
+    assert s.step(opt) is None and s.has_overflow() and torch.equal(p.detach(), before)   # step skipped
+    s.update()
+    assert s.get_scale() == 4.0                     # halved
+    sd = s.state_dict()
+    t = DynamicGradScaler()
+    t.load_state_dict(sd)
+    assert t.get_scale() == 4.0
+    # bf16: scale pinned to one, only the non-finite check remains
+    b = BF16GradScaler()
+    assert b.get_scale() == 1.0 and b.scale(torch.tensor(3.0)).item() == 3.0
+    p.grad = torch.tensor([float("nan"), 0.0])
+    assert b.step(opt) is None and b.has_overflow()
+    b.update()
+    assert b.get_scale() == 1.0
+
+
+def test_pipe_grad_scaler_waits_for_every_local_stage():
+    from atorch_b200.amp.pipe_amp import PipeGradScaler
+
+    p1, p2 = _param_with_grad([2.0]), _param_with_grad([float("inf")])
+    o1, o2 = torch.optim.SGD([p1], lr=1.0), torch.optim.SGD([p2], lr=1.0)
+    s = PipeGradScaler(init_scale=2.0, num_local_stages=2)
+    try:
+        s.step(o1)
+        raise AssertionError("stepped before the second local stage was unscaled")
+    except RuntimeError:
+        pass
+    s.unscale_(o2)
+    assert s.step(o1) is None and s.step(o2) is None and s.has_overflow()     # one stage overflowed: both skip
+    s.update()
+    assert s.get_scale() == 1.0
+    p1.grad, p2.grad = torch.tensor([2.0]), torch.tensor([4.0])
+    s.unscale_(o1)
+    s.unscale_(o2)
+    s.step(o1)
+    s.step(o2)
+    assert p1.item() == -2.0 and p2.item() == -4.0
+
+
+def test_pipe_checkpoint_round_trip(tmp_path):
+    from atorch_b200.utils.pipe_file_utils import atorch_load_pipe_checkpoint, atorch_save_pipe_checkpoint
+
+    torch.manual_seed(0)
+    stages = [nn.Linear(4, 4), nn.Linear(4, 2)]
+    pm = SimpleNamespace(stage_modules=stages, stage_ids=[1, 3], pp_rank=1)
+    opt = torch.optim.AdamW([q for m in stages for q in m.parameters()], lr=1e-2)
+    sum(m(torch.randn(2, 4)).sum() for m in stages[:1]).backward()
+    opt.step()
+    atorch_save_pipe_checkpoint(pm, str(tmp_path), opt)
+    assert sorted(os.listdir(tmp_path)) == ["pipe_optim_001.pt", "pipe_stage_001.pt", "pipe_stage_003.pt"]
+    fresh = [nn.Linear(4, 4), nn.Linear(4, 2)]
+    pm2 = SimpleNamespace(stage_modules=fresh, stage_ids=[1, 3], pp_rank=1)
+    opt2 = torch.optim.AdamW([q for m in fresh for q in m.parameters()], lr=1e-2)
+    atorch_load_pipe_checkpoint(pm2, str(tmp_path), opt2)
+    for a, b in zip(stages, fresh):
+        assert torch.equal(a.weight, b.weight) and torch.equal(a.bias, b.bias)
+    assert opt2.state_dict()["state"][0]["step"] == opt.state_dict()["state"][0]["step"]
