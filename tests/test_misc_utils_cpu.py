@@ -148,3 +148,57 @@ def test_pipe_checkpoint_round_trip(tmp_path):
     for a, b in zip(stages, fresh):
         assert torch.equal(a.weight, b.weight) and torch.equal(a.bias, b.bias)
     assert opt2.state_dict()["state"][0]["step"] == opt.state_dict()["state"][0]["step"]
+
+
+def test_ppo_utils_hand_computed_cases():
+    from atorch_b200.rl import ppo_utils as P
+
+    logits = torch.log(torch.tensor([[[0.25, 0.75], [0.5, 0.5]]]))
+    lp = P.logprobs_of_labels(logits, torch.tensor([[1, 0]]))
+    assert torch.allclose(lp, torch.log(torch.tensor([[0.75, 0.5]])), atol=1e-6)
+    x = torch.tensor([[1.0, 2.0, 3.0, 100.0]])
+    m = torch.tensor([[1.0, 1.0, 1.0, 0.0]])
+    w = P.whiten(x, m)
+    assert abs((w * m).sum().item()) < 1e-5 and abs(((w ** 2) * m).sum().item() / 3 - 1.0) < 1e-4
+    # rewards: KL penalty on every response token, the sequence score on the last one
+    r, kl = P.compute_rewards(torch.tensor([2.0]), torch.tensor([[0.0, -1.0, -1.0]]), torch.tensor([[0.0, -2.0, -1.0]]),
+                              torch.tensor([[1.0, 1.0, 0.0]]), kl_coef=0.1)
+    assert torch.allclose(r, torch.tensor([[0.0, -0.1 + 2.0, 0.0]])) and abs(kl.item() - 1.0) < 1e-6
+    # GAE with gamma = lam = 1 and zero values is the reward-to-go
+    adv, ret = P.gae(torch.zeros(1, 3), torch.tensor([[1.0, 2.0, 3.0]]), torch.ones(1, 3), gamma=1.0, lam=1.0,
+                     use_whitening=False)
+    assert torch.equal(adv, torch.tensor([[6.0, 5.0, 3.0]])) and torch.equal(ret, adv)
+    # PPO loss: unchanged policy -> ratio 1, no clipping; value loss is half the squared error
+    lp0 = torch.tensor([[-1.0, -2.0]])
+    loss, stats = P.ppo_loss(lp0, torch.tensor([[1.0, 1.0]]), lp0, torch.tensor([[1.0, 1.0]]), torch.tensor([[1.0, -1.0]]),
+                             torch.tensor([[2.0, 1.0]]), torch.ones(1, 2), vf_coef=0.5)
+    assert abs(stats["policy_loss"].item()) < 1e-6 and abs(stats["value_loss"].item() - 0.25) < 1e-6
+    assert stats["clipfrac"].item() == 0.0 and abs(loss.item() - 0.125) < 1e-6
+    # a ratio far above 1 + clip with a positive advantage is clipped
+    _, st = P.ppo_loss(torch.tensor([[0.0]]), torch.zeros(1, 1), torch.tensor([[-1.0]]), torch.zeros(1, 1),
+                       torch.ones(1, 1), torch.zeros(1, 1), torch.ones(1, 1), cliprange=0.2)
+    assert abs(st["policy_loss"].item() + 1.2) < 1e-6 and st["clipfrac"].item() == 1.0
+
+
+def test_ib_monitor_reads_counters_of_a_fake_sysfs(tmp_path):
+    import json
+    import time
+
+    from atorch_b200.utils.ib_monitor import IBMonitor, read_counters
+
+    d = tmp_path / "mlx5_0" / "ports" / "1" / "counters"
+    d.mkdir(parents=True)
+    (d / "port_xmit_data").write_text("1000\n")
+    (d / "port_rcv_data").write_text("10\n")
+    c = read_counters(str(tmp_path))
+    assert c == {"mlx5_0/ports/1/counters/port_xmit_data": 4000, "mlx5_0/ports/1/counters/port_rcv_data": 40}
+    out = tmp_path / "ib.json"
+    mon = IBMonitor(interval=0.05, count=2, path=str(out), root=str(tmp_path))
+    mon.start()
+    time.sleep(0.02)
+    (d / "port_xmit_data").write_text("2000\n")
+    time.sleep(0.3)
+    mon.stop()
+    ev = json.loads(out.read_text())["traceEvents"]
+    rates = [e["args"]["bytes_per_s"] for e in ev if e["name"].endswith("port_xmit_data")]
+    assert len(rates) == 2 and max(rates) == 4000 / 0.05 and all(e["ph"] == "C" for e in ev)
