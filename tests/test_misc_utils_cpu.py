@@ -202,3 +202,47 @@ def test_ib_monitor_reads_counters_of_a_fake_sysfs(tmp_path):
     ev = json.loads(out.read_text())["traceEvents"]
     rates = [e["args"]["bytes_per_s"] for e in ev if e["name"].endswith("port_xmit_data")]
     assert len(rates) == 2 and max(rates) == 4000 / 0.05 and all(e["ph"] == "C" for e in ev)
+
+
+def test_safetensors_files_interchange_with_the_safetensors_package(tmp_path):
+    """Files written here are read by the `safetensors` package and the other way round; slices are read by seeking."""
+    import pytest
+
+    st = pytest.importorskip("safetensors.torch")
+    from atorch_b200.utils.safetensors_io import SafeFile, load_file, save_file
+
+    torch.manual_seed(0)
+    tensors = {"w": torch.randn(5, 7), "b": torch.randn(7).bfloat16(), "idx": torch.arange(12).view(3, 4),
+               "flag": torch.tensor([True, False]), "empty": torch.zeros(0, 3)}
+    p = str(tmp_path / "a.safetensors")
+    save_file(tensors, p, metadata={"step": 3})
+    theirs = st.load_file(p)
+    assert set(theirs) == set(tensors) and all(torch.equal(theirs[k], v) for k, v in tensors.items())
+    q = str(tmp_path / "b.safetensors")
+    st.save_file({k: v for k, v in tensors.items()}, q, metadata={"who": "them"})
+    ours = load_file(q)
+    assert all(torch.equal(ours[k], v) and ours[k].dtype == v.dtype for k, v in tensors.items())
+    f = SafeFile(p)
+    assert f.metadata == {"step": "3"} and f.info("w") == (torch.float32, (5, 7))
+    assert torch.equal(f.get_slice("w", 8, 20), tensors["w"].reshape(-1)[8:20])
+    assert f.get_slice("w", 4, 4).numel() == 0
+
+
+def test_tensor_inspector_records_activation_and_gradient_statistics():
+    from atorch_b200.utils.inspector import TensorInspector, fp8_cosine_similarity, tensor_stats
+
+    s = tensor_stats(torch.tensor([0.0, 2.0, -4.0, float("inf")]))
+    assert s["absmax"] == 4.0 and s["zero_frac"] == 0.25 and s["nonfinite_frac"] == 0.25
+    assert fp8_cosine_similarity(torch.randn(4, 256)) > 0.99
+    m = nn.Sequential(nn.Linear(256, 256), nn.ReLU(), nn.Linear(256, 8))
+    ins = TensorInspector(m, module_filter=lambda n, mod: isinstance(mod, nn.Linear), with_fp8=True, interval=2).register()
+    for _ in range(3):
+        m(torch.randn(4, 256)).sum().backward()
+        ins.next_step()
+    ins.remove()
+    kinds = {(r["module"], r["kind"], r["step"]) for r in ins.records}
+    assert kinds == {(n, k, st_) for n in ("0", "2") for k in ("activation", "grad_output") for st_ in (0, 2)}
+    assert all("fp8_cos" in r for r in ins.records if r["module"] == "0")
+    n = len(ins.records)
+    m(torch.randn(4, 256))
+    assert len(ins.records) == n                    # hooks removed
