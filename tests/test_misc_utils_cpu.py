@@ -246,3 +246,66 @@ def test_tensor_inspector_records_activation_and_gradient_statistics():
     n = len(ins.records)
     m(torch.randn(4, 256))
     assert len(ins.records) == n                    # hooks removed
+
+
+def test_dynamic_profiler_follows_its_config_file(tmp_path):
+    """A JSON file dropped next to a running job schedules a profiling session some steps ahead; the trace is written
+    when the session's steps are over; ranks not named in the file ignore it."""
+    import json
+
+    from atorch_b200.utils.dynamic_profiler import DynamicProfiler
+
+    cfg = tmp_path / "profile.json"
+    prof = DynamicProfiler(str(cfg), rank=0, start_monitor=False)
+    other = DynamicProfiler(str(cfg), rank=3, start_monitor=False)
+    for _ in range(2):
+        prof.step()
+    assert prof.state == prof.IDLE and not prof.monitor.poll_once()
+    cfg.write_text(json.dumps({"start_step": 4, "steps": 2, "ranks": [0], "output_dir": str(tmp_path / "out")}))
+    assert prof.monitor.poll_once() and prof.state == prof.SCHEDULED
+    other.monitor.poll_once()
+    assert other.state == other.IDLE
+    x = torch.randn(16, 16)
+    states = []
+    for _ in range(5):
+        (x @ x).sum()
+        prof.step()
+        states.append(prof.state)
+    assert states == ["scheduled", "running", "running", "done", "done"]
+    trace = prof.session["trace"]
+    assert os.path.exists(trace) and "traceEvents" in json.load(open(trace))
+    st = json.load(open(tmp_path / ".dynamic_profile_state.0.json"))
+    assert st["state"] == "done" and st["step"] == 6
+    prof.close()
+    other.close()
+
+
+def _moe_comm(rank, world):
+    import torch.distributed as dist
+
+    from atorch_b200.communication.functions import (all_to_all, gather_from_expert_parallel_region_to_moe,
+                                                     reduce_scatter_to_expert_parallel_region_from_moe)
+
+    g = dist.group.WORLD
+    # uneven all-to-all: rank r sends r + 1 rows to rank 0 and 1 row to rank 1
+    x = (torch.arange((rank + 1) + 1, dtype=torch.float32) + 10 * rank).unsqueeze(1).requires_grad_()
+    ins = [rank + 1, 1]
+    outs = [1, 2] if rank == 0 else [1, 1]
+    y = all_to_all(g, x, outs, ins)
+    expect = torch.tensor([[0.0], [10.0], [11.0]]) if rank == 0 else torch.tensor([[1.0], [12.0]])
+    assert torch.equal(y.detach(), expect)
+    (y * (rank + 1)).sum().backward()                    # the backward is the inverse exchange
+    assert torch.equal(x.grad, torch.tensor([[1.0], [2.0]]) if rank == 0 else torch.tensor([[1.0], [1.0], [2.0]]))
+    # gather / reduce-scatter pair of the expert-parallel region
+    t = torch.full((2, 3), float(rank + 1), requires_grad=True)
+    gathered = gather_from_expert_parallel_region_to_moe(t, g)
+    assert gathered.shape == (4, 3) and torch.equal(gathered[:2].detach(), torch.ones(2, 3))
+    gathered.sum().backward()
+    assert torch.equal(t.grad, torch.full((2, 3), 2.0))  # every rank's copy of the gathered rows contributes
+    u = torch.arange(12, dtype=torch.float32).view(4, 3) * (rank + 1)
+    rs = reduce_scatter_to_expert_parallel_region_from_moe(u, g)
+    assert torch.equal(rs, (torch.arange(12, dtype=torch.float32).view(4, 3) * 3)[rank * 2:(rank + 1) * 2])
+
+
+def test_moe_communication_functions_gloo():
+    run_distributed(_moe_comm, world=2)
