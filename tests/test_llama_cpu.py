@@ -93,3 +93,40 @@ def test_linear_swiglu_falls_back_to_the_two_ops_on_cpu():
     out = ops.linear_swiglu(x, w)
     g = x @ w.t()
     assert torch.allclose(out, torch.nn.functional.silu(g[:, :10]) * g[:, 10:], atol=1e-6)
+
+
+def test_mixtral_logits_match_hugging_face():
+    """The sparse-MoE decoder (top-2 router, grouped expert MLPs, grouped-query attention) against the Hugging Face
+    Mixtral with the same weights; capacity large enough that no token is dropped."""
+    from transformers import MixtralConfig as HFConfig, MixtralForCausalLM
+
+    from atorch_b200.models.mixtral import MixtralConfig, MixtralModel
+
+    torch.manual_seed(0)
+    cfg = MixtralConfig.tiny_moe(capacity_factor=8.0, router_aux_loss_coef=0.0, expert_intermediate_size=192)
+    ours = MixtralModel(cfg).eval()
+    hc = HFConfig(vocab_size=256, hidden_size=128, intermediate_size=192, num_hidden_layers=2, num_attention_heads=2,
+                  num_key_value_heads=1, max_position_embeddings=64, num_local_experts=4, num_experts_per_tok=2,
+                  sliding_window=None, rms_norm_eps=cfg.rms_norm_eps, rope_theta=cfg.rope_theta, attention_dropout=0.0)
+    hc._attn_implementation = "eager"
+    hf = MixtralForCausalLM(hc).eval()
+    sd = {"model.embed_tokens.weight": ours.embed_tokens.weight, "model.norm.weight": ours.norm.weight,
+          "lm_head.weight": ours.lm_head.weight}
+    d = cfg.head_dim
+    for i, l in enumerate(ours.layers):
+        p = f"model.layers.{i}."
+        q, k, v = l.qkv_proj.weight.split([2 * d, d, d], 0)
+        moe = l.block_sparse_moe
+        sd.update({p + "self_attn.q_proj.weight": q, p + "self_attn.k_proj.weight": k, p + "self_attn.v_proj.weight": v,
+                   p + "self_attn.o_proj.weight": l.o_proj.weight, p + "mlp.gate.weight": moe.router.classifier.weight,
+                   p + "mlp.experts.gate_up_proj": moe.experts.w1,                         # [E, 2F, H], gate | up
+                   p + "mlp.experts.down_proj": moe.experts.w2.transpose(1, 2),            # ours [E, F, H]
+                   p + "input_layernorm.weight": l.input_layernorm.weight,
+                   p + "post_attention_layernorm.weight": l.post_attention_layernorm.weight})
+    missing, unexpected = hf.load_state_dict({k: v.detach().clone().contiguous() for k, v in sd.items()}, strict=False)
+    assert not missing and not unexpected, (missing, unexpected)
+    ids = torch.randint(0, 256, (2, 24))
+    out = ours(ids)
+    logits = out[1] if isinstance(out, tuple) else out
+    ref = hf(input_ids=ids).logits
+    assert torch.allclose(logits, ref, atol=2e-4, rtol=1e-3), (logits - ref).abs().max()
