@@ -130,3 +130,25 @@ def test_mixtral_logits_match_hugging_face():
     logits = out[1] if isinstance(out, tuple) else out
     ref = hf(input_ids=ids).logits
     assert torch.allclose(logits, ref, atol=2e-4, rtol=1e-3), (logits - ref).abs().max()
+
+
+@pytest.mark.parametrize("n_kv", [4, 2])
+def test_hugging_face_state_dict_conversion_round_trip(n_kv):
+    """``to_hf_state_dict`` produces a state dict the Hugging Face model loads (and then computes the same logits);
+    ``from_hf_state_dict`` brings it back bit-exactly."""
+    from atorch_b200.models.llama import from_hf_state_dict, to_hf_state_dict
+
+    cfg, ours, hf = _pair(n_kv)
+    with torch.no_grad():
+        for p in hf.parameters():
+            p.normal_()                                   # forget the weights _pair copied in
+    sd = to_hf_state_dict(ours)
+    missing, unexpected = hf.load_state_dict(sd, strict=False)
+    assert not [m for m in missing if "rotary" not in m] and not unexpected
+    ids = torch.randint(0, 120, (2, 19))
+    assert torch.allclose(ours(ids)[1], hf(input_ids=ids).logits, atol=2e-4, rtol=1e-4)
+    torch.manual_seed(9)
+    other = LlamaModel(cfg)
+    from_hf_state_dict(other, hf.state_dict())
+    for (n, a), (_, b) in zip(ours.named_parameters(), other.named_parameters()):
+        assert torch.equal(a, b), n
