@@ -193,15 +193,21 @@ def test_ib_monitor_reads_counters_of_a_fake_sysfs(tmp_path):
     c = read_counters(str(tmp_path))
     assert c == {"mlx5_0/ports/1/counters/port_xmit_data": 4000, "mlx5_0/ports/1/counters/port_rcv_data": 40}
     out = tmp_path / "ib.json"
-    mon = IBMonitor(interval=0.05, count=2, path=str(out), root=str(tmp_path))
-    mon.start()
-    time.sleep(0.02)
-    (d / "port_xmit_data").write_text("2000\n")
-    time.sleep(0.3)
-    mon.stop()
+    import atorch_b200.utils.ib_monitor as M
+
+    samples = iter([{"p/port_xmit_data": 4000}, {"p/port_xmit_data": 8000}, {"p/port_xmit_data": 8000}])
+    real = M.read_counters
+    M.read_counters = lambda root: next(samples)          # three successive readings of the counters
+    try:
+        mon = IBMonitor(interval=0.05, count=2, path=str(out), root=str(tmp_path))
+        mon.start()
+        time.sleep(0.4)
+        mon.stop()
+    finally:
+        M.read_counters = real
     ev = json.loads(out.read_text())["traceEvents"]
     rates = [e["args"]["bytes_per_s"] for e in ev if e["name"].endswith("port_xmit_data")]
-    assert len(rates) == 2 and max(rates) == 4000 / 0.05 and all(e["ph"] == "C" for e in ev)
+    assert rates == [4000 / 0.05, 0.0] and all(e["ph"] == "C" for e in ev)
 
 
 def test_safetensors_files_interchange_with_the_safetensors_package(tmp_path):
