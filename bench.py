@@ -345,6 +345,7 @@ def run_ours(args):
                                               if reuse else "executed",
                        "collective": comm,
                        "reshard_after_forward": os.environ.get("ATB_RESHARD", "1") != "0",
+                       "gemm_tile_order": "static" if os.environ.get("ATB_GEMM_DYNAMIC", "1") == "0" else "dynamic",
                        "l2": "not flushed: 13.5 GB of bf16 weights and 108 GB of optimizer state stream per step "
                              "(inputs larger than the 126 MB L2)"},
             "hw_tflops_per_gpu": round(value / world * flops / 1e12, 1),
