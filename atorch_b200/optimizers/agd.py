@@ -9,7 +9,8 @@ Per parameter and step t (g = gradient, after optional coupled weight decay):
     u   = m_t / den  (optionally clamped to [-clip, clip])
     p  -= lr * sqrt(1-b2^t)/(1-b1^t) * u
 Decoupled weight decay multiplies p by (1 - lr*wd) (or (1 - wd) with ``fixed_decay``) first. The
-``win`` variant keeps a conservative sequence z (z -= step*u, shrunk by 1/(1+wd*step)) and sets
+``win`` variant (no separate weight decay) keeps a conservative sequence z, zero at the start (z -= step*u,
+shrunk by 1/(1+wd*step)) and sets
 p = tau*p - tau*2*step*u + 2*tau*z with tau = 1/(3 + 2*step*wd).
 
 The update runs through the fused flat kernel (csrc/optim.cu) for CUDA fp32 parameters without
@@ -58,7 +59,7 @@ class AGD(Optimizer):
                     if group["amsgrad"]:
                         st["max_exp_avg_sq"] = torch.zeros_like(p, memory_format=torch.preserve_format)
                     if group["win"]:
-                        st["z"] = p.detach().clone()
+                        st["z"] = torch.zeros_like(p, memory_format=torch.preserve_format)   # as the reference does
                 st["step"] += 1
                 t = st["step"]
                 fused = (p.is_cuda and p.dtype == torch.float32 and p.is_contiguous() and not group["amsgrad"]
@@ -78,10 +79,11 @@ class AGD(Optimizer):
         lr, wd = group["lr"], group["weight_decay"]
         m, v = st["exp_avg"], st["exp_avg_sq"]
         bc1, bc2 = 1 - b1 ** t, 1 - b2 ** t
-        if group["weight_decouple"]:
-            p.mul_(1 - wd if group["fixed_decay"] else 1 - lr * wd)
-        elif wd != 0:
-            grad = grad.add(p, alpha=wd)
+        if not group["win"]:              # with win the decay lives in the z / tau expressions below
+            if group["weight_decouple"]:
+                p.mul_(1 - wd if group["fixed_decay"] else 1 - lr * wd)
+            elif wd != 0:
+                grad = grad.add(p, alpha=wd)
         m_old = m.clone()
         m.mul_(b1).add_(grad, alpha=1 - b1)
         s = m / bc1 if t == 1 else m / bc1 - m_old / (1 - b1 ** (t - 1))
@@ -98,7 +100,8 @@ class AGD(Optimizer):
         step = lr * math.sqrt(bc2) / bc1
         if group["win"]:
             # Win acceleration: a conservative sequence z and a reckless step of twice the size,
-            # mixed 1/3 : 2/3 (z starts at the initial weights, as in the Win paper)
+            # mixed 1/3 : 2/3. z starts at zero and the ordinary weight decay is skipped, both as in the reference,
+            # whose trajectory tests/test_reference_parity_cpu.py reproduces
             z = st["z"]
             z.add_(u, alpha=-step).mul_(1.0 / (1.0 + wd * step))
             step2 = 2.0 * step
