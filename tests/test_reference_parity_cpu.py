@@ -93,3 +93,100 @@ def test_agd_follows_the_reference_trajectory(cfg, tmp_path):
 def test_wsam_follows_the_reference_trajectory(cfg, tmp_path):
     ref, ours = _reference("wsam", cfg, tmp_path), _ours("wsam", cfg)
     assert ref.shape == ours.shape and torch.allclose(ours, ref, rtol=1e-4, atol=1e-5), (ours - ref).abs().max()
+
+
+_REF_MISC = r"""
+import json, sys, torch
+import atorch
+assert "baseline/_ref" in atorch.__file__.replace("\\", "/"), atorch.__file__
+what = sys.argv[1]
+out = {}
+if what == "masks":
+    from atorch.npu.layers import (create_additive_mask_by_breakpoint_mask,
+                                   create_additive_pack_mask_by_startpoint_endpoint_mask)
+    B, S = 3, 24
+    glm = torch.tensor([5, 0, 24])
+    pack = torch.tensor([[[0, 10, 18], [6, 14, 24]], [[2, 2, 2], [9, 9, 9]], [[0, 4, 20], [4, 12, 22]]])
+    out["glm"] = create_additive_mask_by_breakpoint_mask(B, S, glm)[:, 0].int().tolist()
+    out["pack"] = create_additive_pack_mask_by_startpoint_endpoint_mask(B, S, pack)[:, 0].int().tolist()
+elif what == "partition":
+    from atorch.pipeline_parallel.pipe_partition import get_rank_stage_info
+    cases = []
+    for total, pp, vpp, style, manual in [(32, 4, 1, "loop", None), (30, 4, 2, "loop", None), (13, 2, 2, "v", None),
+                                          (10, 2, 2, "loop", [1, 2, 3, 4]), (12, 4, 1, "loop", {0: 1, 3: 2}),
+                                          (9, 3, 2, "v", None)]:
+        cases.append([[list(t) for t in get_rank_stage_info(total, r, pp, vpp, style, manual)] for r in range(pp)])
+    out["cases"] = cases
+elif what == "ewma":
+    from atorch.local_sgd.utils.anomaly_detection import OnlineDynamicEWMA
+    g = torch.Generator().manual_seed(3)
+    xs = (1.0 + 0.1 * torch.randn(60, generator=g)).tolist()
+    xs[40], xs[55] = 5.0, 0.2
+    d = OnlineDynamicEWMA(alpha=0.1, warmup_steps=10, base_threshold=3)
+    rec = []
+    for x in xs:
+        x = torch.tensor(x)
+        flag = bool(d.is_outlier(x))
+        if not flag:
+            d.update(x)
+        rec.append([flag, float(d.get_mean()), float(d.get_std())])
+    out["rec"], out["xs"] = rec, xs
+print("OUT" + json.dumps(out))
+"""
+
+
+def _reference_misc(what, tmp_path):
+    if not os.path.isdir(os.path.join(REF, "atorch")):
+        pytest.skip("the reference is not installed under baseline/_ref")
+    script = tmp_path / "ref_misc.py"
+    script.write_text(_REF_MISC)
+    res = subprocess.run([sys.executable, str(script), what], cwd=str(tmp_path), env=dict(os.environ, PYTHONPATH=REF),
+                         capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stdout[-1500:] + res.stderr[-3000:]
+    return json.loads([l for l in res.stdout.splitlines() if l.startswith("OUT")][-1][3:])
+
+
+def test_glm_masks_equal_the_reference_constructions(tmp_path):
+    """Visibility of the GLM break-point mask and of the packed start/end-point mask: the dense mask of this package,
+    and the per-row key intervals its flash kernels take, against the reference's own constructions."""
+    from atorch_b200.ops import flash
+    from atorch_b200.ops.attention import build_dense_mask
+
+    ref = _reference_misc("masks", tmp_path)
+    B, S = 3, 24
+    glm = torch.tensor([5, 0, 24], dtype=torch.int32)
+    pack = torch.tensor([[[0, 10, 18], [6, 14, 24]], [[2, 2, 2], [9, 9, 9]], [[0, 4, 20], [4, 12, 22]]], dtype=torch.int32)
+    j = torch.arange(S)
+    for key, kw in (("glm", dict(glm_mask=glm)), ("pack", dict(pack_glm_mask=pack))):
+        want = torch.tensor(ref[key]).bool()
+        dense = build_dense_mask(B, S, S, torch.device("cpu"), True, kw.get("glm_mask"), kw.get("pack_glm_mask"), None, None)
+        assert torch.equal(dense.expand(B, -1, S, S)[:, 0], want), key
+        lo, hi = flash.row_intervals(B, S, S, torch.device("cpu"), True, kw.get("glm_mask"), kw.get("pack_glm_mask"))
+        vis = (j[None, None] >= lo[:, :, None]) & (j[None, None] < hi[:, :, None])
+        assert torch.equal(vis, want), key
+
+
+def test_pipeline_partition_equals_the_reference(tmp_path):
+    from atorch_b200.pipeline_parallel.pipe_partition import get_rank_stage_info
+
+    ref = _reference_misc("partition", tmp_path)["cases"]
+    mine = []
+    for total, pp, vpp, style, manual in [(32, 4, 1, "loop", None), (30, 4, 2, "loop", None), (13, 2, 2, "v", None),
+                                          (10, 2, 2, "loop", [1, 2, 3, 4]), (12, 4, 1, "loop", {0: 1, 3: 2}),
+                                          (9, 3, 2, "v", None)]:
+        mine.append([[list(t) for t in get_rank_stage_info(total, r, pp, vpp, style, manual)] for r in range(pp)])
+    assert mine == ref
+
+
+def test_online_ewma_outlier_detector_equals_the_reference(tmp_path):
+    from atorch_b200.local_sgd.anomaly import OnlineDynamicEWMA
+
+    ref = _reference_misc("ewma", tmp_path)
+    d = OnlineDynamicEWMA(alpha=0.1, warmup_steps=10, base_threshold=3)
+    for x, (flag, mean, std) in zip(ref["xs"], ref["rec"]):
+        x = torch.tensor(x)
+        mine = bool(d.is_outlier(x))
+        if not mine:
+            d.update(x)
+        assert mine == flag and abs(float(d.get_mean()) - mean) < 1e-6 and abs(float(d.get_std()) - std) < 1e-6, x
+    assert any(r[0] for r in ref["rec"])          # the spike was flagged
