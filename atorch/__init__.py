@@ -23,8 +23,8 @@ _RENAMES = {
     "atorch.local_sgd.configs": "atorch_b200.local_sgd.configs",
     "atorch.local_sgd.DDP": "atorch_b200.local_sgd.averager",
     "atorch.local_sgd.FSDP": "atorch_b200.local_sgd.sharded",
-    "atorch.modules.moe.topk_gating": "atorch_b200.modules.moe.gating",
-    "atorch.modules.moe.switch_gating": "atorch_b200.modules.moe.gating",
+    "atorch.modules.moe.topk_gating": "atorch_b200.modules.moe.prototype_gating",
+    "atorch.modules.moe.switch_gating": "atorch_b200.modules.moe.prototype_gating",
     "atorch.modules.normalization.layernorm": "atorch_b200.modules.normalization",
     "atorch.optimizers.low_bit.optim": "atorch_b200.optimizers.low_bit.optim",
     "atorch.trainer.atorch_trainer_v2": "atorch_b200.trainer.atorch_trainer_v2",

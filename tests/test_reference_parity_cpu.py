@@ -131,6 +131,19 @@ elif what == "ewma":
             d.update(x)
         rec.append([flag, float(d.get_mean()), float(d.get_std())])
     out["rec"], out["xs"] = rec, xs
+elif what == "gating":
+    from atorch.modules.moe.topk_gating import topk_gating
+    from atorch.modules.moe.switch_gating import switch_gating
+    g = torch.Generator().manual_seed(11)
+    logits = torch.randn(16, 2, 4, generator=g)
+    res = []
+    for k, cap, v2 in [(2, -1, False), (2, 3, False), (3, 4, False), (2, 3, True), (3, -1, True)]:
+        l, w, d = topk_gating(logits, k=k, capacity=cap, need_l_aux=True, dispatchV2=v2)
+        res.append([float(l), w.tolist(), (d[0].tolist() if v2 else d.int().tolist())])
+    for cap, v2 in [(-1, False), (2, False), (2, True)]:
+        l, w, d = switch_gating(logits, capacity=cap, need_l_aux=True, dispatchV2=v2)
+        res.append([float(l), w.tolist(), (d[0].tolist() if v2 else d.int().tolist())])
+    out["res"], out["logits"] = res, logits.tolist()
 print("OUT" + json.dumps(out))
 """
 
@@ -190,3 +203,23 @@ def test_online_ewma_outlier_detector_equals_the_reference(tmp_path):
             d.update(x)
         assert mine == flag and abs(float(d.get_mean()) - mean) < 1e-6 and abs(float(d.get_std()) - std) < 1e-6, x
     assert any(r[0] for r in ref["rec"])          # the spike was flagged
+
+
+def test_prototype_gating_equals_the_reference(tmp_path):
+    """M6-T prototype gating (top-k with capacity dropping and the compact dispatch form, switch gating) against the
+    reference's functions on the same logits."""
+    from atorch_b200.modules.moe.prototype_gating import switch_gating, topk_gating
+
+    ref = _reference_misc("gating", tmp_path)
+    logits = torch.tensor(ref["logits"])
+    got = []
+    for k, cap, v2 in [(2, -1, False), (2, 3, False), (3, 4, False), (2, 3, True), (3, -1, True)]:
+        got.append(topk_gating(logits, k=k, capacity=cap, need_l_aux=True, dispatchV2=v2))
+    for cap, v2 in [(-1, False), (2, False), (2, True)]:
+        got.append(switch_gating(logits, capacity=cap, need_l_aux=True, dispatchV2=v2))
+    assert len(got) == len(ref["res"])
+    for (l, w, d), (rl, rw, rd) in zip(got, ref["res"]):
+        assert abs(float(l) - rl) < 1e-6
+        assert torch.allclose(w, torch.tensor(rw), atol=1e-6)
+        mine = d[0] if isinstance(d, tuple) else d.int()
+        assert torch.equal(mine, torch.tensor(rd).to(mine.dtype))
