@@ -223,3 +223,86 @@ def test_prototype_gating_equals_the_reference(tmp_path):
         assert torch.allclose(w, torch.tensor(rw), atol=1e-6)
         mine = d[0] if isinstance(d, tuple) else d.int()
         assert torch.equal(mine, torch.tensor(rd).to(mine.dtype))
+
+
+_REDUCERS = r"""
+import json, os, sys, torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+impl = sys.argv[1]
+if impl == "reference":
+    import atorch
+    assert "baseline/_ref" in atorch.__file__.replace("\\", "/"), atorch.__file__
+    from atorch.local_sgd.utils.reduce_methods import GTAReducer, LinearReducer
+    from atorch.local_sgd.utils.reduce_methods.sparsify import sparsify
+else:
+    from atorch_b200.local_sgd.reducers import GTAReducer, LinearReducer, sparsify
+
+CASES = [("linear", dict(normalize=True)), ("linear", dict(normalize=False)),
+         ("linear", dict(normalize=True, weight_softmax_temperature=0.5)),
+         ("gta", dict(consensus_method="sum")), ("gta", dict(consensus_method="count", int8_mask=True)),
+         ("gta", dict(consensus_method=None, normalize=True)), ("gta", dict(consensus_method="sum", normalize=False)),
+         ("gta", dict(consensus_method="count", weight_softmax_temperature=2.0))]
+
+
+def worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    out = []
+    for kind, kw in CASES:
+        g = torch.Generator().manual_seed(100 + rank)
+        a, b = torch.randn(7, 5, generator=g), torch.randn(11, generator=g)
+        red = (LinearReducer if kind == "linear" else GTAReducer)(dist.group.WORLD, **kw)
+        red.reduce_tensor([a, b], weight=0.5 + rank, step_weight=2.0 - 0.5 * rank, step_weight_ratio=0.25)
+        out.append([a.tolist(), b.tolist()])
+    if rank == 0:
+        g = torch.Generator().manual_seed(9)
+        t = torch.randn(40, generator=g)
+        q.put({"cases": out, "magnitude": sparsify(t.clone(), 0.3, "magnitude").tolist(), "t": t.tolist()})
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ps = [ctx.Process(target=worker, args=(r, 3, int(sys.argv[2]), q)) for r in range(3)]
+    [p.start() for p in ps]
+    res = q.get(timeout=240)
+    [p.join(60) for p in ps]
+    print("OUT" + json.dumps(res))
+"""
+
+
+def _run_reducers(impl, tmp_path, port):
+    script = tmp_path / "reducers_case.py"
+    script.write_text(_REDUCERS)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PYTHONPATH=REF if impl == "reference" else root)
+    res = subprocess.run([sys.executable, str(script), impl, str(port)], cwd=str(tmp_path), env=env, capture_output=True,
+                         text=True, timeout=420)
+    assert res.returncode == 0, res.stdout[-1500:] + res.stderr[-3000:]
+    return json.loads([l for l in res.stdout.splitlines() if l.startswith("OUT")][-1][3:])
+
+
+def test_local_sgd_reducers_equal_the_reference_on_three_gloo_ranks(tmp_path):
+    """Linear and generalised-task-arithmetic reducers (sum / count consensus, int8 mask, softmax weights, step-weight
+    blending) on three gloo ranks, and magnitude sparsification, against the reference's classes with the same inputs."""
+    if not os.path.isdir(os.path.join(REF, "atorch")):
+        pytest.skip("the reference is not installed under baseline/_ref")
+    import socket
+
+    ports = []
+    for _ in range(2):
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            ports.append(s.getsockname()[1])
+    ref = _run_reducers("reference", tmp_path, ports[0])
+    mine = _run_reducers("ours", tmp_path, ports[1])
+    assert mine["t"] == ref["t"]
+    assert torch.allclose(torch.tensor(mine["magnitude"]), torch.tensor(ref["magnitude"]), atol=0)
+    assert len(mine["cases"]) == len(ref["cases"]) == 8
+    for i, (m, r) in enumerate(zip(mine["cases"], ref["cases"])):
+        for x, y in zip(m, r):
+            assert torch.allclose(torch.tensor(x), torch.tensor(y), rtol=1e-5, atol=1e-6), i
