@@ -59,7 +59,7 @@ def test_lowbit_optimizers_converge():
 
 def test_mup_scaling():
     def make(width):
-        return nn.Sequential(MupLinear(8, width), nn.ReLU(), MupLinear(width, width), nn.ReLU(), OutputLayer(width, 4))
+        return nn.Sequential(MupLinear(8, width), nn.ReLU(), MupLinear(width, width), nn.ReLU(), OutputLayer(width, 4, weight_zero_init=True))
     base, delta, model = make(16), make(32), make(64)
     set_base_shapes(model, base, delta)
     assert model[2].weight.infshape.ninf() == 2 and model[2].weight.infshape.width_mult() == 4.0
@@ -70,7 +70,7 @@ def test_mup_scaling():
     assert model[4].weight.abs().sum() == 0
     opt = MuAdam(model.parameters(), lr=1e-2)
     lrs = sorted({g["lr"] for g in opt.param_groups})
-    assert lrs == [1e-2 / 4, 1e-2]
+    assert lrs == [1e-2 / 4, 1e-2] and isinstance(opt, torch.optim.AdamW)
     opt2 = MuSGD(model.parameters(), lr=1e-1)
     assert any(abs(g["lr"] - 0.4) < 1e-9 for g in opt2.param_groups)
     model(torch.randn(2, 8)).sum().backward()

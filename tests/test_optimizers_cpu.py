@@ -125,7 +125,7 @@ def test_partition_adam_matches_adamw_and_keeps_state_in_host_blocks():
 def test_mup_qkv_and_q_layers_zero_the_query_rows():
     import torch.nn as nn
 
-    from atorch_b200.mup import MupModule, QKVLayer, QLayer
+    from atorch_b200.mup import MupModule, QKVLayer, QLayer, set_base_shapes
 
     class Attn(MupModule):
         def __init__(self):
@@ -133,6 +133,7 @@ def test_mup_qkv_and_q_layers_zero_the_query_rows():
             self.qkv, self.q, self.plain = QKVLayer(8, 24), QLayer(8, 8), QKVLayer(8, 24, q_zero_init=False)
 
     m = Attn()
+    set_base_shapes(m, None)
     m.mup_initial("mup")
     assert m.qkv.weight[:8].abs().sum() == 0 and m.qkv.weight[8:].abs().sum() > 0
     assert m.q.weight.abs().sum() == 0 and m.plain.weight[:8].abs().sum() > 0

@@ -306,3 +306,113 @@ def test_local_sgd_reducers_equal_the_reference_on_three_gloo_ranks(tmp_path):
     for i, (m, r) in enumerate(zip(mine["cases"], ref["cases"])):
         for x, y in zip(m, r):
             assert torch.allclose(torch.tensor(x), torch.tensor(y), rtol=1e-5, atol=1e-6), i
+
+
+_MUP = r"""
+import json, sys, torch
+from torch import nn
+impl, tmp = sys.argv[1], sys.argv[2]
+if impl == "reference":
+    import atorch
+    assert "baseline/_ref" in atorch.__file__.replace("\\", "/"), atorch.__file__
+    from atorch import mup
+    from atorch.mup.module import MupLinear, MupModule, OutputLayer, QKVLayer, QLayer
+    from atorch.mup.optim import MuAdamParamGroupsAdjust, MuSGDParamGroupsAdjust
+    from atorch.mup.shape import get_infshapes, make_base_shapes, set_base_shapes
+    from atorch.mup import init as minit
+else:
+    from atorch_b200.mup import (MupLinear, MupModule, OutputLayer, QKVLayer, QLayer, MuAdamParamGroupsAdjust,
+                                 MuSGDParamGroupsAdjust, get_infshapes, make_base_shapes, set_base_shapes)
+    from atorch_b200.mup import init as minit
+
+SAMPLERS = [("normal", dict(std=0.5)), ("uniform", dict(a=-0.3, b=0.3)), ("xavier_uniform", dict(gain=1.5)),
+            ("xavier_normal", {}), ("kaiming_uniform", dict(a=0.1)), ("kaiming_normal", dict(mode="fan_out"))]
+
+
+class Net(MupModule):
+    def __init__(self, width, heads_dim=8):
+        super().__init__()
+        self.emb = nn.Embedding(11, width)
+        self.hidden = nn.ModuleList([MupLinear(width, 2 * width, sampler=s, bias_zero_init=(i % 2 == 0), **kw)
+                                     for i, (s, kw) in enumerate(SAMPLERS)])
+        self.qkv = QKVLayer(width, 3 * width, sampler="normal", std=0.2)
+        self.q = QLayer(width, width)
+        self.inp = MupLinear(5, width, sampler="kaiming_normal", bias_zero_init=False)
+        self.out = OutputLayer(width, 7, output_mult=2.0, sampler="normal", std=0.1, bias_zero_init=False)
+        self.out0 = OutputLayer(width, 3, weight_zero_init=True, bias=False)
+
+
+def dump(model):
+    return {n: p.detach().double().flatten().tolist() for n, p in model.named_parameters()}
+
+
+out = {}
+base, delta = Net(6), Net(12)      # multiples of 3: the reference's QLayer wants three row blocks
+table = make_base_shapes(base, delta, savefile=tmp + "/" + impl + ".bsh")
+out["file"] = open(tmp + "/" + impl + ".bsh").read().split("\n", 2)[2] if impl == "reference" else None
+out["file_lines"] = sorted(l for l in open(tmp + "/" + impl + ".bsh").read().splitlines() if not l.startswith("#"))
+for width, how in ((24, "models"), (6, "models"), (18, "file")):
+    torch.manual_seed(width)
+    m = Net(width)
+    if how == "models":
+        set_base_shapes(m, base, delta=delta)
+    else:
+        set_base_shapes(m, tmp + "/" + impl + ".bsh")
+    rec = {"infshapes": {n: s.serialize() for n, s in get_infshapes(m).items()},
+           "ninf": {n: s.ninf() for n, s in get_infshapes(m).items()},
+           "mult": {n: float(s.width_mult()) for n, s in get_infshapes(m).items()}}
+    for mode in ("mup", "sp"):
+        torch.manual_seed(100 + width)
+        m.mup_initial(mode)
+        rec[mode] = dump(m)
+    x = torch.linspace(-1, 1, 2 * width).reshape(2, width)
+    rec["readout"] = m.out(x).detach().double().flatten().tolist()
+    sizes = lambda groups: [[round(g["lr"], 12), round(g["weight_decay"], 12), sorted(p.numel() for p in g["params"])]
+                            for g in groups if g["params"]]
+    rec["adam"] = sizes(MuAdamParamGroupsAdjust(m.parameters(), lr=0.01, weight_decay=0.1))
+    rec["adam_nowd"] = sizes(MuAdamParamGroupsAdjust([{"params": list(m.hidden.parameters()), "lr": 0.5},
+                                                      {"params": list(m.out.parameters())}], scaled_wd=False, lr=0.01,
+                                                     weight_decay=0.2))
+    rec["sgd"] = sizes(MuSGDParamGroupsAdjust(m.parameters(), lr=0.1, weight_decay=0.01))
+    torch.manual_seed(7)
+    t = torch.empty(2 * width, width); t.infshape = m.hidden[0].weight.infshape
+    v = torch.empty(width); v.infshape = m.inp.bias.infshape
+    rec["trunc"] = minit.trunc_normal_(t, std=0.3, a=-0.5, b=0.5).double().flatten().tolist()
+    rec["ones"] = minit.ones_(v).tolist() if v.infshape.ninf() == 1 else None
+    out[str(width)] = rec
+print("OUT" + json.dumps(out))
+"""
+
+
+def _run_mup(impl, tmp_path):
+    script = tmp_path / "mup_case.py"
+    script.write_text(_MUP)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PYTHONPATH=REF if impl == "reference" else root)
+    res = subprocess.run([sys.executable, str(script), impl, str(tmp_path)], cwd=str(tmp_path), env=env,
+                         capture_output=True, text=True, timeout=420)
+    assert res.returncode == 0, res.stdout[-1500:] + res.stderr[-3000:]
+    return json.loads([l for l in res.stdout.splitlines() if l.startswith("OUT")][-1][3:])
+
+
+def test_mup_shapes_initialisers_and_optimizer_groups_equal_the_reference(tmp_path):
+    """muP end to end on one network (every sampler, q/k/v layers, two readouts): width marks from a base/delta pair
+    and from a base-shape file, the weights drawn by ``mup_initial`` in both modes from the same seed, the readout's
+    forward, and the (lr, weight decay, members) of the MuAdam / MuSGD groups."""
+    if not os.path.isdir(os.path.join(REF, "atorch")):
+        pytest.skip("the reference is not installed under baseline/_ref")
+    ref, mine = _run_mup("reference", tmp_path), _run_mup("ours", tmp_path)
+    assert mine["file_lines"] == ref["file_lines"]
+    for width in ("24", "6", "18"):
+        r, m = ref[width], mine[width]
+        assert m["infshapes"] == r["infshapes"] and m["ninf"] == r["ninf"] and m["mult"] == r["mult"], width
+        for mode in ("mup", "sp"):
+            assert m[mode].keys() == r[mode].keys()
+            for name in r[mode]:
+                assert torch.allclose(torch.tensor(m[mode][name]), torch.tensor(r[mode][name]), rtol=1e-6, atol=1e-7), \
+                    (width, mode, name)
+        assert torch.allclose(torch.tensor(m["readout"]), torch.tensor(r["readout"]), rtol=1e-6, atol=1e-7)
+        for key in ("adam", "adam_nowd", "sgd"):
+            assert sorted(m[key]) == sorted(r[key]), (width, key, m[key], r[key])
+        assert torch.allclose(torch.tensor(m["trunc"]), torch.tensor(r["trunc"]), rtol=1e-6, atol=1e-7)
+        assert m["ones"] == r["ones"]
