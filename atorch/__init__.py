@@ -20,13 +20,45 @@ _RENAMES = {
     "atorch.auto.opt_lib.amp_optimization": "atorch_b200.auto.opt_lib.amp",
     "atorch.auto.opt_lib.checkpoint_optimization": "atorch_b200.auto.opt_lib.checkpoint",
     "atorch.auto.opt_lib.parallel_mode_optimization": "atorch_b200.auto.opt_lib.parallel_mode",
-    "atorch.local_sgd.configs": "atorch_b200.local_sgd.configs",
-    "atorch.local_sgd.DDP": "atorch_b200.local_sgd.averager",
+    "atorch.local_sgd.configs": "atorch_b200.local_sgd",
+    "atorch.local_sgd.configs.configs": "atorch_b200.local_sgd.configs",
+    "atorch.local_sgd.DDP": "atorch_b200.local_sgd",
+    "atorch.local_sgd.DDP.outer_optim_model_averager": "atorch_b200.local_sgd.averager",
+    "atorch.local_sgd.DDP.stateful_post_localSGD_optimizer": "atorch_b200.local_sgd.averager",
+    "atorch.local_sgd.utils": "atorch_b200.local_sgd",
+    "atorch.local_sgd.utils.anomaly_detection": "atorch_b200.local_sgd.anomaly",
+    "atorch.local_sgd.utils.reduce_methods": "atorch_b200.local_sgd",
+    "atorch.local_sgd.utils.reduce_methods.base": "atorch_b200.local_sgd.reducers",
+    "atorch.local_sgd.utils.reduce_methods.linear": "atorch_b200.local_sgd.reducers",
+    "atorch.local_sgd.utils.reduce_methods.generalized_task_arithmetic": "atorch_b200.local_sgd.reducers",
+    "atorch.local_sgd.utils.reduce_methods.sparsify": "atorch_b200.local_sgd.reducers",
+    "atorch.auto.engine.acceleration_engine": "atorch_b200.auto.engine.service",
+    "atorch.auto.engine.servicer": "atorch_b200.auto.engine.service",
+    "atorch.auto.task": "atorch_b200.auto.engine.task",
+    "atorch.auto.opt_lib.dynamo_optimization": "atorch_b200.auto.opt_lib.misc",
+    "atorch.auto.opt_lib.mixed_parallel_optimization": "atorch_b200.auto.opt_lib.misc",
+    "atorch.auto.opt_lib.sequence_parallel_optimization": "atorch_b200.auto.opt_lib.misc",
+    "atorch.auto.opt_lib.tensor_parallel_optimization": "atorch_b200.auto.opt_lib.misc",
+    "atorch.auto.opt_lib.half_optimization": "atorch_b200.auto.opt_lib.optimization_library",
+    "atorch.auto.opt_lib.shard_planners": "atorch_b200.auto",
+    "atorch.auto.opt_lib.shard_planners.dim_planner": "atorch_b200.auto.planner",
+    "atorch.auto.opt_lib.shard_planners.mip_tp_planner": "atorch_b200.auto.mip_tp_planner",
+    "atorch.distributed.mesh": "atorch_b200.distributed",
+    "atorch.modules.distributed_modules.materialize_modules": "atorch_b200.utils.meta_model_utils",
+    "atorch.optimizers.low_bit.optim.q_adamw": "atorch_b200.optimizers.low_bit.optim",
+    "atorch.optimizers.low_bit.optim.q_agd": "atorch_b200.optimizers.low_bit.optim",
+    "atorch.optimizers.low_bit.optim.q_came": "atorch_b200.optimizers.low_bit.optim",
+    "atorch.optimizers.low_bit.optim.q_adafactor": "atorch_b200.optimizers.low_bit.optim",
+    "atorch.rl.replay_buffer": "atorch_b200.rl",
+    "atorch.rl.replay_buffer.replay_buffer": "atorch_b200.rl.trainer",
+    "atorch.rl.trainer": "atorch_b200.rl",
+    "atorch.rl.trainer.ppo_trainer": "atorch_b200.rl.trainer",
+    "atorch.trainer.base.atorch_train_engine": "atorch_b200.trainer.engine",
     "atorch.local_sgd.FSDP": "atorch_b200.local_sgd.sharded",
     "atorch.modules.moe.topk_gating": "atorch_b200.modules.moe.prototype_gating",
     "atorch.modules.moe.switch_gating": "atorch_b200.modules.moe.prototype_gating",
     "atorch.modules.normalization.layernorm": "atorch_b200.modules.normalization",
-    "atorch.optimizers.low_bit.optim": "atorch_b200.optimizers.low_bit.optim",
+    "atorch.optimizers.low_bit.optim": "atorch_b200.optimizers.low_bit",
     "atorch.trainer.atorch_trainer_v2": "atorch_b200.trainer.atorch_trainer_v2",
     "atorch.trainer.fsdp.fsdp_shard_async_saver": "atorch_b200.trainer.fsdp.fsdp_ckpt_saver",
     "atorch.trainer.fsdp.fsdp_shard_dcp_loader": "atorch_b200.trainer.fsdp.fsdp_ckpt_saver",

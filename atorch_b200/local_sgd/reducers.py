@@ -9,15 +9,33 @@ generalized_task_arithmetic.py:11-93, sparsify.py:12-56}.)
 """
 from __future__ import annotations
 
+from enum import Enum
 from typing import Iterable, Optional, Union
 
 import torch
 import torch.distributed as dist
 
 
+class SparsificationMethod(str, Enum):
+    magnitude = "magnitude"
+    random = "random"
+    rescaled_random = "rescaled_random"
+
+
+def magnitude(tensor: torch.Tensor, density: float) -> torch.Tensor:
+    """Keeps the ``density`` fraction of entries with the largest magnitude, zeroes the rest."""
+    return sparsify(tensor, density, "magnitude")
+
+
+def bernoulli(tensor: torch.Tensor, density: float, rescale: bool = True) -> torch.Tensor:
+    """Keeps every entry with probability ``density`` (and divides the survivors by it when ``rescale``)."""
+    return sparsify(tensor, density, "rescaled_random" if rescale else "random")
+
+
 def sparsify(t: torch.Tensor, density: float, method: str) -> torch.Tensor:
     if density >= 1 or method is None:
         return t
+    method = getattr(method, "value", method)
     flat = t.view(-1)
     if method == "magnitude":
         k = int(density * flat.numel())
@@ -104,6 +122,11 @@ def consensus_mask(delta: torch.Tensor, method: str, mask_dtype, group) -> torch
     dist.all_reduce(tot, group=group)
     majority = (tot >= 0).to(mask_dtype) * 2 - 1
     return delta.sign().to(mask_dtype) == majority
+
+
+def get_consensus_mask_distributed(delta, method="sum", mask_dtype=None, process_group=None) -> torch.Tensor:
+    """``consensus_mask`` under the reference's name and argument order."""
+    return consensus_mask(delta, method, delta.dtype if mask_dtype is None else mask_dtype, process_group)
 
 
 class GTAReducer(TensorReducer):

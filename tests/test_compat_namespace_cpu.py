@@ -57,6 +57,31 @@ PATHS = [
     ("atorch.utils.timer", ["ThroughputTimer"]),
     ("atorch.utils.loss_spike_utils", ["TokenLossSpike"]),
     ("atorch.common.util_func", ["data_to_device"]),
+    ("atorch.local_sgd.configs.configs", ["LocalSGDConfig", "GTAConfig", "OuterOptimizerConfig"]),
+    ("atorch.local_sgd.DDP.outer_optim_model_averager", ["OuterOptimPeriodicModelAverager"]),
+    ("atorch.local_sgd.DDP.stateful_post_localSGD_optimizer", ["StatefulPostLocalSGDOptimizer"]),
+    ("atorch.local_sgd.utils.anomaly_detection", ["OnlineDynamicEWMA"]),
+    ("atorch.local_sgd.utils.reduce_methods", ["GTAReducer", "LinearReducer", "TensorReducer"]),
+    ("atorch.local_sgd.utils.reduce_methods.sparsify", ["SparsificationMethod", "magnitude", "bernoulli", "sparsify"]),
+    ("atorch.local_sgd.utils.reduce_methods.generalized_task_arithmetic", ["GTAReducer",
+                                                                           "get_consensus_mask_distributed"]),
+    ("atorch.auto.engine.acceleration_engine", ["AccelerationEngine"]),
+    ("atorch.auto.task", ["Task"]),
+    ("atorch.auto.opt_lib.half_optimization", ["HalfOptimization"]),
+    ("atorch.auto.opt_lib.shard_planners.mip_tp_planner", ["MIPTensorParallelPlanner"]),
+    ("atorch.optimizers.low_bit.optim.q_agd", ["Q_AGD"]),
+    ("atorch.rl.replay_buffer.replay_buffer", ["ReplayBuffer"]),
+    ("atorch.rl.trainer.ppo_trainer", ["PPOTrainer"]),
+    ("atorch.trainer.base.atorch_train_engine", ["AtorchTrainEngine"]),
+    ("atorch.mup.shape", ["set_base_shapes", "make_base_shapes", "save_base_shapes", "load_base_shapes"]),
+    ("atorch.mup.optim", ["MuAdam", "MuSGD", "MuAdamParamGroupsAdjust"]),
+    ("atorch.mup.init", ["normal_", "xavier_uniform_", "kaiming_normal_", "trunc_normal_"]),
+    ("atorch.utils.path_utils", ["path_is_empty"]),
+    ("atorch.common.singleton", ["SingletonMeta"]),
+    ("atorch.utils.hooks", ["ATorchHooks"]),
+    ("atorch.utils.metric_util", ["calc_mlm_acc", "MaskedLM"]),
+    ("atorch.utils.graph_transform_utils", ["topo_sort", "map_aggregate", "combine_map_aggregate"]),
+    ("atorch.utils.dev_utils", ["raise_not_impl"]),
 ]
 
 

@@ -3,6 +3,7 @@ per-stage pipeline checkpoints, dynamic gradient scalers."""
 import os
 from types import SimpleNamespace
 
+import pytest
 import torch
 import torch.nn as nn
 
@@ -315,3 +316,75 @@ def _moe_comm(rank, world):
 
 def test_moe_communication_functions_gloo():
     run_distributed(_moe_comm, world=2)
+
+
+def test_small_utilities_paths_singleton_hooks_metrics_and_graph_helpers(tmp_path):
+    import collections
+
+    import torch
+    import torch.fx
+
+    from atorch_b200.common.singleton import SingletonMeta
+    from atorch_b200.utils.dev_utils import raise_not_impl
+    from atorch_b200.utils.graph_transform_utils import combine_map_aggregate, map_aggregate, topo_sort
+    from atorch_b200.utils.hooks import ATorchHooks
+    from atorch_b200.utils.metric_util import MaskedLM, calc_mlm_acc
+    from atorch_b200.utils.path_utils import path_is_empty
+
+    assert path_is_empty(None) and path_is_empty(tmp_path) and path_is_empty(tmp_path / "missing")
+    (tmp_path / "f").write_text("x")
+    assert not path_is_empty(tmp_path) and path_is_empty(tmp_path / "f")
+
+    class One(metaclass=SingletonMeta):
+        def __init__(self, v=1):
+            self.v = v
+
+    a = One(5)
+    assert One() is a and a.v == 5
+    with pytest.raises(AssertionError):
+        One(6)
+
+    class Iface:
+        @raise_not_impl
+        def run(self):
+            pass
+
+    with pytest.raises(NotImplementedError, match="Iface does not implement function run"):
+        Iface().run()
+
+    seen = []
+    fn = lambda *a, **k: seen.append((a, k))      # noqa: E731
+    ATorchHooks.register_hook(ATorchHooks.REPORT_METRICS_HOOK, fn)
+    ATorchHooks.register_hook(ATorchHooks.REPORT_METRICS_HOOK, fn)
+    ATorchHooks.call_hooks(ATorchHooks.REPORT_METRICS_HOOK, 1, x=2)
+    ATorchHooks.call_hooks(ATorchHooks.COMPUTE_GPU_UTIL_HOOK, 3)
+    ATorchHooks.remove_hook(ATorchHooks.REPORT_METRICS_HOOK, fn)
+    ATorchHooks.call_hooks(ATorchHooks.REPORT_METRICS_HOOK, 4)
+    assert seen == [((1,), {"x": 2})]
+
+    logits = torch.tensor([[[0.1, 2.0, 0.0], [3.0, 0.0, 0.0], [0.0, 0.0, 1.0], [0.0, 5.0, 0.0]]])
+    labels = torch.tensor([[1, -100, 0, 1]])
+    assert abs(calc_mlm_acc({"logits": logits}, labels).item() - 2 / 3) < 1e-6
+    m = MaskedLM()
+    m.record({"logits": logits}, labels)
+    m.record({"logits": logits[:, :2]}, labels[:, :2])
+    assert abs(m.compute().item() - 3 / 4) < 1e-6
+
+    Pt = collections.namedtuple("Pt", "x y")
+    out = map_aggregate({"a": [1, (2, 3)], "p": Pt(4, 5), "s": slice(1, 6, 2)}, lambda v: v * 10)
+    assert out == {"a": [10, (20, 30)], "p": Pt(40, 50), "s": slice(10, 60, 20)} and isinstance(out["p"], Pt)
+    dst = {"a": [torch.zeros(2), torch.zeros(1)], "b": (torch.zeros(1),)}
+    src = {"a": [torch.ones(2), torch.full((1,), 2.0)], "b": (torch.full((1,), 3.0),)}
+    res = combine_map_aggregate(dst, src, lambda d, s: d.copy_(s))
+    assert res is dst and dst["a"][1].item() == 2.0 and dst["b"][0].item() == 3.0
+
+    class Net(torch.nn.Module):
+        def forward(self, x):
+            a = x + 1
+            b = a * 2
+            return a + b
+
+    nodes = list(torch.fx.symbolic_trace(Net()).graph.nodes)
+    order = topo_sort(nodes[::-1])
+    pos = {n: i for i, n in enumerate(order)}
+    assert len(order) == len(nodes) and all(pos[i] < pos[n] for n in nodes for i in n.all_input_nodes)
