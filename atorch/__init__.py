@@ -49,6 +49,10 @@ _RENAMES = {
     "atorch.optimizers.low_bit.optim.q_agd": "atorch_b200.optimizers.low_bit.optim",
     "atorch.optimizers.low_bit.optim.q_came": "atorch_b200.optimizers.low_bit.optim",
     "atorch.optimizers.low_bit.optim.q_adafactor": "atorch_b200.optimizers.low_bit.optim",
+    "atorch.rl.ppo_utils": "atorch_b200.rl",
+    "atorch.rl.ppo_utils.ppo_util": "atorch_b200.rl.ppo_util",
+    "atorch.rl.model_utils": "atorch_b200.rl",
+    "atorch.rl.model_utils.model_util": "atorch_b200.rl.model_util",
     "atorch.rl.replay_buffer": "atorch_b200.rl",
     "atorch.rl.replay_buffer.replay_buffer": "atorch_b200.rl.trainer",
     "atorch.rl.trainer": "atorch_b200.rl",

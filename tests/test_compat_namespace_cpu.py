@@ -82,6 +82,10 @@ PATHS = [
     ("atorch.utils.metric_util", ["calc_mlm_acc", "MaskedLM"]),
     ("atorch.utils.graph_transform_utils", ["topo_sort", "map_aggregate", "combine_map_aggregate"]),
     ("atorch.utils.dev_utils", ["raise_not_impl"]),
+    ("atorch.rl.ppo_utils.ppo_util", ["dist_fn", "get_kl_penalty", "get_rewards", "loss", "get_advantages_and_returns"]),
+    ("atorch.rl.model_utils.model_util", ["RunningMoments", "FixedKLController", "get_tensor_stats", "whiten",
+                                          "logprobs_of_labels", "flatten_dict", "hf_get_decoder_blocks", "make_head",
+                                          "freeze_bottom_causal_layers", "get_global_statistics", "set_seed"]),
 ]
 
 

@@ -416,3 +416,96 @@ def test_mup_shapes_initialisers_and_optimizer_groups_equal_the_reference(tmp_pa
             assert sorted(m[key]) == sorted(r[key]), (width, key, m[key], r[key])
         assert torch.allclose(torch.tensor(m["trunc"]), torch.tensor(r["trunc"]), rtol=1e-6, atol=1e-7)
         assert m["ones"] == r["ones"]
+
+
+_PPO = r"""
+import json, sys, types, torch
+impl = sys.argv[1]
+if impl == "reference":
+    import atorch
+    assert "baseline/_ref" in atorch.__file__.replace("\\", "/"), atorch.__file__
+    from atorch.rl.ppo_utils.ppo_util import get_advantages_and_returns, get_kl_penalty, get_rewards, loss
+    from atorch.rl.model_utils.model_util import (FixedKLController, RunningMoments, findattr, flatten_dict,
+                                                  get_tensor_stats, rgetattr, rhasattr, whiten)
+else:
+    from atorch_b200.rl.ppo_util import get_advantages_and_returns, get_kl_penalty, get_rewards, loss
+    from atorch_b200.rl.model_util import (FixedKLController, RunningMoments, findattr, flatten_dict, get_tensor_stats,
+                                           rgetattr, rhasattr, whiten)
+
+g = torch.Generator().manual_seed(21)
+B, P, R, V = 3, 4, 6, 13
+T = P + R
+logits, ref_logits = torch.randn(B, T, V, generator=g), torch.randn(B, T, V, generator=g)
+samples = torch.randint(0, V, (B, T), generator=g)
+attn = torch.ones(B, T, dtype=torch.long)
+attn[0, -2:] = 0
+attn[2, P - 1:] = 0            # a sample whose response is empty
+prompt = types.SimpleNamespace(input_ids=samples[:, :P])
+lp, klp, mean_kl, st = get_kl_penalty(logits, ref_logits, samples, prompt, attn, 0.07)
+scores = torch.tensor([1.5, -0.5, 2.0])
+rewards = get_rewards([k.clone() for k in klp], scores, lp)
+out = {"lp": [x.tolist() for x in lp], "klp": [x.tolist() for x in klp], "mean_kl": float(mean_kl), "st": st,
+       "rewards": [x.tolist() for x in rewards]}
+
+cfg = types.SimpleNamespace(clip_ratio=False, cliprange=0.2, cliprange_value=0.15, vf_coef=0.7, ent_coef=0.01, gamma=0.97,
+                            lam=0.9)
+values, old_values = torch.randn(B, R, generator=g), torch.randn(B, R, generator=g)
+rew = torch.randn(B, R, generator=g)
+for wh in (True, False):
+    adv, ret = get_advantages_and_returns(old_values, rew, R, use_whitening=wh, config=cfg)
+    out["gae_%s" % wh] = [adv.tolist(), ret.tolist()]
+new_lp, old_lp = -torch.rand(B, R, generator=g), -torch.rand(B, R, generator=g)
+mask = torch.ones(B, R)
+mask[1, 4:] = 0
+lg = torch.randn(B, R, V, generator=g)
+for clip in (False, True):
+    cfg.clip_ratio = clip
+    l, stats = loss(new_lp, values, old_lp, old_values, adv, ret, mask, lg, config=cfg)
+    out["loss_%s" % clip] = [float(l), flatten_dict(stats)]
+out["stats"] = get_tensor_stats(values, mask, mask.sum())
+out["whiten"] = [whiten(values).tolist(), whiten(values, shift_mean=False).tolist()]
+rm = RunningMoments()
+rec = []
+for i in range(3):
+    m, s = rm.update(torch.randn(17, generator=g) * (i + 1) + i)
+    rec.append([float(m), float(s), float(rm.mean), float(rm.std), float(rm.var), float(rm.count)])
+out["moments"] = rec
+obj = types.SimpleNamespace(a=types.SimpleNamespace(b=types.SimpleNamespace(c=5)))
+out["attr"] = [rhasattr(obj, "a.b.c"), rhasattr(obj, "a.x.c"), rgetattr(obj, "a.b.c"), findattr(obj, ("q", "a.b")).c,
+               FixedKLController(0.3).value]
+print("OUT" + json.dumps(out))
+"""
+
+
+def _run_ppo(impl, tmp_path):
+    script = tmp_path / "ppo_case.py"
+    script.write_text(_PPO)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PYTHONPATH=REF if impl == "reference" else root)
+    res = subprocess.run([sys.executable, str(script), impl], cwd=str(tmp_path), env=env, capture_output=True, text=True,
+                         timeout=420)
+    assert res.returncode == 0, res.stdout[-1500:] + res.stderr[-3000:]
+    return json.loads([l for l in res.stdout.splitlines() if l.startswith("OUT")][-1][3:])
+
+
+def _same(a, b, path=""):
+    if isinstance(a, dict):
+        assert a.keys() == b.keys(), path
+        for k in a:
+            _same(a[k], b[k], path + "/" + str(k))
+    elif isinstance(a, (list, tuple)):
+        assert len(a) == len(b), path
+        for i, (x, y) in enumerate(zip(a, b)):
+            _same(x, y, path + "/" + str(i))
+    elif isinstance(a, float):
+        assert abs(a - b) <= 1e-5 + 1e-5 * abs(b), (path, a, b)
+    else:
+        assert a == b, (path, a, b)
+
+
+def test_ppo_step_functions_and_statistics_equal_the_reference(tmp_path):
+    """KL penalty slices, rewards, GAE (with and without whitening), the clipped loss with its nested statistics,
+    masked tensor statistics, running moments and the dotted-attribute helpers on the same random inputs."""
+    if not os.path.isdir(os.path.join(REF, "atorch")):
+        pytest.skip("the reference is not installed under baseline/_ref")
+    _same(_run_ppo("ours", tmp_path), _run_ppo("reference", tmp_path))
