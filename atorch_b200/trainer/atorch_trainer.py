@@ -43,6 +43,7 @@ PREFIX_CHECKPOINT_DIR = "checkpoint"
 def get_scheduler(name: str, optimizer, num_warmup_steps: int, num_training_steps: int):
     from ..parallel.fsdp import FusedShardedOptimizer
     from ..auto.model_context import _SchedulerShim
+    from ..utils.trainer_utils import log_warmup_linear_decay_factor
 
     target = getattr(optimizer, "optimizer", optimizer)
     if not isinstance(target, torch.optim.Optimizer):
@@ -51,9 +52,9 @@ def get_scheduler(name: str, optimizer, num_warmup_steps: int, num_training_step
     def lam(step: int) -> float:
         if name == "constant":
             return 1.0
+        if name == "log_warmup_linear_decay":
+            return log_warmup_linear_decay_factor(step, num_warmup_steps, num_training_steps)
         if step < num_warmup_steps:
-            if name == "log_warmup_linear_decay":
-                return math.log(step + 1) / math.log(num_warmup_steps + 1)
             return step / max(1, num_warmup_steps)
         if name == "constant_with_warmup":
             return 1.0

@@ -1,6 +1,7 @@
 """AtorchTrainer on CPU: training, logging, evaluation with metrics, checkpoint rotation, resume."""
 import os
 
+import pytest
 import torch
 import torch.nn as nn
 
@@ -152,3 +153,37 @@ def test_trainer_v2_flow_callback_samples_dynamic_steps_test_and_profiler(tmp_pa
     json.dump(js, open(tmp_path / "out" / "trainer_state.json", "w"))
     filled = AtorchTrainerState.load_from_json(str(tmp_path / "out" / "trainer_state.json"), AtorchTrainerState())
     assert filled.global_step == 6 and not hasattr(filled, "future_field")
+
+
+def test_log_warmup_linear_decay_schedule_values():
+    """Zero at steps 0 and 1, one at the end of the logarithmic warm-up, linear decay to zero afterwards; the trainer's
+    scheduler factory and the standalone one agree; Hugging Face names are passed through."""
+    import math
+
+    from atorch_b200.trainer.atorch_trainer import get_scheduler as trainer_sched
+    from atorch_b200.utils.trainer_utils import (AtorchSchedulerType, get_linear_schedule_with_log_warmup, get_scheduler,
+                                                 log_warmup_linear_decay_factor)
+
+    W, T = 10, 50
+    f = [log_warmup_linear_decay_factor(s, W, T) for s in range(T + 5)]
+    assert f[0] == 0.0 and abs(f[1]) < 1e-5 and abs(f[5] - math.log(5) / math.log(10)) < 1e-5
+    assert f[W] == 1.0 and abs(f[30] - 0.5) < 1e-12 and f[T] == 0.0 and f[T + 3] == 0.0
+    p = torch.nn.Parameter(torch.zeros(1))
+    lrs = []
+    for make in (lambda o: get_linear_schedule_with_log_warmup(o, W, T),
+                 lambda o: get_scheduler(AtorchSchedulerType.LOG_WARMUP_LINEAR_DECAY, o, W, T),
+                 lambda o: trainer_sched("log_warmup_linear_decay", o, W, T)):
+        opt = torch.optim.SGD([p], lr=2.0)
+        sch = make(opt)
+        seq = []
+        for _ in range(T):
+            seq.append(opt.param_groups[0]["lr"])
+            opt.step()
+            sch.step()
+        lrs.append(seq)
+    assert lrs[0] == lrs[1] == lrs[2] and lrs[0][:W + 1] == [2.0 * x for x in f[:W + 1]]
+    opt = torch.optim.SGD([p], lr=1.0)
+    cos = get_scheduler("cosine", opt, W, T)
+    assert type(cos).__name__ == "LambdaLR"
+    with pytest.raises(ValueError):
+        get_scheduler("no_such_schedule", opt, W, T)
