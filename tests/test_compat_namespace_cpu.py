@@ -82,6 +82,11 @@ PATHS = [
     ("atorch.utils.metric_util", ["calc_mlm_acc", "MaskedLM"]),
     ("atorch.utils.graph_transform_utils", ["topo_sort", "map_aggregate", "combine_map_aggregate"]),
     ("atorch.utils.dev_utils", ["raise_not_impl"]),
+    ("atorch.modules.distributed_modules.activation_checkpointing", [
+        "CudaRNGStatesTracker", "get_cuda_rng_tracker", "model_parallel_cuda_manual_seed", "CheckpointFunction",
+        "checkpoint", "TPCheckpointWrapper", "tp_wrap_fn"]),
+    ("atorch.utils.trainer_utils", ["AtorchSchedulerType", "get_linear_schedule_with_log_warmup", "get_scheduler",
+                                    "AsyncCheckpointSignal", "PipeMessageEntity"]),
     ("atorch.rl.ppo_utils.ppo_util", ["dist_fn", "get_kl_penalty", "get_rewards", "loss", "get_advantages_and_returns"]),
     ("atorch.rl.model_utils.model_util", ["RunningMoments", "FixedKLController", "get_tensor_stats", "whiten",
                                           "logprobs_of_labels", "flatten_dict", "hf_get_decoder_blocks", "make_head",

@@ -249,3 +249,85 @@ def test_sharded_weight_linear_reference_form_gloo():
     from tests.dist_utils import run_distributed
 
     run_distributed(_sharded_weight_ref, world=2, backend="gloo", timeout=120)
+
+
+def _tp_activation_checkpoint(rank, world):
+    import torch.nn.functional as F
+
+    from atorch_b200.distributed.distributed import create_parallel_group
+    from atorch_b200.modules.distributed_modules.activation_checkpointing import (
+        TPCheckpointWrapper, checkpoint, gather_split_1d_tensor, get_cuda_rng_tracker, model_parallel_cuda_manual_seed,
+        split_tensor_into_1d_equal_chunks, tp_wrap_fn)
+
+    create_parallel_group(([("tensor", world)], None))
+    model_parallel_cuda_manual_seed(77)
+    tracker = get_cuda_rng_tracker()
+
+    class Block(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            torch.manual_seed(3)
+            self.a, self.b = torch.nn.Linear(8, 16), torch.nn.Linear(16, 8)
+
+        def forward(self, x, scale=1.0, extra=None):
+            h = F.dropout(self.a(x), 0.3)                     # default stream
+            with tracker.fork():
+                h = F.dropout(torch.tanh(h), 0.3)             # model-parallel stream
+            return self.b(h) * scale + (0 if extra is None else extra)
+
+    torch.manual_seed(11)
+    x = torch.randn(4, 6, 8)                                  # replicated input, first dim divisible by tp
+    extra = torch.randn(4, 6, 8)
+    chunk = split_tensor_into_1d_equal_chunks(x, new_buffer=True)
+    assert chunk.numel() == x.numel() // world
+    assert torch.equal(gather_split_1d_tensor(chunk).view_as(x), x)
+
+    def run(wrapped):
+        blk = Block()
+        mod = tp_wrap_fn(blk) if wrapped else blk
+        model_parallel_cuda_manual_seed(77)
+        torch.manual_seed(5)
+        xi, ei = x.clone().requires_grad_(), extra.clone().requires_grad_()
+        y = mod(xi, scale=2.0, extra=ei)
+        torch.randn(3)                                        # other random draws between forward and backward
+        with tracker.fork():
+            torch.randn(3)
+        after = torch.get_rng_state().clone(), tracker.get_states()[next(iter(tracker.get_states()))].clone()
+        y.square().sum().backward()
+        # the recomputation left the streams where the forward pass (and what followed) had put them
+        assert torch.equal(torch.get_rng_state(), after[0])
+        assert torch.equal(tracker.get_states()[next(iter(tracker.get_states()))], after[1])
+        return y.detach(), xi.grad, ei.grad, [p.grad for p in blk.parameters()], mod
+
+    y0, gx0, ge0, gp0, _ = run(False)
+    y1, gx1, ge1, gp1, mod = run(True)
+    assert isinstance(mod, TPCheckpointWrapper) and mod.a is mod._checkpoint_wrapped_module.a
+    assert torch.equal(y0, y1) and torch.allclose(gx0, gx1, atol=1e-6) and torch.allclose(ge0, ge1, atol=1e-6)
+    for a, b in zip(gp0, gp1):
+        assert torch.allclose(a, b, atol=1e-6)
+
+    # what the checkpoint keeps of the first argument is this rank's slice
+    saved = []
+    with torch.autograd.graph.saved_tensors_hooks(lambda t: saved.append(t.numel()) or t, lambda t: t):
+        xi = x.clone().requires_grad_()
+        y = checkpoint(lambda t, s: torch.tanh(t) * s, True, xi, 3.0)
+    assert saved == [x.numel() // world], saved
+    y.sum().backward()
+    assert torch.allclose(xi.grad, 3.0 * (1 - torch.tanh(x) ** 2), atol=1e-6)
+    # without distribution the whole input is kept
+    saved.clear()
+    with torch.autograd.graph.saved_tensors_hooks(lambda t: saved.append(t.numel()) or t, lambda t: t):
+        checkpoint(lambda t: torch.tanh(t), False, x.clone().requires_grad_())
+    assert saved == [x.numel()]
+    # the tracker refuses duplicate names and seeds
+    import pytest
+
+    with pytest.raises(Exception, match="already exists"):
+        tracker.add("model-parallel-rng", 1)
+    with pytest.raises(Exception, match="is not added"):
+        with tracker.fork("missing"):
+            pass
+
+
+def test_tp_activation_checkpoint_keeps_a_slice_and_replays_rng_gloo():
+    run_distributed(_tp_activation_checkpoint, world=2)
