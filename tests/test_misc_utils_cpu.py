@@ -388,3 +388,53 @@ def test_small_utilities_paths_singleton_hooks_metrics_and_graph_helpers(tmp_pat
     order = topo_sort(nodes[::-1])
     pos = {n: i for i, n in enumerate(order)}
     assert len(order) == len(nodes) and all(pos[i] < pos[n] for n in nodes for i in n.all_input_nodes)
+
+
+def test_dataclass_helpers_dump_diff_map_and_keep_unknown_arguments(monkeypatch):
+    import enum
+    import json
+    from dataclasses import dataclass, field
+
+    from atorch_b200.utils.dataclass_utils import (AutoMapperExtraConfigs, DataclassMixin, DynamicDataClass,
+                                                   clear_environment, is_json_serializable)
+
+    class Mode(enum.Enum):
+        A = "a"
+        B = "b"
+
+    def fn():
+        pass
+
+    @dataclass
+    class Args(DataclassMixin, AutoMapperExtraConfigs):
+        steps: int = int(os.environ.get("NO_SUCH_VAR_FOR_TEST", 10))
+        mode: Mode = Mode.A
+        modes: tuple = (Mode.A, Mode.B)
+        hook: object = fn
+        nested: dict = field(default_factory=lambda: {"f": fn, "dev": torch.device("cpu")})
+        logging_steps: int = 5
+
+    a = Args(steps=20, mode=Mode.B, extra_configs={"log_interval": 7, "other": None})
+    d = a.to_dict()
+    assert d["mode"] == "b" and d["modes"] == ("a", "b") and d["hook"] == "fn" and d["nested"] == {"f": "fn", "dev": "cpu"}
+    assert json.loads(a.to_json_string())["steps"] == 20 and is_json_serializable(d) and not is_json_serializable({1, 2})
+    assert a.to_kwargs() == {"steps": 20, "mode": "b", "extra_configs": {"log_interval": 7, "other": None}}
+    mapped = a.do_auto_mapping({"logging_steps": "log_interval", "steps": "train_iters", "mode": "other"})
+    assert mapped["log_interval"] == 7 and a.logging_steps == 7          # the other system's name wins
+    assert mapped["train_iters"] == 20 and mapped["other"] == Mode.B     # filled from the own fields
+    assert "train_iters" not in a.extra_configs                          # a copy unless asked to overwrite
+    monkeypatch.setenv("ATB_TEST_ENV", "1")
+    with clear_environment():
+        assert "ATB_TEST_ENV" not in os.environ and not os.environ
+    assert os.environ["ATB_TEST_ENV"] == "1"
+
+    @dataclass(init=False)
+    class Dyn(DynamicDataClass):
+        lr: float = 0.1
+        name: str = "x"
+
+    dyn = Dyn(lr=0.5, warmup=3, sched={"k": [1, 2]})
+    assert dyn.lr == 0.5 and dyn.name == "x" and dyn.warmup == 3 and dyn.sched == {"k": [1, 2]}
+    assert dyn.to_dict() == {"lr": 0.5, "name": "x", "warmup": 3, "sched": {"k": [1, 2]}}
+    with pytest.raises(AttributeError):
+        dyn.missing
