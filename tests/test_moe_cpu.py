@@ -130,3 +130,46 @@ def _moe_ddp(rank, world):
 
 def test_moe_mixture_ddp_gloo():
     run_distributed(_moe_ddp, world=4)
+
+
+def _group_aware_norms(rank, world):
+    import math
+
+    from atorch_b200.distributed.distributed import create_parallel_group, parallel_group
+    from atorch_b200.utils.moe_util import clip_grad_norm_, compute_grad_norm_, compute_param_norm_, compute_single_param_std_
+
+    create_parallel_group(([("expert", world)], None))
+    torch.manual_seed(1)
+    dense = torch.nn.Parameter(torch.randn(5, 3))                  # the same on every rank
+    torch.manual_seed(10 + rank)
+    expert = torch.nn.Parameter(torch.randn(4, 2))                 # a different expert on every rank
+    expert.expert = True
+    tagged = torch.nn.Parameter(torch.randn(3))                    # explicit group
+    tagged.norm_group = parallel_group("expert")
+    for p in (dense, expert, tagged):
+        p.grad = p.detach() * 0.5 + 1.0
+    params = [dense, expert, tagged]
+    everything = [dense.grad.reshape(-1)]
+    for r in range(world):
+        torch.manual_seed(10 + r)
+        e = torch.randn(4, 2)
+        t = torch.randn(3)
+        everything += [(e * 0.5 + 1.0).reshape(-1), (t * 0.5 + 1.0).reshape(-1)]
+    flat = torch.cat(everything)
+    for nt in (2.0, 1.0, math.inf):
+        got = compute_grad_norm_(params, nt)
+        assert torch.allclose(got, torch.linalg.vector_norm(flat, nt), rtol=1e-5), (nt, got)
+    assert compute_param_norm_(params).item() > 0
+    assert torch.allclose(compute_single_param_std_(dense), dense.detach().std(), rtol=1e-5)
+    before = [p.grad.clone() for p in params]
+    total = clip_grad_norm_(params, max_norm=1.0)
+    coef = 1.0 / (torch.linalg.vector_norm(flat, 2.0) + 1e-6)
+    assert torch.allclose(total, torch.linalg.vector_norm(flat, 2.0), rtol=1e-5)
+    for p, b in zip(params, before):
+        assert torch.allclose(p.grad, b * coef, rtol=1e-5)
+
+
+def test_norms_over_parameters_partitioned_on_different_groups_gloo():
+    from tests.dist_utils import run_distributed
+
+    run_distributed(_group_aware_norms, world=2)
