@@ -35,6 +35,10 @@ _RENAMES = {
     "atorch.auto.engine.acceleration_engine": "atorch_b200.auto.engine.service",
     "atorch.auto.engine.servicer": "atorch_b200.auto.engine.service",
     "atorch.auto.task": "atorch_b200.auto.engine.task",
+    "atorch.auto.engine.sg_algo.sg_algorithm": "atorch_b200.auto.engine.sg_algo",
+    "atorch.auto.engine.sg_algo.sg_algo_lib": "atorch_b200.auto.engine.sg_algo",
+    "atorch.auto.engine.sg_algo.combination_sg": "atorch_b200.auto.engine.sg_algo",
+    "atorch.auto.engine.sg_algo.bayes_opt_sg": "atorch_b200.auto.engine.sg_algo",
     "atorch.auto.opt_lib.dynamo_optimization": "atorch_b200.auto.opt_lib.misc",
     "atorch.auto.opt_lib.mixed_parallel_optimization": "atorch_b200.auto.opt_lib.misc",
     "atorch.auto.opt_lib.sequence_parallel_optimization": "atorch_b200.auto.opt_lib.misc",

@@ -53,7 +53,7 @@ class Executor:
         self.current_parallel_mode = None
         self.terminate_task_id: Optional[int] = None
         self._candidates: Optional[Deque[StrategyRecord]] = None
-        self._bayes = None
+        self._sg_algo = None
         if load_strategy is not None:          # nothing to search: hand the given strategy to every process
             self.strategies.append(StrategyRecord(load_strategy))
             self.strategies[0].status = StrategyRecord.SUCCEED
@@ -81,28 +81,20 @@ class Executor:
 
     # ------------------------------------------------------------------ planning
     def _generate_candidates(self) -> None:
-        from .search import BayesianGenerator, combination_candidates
+        """Pick the strategy-generation algorithm; it fills ``_candidates`` stage by stage."""
+        from .sg_algo import StrategyGenerationAlgorithmLibrary
 
-        world = self.total_process
-        seen, out = set(), deque()
-        for st in combination_candidates(world, self.analysis, self.excluded, self.included):
-            key = tuple(st.names())
-            if key not in seen:
-                seen.add(key)
-                out.append(StrategyRecord(st))
-        self._candidates = out
-        if self.algo == "bo":
-            self._bayes = BayesianGenerator()
-            self._candidates = deque()
+        name = {"combination": "combination_sg", "bo": "bo_sg"}.get(self.algo, self.algo)
+        self._sg_algo = StrategyGenerationAlgorithmLibrary()[name]
+        if self._sg_algo is None:
+            raise ValueError(f"unknown strategy generation algorithm {self.algo!r}")
+        self._candidates = deque()
 
     def _next_candidate(self) -> Optional[StrategyRecord]:
         if self._expired():
             return None
-        if self._bayes is not None:
-            combo = self._bayes.suggest()
-            if combo is None:
-                return None
-            return StrategyRecord(self._bayes.to_strategy(combo, self.total_process, self.analysis), combo)
+        if not self._candidates and not self._sg_algo.is_done:
+            self._sg_algo(self)
         return self._candidates.popleft() if self._candidates else None
 
     def _schedule_strategy(self, rec: StrategyRecord) -> None:
@@ -216,8 +208,6 @@ class Executor:
             rec = self.strategies[t.strategy_id]
             rec.dryrun_result = result if isinstance(result, dict) else {}
             rec.status = StrategyRecord.SUCCEED if (ok and rec.throughput > 0) else StrategyRecord.FAILED
-            if self._bayes is not None and rec.combo is not None:
-                self._bayes.observe(rec.combo, rec.throughput)
 
     def best_strategy(self) -> Optional[Strategy]:
         ok = [r for r in self.strategies if r.status == StrategyRecord.SUCCEED]

@@ -178,3 +178,45 @@ def test_engine_service_round_trip_over_grpc():
     eng.tear_down(timeout=5)
     assert ran[0] == TaskType.ANALYSE and ran.count(TaskType.DRYRUN) >= 4
     assert "fsdp" in best.names() and "amp_native" in best.names()
+
+
+def test_strategy_generation_algorithms_fill_the_executor_stage_by_stage():
+    """The combination algorithm adds its whole set in one call; the Bayesian one proposes a candidate per call, learns
+    from the throughputs recorded in between and stops by itself; the library hands them out by name."""
+    from atorch_b200.auto.engine.executor import Executor, StrategyRecord
+    from atorch_b200.auto.engine.sg_algo import (BOAlgorithm, CombinationAlgorithm, StrategyGenerationAlgorithm,
+                                                 StrategyGenerationAlgorithmLibrary)
+
+    lib = StrategyGenerationAlgorithmLibrary()
+    assert isinstance(lib["combination_sg"], CombinationAlgorithm) and isinstance(lib["bo_sg"], BOAlgorithm)
+    assert lib["nope"] is None and StrategyGenerationAlgorithm("x")(None) == (True, None, 0)
+
+    ex = Executor({"node_num": 1, "nproc_per_node": 2})
+    ex.analysis = {"opt_config_submodule_names": ("Block",), "replaceable_pairs": ["x"]}
+    ex._generate_candidates()
+    algo = CombinationAlgorithm()
+    done, tasks, n = algo(ex)
+    assert done and tasks is None and n == len(ex._candidates) == 9
+    assert algo(ex) == (True, None, 0)
+    names = {tuple(r.strategy.names()) for r in ex._candidates}
+    assert ("parallel_mode",) in names and ("parallel_mode", "module_replace", "amp_native", "fsdp") in names
+
+    ex = Executor({"node_num": 1, "nproc_per_node": 2}, algo="bo")
+    ex.analysis = {"opt_config_submodule_names": ("Block",)}
+    ex._generate_candidates()
+    bo = BOAlgorithm(max_iter=10, patience=3, random_sample=2)
+    proposed = []
+    for _ in range(40):
+        done, _, n = bo(ex)
+        if done:
+            break
+        assert n == 1
+        rec = ex._candidates.popleft()
+        assert rec.combo not in proposed
+        proposed.append(rec.combo)
+        rec.status = StrategyRecord.SUCCEED
+        rec.dryrun_result = {"throughput": 10.0 + (rec.combo[0] is not None) + 2 * (rec.combo[1] == "fsdp")}
+        ex.strategies.append(rec)
+    assert bo.is_done and 3 <= len(proposed) <= 10
+    best = max(ex.strategies, key=lambda r: r.throughput)
+    assert best.combo[1] == "fsdp"                      # the search reached the better zero choice
