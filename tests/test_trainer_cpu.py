@@ -187,3 +187,57 @@ def test_log_warmup_linear_decay_schedule_values():
     assert type(cos).__name__ == "LambdaLR"
     with pytest.raises(ValueError):
         get_scheduler("no_such_schedule", opt, W, T)
+
+
+def _trainer_utils(rank, world):
+    from atorch_b200.distributed.distributed import create_parallel_group
+    from atorch_b200.trainer.utils import (dict_to_tensor, distributed_std, is_last_rank_on_current_stage,
+                                           is_main_process, tensor_to_dict)
+
+    create_parallel_group(([("data", world)], None))
+    assert is_main_process() == (rank == 0) and is_last_rank_on_current_stage() == (rank == world - 1)
+    payload = {"a": [1, 2, {"b": "x"}], "r": 0}
+    t = dict_to_tensor(payload if rank == 0 else {"pad": "y" * 40}, device="cpu")
+    n = torch.tensor([t.numel()])
+    torch.distributed.broadcast(n, 0)
+    buf = t if rank == 0 else torch.empty(int(n), dtype=torch.uint8)
+    torch.distributed.broadcast(buf, 0)
+    assert tensor_to_dict(buf) == payload
+    torch.manual_seed(3)
+    full = torch.randn(world * 6, 5)
+    piece = full.chunk(world)[rank].clone()                 # this rank's shard of a sharded parameter
+    assert torch.allclose(distributed_std("w", piece), full.std(), rtol=1e-5)
+
+
+def test_trainer_utils_roles_object_transport_and_sharded_std_gloo():
+    from tests.dist_utils import run_distributed
+
+    run_distributed(_trainer_utils, world=2)
+
+
+def test_trainer_utils_tensorboard_writer_and_banner(caplog):
+    import logging
+
+    from atorch_b200.trainer.utils import (DistributedType, IntervalStrategy, print_all_args_before_training,
+                                           write_dict_to_tensorboard)
+
+    class W:
+        def __init__(self):
+            self.rows = []
+
+        def add_scalar(self, k, v, i):
+            self.rows.append((k, v, i))
+
+        def log(self, d, i):
+            self.rows.append((d, i))
+
+    tb, wb = W(), W()
+    write_dict_to_tensorboard(tb, wb, 7, {"loss": 1.5, "grad": {"norm": 2.0, "layers": {"l0": 0.1}}}, prefix="train/")
+    assert tb.rows == [("train/loss", 1.5, 7), ("train/grad/norm", 2.0, 7), ("train/grad/layers/l0", 0.1, 7)]
+    assert wb.rows[1] == ({"train/grad/norm": 2.0}, 7)
+    assert IntervalStrategy("steps") is IntervalStrategy.STEPS and DistributedType.FSDP.value == "FSDP"
+    with caplog.at_level(logging.INFO, logger="atorch.logger"):
+        print_all_args_before_training({"Train": {"lr": 0.1, "Batch": 4}})
+    lines = [r.getMessage() for r in caplog.records]
+    assert any(l.startswith("  Batch ****") and l.endswith(" 4") for l in lines)
+    assert lines.index(next(l for l in lines if l.startswith("  Batch"))) < lines.index(next(l for l in lines if l.startswith("  lr")))
