@@ -70,3 +70,8 @@ def get_randomizer(*same_groups: str) -> MultiDimParallelRandomizer:
     if key not in _RANDOMIZERS:
         _RANDOMIZERS[key] = MultiDimParallelRandomizer(*same_groups)
     return _RANDOMIZERS[key]
+
+
+def get_MDPRInstance() -> MultiDimParallelRandomizer:
+    """The stream that differs on every rank (the name the original package uses for its default instance)."""
+    return get_randomizer()

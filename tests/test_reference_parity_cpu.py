@@ -165,6 +165,9 @@ def test_glm_masks_equal_the_reference_constructions(tmp_path):
     from atorch_b200.ops import flash
     from atorch_b200.ops.attention import build_dense_mask
 
+    from atorch_b200.npu.layers import (create_additive_mask_by_breakpoint_mask,
+                                        create_additive_pack_mask_by_startpoint_endpoint_mask)
+
     ref = _reference_misc("masks", tmp_path)
     B, S = 3, 24
     glm = torch.tensor([5, 0, 24], dtype=torch.int32)
@@ -177,6 +180,11 @@ def test_glm_masks_equal_the_reference_constructions(tmp_path):
         lo, hi = flash.row_intervals(B, S, S, torch.device("cpu"), True, kw.get("glm_mask"), kw.get("pack_glm_mask"))
         vis = (j[None, None] >= lo[:, :, None]) & (j[None, None] < hi[:, :, None])
         assert torch.equal(vis, want), key
+    assert torch.equal(create_additive_mask_by_breakpoint_mask(B, S, glm.long())[:, 0].bool(), torch.tensor(ref["glm"]).bool())
+    assert torch.equal(create_additive_pack_mask_by_startpoint_endpoint_mask(B, S, pack.long())[:, 0].bool(),
+                       torch.tensor(ref["pack"]).bool())
+    one = create_additive_mask_by_breakpoint_mask(B, S, torch.tensor(5))
+    assert one.shape == (1, 1, S, S) and torch.equal(one[0, 0].bool(), torch.tensor(ref["glm"][0]).bool())
 
 
 def test_pipeline_partition_equals_the_reference(tmp_path):
