@@ -48,6 +48,7 @@ _RENAMES = {
     "atorch.auto.opt_lib.shard_planners.dim_planner": "atorch_b200.auto.planner",
     "atorch.auto.opt_lib.shard_planners.mip_tp_planner": "atorch_b200.auto.mip_tp_planner",
     "atorch.distributed.mesh": "atorch_b200.distributed",
+    "atorch.pipeline_parallel.scheduler": "atorch_b200.pipeline_parallel.pipe_engine",
     "atorch.modules.distributed_modules.randomizer": "atorch_b200.parallel.randomizer",
     "atorch.modules.distributed_modules.materialize_modules": "atorch_b200.utils.meta_model_utils",
     "atorch.optimizers.low_bit.optim.q_adamw": "atorch_b200.optimizers.low_bit.optim",

@@ -164,3 +164,53 @@ def _run_meta_pipe(rank, world, out_file):
 
 def test_pipe_module_from_meta_model(tmp_path):
     run_distributed(_run_meta_pipe, world=2, args=(str(tmp_path / "m"),))
+
+
+def _run_pipe_engine(rank, world, out_file):
+    from atorch_b200.distributed import distributed as D
+    from atorch_b200.pipeline_parallel.pipe_engine import PipeEngine, PipeSchedulerType, is_batch_on_device
+    from atorch_b200.pipeline_parallel.pipe_module import PipeModuleConfig, make_pipe_module
+
+    D.create_parallel_group(([("pipe", world)], None))
+    with torch.device("meta"):
+        meta = _Chain()
+    cfg = PipeModuleConfig(total_layer_num=4, sche_name="Schedule1F1B", n_microbatches=2, auto_ddp=False)
+    pm = make_pipe_module(meta_model=meta, loss_func=lambda o, t: ((o - t) ** 2).mean(), config=cfg)
+    st = pm.stage_modules[0]
+    torch.manual_seed(5)
+    full = _Chain()
+    mine = {0: [full.embed, full.layers[0], full.layers[1]], 1: [full.layers[2], full.layers[3], full.norm, full.head]}[rank]
+    for dst, src in zip(list(st.pre) + list(st.layers) + list(st.post), mine):
+        dst.load_state_dict(src.state_dict())
+    g = torch.Generator().manual_seed(3)
+    x, y = torch.randn(8, 8, generator=g), torch.randn(8, 8, generator=g)
+    batches = [(x[i: i + 2], y[i: i + 2]) for i in range(0, 8, 2)]
+    assert is_batch_on_device(batches, "cpu") and is_batch_on_device({"a": [x, 3]}, "cpu")
+    for sched, avg in (("OneForwardOneBackward", False), ("ForwardBackwardNoPipelinging", True)):
+        eng = PipeEngine(pm, {"scheduler": sched, "global_batchsize": 8, "micro_batchsize": 2, "device": "cpu",
+                              "return_average_loss": avg})
+        assert eng.config.scheduler is PipeSchedulerType(sched) and eng.n_microbatches == 4
+        assert eng.config.virtual_pp_size == 1
+        for p in st.parameters():
+            p.grad = None
+        out = eng.train_batch_step(iter(batches))
+        ref = [((full(xm) - ym) ** 2).mean() for xm, ym in batches]
+        if rank == world - 1:
+            if avg:
+                assert abs(out.item() - (sum(ref) / 4).item()) < 1e-5
+            else:
+                assert len(out) == 4 and all(abs(a.item() - b.item()) < 1e-5 for a, b in zip(out, ref))
+        else:
+            assert out == []
+        full.zero_grad()
+        (sum(ref) / 4).backward()
+        for dst, src in zip(list(st.pre) + list(st.layers) + list(st.post), mine):
+            for a, b in zip(dst.parameters(), src.parameters()):
+                assert torch.allclose(a.grad, b.grad, atol=1e-5)
+    torch.save(True, f"{out_file}.{rank}")
+
+
+def test_pipe_engine_runs_a_step_from_a_data_iterator(tmp_path):
+    f = str(tmp_path / "engine")
+    run_distributed(_run_pipe_engine, world=2, args=(f,))
+    assert all(torch.load(f"{f}.{r}") for r in range(2))
